@@ -1,0 +1,330 @@
+#!/usr/bin/env python
+"""Benchmark of the MoE layer on B200: tokens/s of one layer pass over one
+batch of synthetic tokens, with the roofline of its dominant kernel and the
+reference's CPU implementation timed beside it.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1] [--impl ours|reference]
+
+A step is one pass of router -> dispatch -> grouped MXFP4 gated MLP -> combine
+over one batch.  ``value`` is measured with the batch already resident in HBM
+(CUDA events on the stream the kernels run on, max over ranks); ``e2e`` goes
+through the host-buffer entry point ``csk_moe_forward`` with pinned host
+buffers, so it includes the host->device and device->host copies.
+
+N > 1 (launched by torchrun, one rank per GPU): expert parallelism.  Each rank
+holds E/N experts and its own batch of tokens (weak scaling); dispatch and
+combine are NCCL all-to-all.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from coalsack_b200 import synth  # noqa: E402
+
+METRIC = "moe_layer_prefill_tokens_per_s"
+UNIT = "tokens/s"
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "tflops": d["bf16_tflops"], "tflops_sustained": d["bf16_tflops_sustained"],
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1590.0, "tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi samples of SM clock and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index=0):
+        self.gpu, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.gpu)], stdout=subprocess.PIPE, text=True)
+            self.th = threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True)
+            self.th.start()
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        self.th.join(timeout=2)
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        # samples under load are the faster half (idle samples sit at a low clock)
+        sm.sort()
+        return {"sm_mhz": float(np.median(sm[len(sm) // 2:])), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def workload_shape(name, tokens=None):
+    sh = synth.CONFIGS[name]
+    return sh.with_(tokens=tokens) if tokens else sh
+
+
+def algorithmic_flops(sh, T):
+    """T*k*6*H*F for the experts (the reference bench's own convention,
+    test/bench_expert_mlp_mxfp4.cpp:148) + T*2*E*H for the router."""
+    return T * sh.top_k * 6.0 * sh.hidden * sh.ffn + T * 2.0 * sh.num_experts * sh.hidden
+
+
+# ---------------------------------------------------------------------------
+# reference arm: the reference's own CPU code on the host cores
+# ---------------------------------------------------------------------------
+def time_reference(sh, steps, warmup, budget_s=12.0):
+    """tokens/s of the reference's CPU implementation (oracle/_ref when it was
+    compiled, else the plain-C restatement) with every host thread, each step a
+    bounded sample of the workload's tokens."""
+    import oracle
+    kind = "reference" if oracle.have_ref() else "port"
+    lib = oracle.ref() if kind == "reference" else oracle.port()
+    cores = os.cpu_count() or 1
+    Wg, rb = synth.router_weight(sh), synth.router_bias(sh)
+    # experts actually hit by the sample are generated lazily: the sample is small
+    n0 = max(cores, 16)
+    h0 = synth.hidden_states(sh, min(sh.tokens, 2048)) if sh.tokens >= n0 else synth.hidden_states(sh, n0)
+    ro = oracle.port().router(h0, Wg, rb, sh.top_k)
+    need = sorted(set(ro[..., 0].astype(int).ravel().tolist()))
+    dummy = np.zeros(17 * sh.hidden * sh.ffn // 32, np.uint8)
+    cache = {e: synth.expert_weights(sh, e) for e in need}
+    ex = {k: [cache[e][k] if e in cache else dummy for e in range(sh.num_experts)] for k in ("w_up", "w_gate", "w_down")}
+    for k in ("b_up", "b_gate", "b_down"):
+        ex[k] = ([cache[e][k] if e in cache else np.zeros(1, np.float32) for e in range(sh.num_experts)]
+                 if sh.has_bias else None)
+    # size the sample: one probe, then scale to the time budget
+    t0 = time.perf_counter()
+    lib.moe_layer(h0[:n0], Wg, rb, ex, sh.top_k, sh.act, nthreads=cores)
+    per_tok = (time.perf_counter() - t0) / n0
+    n = int(min(h0.shape[0], max(n0, budget_s / max(per_tok, 1e-9) / max(steps + warmup, 1))))
+    for _ in range(warmup):
+        lib.moe_layer(h0[:n], Wg, rb, ex, sh.top_k, sh.act, nthreads=cores)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        lib.moe_layer(h0[:n], Wg, rb, ex, sh.top_k, sh.act, nthreads=cores)
+    dt = (time.perf_counter() - t0) / max(steps, 1)
+    return {"value": n / dt, "unit": UNIT, "cores": cores, "kind": kind,
+            "sample": f"{n} of the workload's tokens per step, router + {sh.top_k} expert calls per token + merge, "
+                      f"{cores} host threads over tokens; tokens/s extrapolates linearly in tokens"}, dt * 1e3
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sh = workload_shape(args.workload, args.tokens)
+    cb, ms = time_reference(sh, args.steps, args.warmup)
+    line = {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": config_of(sh, args), "cpu_baseline": cb,
+            "e2e": {"value": cb["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def config_of(sh, args):
+    return {"workload": f"{sh.name}: E={sh.num_experts} top-{sh.top_k} H={sh.hidden} F={sh.ffn} MXFP4, "
+                        f"T={sh.tokens} tokens per GPU, router bias {sh.router_bias}, seed {sh.seed}",
+            "tokens_per_gpu": sh.tokens, "experts": sh.num_experts, "top_k": sh.top_k, "hidden": sh.hidden,
+            "ffn": sh.ffn, "parallelism": "single GPU" if args.gpus == 1 else f"expert-parallel x{args.gpus}",
+            "l2": "weights + grouped activations per step exceed the 126 MB L2 (no flush needed)"}
+
+
+# ---------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    from coalsack_b200 import MoeLayer
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun for N > 1")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    sh = workload_shape(args.workload, args.tokens)
+    T, H, k, E = sh.tokens, sh.hidden, sh.top_k, sh.num_experts
+
+    if world > 1:
+        from coalsack_b200 import ep
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+        runner = ep.EpBench(sh, rank, world, local)
+    else:
+        runner = SingleGpu(sh, local)
+
+    sampler = ClockSampler(local)
+    for _ in range(max(args.warmup, 3)):
+        runner.step_dev()
+    runner.sync()
+
+    # ---- device-resident timing ------------------------------------------------
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    torch.cuda.synchronize()
+    if rank == 0:
+        sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    stream = runner.torch_stream
+    with torch.cuda.stream(stream):
+        ev0.record(stream)
+        for _ in range(args.steps):
+            runner.step_dev()
+        ev1.record(stream)
+    torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    clocks = sampler.stop() if rank == 0 else None
+    runner.sync()
+    ms_per_step = ms / args.steps
+    value = T * world / (ms_per_step * 1e-3)
+
+    # ---- per-kernel timing for the roofline (separate pass, timers on) -------------
+    stage = runner.stage_times(args.steps)
+
+    # ---- end to end through the host-buffer entry point -----------------------------
+    e2e_ms = runner.time_e2e(args.steps, max(args.warmup, 3))
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+
+    if rank != 0:
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+
+    peaks = measured_peaks()
+    rows = T * k
+    gu_flops = rows * 4.0 * H * sh.ffn     # gate and up projections: 2 * rows * 2F * H
+    gu_ms = stage["gate_up_ms"]
+    achieved = gu_flops / (gu_ms * 1e-3) / 1e12 if gu_ms > 0 else 0.0
+    roofline = {"bound": "tensor", "kernel": stage["gate_up_kernel"], "achieved": achieved, "peak": peaks["tflops"],
+                "unit": "TFLOP/s", "frac": achieved / peaks["tflops"], "peak_source": peaks["source"] + " (burst bf16 cuBLAS)",
+                "traffic": None, "ms_per_launch": gu_ms,
+                "layer_tflops": algorithmic_flops(sh, T * world) / (ms_per_step * 1e-3) / 1e12,
+                "stages_ms": {n: stage[n] for n in ("route_ms", "permute_ms", "gate_up_ms", "down_ms", "combine_ms", "total_ms")}}
+    cb, _ = time_reference(sh, 2, 1) if world == 1 else (None, None)
+    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f16 operands (MXFP4 weights dequantised exactly), f32 accumulate; f32 router",
+            "data": "synthetic", "config": config_of(sh, args), "clocks": clocks,
+            "e2e": {"value": T * world / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": T * H * 4 * world, "d2h_bytes_per_step": T * H * 4 * world},
+            "gpu_launches": int(stage["launches"]) * args.steps, "path": stage["path"], "roofline": roofline}
+    if cb:
+        line["cpu_baseline"] = cb
+    print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+class SingleGpu:
+    """The layer on one GPU: weights resident, one batch in HBM (``step_dev``)
+    or in pinned host memory (``time_e2e``)."""
+
+    def __init__(self, sh, local):
+        import torch
+        from coalsack_b200 import MoeLayer
+        self.torch = torch
+        self.sh = sh
+        dev = torch.device("cuda", local)
+        self.layer = MoeLayer.from_shape(sh, device=local, max_tokens=sh.tokens)
+        self.layer.set_router(synth.router_weight(sh), synth.router_bias(sh))
+        for e in range(sh.num_experts):
+            w = synth.expert_weights(sh, e)
+            self.layer.load_expert(e, w["w_up"], w["w_gate"], w["w_down"], w["b_up"], w["b_gate"], w["b_down"])
+        h = synth.hidden_states(sh)
+        self.h_host = torch.from_numpy(h).pin_memory()
+        self.out_host = torch.empty_like(self.h_host).pin_memory()
+        self.d_hidden = self.h_host.to(dev)
+        self.d_out = torch.empty_like(self.d_hidden)
+        self.torch_stream = torch.cuda.Stream(device=dev)
+        self.T = sh.tokens
+
+    def step_dev(self):
+        self.layer.forward_dev(self.d_hidden, self.T, self.d_out, stream=self.torch_stream.cuda_stream)
+
+    def sync(self):
+        self.torch.cuda.synchronize()
+        self.layer.sync()
+
+    def stage_times(self, steps):
+        self.layer.enable_timing(True)
+        acc = None
+        n = max(3, min(steps, 20))
+        for _ in range(n):
+            self.step_dev()
+            self.layer.sync()
+            t = self.layer.timings()
+            acc = t if acc is None else {k: acc[k] + t[k] for k in t}
+        self.layer.enable_timing(False)
+        out = {k: acc[k] / n for k in acc}
+        out["path"] = {1: "stream", 2: "tile"}.get(int(round(out["path"])), "?")
+        out["gate_up_kernel"] = "k_stream<gated>" if out["path"] == "stream" else "k_tile<gated>"
+        return out
+
+    def time_e2e(self, steps, warmup):
+        for _ in range(warmup):
+            self.layer.forward(self.h_host, out=self.out_host)
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            self.layer.forward(self.h_host, out=self.out_host)
+        return (time.perf_counter() - t0) * 1e3 / steps
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c1", choices=sorted(synth.CONFIGS))
+    ap.add_argument("--tokens", type=int, default=None, help="override the workload's tokens per GPU")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,147 @@
+// Shared definitions of the MoE library: the repacked MXFP4 device layout, the
+// dequantisation helpers and the handle.  sm_100a only.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "csk_moe.h"
+
+namespace csk {
+
+// ---------------------------------------------------------------------------
+// Device layout of one repacked MXFP4 matrix W[N, K] (K = contraction dim).
+//
+// The matrix is cut into tiles of BN rows x 64 columns, stored tile after tile
+// as [n_tile][k_tile]; a tile is BN/16 records ("sub-tiles") of 16 rows x 64
+// columns, 544 bytes each:
+//
+//   bytes   0..511  codes, lane-major for a warp: lane l = 4*g + q owns 16 bytes
+//                   = four 32-bit words
+//                     word 0: row g,   columns 32*0 + 8q .. +7
+//                     word 1: row g,   columns 32*1 + 8q .. +7
+//                     word 2: row g+8, columns 32*0 + 8q .. +7
+//                     word 3: row g+8, columns 32*1 + 8q .. +7
+//                   nibble i of a word (bits 4i..4i+3) is the E2M1 code of
+//                   column 8q + i, i.e. the codes are in natural column order.
+//   bytes 512..543  E8M0 scales: for g = 0..7 four bytes
+//                     (row g blk 0, row g blk 1, row g+8 blk 0, row g+8 blk 1)
+//
+// One warp reads a sub-tile with a single 128-bit load per lane (plus one
+// 32-bit scale load); a whole tile is one contiguous span, so the tensor-core
+// kernel fetches it with one bulk copy.  Rows >= N and columns >= K are padded
+// with zero codes.
+//
+// For the fused gate/up matrix the tile's first BN/2 rows are gate features
+// [n_tile*BN/2, (n_tile+1)*BN/2) and its last BN/2 rows the same up features,
+// so one tile (and one warp's pair of sub-tiles) sees both operands of the
+// gated activation.
+// ---------------------------------------------------------------------------
+constexpr int kSubBytes = 544;
+constexpr int kSubCodeBytes = 512;
+constexpr int kTileK = 64;
+
+struct MatLayout {
+  int N;        // logical rows (for gate/up: F features, stored as 2 x F rows)
+  int K;        // logical columns
+  int BN;       // tile rows
+  int paired;   // 1 = fused gate/up
+  int n_tiles;  // tiles along N
+  int k_tiles;  // tiles along K
+  int subs;     // BN / 16
+  __host__ __device__ int rows_per_tile() const { return paired ? BN / 2 : BN; }
+  __host__ __device__ size_t tile_bytes() const { return (size_t)subs * kSubBytes; }
+  __host__ __device__ size_t bytes() const { return (size_t)n_tiles * k_tiles * tile_bytes(); }
+  __host__ __device__ int k_pad() const { return k_tiles * kTileK; }
+  __host__ __device__ int n_pad() const { return n_tiles * rows_per_tile(); }
+};
+
+inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// Tile height that wastes the least padding (ties -> the larger tile).
+inline MatLayout make_layout(int N, int K, bool paired) {
+  MatLayout L{};
+  L.N = N;
+  L.K = K;
+  L.paired = paired ? 1 : 0;
+  int best = 0, best_pad = 1 << 30;
+  for (int bn : {128, 192, 256}) {
+    int rows = paired ? bn / 2 : bn;
+    int pad = ceil_div(N, rows) * rows;
+    if (pad < best_pad || (pad == best_pad && bn > best)) {
+      best = bn;
+      best_pad = pad;
+    }
+  }
+  L.BN = best;
+  L.subs = best / 16;
+  L.n_tiles = ceil_div(N, L.rows_per_tile());
+  L.k_tiles = ceil_div(K, kTileK);
+  return L;
+}
+
+// E8M0 byte -> fp32 scale for codes read as E2M1 VALUES (0, 0.5 .. 6): the
+// reference multiplies doubled code values (0, 1 .. 12) by 2^(e-128)
+// (gguf_dequant.h:413-433), which is value * 2^(e-127).  e = 0 gives the fp32
+// subnormal 2^-127.  e = 255 (NaN in the OCP MX spec, 2^127 in the reference)
+// is clamped to e = 254.
+__device__ __forceinline__ float e8m0_scale_f32(uint32_t e) {
+  e = e > 254u ? 254u : e;
+  uint32_t bits = e ? (e << 23) : 0x00400000u;
+  return __uint_as_float(bits);
+}
+
+// Two packed E2M1 codes (one byte) -> half2, low nibble in the low half.
+__device__ __forceinline__ uint32_t e2m1x2_to_h2(uint32_t byte) {
+  uint32_t r;
+  asm("{\n\t.reg .b8 b;\n\tcvt.u8.u32 b, %1;\n\tcvt.rn.f16x2.e2m1x2 %0, b;\n\t}" : "=r"(r) : "r"(byte));
+  return r;
+}
+
+// A word of eight codes -> four half2 (columns 0-1, 2-3, 4-5, 6-7).
+__device__ __forceinline__ void dequant_word(uint32_t w, uint32_t (&h)[4]) {
+  asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+      "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %2, b2;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %3, b3;\n\t}"
+      : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3])
+      : "r"(w));
+}
+
+// Gated activations of the reference (expert_mlp_node.h:657-658, 699-707).
+__device__ __forceinline__ float gated_act(float gate, float up, int act) {
+  if (act == CSK_ACT_MODIFIED_SWIGLU) {
+    const float lim = 7.0f, alpha = 1.702f;
+    float g = fminf(gate, lim);
+    float u = fminf(fmaxf(up, -lim), lim);
+    float glu = g / (1.0f + expf(alpha * (-g)));
+    return glu * (u + 1.0f);
+  }
+  float silu = gate / (1.0f + expf(-gate));
+  return silu * up;
+}
+
+// Work item lists built on the device by the permutation step.
+struct RowTile {
+  int expert;  // expert index local to this device
+  int row0;    // first row of the tile in the grouped activation buffer
+  int rows;    // rows in the tile (1 .. tile height)
+  int pad;
+};
+
+// Device-side status word values (or-ed).
+enum : int {
+  kDevErrExpertRange = 1,   // router output names an expert outside [0, E)
+  kDevErrCapacity = 2,      // more rows than the scratch buffers hold
+  kDevErrWaitTimeout = 4,   // a bounded wait in a kernel ran out
+  kDevErrNotResident = 8,   // rows were routed to an expert that is not loaded
+};
+
+}  // namespace csk

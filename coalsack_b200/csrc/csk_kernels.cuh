@@ -1,0 +1,508 @@
+// The small kernels around the expert contractions: MXFP4 repack, router,
+// permutation by expert, gather to fp16 rows, weighted combine.
+#pragma once
+
+#include "csk_common.cuh"
+
+namespace csk {
+
+// ---------------------------------------------------------------------------
+// Repack: 17-byte MXFP4 blocks (row-major, [rows][K/32]) -> device tile layout.
+// src0 is the matrix itself, or the gate matrix of a fused gate/up pair whose
+// up matrix is src1.  One thread per destination word; the last 8 "words" of a
+// sub-tile record are its scale bytes.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t raw_code(const uint8_t* src, int K, int row, int col) {
+  const uint8_t* blk = src + ((size_t)row * (K / 32) + col / 32) * 17;
+  const int j = col & 31;
+  const uint8_t byte = blk[1 + (j & 15)];
+  return j < 16 ? (byte & 0xF) : (byte >> 4);
+}
+
+__global__ void k_repack(const uint8_t* __restrict__ src0, const uint8_t* __restrict__ src1,
+                         uint8_t* __restrict__ dst, MatLayout L) {
+  const size_t n_words = L.bytes() / 4;
+  for (size_t w = (size_t)blockIdx.x * blockDim.x + threadIdx.x; w < n_words;
+       w += (size_t)gridDim.x * blockDim.x) {
+    const size_t rec = w / (kSubBytes / 4);
+    const int wi = (int)(w % (kSubBytes / 4));
+    const int sub = (int)(rec % L.subs);
+    const int kt = (int)((rec / L.subs) % L.k_tiles);
+    const int n_tile = (int)(rec / ((size_t)L.subs * L.k_tiles));
+    uint32_t out = 0;
+    if (wi < kSubCodeBytes / 4) {
+      const int lane = wi >> 2, word = wi & 3;
+      const int g = lane >> 2, q = lane & 3;
+      int r_in_tile = sub * 16 + g + ((word & 2) ? 8 : 0);
+      const int col = kt * kTileK + (word & 1) * 32 + q * 8;
+      const uint8_t* src = src0;
+      if (L.paired && r_in_tile >= L.BN / 2) {
+        src = src1;
+        r_in_tile -= L.BN / 2;
+      }
+      const int row = n_tile * L.rows_per_tile() + r_in_tile;
+      if (row < L.N && col < L.K) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) out |= raw_code(src, L.K, row, col + i) << (4 * i);
+      }
+    } else {
+      const int g = wi - kSubCodeBytes / 4;
+#pragma unroll
+      for (int slot = 0; slot < 4; ++slot) {
+        int r_in_tile = sub * 16 + g + ((slot & 2) ? 8 : 0);
+        const int col = kt * kTileK + (slot & 1) * 32;
+        const uint8_t* src = src0;
+        if (L.paired && r_in_tile >= L.BN / 2) {
+          src = src1;
+          r_in_tile -= L.BN / 2;
+        }
+        const int row = n_tile * L.rows_per_tile() + r_in_tile;
+        uint32_t e = 127;
+        if (row < L.N && col < L.K) e = src[((size_t)row * (L.K / 32) + col / 32) * 17];
+        out |= e << (8 * slot);
+      }
+    }
+    reinterpret_cast<uint32_t*>(dst)[w] = out;
+  }
+}
+
+// Inverse of k_repack for one source matrix (which_half: 0 = the matrix itself
+// or the gate half, 1 = the up half).  One thread per 17-byte block.
+__global__ void k_unpack(const uint8_t* __restrict__ packed, uint8_t* __restrict__ out, MatLayout L,
+                         int which_half) {
+  const int kb = L.K / 32;
+  const size_t n_blocks = (size_t)L.N * kb;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_blocks;
+       i += (size_t)gridDim.x * blockDim.x) {
+    const int row = (int)(i / kb), blk = (int)(i % kb);
+    const int n_tile = row / L.rows_per_tile();
+    int r_in_tile = row % L.rows_per_tile() + (which_half ? L.BN / 2 : 0);
+    const int sub = r_in_tile / 16, r16 = r_in_tile % 16;
+    const int g = r16 & 7, hi = r16 >> 3;
+    const int kt = blk / 2, b = blk & 1;
+    const uint8_t* rec = packed + (((size_t)n_tile * L.k_tiles + kt) * L.subs + sub) * kSubBytes;
+    uint8_t* o = out + i * 17;
+    o[0] = rec[kSubCodeBytes + g * 4 + hi * 2 + b];
+    uint32_t codes[32];
+    for (int q = 0; q < 4; ++q) {
+      const uint32_t w = reinterpret_cast<const uint32_t*>(rec)[(g * 4 + q) * 4 + hi * 2 + b];
+      for (int t = 0; t < 8; ++t) codes[q * 8 + t] = (w >> (4 * t)) & 0xF;
+    }
+    for (int j = 0; j < 16; ++j) o[1 + j] = (uint8_t)(codes[j] | (codes[j + 16] << 4));
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Router (moe_router_node::compute_impl, moe_router_node.h:140-214).
+//
+// The selected expert indices must equal the reference's bit for bit, and the
+// reference accumulates each logit sequentially in fp32 with separate multiply
+// and add.  So each (token, expert) logit is one thread's in-order chain of
+// __fmul_rn/__fadd_rn (never contracted into an FMA).  A block covers
+// kRouterTok tokens for each of its token sub-groups; thread = one expert of
+// one sub-group, keeping kRouterTok running sums while it walks the hidden
+// dimension once.  Top-k: one warp per token, k rounds of arg-max by shuffles
+// (ties -> lower expert id; the reference leaves ties unspecified).
+// ---------------------------------------------------------------------------
+constexpr int kRouterTok = 8;
+constexpr int kRouterChunk = 256;
+constexpr int kRouterThreads = 128;
+constexpr int kMaxTopK = 16;
+
+__global__ void __launch_bounds__(kRouterThreads)
+k_router(const float* __restrict__ hidden, const float* __restrict__ wgT,
+         const float* __restrict__ bias, float* __restrict__ router_out, int T, int H, int E,
+         int E_stride, int k, int sigmoid, int e_lanes /* pow2 >= min(E,128) */) {
+  extern __shared__ float smem[];
+  const int groups = kRouterThreads / e_lanes;           // token sub-groups per block
+  const int tok_per_block = groups * kRouterTok;
+  float* hs = smem;                                      // [tok_per_block][kRouterChunk]
+  float* lg = smem + tok_per_block * kRouterChunk;       // [tok_per_block][E]
+  const int tid = threadIdx.x;
+  const int grp = tid / e_lanes, el = tid % e_lanes;
+  const int t_block = blockIdx.x * tok_per_block;
+
+  for (int e0 = 0; e0 < E; e0 += e_lanes) {
+    const int e = e0 + el;
+    float acc[kRouterTok];
+#pragma unroll
+    for (int t = 0; t < kRouterTok; ++t) acc[t] = 0.f;
+    for (int d0 = 0; d0 < H; d0 += kRouterChunk) {
+      const int dc = min(kRouterChunk, H - d0);
+      __syncthreads();
+      for (int i = tid; i < tok_per_block * kRouterChunk; i += kRouterThreads) {
+        const int tt = i / kRouterChunk, d = i % kRouterChunk;
+        const int t = t_block + tt;
+        hs[i] = (t < T && d < dc) ? hidden[(size_t)t * H + d0 + d] : 0.f;
+      }
+      __syncthreads();
+      if (e < E) {
+        const float* hrow = hs + grp * kRouterTok * kRouterChunk;
+        const float* wcol = wgT + (size_t)d0 * E_stride + e;
+        int d = 0;
+        for (; d + 4 <= dc; d += 4) {
+          float w0 = wcol[(size_t)(d + 0) * E_stride], w1 = wcol[(size_t)(d + 1) * E_stride];
+          float w2 = wcol[(size_t)(d + 2) * E_stride], w3 = wcol[(size_t)(d + 3) * E_stride];
+#pragma unroll
+          for (int t = 0; t < kRouterTok; ++t) {
+            const float4 h4 = *reinterpret_cast<const float4*>(hrow + t * kRouterChunk + d);
+            float a = acc[t];
+            a = __fadd_rn(a, __fmul_rn(h4.x, w0));
+            a = __fadd_rn(a, __fmul_rn(h4.y, w1));
+            a = __fadd_rn(a, __fmul_rn(h4.z, w2));
+            a = __fadd_rn(a, __fmul_rn(h4.w, w3));
+            acc[t] = a;
+          }
+        }
+        for (; d < dc; ++d) {
+          const float w0 = wcol[(size_t)d * E_stride];
+#pragma unroll
+          for (int t = 0; t < kRouterTok; ++t)
+            acc[t] = __fadd_rn(acc[t], __fmul_rn(hrow[t * kRouterChunk + d], w0));
+        }
+      }
+    }
+    if (e < E) {
+      const float b = bias ? bias[e] : 0.f;
+#pragma unroll
+      for (int t = 0; t < kRouterTok; ++t)
+        lg[(grp * kRouterTok + t) * E + e] = __fadd_rn(acc[t], b);
+    }
+  }
+  __syncthreads();
+
+  // top-k + routing weights, one warp per token
+  const int lane = tid & 31, warp = tid >> 5;
+  for (int tt = warp; tt < tok_per_block; tt += kRouterThreads / 32) {
+    const int t = t_block + tt;
+    if (t >= T) continue;
+    float* l = lg + tt * E;
+    float sel_v[kMaxTopK];
+    int sel_i[kMaxTopK];
+    for (int j = 0; j < k; ++j) {
+      float bv = -INFINITY;
+      int bi = 0x7fffffff;
+      for (int e = lane; e < E; e += 32) {
+        const float v = l[e];
+        if (v > bv || (v == bv && e < bi)) {
+          bv = v;
+          bi = e;
+        }
+      }
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) {
+          bv = ov;
+          bi = oi;
+        }
+      }
+      sel_v[j] = bv;
+      sel_i[j] = bi;
+      __syncwarp();
+      if (lane == 0 && bi < E) l[bi] = __int_as_float(0xffc00000);  // NaN: never wins a '>' test
+      __syncwarp();
+    }
+    if (lane == 0) {
+      float w[kMaxTopK];
+      if (sigmoid) {
+        for (int j = 0; j < k; ++j) w[j] = 1.0f / (1.0f + expf(-sel_v[j]));
+      } else {
+        float mx = sel_v[0];
+        for (int j = 1; j < k; ++j) mx = fmaxf(mx, sel_v[j]);
+        float se = 0.f;
+        for (int j = 0; j < k; ++j) {
+          w[j] = expf(sel_v[j] - mx);
+          se += w[j];
+        }
+        const float inv = se > 0.f ? 1.0f / se : 0.f;
+        for (int j = 0; j < k; ++j) w[j] *= inv;
+      }
+      for (int j = 0; j < k; ++j) {
+        router_out[((size_t)t * k + j) * 2 + 0] = (float)sel_i[j];
+        router_out[((size_t)t * k + j) * 2 + 1] = w[j];
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Permutation by expert ("dispatch").  The reference's dispatch
+// (moe_weight_fetch_node::extract_selected_experts, moe_weight_fetch_node.h:31-60,
+// and the per-expert membership scans of expert_mlp_node.h:784-822) only finds
+// WHICH experts were selected; grouping the (token, expert) rows by expert is
+// what lets every expert's weights be read once.
+//
+// meta layout (int32): [0] row tiles, [1] total rows, [2] distinct experts,
+//                      [3] device status word (or-ed kDevErr*), [4..7] spare.
+// ---------------------------------------------------------------------------
+__global__ void k_hist(const float* __restrict__ router_out, int n_pairs, int E, int only_expert,
+                       int* __restrict__ counts, int* __restrict__ meta) {
+  extern __shared__ int sc[];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) sc[e] = 0;
+  __syncthreads();
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_pairs; i += gridDim.x * blockDim.x) {
+    const int e = (int)router_out[2 * (size_t)i];
+    if (e < 0 || e >= E) {
+      atomicOr(&meta[3], kDevErrExpertRange);
+      continue;
+    }
+    if (only_expert >= 0 && e != only_expert) continue;
+    atomicAdd(&sc[e], 1);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x)
+    if (sc[e]) atomicAdd(&counts[e], sc[e]);
+}
+
+// Exclusive scan of the per-expert row counts, row-tile list for tiles of
+// `tile_rows` rows, cursor reset.  One block of 1024 threads, E <= 1024.
+// counts are indexed by GLOBAL expert id; tiles carry the id local to this
+// device (e - e_begin); rows of experts outside [e_begin, e_begin+e_count) get
+// offsets but no tiles (under expert parallelism they belong to other devices).
+__global__ void __launch_bounds__(1024)
+k_scan(const int* __restrict__ counts, int E, int e_begin, int e_count, int tile_rows, int max_rows,
+       int max_tiles, const uint8_t* __restrict__ resident, int* __restrict__ offsets,
+       int* __restrict__ cursor, RowTile* __restrict__ tiles, int* __restrict__ meta) {
+  __shared__ int s_row_off[1025];
+  __shared__ int s_tile_off[1025];
+  __shared__ int s_warp[2][32];
+  __shared__ int s_distinct;
+  const int e = threadIdx.x, lane = e & 31, warp = e >> 5;
+  if (e == 0) s_distinct = 0;
+  __syncthreads();
+  const int c = e < E ? counts[e] : 0;
+  const bool local = e >= e_begin && e < e_begin + e_count;
+  const int nt = local ? (c + tile_rows - 1) / tile_rows : 0;
+  if (c > 0) {
+    atomicAdd(&s_distinct, 1);
+    if (local && resident && !resident[e - e_begin]) atomicOr(&meta[3], kDevErrNotResident);
+  }
+  // block-wide inclusive scans of (c, nt)
+  int rc = c, rt = nt;
+  for (int o = 1; o < 32; o <<= 1) {
+    const int a = __shfl_up_sync(0xffffffffu, rc, o), b = __shfl_up_sync(0xffffffffu, rt, o);
+    if (lane >= o) {
+      rc += a;
+      rt += b;
+    }
+  }
+  if (lane == 31) {
+    s_warp[0][warp] = rc;
+    s_warp[1][warp] = rt;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    int a = s_warp[0][lane], b = s_warp[1][lane];
+    for (int o = 1; o < 32; o <<= 1) {
+      const int ua = __shfl_up_sync(0xffffffffu, a, o), ub = __shfl_up_sync(0xffffffffu, b, o);
+      if (lane >= o) {
+        a += ua;
+        b += ub;
+      }
+    }
+    s_warp[0][lane] = a;
+    s_warp[1][lane] = b;
+  }
+  __syncthreads();
+  const int base_c = warp ? s_warp[0][warp - 1] : 0, base_t = warp ? s_warp[1][warp - 1] : 0;
+  const int row_off = base_c + rc - c, tile_off = base_t + rt - nt;
+  s_row_off[e] = row_off;
+  s_tile_off[e] = tile_off;
+  if (e < E) {
+    offsets[e] = row_off;
+    cursor[e] = 0;
+  }
+  const int total_rows = s_warp[0][31], total_tiles = s_warp[1][31];
+  if (e == 0) {
+    s_row_off[1024] = total_rows;
+    s_tile_off[1024] = total_tiles;
+    offsets[E] = total_rows;
+    const bool over = total_rows > max_rows || total_tiles > max_tiles;
+    if (over) atomicOr(&meta[3], kDevErrCapacity);
+    meta[0] = over ? 0 : total_tiles;
+    meta[1] = total_rows;
+  }
+  __syncthreads();
+  if (e == 0) meta[2] = s_distinct;
+  if (total_rows > max_rows || total_tiles > max_tiles) return;
+  for (int i = threadIdx.x; i < total_tiles; i += blockDim.x) {
+    // largest expert x with s_tile_off[x] <= i (experts without tiles repeat an offset)
+    int lo = 0, hi = 1023;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (s_tile_off[mid] <= i) lo = mid; else hi = mid - 1;
+    }
+    // step back over empty experts that share the offset: the owner is the last
+    // expert with that offset that actually has tiles, i.e. the largest index.
+    const int r = (i - s_tile_off[lo]) * tile_rows;
+    const int cnt = (lo < 1023 ? s_row_off[lo + 1] : s_row_off[1024]) - s_row_off[lo];
+    RowTile t;
+    t.expert = lo - e_begin;
+    t.row0 = s_row_off[lo] + r;
+    t.rows = min(tile_rows, cnt - r);
+    t.pad = 0;
+    tiles[i] = t;
+  }
+}
+
+// One warp per (token, slot) pair: claim a row in the expert's segment, record
+// the maps, and write the token's hidden row there as fp16 (times the routing
+// weight when it is applied before the expert).
+__global__ void k_scatter(const float* __restrict__ router_out, const float* __restrict__ hidden,
+                          int n_pairs, int k, int H, int E, int only_expert,
+                          const int* __restrict__ offsets, int* __restrict__ cursor,
+                          int* __restrict__ row_of_pair, __half* __restrict__ x16, int ldx,
+                          int max_rows, int weight_before_ffn) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  for (int i = blockIdx.x * warps_per_block + (threadIdx.x >> 5); i < n_pairs;
+       i += gridDim.x * warps_per_block) {
+    const int e = (int)router_out[2 * (size_t)i];
+    const float w = router_out[2 * (size_t)i + 1];
+    int pos = -1;
+    if (e >= 0 && e < E && (only_expert < 0 || e == only_expert)) {
+      if (lane == 0) pos = offsets[e] + atomicAdd(&cursor[e], 1);
+      pos = __shfl_sync(0xffffffffu, pos, 0);
+      if (pos >= max_rows) pos = -1;
+    }
+    if (lane == 0) row_of_pair[i] = pos;
+    if (pos < 0) continue;
+    const float* src = hidden + (size_t)(i / k) * H;
+    __half* dst = x16 + (size_t)pos * ldx;
+    const float mul = weight_before_ffn ? w : 1.0f;
+    for (int d = lane * 4; d < H; d += 128) {
+      const float4 v = *reinterpret_cast<const float4*>(src + d);
+      __half2 a = __floats2half2_rn(v.x * mul, v.y * mul);
+      __half2 b = __floats2half2_rn(v.z * mul, v.w * mul);
+      uint2 o;
+      o.x = *reinterpret_cast<uint32_t*>(&a);
+      o.y = *reinterpret_cast<uint32_t*>(&b);
+      *reinterpret_cast<uint2*>(dst + d) = o;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Weighted combine (expert_merge_node::compute, expert_merge_node.h:88-131):
+// out[t] = sum over slots j = 0..k-1, in that order, of w[t,j] * y[row(t,j)],
+// a separate multiply and add per term as the reference does.  mode 1 is the
+// dense single-expert output of expert_mlp_node (expert_mlp_node.h:503-529):
+// the token's row unweighted, or zeros.
+// ---------------------------------------------------------------------------
+__global__ void k_combine(const float* __restrict__ router_out, const int* __restrict__ row_of_pair,
+                          const float* __restrict__ y, int ldy, float* __restrict__ out, int T,
+                          int k, int H, int unweighted, int dense_single) {
+  const int t = blockIdx.x;
+  if (t >= T) return;
+  for (int d = threadIdx.x * 4; d < H; d += blockDim.x * 4) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int j = 0; j < k; ++j) {
+      const int row = row_of_pair[(size_t)t * k + j];
+      if (row < 0) continue;
+      const float4 v = *reinterpret_cast<const float4*>(y + (size_t)row * ldy + d);
+      if (dense_single) {
+        acc = v;
+        break;
+      }
+      if (unweighted) {
+        acc.x = __fadd_rn(acc.x, v.x);
+        acc.y = __fadd_rn(acc.y, v.y);
+        acc.z = __fadd_rn(acc.z, v.z);
+        acc.w = __fadd_rn(acc.w, v.w);
+      } else {
+        const float w = router_out[((size_t)t * k + j) * 2 + 1];
+        acc.x = __fadd_rn(acc.x, __fmul_rn(w, v.x));
+        acc.y = __fadd_rn(acc.y, __fmul_rn(w, v.y));
+        acc.z = __fadd_rn(acc.z, __fmul_rn(w, v.z));
+        acc.w = __fadd_rn(acc.w, __fmul_rn(w, v.w));
+      }
+    }
+    *reinterpret_cast<float4*>(out + (size_t)t * H + d) = acc;
+  }
+}
+
+// [E,H] -> [H,E_stride] transpose of the router weights (coalesced reads by expert).
+__global__ void k_transpose_router(const float* __restrict__ wg, float* __restrict__ wgT, int E, int H,
+                                   int E_stride) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < (size_t)E * H;
+       i += (size_t)gridDim.x * blockDim.x) {
+    const int e = (int)(i / H), d = (int)(i % H);
+    wgT[(size_t)d * E_stride + e] = wg[i];
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Expert-parallel receive side.  Rows arrive as n_src segments (one per source
+// device), each ordered by local expert; the contractions want them grouped by
+// expert.  seg layout (int32): [0..1024] exclusive offsets of the (src, expert)
+// segments in arrival order, [1025..2048] rows of the same expert that arrive
+// from lower-numbered sources.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024)
+k_ep_plan(const int* __restrict__ recv_counts, int n_src, int e_count, int e_begin,
+          int* __restrict__ counts, int* __restrict__ seg) {
+  __shared__ int s_warp[32];
+  const int i = threadIdx.x, lane = i & 31, warp = i >> 5;
+  const int n_seg = n_src * e_count;
+  const int c = i < n_seg ? recv_counts[i] : 0;
+  int r = c;
+  for (int o = 1; o < 32; o <<= 1) {
+    const int a = __shfl_up_sync(0xffffffffu, r, o);
+    if (lane >= o) r += a;
+  }
+  if (lane == 31) s_warp[warp] = r;
+  __syncthreads();
+  if (warp == 0) {
+    int a = s_warp[lane];
+    for (int o = 1; o < 32; o <<= 1) {
+      const int u = __shfl_up_sync(0xffffffffu, a, o);
+      if (lane >= o) a += u;
+    }
+    s_warp[lane] = a;
+  }
+  __syncthreads();
+  const int base = warp ? s_warp[warp - 1] : 0;
+  seg[i] = base + r - c;
+  if (i == 0) seg[1024] = s_warp[31];
+  if (i < n_seg) {
+    const int src = i / e_count, e = i % e_count;
+    int before = 0;
+    for (int s2 = 0; s2 < src; ++s2) before += recv_counts[s2 * e_count + e];
+    seg[1025 + i] = before;
+    if (src == 0) {
+      int tot = 0;
+      for (int s2 = 0; s2 < n_src; ++s2) tot += recv_counts[s2 * e_count + e];
+      counts[e_begin + e] = tot;
+    }
+  }
+}
+
+// One block per (src, expert) segment: copy its rows to their expert-major
+// place and remember where each came from.
+__global__ void k_ep_regroup(const __half* __restrict__ recv, __half* __restrict__ x16, int ldx,
+                             const int* __restrict__ seg, const int* __restrict__ offsets, int n_src,
+                             int e_count, int e_begin, int* __restrict__ out_row_map) {
+  const int b = blockIdx.x;
+  const int e = b % e_count;
+  const int src_row0 = seg[b], n = seg[b + 1] - seg[b];
+  const int dst_row0 = offsets[e_begin + e] + seg[1025 + b];
+  const uint4* s = reinterpret_cast<const uint4*>(recv + (size_t)src_row0 * ldx);
+  uint4* d = reinterpret_cast<uint4*>(x16 + (size_t)dst_row0 * ldx);
+  const size_t n16 = (size_t)n * ldx / 8;
+  for (size_t i = threadIdx.x; i < n16; i += blockDim.x) d[i] = s[i];
+  for (int r = threadIdx.x; r < n; r += blockDim.x) out_row_map[dst_row0 + r] = src_row0 + r;
+}
+
+// Stream path only: rows computed in expert-major order go back to arrival order.
+__global__ void k_ep_ungroup(const float* __restrict__ y, float* __restrict__ ret, int H,
+                             const int* __restrict__ out_row_map, int rows) {
+  const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+  for (int r = blockIdx.x * wpb + (threadIdx.x >> 5); r < rows; r += gridDim.x * wpb) {
+    const float4* s = reinterpret_cast<const float4*>(y + (size_t)r * H);
+    float4* d = reinterpret_cast<float4*>(ret + (size_t)out_row_map[r] * H);
+    for (int i = lane; i < H / 4; i += 32) d[i] = s[i];
+  }
+}
+
+}  // namespace csk

@@ -1,0 +1,774 @@
+// C ABI of the MoE layer (see include/csk_moe.h): handle, weight repack,
+// host- and device-buffer entry points, expert-parallel stages.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+#include "csk_common.cuh"
+#include "csk_kernels.cuh"
+#include "csk_stream.cuh"
+#include "csk_tile.cuh"
+
+using namespace csk;
+
+namespace {
+std::mutex g_err_mu;
+std::string g_create_error;
+}  // namespace
+
+struct csk_moe_layer {
+  csk_moe_config cfg{};
+  int E = 0, k = 0, H = 0, F = 0, e0 = 0, Eloc = 0;
+  MatLayout Lgu{}, Ld{};
+  size_t off_gu = 0, off_d = 0, off_bias = 0, expert_stride = 0;
+  uint8_t* d_weights = nullptr;
+  uint8_t* d_resident = nullptr;  // [Eloc] flags on the device
+  std::vector<uint8_t> resident;
+  uint8_t* d_stage = nullptr;     // raw 17-byte blocks during load / unpack
+  size_t stage_bytes = 0;
+
+  float* d_wg = nullptr;   // [E,H]
+  float* d_wgT = nullptr;  // [H,E_stride]
+  float* d_rbias = nullptr;
+  int E_stride = 0;
+  bool router_set = false, has_rbias = false;
+
+  int64_t max_T = 0, max_rows = 0;
+  int max_tiles = 0;
+  float* d_hidden = nullptr;  // [max_T,H] staging for the host entry points
+  float* d_router = nullptr;  // [max_T,k,2]
+  float* d_out = nullptr;     // [max_T,H]
+  __half* d_x16 = nullptr;    // [max_rows+pad, ldx]
+  __half* d_a16 = nullptr;    // [max_rows+pad, lda]
+  float* d_y = nullptr;       // [max_rows, H]
+  int ldx = 0, lda = 0;
+  int* d_counts = nullptr;       // [E]
+  int* d_offsets = nullptr;      // [E+1]
+  int* d_cursor = nullptr;       // [E]
+  int* d_row_of_pair = nullptr;  // [max_rows]
+  int* d_out_row_map = nullptr;  // [max_rows] (expert-parallel receive side)
+  int* d_seg = nullptr;          // [2*1024+2] segment plan (expert-parallel receive side)
+  RowTile* d_tiles = nullptr;
+  int* d_meta = nullptr;  // 8 ints
+  int* h_meta = nullptr;  // pinned mirror
+  int64_t* h_counts64 = nullptr;
+
+  cudaStream_t stream = nullptr;
+  cudaEvent_t ev[8]{};
+  bool timing = false;
+  csk_moe_timings last{};
+  int path = CSK_PATH_AUTO;
+  int sm_count = 148;
+  TileState tile;  // tensor maps and launch state of the tensor-core path
+
+  std::string err;
+  int64_t last_T = 0;
+  int n_marks = 0;
+  bool last_routed = false;
+  cudaStream_t last_stream = nullptr;
+};
+
+namespace {
+
+int fail(csk_moe_layer* L, int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  if (L) {
+    L->err = buf;
+  } else {
+    std::lock_guard<std::mutex> lk(g_err_mu);
+    g_create_error = buf;
+  }
+  return code;
+}
+
+#define CSK_CUDA(L, call)                                                                    \
+  do {                                                                                       \
+    cudaError_t _e = (call);                                                                 \
+    if (_e != cudaSuccess)                                                                   \
+      return fail(L, CSK_ERR_CUDA, "%s failed: %s (%s:%d)", #call, cudaGetErrorString(_e),   \
+                  __FILE__, __LINE__);                                                       \
+  } while (0)
+
+int grid_for(size_t work_items, int threads, int cap) {
+  size_t b = (work_items + threads - 1) / threads;
+  return (int)std::max<size_t>(1, std::min<size_t>(b, (size_t)cap));
+}
+
+cudaStream_t pick(csk_moe_layer* L, void* s) { return s ? (cudaStream_t)s : L->stream; }
+
+struct StageTimer {
+  csk_moe_layer* L;
+  cudaStream_t s;
+  int n = 0;
+  StageTimer(csk_moe_layer* l, cudaStream_t st) : L(l), s(st) {}
+  void mark() {
+    if (L->timing && n < 8) cudaEventRecord(L->ev[n++], s);
+  }
+};
+
+// ---- the stages ----------------------------------------------------------
+
+int launch_router(csk_moe_layer* L, const float* d_hidden, int64_t T, float* d_router,
+                  cudaStream_t s) {
+  if (!L->router_set) return fail(L, CSK_ERR_INVALID, "router weights were never set");
+  int e_lanes = 16;  // at most 64 tokens per block, whatever E is
+  while (e_lanes < L->E && e_lanes < kRouterThreads) e_lanes <<= 1;
+  const int tok_per_block = kRouterThreads / e_lanes * kRouterTok;
+  const size_t smem = (size_t)tok_per_block * (kRouterChunk + L->E) * sizeof(float);
+  const int blocks = (int)((T + tok_per_block - 1) / tok_per_block);
+  k_router<<<blocks, kRouterThreads, smem, s>>>(d_hidden, L->d_wgT, L->has_rbias ? L->d_rbias : nullptr,
+                                                 d_router, (int)T, L->H, L->E, L->E_stride, L->k,
+                                                 L->cfg.sigmoid_gating, e_lanes);
+  CSK_CUDA(L, cudaGetLastError());
+  L->last.launches++;
+  return CSK_OK;
+}
+
+// histogram -> scan (+ row tiles of `tile_rows`) -> scatter rows as fp16 into x16
+int launch_permute(csk_moe_layer* L, const float* d_hidden, const float* d_router, int64_t T,
+                   int only_expert, int tile_rows, int e_begin, int e_count, __half* x16, int ldx,
+                   int64_t max_rows, cudaStream_t s) {
+  const int n_pairs = (int)(T * L->k);
+  CSK_CUDA(L, cudaMemsetAsync(L->d_counts, 0, sizeof(int) * L->E, s));
+  CSK_CUDA(L, cudaMemsetAsync(L->d_meta, 0, sizeof(int) * 8, s));
+  k_hist<<<grid_for(n_pairs, 256, 2 * L->sm_count), 256, sizeof(int) * L->E, s>>>(
+      d_router, n_pairs, L->E, only_expert, L->d_counts, L->d_meta);
+  k_scan<<<1, 1024, 0, s>>>(L->d_counts, L->E, e_begin, e_count, tile_rows, (int)max_rows,
+                            L->max_tiles, e_count ? L->d_resident : nullptr, L->d_offsets,
+                            L->d_cursor, L->d_tiles, L->d_meta);
+  k_scatter<<<grid_for(n_pairs, 8, 8 * L->sm_count), 256, 0, s>>>(
+      d_router, d_hidden, n_pairs, L->k, L->H, L->E, only_expert, L->d_offsets, L->d_cursor,
+      L->d_row_of_pair, x16, ldx, (int)max_rows, L->cfg.weight_before_ffn);
+  CSK_CUDA(L, cudaGetLastError());
+  L->last.launches += 3;
+  return CSK_OK;
+}
+
+template <int NT8>
+void launch_stream_pair(csk_moe_layer* L, const __half* x16, float* y, int ldy, cudaStream_t s,
+                        StageTimer& tm) {
+  StreamArgs a{};
+  a.weights = L->d_weights;
+  a.expert_stride = L->expert_stride;
+  a.bias_offset = L->off_bias;
+  a.tiles = L->d_tiles;
+  a.n_tiles_ptr = L->d_meta;
+  a.has_bias = L->cfg.has_bias;
+  a.act = L->cfg.activation;
+  a.F = L->F;
+  const int grid = L->sm_count * 8;
+  // gate/up + activation
+  a.mat_offset = L->off_gu;
+  a.L = L->Lgu;
+  a.x = x16;
+  a.ldx = L->ldx;
+  a.a_out = L->d_a16;
+  a.lda = L->lda;
+  k_stream<NT8, true><<<grid, 128, 0, s>>>(a);
+  tm.mark();
+  // down
+  a.mat_offset = L->off_d;
+  a.L = L->Ld;
+  a.x = L->d_a16;
+  a.ldx = L->lda;
+  a.y_out = y;
+  a.ldy = ldy;
+  k_stream<NT8, false><<<grid, 128, 0, s>>>(a);
+  tm.mark();
+  L->last.launches += 2;
+}
+
+int stream_tile_rows(const csk_moe_layer* L, int64_t rows) {
+  // short row tiles while most experts see a couple of rows, taller ones after
+  return rows <= 2 * (int64_t)std::max(1, L->Eloc) ? 8 : 32;
+}
+
+int choose_path(const csk_moe_layer* L, int64_t rows) {
+  if (L->path == CSK_PATH_STREAM) return CSK_PATH_STREAM;
+  if (L->path == CSK_PATH_TILE) return CSK_PATH_TILE;
+  // the tensor-core tiles are 128 rows tall: worth it once the average expert
+  // fills a good part of one
+  return rows >= 48 * (int64_t)std::max(1, L->Eloc) ? CSK_PATH_TILE : CSK_PATH_STREAM;
+}
+
+int tile_rows_for(const csk_moe_layer* L, int path, int64_t rows) {
+  return path == CSK_PATH_TILE ? kTileM : stream_tile_rows(L, rows);
+}
+
+// grouped gate/up + activation + down over the row tiles listed in d_tiles;
+// x16 holds the grouped rows; output rows go to y (through out_row_map if set)
+int launch_experts(csk_moe_layer* L, int path, int tile_rows, const __half* x16, float* y, int ldy,
+                   const int* out_row_map, cudaStream_t s, StageTimer& tm) {
+  if (path == CSK_PATH_TILE) {
+    int rc = tile_launch(L->tile, L->d_weights, L->expert_stride, L->off_gu, L->off_d, L->off_bias,
+                         L->Lgu, L->Ld, x16, L->ldx, L->d_a16, L->lda, y, ldy, out_row_map,
+                         L->d_tiles, L->d_meta, L->cfg.has_bias, L->cfg.activation, L->F, L->H,
+                         L->sm_count, s, [&]() { tm.mark(); });
+    if (rc) return fail(L, rc, "tensor-core path: %s", L->tile.err.c_str());
+    L->last.launches += 2;
+  } else {
+    if (out_row_map) return fail(L, CSK_ERR_INVALID, "row map needs the tile path");
+    if (tile_rows == 8) {
+      launch_stream_pair<1>(L, x16, y, ldy, s, tm);
+    } else {
+      launch_stream_pair<4>(L, x16, y, ldy, s, tm);
+    }
+  }
+  CSK_CUDA(L, cudaGetLastError());
+  L->last.path = path;
+  return CSK_OK;
+}
+
+int check_device_status(csk_moe_layer* L, cudaStream_t s) {
+  CSK_CUDA(L, cudaMemcpyAsync(L->h_meta, L->d_meta, sizeof(int) * 8, cudaMemcpyDeviceToHost, s));
+  CSK_CUDA(L, cudaStreamSynchronize(s));
+  const int st = L->h_meta[3];
+  if (st & kDevErrExpertRange)
+    return fail(L, CSK_ERR_INVALID, "expert_idx out of range in router output");
+  if (st & kDevErrCapacity)
+    return fail(L, CSK_ERR_NOMEM, "more rows than max_tokens allows (%d rows)", L->h_meta[1]);
+  if (st & kDevErrNotResident)
+    return fail(L, CSK_ERR_MISSING, "tokens were routed to an expert whose weights are not loaded");
+  if (st & kDevErrWaitTimeout)
+    return fail(L, CSK_ERR_DEVICE, "a bounded device-side wait ran out");
+  return CSK_OK;
+}
+
+void finish_timings(csk_moe_layer* L, int n_marks, bool routed) {
+  if (!L->timing) return;
+  float ms[8] = {0};
+  for (int i = 0; i + 1 < n_marks; ++i) cudaEventElapsedTime(&ms[i], L->ev[i], L->ev[i + 1]);
+  int i = 0;
+  L->last.route_ms = routed ? ms[i++] : 0.f;
+  L->last.permute_ms = ms[i++];
+  L->last.gate_up_ms = ms[i++];
+  L->last.down_ms = ms[i++];
+  L->last.combine_ms = ms[i++];
+  cudaEventElapsedTime(&L->last.total_ms, L->ev[0], L->ev[n_marks - 1]);
+}
+
+// The whole layer on device buffers.  only_expert >= 0 gives the dense output
+// of that single expert node.
+int forward_dev(csk_moe_layer* L, const float* d_hidden, int64_t T, const float* d_router_in,
+                float* d_router_out, float* d_out, int only_expert, cudaStream_t s, bool sync_check) {
+  if (T <= 0 || T > L->max_T) return fail(L, CSK_ERR_NOMEM, "T=%lld outside (0, max_tokens=%lld]",
+                                          (long long)T, (long long)L->max_T);
+  L->last = csk_moe_timings{};
+  L->last_T = T;
+  StageTimer tm(L, s);
+  tm.mark();
+  const float* router = d_router_in;
+  const bool routed = d_router_in == nullptr;
+  if (routed) {
+    int rc = launch_router(L, d_hidden, T, L->d_router, s);
+    if (rc) return rc;
+    router = L->d_router;
+    tm.mark();
+  }
+  if (d_router_out && d_router_out != router)
+    CSK_CUDA(L, cudaMemcpyAsync(d_router_out, router, sizeof(float) * T * L->k * 2,
+                                cudaMemcpyDeviceToDevice, s));
+  const int64_t rows = only_expert >= 0 ? T : T * L->k;
+  const int path = choose_path(L, only_expert >= 0 ? rows * std::max(1, L->Eloc) : rows);
+  const int tile_rows = tile_rows_for(L, path, only_expert >= 0 ? rows * std::max(1, L->Eloc) : rows);
+  int rc = launch_permute(L, d_hidden, router, T, only_expert, tile_rows, L->e0, L->Eloc, L->d_x16,
+                          L->ldx, L->max_rows, s);
+  if (rc) return rc;
+  tm.mark();
+  rc = launch_experts(L, path, tile_rows, L->d_x16, L->d_y, L->H, nullptr, s, tm);
+  if (rc) return rc;
+  k_combine<<<(unsigned)T, 256, 0, s>>>(router, L->d_row_of_pair, L->d_y, L->H, d_out, (int)T, L->k,
+                                        L->H, L->cfg.weight_before_ffn, only_expert >= 0);
+  CSK_CUDA(L, cudaGetLastError());
+  L->last.launches++;
+  tm.mark();
+  L->n_marks = tm.n;
+  L->last_routed = routed;
+  L->last_stream = s;
+  if (!sync_check) return CSK_OK;
+  rc = check_device_status(L, s);
+  if (rc) return rc;
+  finish_timings(L, tm.n, routed);
+  return CSK_OK;
+}
+
+int check_layer(csk_moe_layer* L) { return L ? CSK_OK : CSK_ERR_INVALID; }
+
+}  // namespace
+
+// ===========================================================================
+extern "C" {
+
+int csk_moe_device_ok(int device) {
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess || device < 0 || device >= n) {
+    cudaGetLastError();
+    return 0;
+  }
+  cudaDeviceProp p{};
+  if (cudaGetDeviceProperties(&p, device) != cudaSuccess) return 0;
+  return p.major == 10 ? 1 : 0;
+}
+
+const char* csk_moe_last_error(const csk_moe_layer* layer) {
+  if (layer) return layer->err.c_str();
+  std::lock_guard<std::mutex> lk(g_err_mu);
+  return g_create_error.c_str();
+}
+
+int csk_moe_create(const csk_moe_config* cfg, csk_moe_layer** out) {
+  if (!cfg || !out) return fail(nullptr, CSK_ERR_INVALID, "null argument");
+  *out = nullptr;
+  if (cfg->num_experts <= 0 || cfg->num_experts > 1024)
+    return fail(nullptr, CSK_ERR_INVALID, "num_experts must be in [1,1024], got %d", cfg->num_experts);
+  if (cfg->top_k <= 0 || cfg->top_k > kMaxTopK || cfg->top_k > cfg->num_experts)
+    return fail(nullptr, CSK_ERR_INVALID, "top_k must be in [1,%d] and <= num_experts, got %d",
+                kMaxTopK, cfg->top_k);
+  if (cfg->hidden <= 0 || cfg->hidden % 32)
+    return fail(nullptr, CSK_ERR_INVALID,
+                "expert_mlp: hidden_dim must be a multiple of 32 for MXFP4, got %d", cfg->hidden);
+  if (cfg->ffn <= 0 || cfg->ffn % 32)
+    return fail(nullptr, CSK_ERR_INVALID,
+                "expert_mlp: expert_ffn_dim must be a multiple of 32 for MXFP4, got %d", cfg->ffn);
+  if (cfg->activation != CSK_ACT_MODIFIED_SWIGLU && cfg->activation != CSK_ACT_STANDARD_SWIGLU)
+    return fail(nullptr, CSK_ERR_INVALID, "unknown activation %d", cfg->activation);
+  if (cfg->max_tokens <= 0 || cfg->max_tokens * cfg->top_k > (1 << 28))
+    return fail(nullptr, CSK_ERR_INVALID, "max_tokens out of range");
+  const int eloc = cfg->expert_count ? cfg->expert_count : cfg->num_experts;
+  const int e0 = cfg->expert_count ? cfg->expert_begin : 0;
+  if (e0 < 0 || eloc <= 0 || e0 + eloc > cfg->num_experts)
+    return fail(nullptr, CSK_ERR_INVALID, "expert range [%d,%d) outside [0,%d)", e0, e0 + eloc,
+                cfg->num_experts);
+  if (!csk_moe_device_ok(cfg->device))
+    return fail(nullptr, CSK_ERR_CUDA, "device %d is not a usable sm_100 GPU (no CPU fallback exists)",
+                cfg->device);
+
+  csk_moe_layer* L = new (std::nothrow) csk_moe_layer();
+  if (!L) return fail(nullptr, CSK_ERR_NOMEM, "out of host memory");
+  L->cfg = *cfg;
+  L->E = cfg->num_experts;
+  L->k = cfg->top_k;
+  L->H = cfg->hidden;
+  L->F = cfg->ffn;
+  L->e0 = e0;
+  L->Eloc = eloc;
+  L->Lgu = make_layout(L->F, L->H, true);
+  L->Ld = make_layout(L->H, L->F, false);
+  L->off_gu = 0;
+  L->off_d = (L->Lgu.bytes() + 255) / 256 * 256;
+  L->off_bias = L->off_d + (L->Ld.bytes() + 255) / 256 * 256;
+  L->expert_stride = (L->off_bias + sizeof(float) * (2 * (size_t)L->F + L->H) + 255) / 256 * 256;
+  L->resident.assign(eloc, 0);
+  L->max_T = cfg->max_tokens;
+  L->max_rows = cfg->max_tokens * cfg->top_k;
+  L->ldx = L->Lgu.k_pad();
+  L->lda = L->Ld.k_pad();
+  L->max_tiles = (int)(L->max_rows / 8 + eloc + 8);
+  L->E_stride = (L->E + 31) / 32 * 32;
+
+#define CK(call)                                                                              \
+  do {                                                                                        \
+    cudaError_t _e = (call);                                                                  \
+    if (_e != cudaSuccess) {                                                                  \
+      int rc = fail(nullptr, _e == cudaErrorMemoryAllocation ? CSK_ERR_NOMEM : CSK_ERR_CUDA,  \
+                    "%s failed: %s", #call, cudaGetErrorString(_e));                          \
+      csk_moe_destroy(L);                                                                     \
+      return rc;                                                                              \
+    }                                                                                         \
+  } while (0)
+
+  CK(cudaSetDevice(cfg->device));
+  cudaDeviceProp prop{};
+  CK(cudaGetDeviceProperties(&prop, cfg->device));
+  L->sm_count = prop.multiProcessorCount;
+  CK(cudaStreamCreateWithFlags(&L->stream, cudaStreamNonBlocking));
+  for (auto& e : L->ev) CK(cudaEventCreate(&e));
+  CK(cudaMalloc(&L->d_weights, L->expert_stride * eloc));
+  CK(cudaMemset(L->d_weights, 0, L->expert_stride * eloc));
+  CK(cudaMalloc(&L->d_resident, eloc));
+  CK(cudaMemset(L->d_resident, 0, eloc));
+  L->stage_bytes = (size_t)L->H * L->F / 32 * 17;
+  CK(cudaMalloc(&L->d_stage, 3 * L->stage_bytes));
+  CK(cudaMalloc(&L->d_wg, sizeof(float) * L->E * L->H));
+  CK(cudaMalloc(&L->d_wgT, sizeof(float) * L->E_stride * L->H));
+  CK(cudaMemset(L->d_wgT, 0, sizeof(float) * L->E_stride * L->H));
+  CK(cudaMalloc(&L->d_rbias, sizeof(float) * L->E));
+  CK(cudaMalloc(&L->d_hidden, sizeof(float) * L->max_T * L->H));
+  CK(cudaMalloc(&L->d_router, sizeof(float) * L->max_T * L->k * 2));
+  CK(cudaMalloc(&L->d_out, sizeof(float) * L->max_T * L->H));
+  const size_t pad_rows = kTileM;
+  CK(cudaMalloc(&L->d_x16, sizeof(__half) * (L->max_rows + pad_rows) * L->ldx));
+  CK(cudaMemset(L->d_x16, 0, sizeof(__half) * (L->max_rows + pad_rows) * L->ldx));
+  CK(cudaMalloc(&L->d_a16, sizeof(__half) * (L->max_rows + pad_rows) * L->lda));
+  CK(cudaMemset(L->d_a16, 0, sizeof(__half) * (L->max_rows + pad_rows) * L->lda));
+  CK(cudaMalloc(&L->d_y, sizeof(float) * L->max_rows * L->H));
+  CK(cudaMalloc(&L->d_counts, sizeof(int) * L->E));
+  CK(cudaMalloc(&L->d_offsets, sizeof(int) * (L->E + 1)));
+  CK(cudaMalloc(&L->d_cursor, sizeof(int) * L->E));
+  CK(cudaMalloc(&L->d_row_of_pair, sizeof(int) * L->max_rows));
+  CK(cudaMalloc(&L->d_out_row_map, sizeof(int) * L->max_rows));
+  CK(cudaMalloc(&L->d_seg, sizeof(int) * (3 * 1024 + 8)));
+  CK(cudaMalloc(&L->d_tiles, sizeof(RowTile) * L->max_tiles));
+  CK(cudaMalloc(&L->d_meta, sizeof(int) * 8));
+  CK(cudaMemset(L->d_meta, 0, sizeof(int) * 8));
+  CK(cudaMallocHost(&L->h_meta, sizeof(int) * 8));
+  CK(cudaMallocHost(&L->h_counts64, sizeof(int64_t) * L->E));
+  CK(cudaFuncSetAttribute(k_router, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+  {
+    int rc = tile_init(L->tile, cfg->device);
+    if (rc) {
+      rc = fail(nullptr, rc, "tensor-core path setup: %s", L->tile.err.c_str());
+      csk_moe_destroy(L);
+      return rc;
+    }
+  }
+  CK(cudaDeviceSynchronize());
+#undef CK
+  *out = L;
+  return CSK_OK;
+}
+
+int csk_moe_destroy(csk_moe_layer* L) {
+  if (!L) return CSK_OK;
+  cudaSetDevice(L->cfg.device);
+  if (L->stream) cudaStreamSynchronize(L->stream);
+  tile_destroy(L->tile);
+  void* dev[] = {L->d_weights, L->d_resident, L->d_stage, L->d_wg, L->d_wgT, L->d_rbias, L->d_hidden,
+                 L->d_router, L->d_out, L->d_x16, L->d_a16, L->d_y, L->d_counts, L->d_offsets,
+                 L->d_cursor, L->d_row_of_pair, L->d_out_row_map, L->d_seg, L->d_tiles, L->d_meta};
+  for (void* p : dev)
+    if (p) cudaFree(p);
+  if (L->h_meta) cudaFreeHost(L->h_meta);
+  if (L->h_counts64) cudaFreeHost(L->h_counts64);
+  for (auto& e : L->ev)
+    if (e) cudaEventDestroy(e);
+  if (L->stream) cudaStreamDestroy(L->stream);
+  delete L;
+  return CSK_OK;
+}
+
+int csk_moe_set_router(csk_moe_layer* L, const float* gate_w, const float* gate_bias) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  if (!gate_w) return fail(L, CSK_ERR_INVALID, "gate_weights is null");
+  CSK_CUDA(L, cudaSetDevice(L->cfg.device));
+  CSK_CUDA(L, cudaMemcpyAsync(L->d_wg, gate_w, sizeof(float) * L->E * L->H, cudaMemcpyHostToDevice,
+                              L->stream));
+  k_transpose_router<<<grid_for((size_t)L->E * L->H, 256, 1024), 256, 0, L->stream>>>(
+      L->d_wg, L->d_wgT, L->E, L->H, L->E_stride);
+  L->has_rbias = gate_bias != nullptr;
+  if (gate_bias)
+    CSK_CUDA(L, cudaMemcpyAsync(L->d_rbias, gate_bias, sizeof(float) * L->E, cudaMemcpyHostToDevice,
+                                L->stream));
+  CSK_CUDA(L, cudaStreamSynchronize(L->stream));
+  L->router_set = true;
+  return CSK_OK;
+}
+
+int csk_moe_load_expert_mxfp4(csk_moe_layer* L, int32_t expert_id, const uint8_t* w_up,
+                              const uint8_t* w_gate, const uint8_t* w_down, const float* b_up,
+                              const float* b_gate, const float* b_down) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  if (expert_id < L->e0 || expert_id >= L->e0 + L->Eloc)
+    return fail(L, CSK_ERR_INVALID, "expert %d is not resident on this device (range [%d,%d))",
+                expert_id, L->e0, L->e0 + L->Eloc);
+  if (!w_up || !w_gate || !w_down) return fail(L, CSK_ERR_INVALID, "null weight pointer");
+  if (L->cfg.has_bias && (!b_up || !b_gate || !b_down))
+    return fail(L, CSK_ERR_INVALID, "layer has biases but a bias pointer is null");
+  CSK_CUDA(L, cudaSetDevice(L->cfg.device));
+  const int le = expert_id - L->e0;
+  uint8_t* base = L->d_weights + (size_t)le * L->expert_stride;
+  cudaStream_t s = L->stream;
+  uint8_t *s_up = L->d_stage, *s_gate = L->d_stage + L->stage_bytes, *s_down = L->d_stage + 2 * L->stage_bytes;
+  CSK_CUDA(L, cudaMemcpyAsync(s_up, w_up, L->stage_bytes, cudaMemcpyHostToDevice, s));
+  CSK_CUDA(L, cudaMemcpyAsync(s_gate, w_gate, L->stage_bytes, cudaMemcpyHostToDevice, s));
+  CSK_CUDA(L, cudaMemcpyAsync(s_down, w_down, L->stage_bytes, cudaMemcpyHostToDevice, s));
+  k_repack<<<grid_for(L->Lgu.bytes() / 4, 256, 4096), 256, 0, s>>>(s_gate, s_up, base + L->off_gu, L->Lgu);
+  k_repack<<<grid_for(L->Ld.bytes() / 4, 256, 4096), 256, 0, s>>>(s_down, nullptr, base + L->off_d, L->Ld);
+  CSK_CUDA(L, cudaGetLastError());
+  if (L->cfg.has_bias) {
+    float* b = reinterpret_cast<float*>(base + L->off_bias);
+    CSK_CUDA(L, cudaMemcpyAsync(b, b_up, sizeof(float) * L->F, cudaMemcpyHostToDevice, s));
+    CSK_CUDA(L, cudaMemcpyAsync(b + L->F, b_gate, sizeof(float) * L->F, cudaMemcpyHostToDevice, s));
+    CSK_CUDA(L, cudaMemcpyAsync(b + 2 * L->F, b_down, sizeof(float) * L->H, cudaMemcpyHostToDevice, s));
+  }
+  const uint8_t one = 1;
+  CSK_CUDA(L, cudaMemcpyAsync(L->d_resident + le, &one, 1, cudaMemcpyHostToDevice, s));
+  CSK_CUDA(L, cudaStreamSynchronize(s));
+  L->resident[le] = 1;
+  return CSK_OK;
+}
+
+int csk_moe_unpack_expert_mxfp4(csk_moe_layer* L, int32_t expert_id, int32_t which, uint8_t* out) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  if (expert_id < L->e0 || expert_id >= L->e0 + L->Eloc || !L->resident[expert_id - L->e0])
+    return fail(L, CSK_ERR_MISSING, "expert %d is not loaded", expert_id);
+  if (which < 0 || which > 2 || !out) return fail(L, CSK_ERR_INVALID, "bad argument");
+  CSK_CUDA(L, cudaSetDevice(L->cfg.device));
+  const uint8_t* base = L->d_weights + (size_t)(expert_id - L->e0) * L->expert_stride;
+  const MatLayout& lay = which == 2 ? L->Ld : L->Lgu;
+  const uint8_t* packed = base + (which == 2 ? L->off_d : L->off_gu);
+  k_unpack<<<grid_for((size_t)lay.N * (lay.K / 32), 128, 4096), 128, 0, L->stream>>>(
+      packed, L->d_stage, lay, which == 0 ? 1 : 0);
+  CSK_CUDA(L, cudaGetLastError());
+  CSK_CUDA(L, cudaMemcpyAsync(out, L->d_stage, L->stage_bytes, cudaMemcpyDeviceToHost, L->stream));
+  CSK_CUDA(L, cudaStreamSynchronize(L->stream));
+  return CSK_OK;
+}
+
+int csk_moe_expert_resident(const csk_moe_layer* L, int32_t expert_id) {
+  if (!L || expert_id < L->e0 || expert_id >= L->e0 + L->Eloc) return 0;
+  return L->resident[expert_id - L->e0];
+}
+
+int csk_moe_set_path(csk_moe_layer* L, int32_t path) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  if (path < CSK_PATH_AUTO || path > CSK_PATH_TILE) return fail(L, CSK_ERR_INVALID, "unknown path %d", path);
+  L->path = path;
+  return CSK_OK;
+}
+
+int csk_moe_enable_timing(csk_moe_layer* L, int32_t on) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  L->timing = on != 0;
+  return CSK_OK;
+}
+
+int csk_moe_sync(csk_moe_layer* L) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  CSK_CUDA(L, cudaSetDevice(L->cfg.device));
+  int rc = check_device_status(L, L->last_stream ? L->last_stream : L->stream);
+  if (rc) return rc;
+  if (L->timing && L->n_marks > 1) finish_timings(L, L->n_marks, L->last_routed);
+  return CSK_OK;
+}
+
+int csk_moe_get_timings(csk_moe_layer* L, csk_moe_timings* out) {
+  if (check_layer(L) || !out) return CSK_ERR_INVALID;
+  *out = L->last;
+  return CSK_OK;
+}
+
+int csk_moe_get_counters(csk_moe_layer* L, int64_t* rows_per_expert, int64_t* distinct,
+                         int64_t* weight_bytes) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  CSK_CUDA(L, cudaSetDevice(L->cfg.device));
+  std::vector<int> c(L->E);
+  CSK_CUDA(L, cudaMemcpy(c.data(), L->d_counts, sizeof(int) * L->E, cudaMemcpyDeviceToHost));
+  int64_t d = 0;
+  for (int e = 0; e < L->E; ++e) {
+    if (rows_per_expert) rows_per_expert[e] = c[e];
+    if (c[e] > 0) ++d;
+  }
+  if (distinct) *distinct = d;
+  if (weight_bytes) {
+    const int64_t per = (int64_t)3 * L->H * L->F / 32 * 17 +
+                        (L->cfg.has_bias ? (int64_t)sizeof(float) * (2 * L->F + L->H) : 0);
+    *weight_bytes = d * per;
+  }
+  return CSK_OK;
+}
+
+// ---- device-buffer entry points -------------------------------------------
+int csk_moe_route_dev(csk_moe_layer* L, const float* d_hidden, int64_t T, float* d_router_out, void* stream) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  if (!d_hidden || !d_router_out) return fail(L, CSK_ERR_INVALID, "null argument");
+  if (T <= 0 || T > L->max_T) return fail(L, CSK_ERR_NOMEM, "T=%lld outside (0, max_tokens]", (long long)T);
+  CSK_CUDA(L, cudaSetDevice(L->cfg.device));
+  L->last = csk_moe_timings{};
+  return launch_router(L, d_hidden, T, d_router_out, pick(L, stream));
+}
+
+int csk_moe_forward_dev(csk_moe_layer* L, const float* d_hidden, int64_t T, const float* d_router_in,
+                        float* d_router_out, float* d_out, void* stream) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  if (!d_hidden || !d_out) return fail(L, CSK_ERR_INVALID, "null argument");
+  CSK_CUDA(L, cudaSetDevice(L->cfg.device));
+  return forward_dev(L, d_hidden, T, d_router_in, d_router_out, d_out, -1, pick(L, stream), false);
+}
+
+// ---- host-buffer entry points ----------------------------------------------
+int csk_moe_route(csk_moe_layer* L, const float* hidden, int64_t T, float* router_out) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  if (!hidden || !router_out) return fail(L, CSK_ERR_INVALID, "null argument");
+  if (T <= 0 || T > L->max_T) return fail(L, CSK_ERR_NOMEM, "T=%lld outside (0, max_tokens]", (long long)T);
+  CSK_CUDA(L, cudaSetDevice(L->cfg.device));
+  cudaStream_t s = L->stream;
+  L->last = csk_moe_timings{};
+  CSK_CUDA(L, cudaMemcpyAsync(L->d_hidden, hidden, sizeof(float) * T * L->H, cudaMemcpyHostToDevice, s));
+  int rc = launch_router(L, L->d_hidden, T, L->d_router, s);
+  if (rc) return rc;
+  CSK_CUDA(L, cudaMemcpyAsync(router_out, L->d_router, sizeof(float) * T * L->k * 2, cudaMemcpyDeviceToHost, s));
+  CSK_CUDA(L, cudaStreamSynchronize(s));
+  return CSK_OK;
+}
+
+int csk_moe_forward(csk_moe_layer* L, const float* hidden, int64_t T, const float* router_in,
+                    float* router_out, float* out) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  if (!hidden || !out) return fail(L, CSK_ERR_INVALID, "null argument");
+  if (T <= 0 || T > L->max_T) return fail(L, CSK_ERR_NOMEM, "T=%lld outside (0, max_tokens]", (long long)T);
+  CSK_CUDA(L, cudaSetDevice(L->cfg.device));
+  cudaStream_t s = L->stream;
+  CSK_CUDA(L, cudaMemcpyAsync(L->d_hidden, hidden, sizeof(float) * T * L->H, cudaMemcpyHostToDevice, s));
+  if (router_in)
+    CSK_CUDA(L, cudaMemcpyAsync(L->d_router, router_in, sizeof(float) * T * L->k * 2, cudaMemcpyHostToDevice, s));
+  int rc = forward_dev(L, L->d_hidden, T, router_in ? L->d_router : nullptr, nullptr, L->d_out, -1, s, true);
+  if (rc) return rc;
+  CSK_CUDA(L, cudaMemcpyAsync(out, L->d_out, sizeof(float) * T * L->H, cudaMemcpyDeviceToHost, s));
+  if (router_out)
+    CSK_CUDA(L, cudaMemcpyAsync(router_out, L->d_router, sizeof(float) * T * L->k * 2, cudaMemcpyDeviceToHost, s));
+  CSK_CUDA(L, cudaStreamSynchronize(s));
+  return CSK_OK;
+}
+
+int csk_moe_expert_forward(csk_moe_layer* L, int32_t expert_id, const float* hidden, int64_t T,
+                           const float* router_out, float* out, int32_t* selected) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  if (!hidden || !router_out || !out || !selected) return fail(L, CSK_ERR_INVALID, "null argument");
+  if (T <= 0 || T > L->max_T) return fail(L, CSK_ERR_NOMEM, "T=%lld outside (0, max_tokens]", (long long)T);
+  if (expert_id < L->e0 || expert_id >= L->e0 + L->Eloc || !L->resident[expert_id - L->e0])
+    return fail(L, CSK_ERR_MISSING, "expert %d is not loaded", expert_id);
+  // the reference's early return: no token selected this expert (expert_mlp_node.h:441-443)
+  bool any = false;
+  for (int64_t i = 0; i < T * L->k && !any; ++i) any = (int)router_out[2 * i] == expert_id;
+  *selected = any ? 1 : 0;
+  if (!any) return CSK_OK;
+  CSK_CUDA(L, cudaSetDevice(L->cfg.device));
+  cudaStream_t s = L->stream;
+  CSK_CUDA(L, cudaMemcpyAsync(L->d_hidden, hidden, sizeof(float) * T * L->H, cudaMemcpyHostToDevice, s));
+  CSK_CUDA(L, cudaMemcpyAsync(L->d_router, router_out, sizeof(float) * T * L->k * 2, cudaMemcpyHostToDevice, s));
+  int rc = forward_dev(L, L->d_hidden, T, L->d_router, nullptr, L->d_out, expert_id, s, true);
+  if (rc) return rc;
+  CSK_CUDA(L, cudaMemcpyAsync(out, L->d_out, sizeof(float) * T * L->H, cudaMemcpyDeviceToHost, s));
+  CSK_CUDA(L, cudaStreamSynchronize(s));
+  return CSK_OK;
+}
+
+int csk_moe_merge(csk_moe_layer* L, const float* router_out, int64_t T, const float* const* expert_outs,
+                  float* out) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  if (!router_out || !expert_outs || !out) return fail(L, CSK_ERR_INVALID, "null argument");
+  if (T <= 0 || T > L->max_T) return fail(L, CSK_ERR_NOMEM, "T=%lld outside (0, max_tokens]", (long long)T);
+  bool any = false;
+  for (int e = 0; e < L->E; ++e) any = any || expert_outs[e];
+  if (!any) return fail(L, CSK_ERR_INVALID, "expert_merge: no non-empty expert outputs found");
+  // Only the k rows each token actually uses travel to the device: row (t,j)
+  // of expert e(t,j), or nothing when that expert's output is the empty tensor.
+  std::vector<int> rows((size_t)T * L->k, -1);
+  std::vector<float> packed;
+  packed.reserve((size_t)T * L->k * L->H);
+  int n = 0;
+  for (int64_t t = 0; t < T; ++t)
+    for (int j = 0; j < L->k; ++j) {
+      const int e = (int)router_out[(t * L->k + j) * 2];
+      if (e < 0 || e >= L->E)
+        return fail(L, CSK_ERR_INVALID, "expert_merge: expert_idx out of range: %d", e);
+      if (!expert_outs[e]) continue;
+      rows[t * L->k + j] = n++;
+      const float* src = expert_outs[e] + t * L->H;
+      packed.insert(packed.end(), src, src + L->H);
+    }
+  CSK_CUDA(L, cudaSetDevice(L->cfg.device));
+  cudaStream_t s = L->stream;
+  CSK_CUDA(L, cudaMemcpyAsync(L->d_y, packed.data(), sizeof(float) * packed.size(), cudaMemcpyHostToDevice, s));
+  CSK_CUDA(L, cudaMemcpyAsync(L->d_row_of_pair, rows.data(), sizeof(int) * rows.size(), cudaMemcpyHostToDevice, s));
+  CSK_CUDA(L, cudaMemcpyAsync(L->d_router, router_out, sizeof(float) * T * L->k * 2, cudaMemcpyHostToDevice, s));
+  k_combine<<<(unsigned)T, 256, 0, s>>>(L->d_router, L->d_row_of_pair, L->d_y, L->H, L->d_out, (int)T,
+                                        L->k, L->H, L->cfg.weight_before_ffn, 0);
+  CSK_CUDA(L, cudaGetLastError());
+  CSK_CUDA(L, cudaMemcpyAsync(out, L->d_out, sizeof(float) * T * L->H, cudaMemcpyDeviceToHost, s));
+  CSK_CUDA(L, cudaStreamSynchronize(s));
+  return CSK_OK;
+}
+
+// ---- expert parallelism -------------------------------------------------------
+int csk_moe_ep_row_pitch(const csk_moe_layer* L) { return L ? L->ldx : CSK_ERR_INVALID; }
+
+int csk_moe_ep_dispatch_dev(csk_moe_layer* L, const float* d_hidden, int64_t T, const float* d_router_in,
+                            void* d_send_f16, int32_t* d_counts, void* stream) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  if (!d_hidden || !d_send_f16 || !d_counts) return fail(L, CSK_ERR_INVALID, "null argument");
+  if (T <= 0 || T > L->max_T) return fail(L, CSK_ERR_NOMEM, "T=%lld outside (0, max_tokens]", (long long)T);
+  CSK_CUDA(L, cudaSetDevice(L->cfg.device));
+  cudaStream_t s = pick(L, stream);
+  L->last = csk_moe_timings{};
+  L->last_T = T;
+  if (!d_router_in) {
+    int rc = launch_router(L, d_hidden, T, L->d_router, s);
+    if (rc) return rc;
+  } else if (d_router_in != L->d_router) {
+    CSK_CUDA(L, cudaMemcpyAsync(L->d_router, d_router_in, sizeof(float) * T * L->k * 2,
+                                cudaMemcpyDeviceToDevice, s));
+  }
+  // group by global expert id; no tiles are built here (e_count = 0)
+  int rc = launch_permute(L, d_hidden, L->d_router, T, -1, 8, 0, 0, (__half*)d_send_f16, L->ldx,
+                          T * L->k, s);
+  if (rc) return rc;
+  CSK_CUDA(L, cudaMemcpyAsync(d_counts, L->d_counts, sizeof(int) * L->E, cudaMemcpyDeviceToDevice, s));
+  return CSK_OK;
+}
+
+int csk_moe_ep_experts_dev(csk_moe_layer* L, const void* d_recv_f16, const int32_t* d_recv_counts,
+                           int32_t n_src, int64_t total_rows, float* d_ret, void* stream) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  if (!d_recv_f16 || !d_recv_counts || !d_ret) return fail(L, CSK_ERR_INVALID, "null argument");
+  if (n_src <= 0 || (int64_t)n_src * L->Eloc > 1024)
+    return fail(L, CSK_ERR_INVALID, "n_src * local experts must be in [1,1024]");
+  if (total_rows < 0 || total_rows > L->max_rows)
+    return fail(L, CSK_ERR_NOMEM, "%lld received rows exceed max_tokens*top_k = %lld",
+                (long long)total_rows, (long long)L->max_rows);
+  CSK_CUDA(L, cudaSetDevice(L->cfg.device));
+  cudaStream_t s = pick(L, stream);
+  if (total_rows == 0) return CSK_OK;
+  const int path = choose_path(L, total_rows);
+  const int tile_rows = tile_rows_for(L, path, total_rows);
+  CSK_CUDA(L, cudaMemsetAsync(L->d_meta, 0, sizeof(int) * 8, s));
+  CSK_CUDA(L, cudaMemsetAsync(L->d_counts, 0, sizeof(int) * L->E, s));
+  k_ep_plan<<<1, 1024, 0, s>>>(d_recv_counts, n_src, L->Eloc, L->e0, L->d_counts, L->d_seg);
+  k_scan<<<1, 1024, 0, s>>>(L->d_counts, L->E, L->e0, L->Eloc, tile_rows, (int)L->max_rows, L->max_tiles,
+                            L->d_resident, L->d_offsets, L->d_cursor, L->d_tiles, L->d_meta);
+  k_ep_regroup<<<n_src * L->Eloc, 256, 0, s>>>((const __half*)d_recv_f16, L->d_x16, L->ldx, L->d_seg,
+                                               L->d_offsets, n_src, L->Eloc, L->e0, L->d_out_row_map);
+  CSK_CUDA(L, cudaGetLastError());
+  StageTimer tm(L, s);
+  int rc;
+  if (path == CSK_PATH_TILE) {
+    rc = launch_experts(L, path, tile_rows, L->d_x16, d_ret, L->H, L->d_out_row_map, s, tm);
+  } else {
+    rc = launch_experts(L, path, tile_rows, L->d_x16, L->d_y, L->H, nullptr, s, tm);
+    if (!rc) {
+      k_ep_ungroup<<<grid_for((size_t)total_rows, 8, 8 * L->sm_count), 256, 0, s>>>(
+          L->d_y, d_ret, L->H, L->d_out_row_map, (int)total_rows);
+      CSK_CUDA(L, cudaGetLastError());
+    }
+  }
+  if (rc) return rc;
+  return check_device_status(L, s);
+}
+
+int csk_moe_ep_combine_dev(csk_moe_layer* L, const float* d_back, int64_t T, float* d_out,
+                           float* d_router_out, void* stream) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  if (!d_back || !d_out) return fail(L, CSK_ERR_INVALID, "null argument");
+  if (T != L->last_T) return fail(L, CSK_ERR_INVALID, "combine T=%lld does not match dispatch T=%lld",
+                                  (long long)T, (long long)L->last_T);
+  CSK_CUDA(L, cudaSetDevice(L->cfg.device));
+  cudaStream_t s = pick(L, stream);
+  k_combine<<<(unsigned)T, 256, 0, s>>>(L->d_router, L->d_row_of_pair, d_back, L->H, d_out, (int)T, L->k,
+                                        L->H, L->cfg.weight_before_ffn, 0);
+  CSK_CUDA(L, cudaGetLastError());
+  if (d_router_out)
+    CSK_CUDA(L, cudaMemcpyAsync(d_router_out, L->d_router, sizeof(float) * T * L->k * 2,
+                                cudaMemcpyDeviceToDevice, s));
+  return CSK_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,392 @@
+"""Host-side mirror, in Python, of the reference's operator interface for the
+MoE path, over the C ABI of ``libcsk_moe.so``.
+
+``MoeLayer`` wraps one ``csk_moe_layer`` handle.  The node classes keep the
+names, setters, argument meaning and error behaviour of the reference's
+operators so tests written against the reference read the same here:
+
+    moe_router_node    include/coalsack/nn/nn_ops/moe_router_node.h:22-124
+    expert_mlp_node    include/coalsack/nn/nn_ops/expert_mlp_node.h:25-148, 392-530
+    expert_merge_node  include/coalsack/nn/nn_ops/expert_merge_node.h:9-134
+
+Every computation runs on the GPU; nothing here falls back to the CPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import enum
+
+import numpy as np
+
+from . import _lib
+from ._lib import Config, Timings
+
+PATH_AUTO, PATH_STREAM, PATH_TILE = 0, 1, 2
+
+
+class CskError(RuntimeError):
+    """A non-zero status from the C ABI (the C++ node shim throws std::runtime_error)."""
+
+    def __init__(self, code: int, msg: str):
+        super().__init__(msg)
+        self.code = code
+
+
+def _np_f32(a):
+    return None if a is None else np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _np_u8(a):
+    return None if a is None else np.ascontiguousarray(a, dtype=np.uint8)
+
+
+def _p(a):
+    """void* of a numpy array, a torch tensor, an int address or None."""
+    if a is None:
+        return None
+    if isinstance(a, np.ndarray):
+        return a.ctypes.data
+    if isinstance(a, int):
+        return a
+    return a.data_ptr()
+
+
+class MoeLayer:
+    """One MoE layer resident on one GPU (a ``csk_moe_layer`` handle)."""
+
+    def __init__(self, num_experts, top_k, hidden, ffn, activation=0, has_bias=True,
+                 sigmoid_gating=False, weight_before_ffn=False, device=0, expert_begin=0,
+                 expert_count=0, max_tokens=1024):
+        self._lib = _lib.load()
+        self.cfg = Config(num_experts, top_k, hidden, ffn, int(activation), int(has_bias),
+                          int(sigmoid_gating), int(weight_before_ffn), device, expert_begin,
+                          expert_count, 0, max_tokens)
+        self.E, self.k, self.H, self.F = num_experts, top_k, hidden, ffn
+        self.max_tokens = max_tokens
+        self._h = C.c_void_p()
+        rc = self._lib.csk_moe_create(C.byref(self.cfg), C.byref(self._h))
+        if rc:
+            raise CskError(rc, self._lib.csk_moe_last_error(None).decode())
+
+    @classmethod
+    def from_shape(cls, shape, device=0, max_tokens=None, expert_begin=0, expert_count=0, **kw):
+        return cls(shape.num_experts, shape.top_k, shape.hidden, shape.ffn, shape.act, shape.has_bias,
+                   device=device, expert_begin=expert_begin, expert_count=expert_count,
+                   max_tokens=max_tokens or shape.tokens, **kw)
+
+    # -- plumbing -----------------------------------------------------------
+    def _check(self, rc):
+        if rc:
+            raise CskError(rc, self._lib.csk_moe_last_error(self._h).decode())
+
+    def close(self):
+        if self._h:
+            self._lib.csk_moe_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- weights ------------------------------------------------------------
+    def set_router(self, gate_w, gate_bias=None):
+        gate_w, gate_bias = _np_f32(gate_w), _np_f32(gate_bias)
+        if gate_w.shape != (self.E, self.H):
+            raise RuntimeError(f"moe_router: gate_weights shape mismatch, expected [{self.E}, {self.H}], "
+                               f"got [{gate_w.shape[0]}, {gate_w.shape[1]}]")
+        self._check(self._lib.csk_moe_set_router(self._h, _p(gate_w), _p(gate_bias)))
+
+    def load_expert(self, expert_id, w_up, w_gate, w_down, b_up=None, b_gate=None, b_down=None):
+        nbytes = self.H * self.F // 32 * 17
+        arrs = [_np_u8(w_up).reshape(-1), _np_u8(w_gate).reshape(-1), _np_u8(w_down).reshape(-1)]
+        for a in arrs:
+            if a.size != nbytes:
+                raise RuntimeError("expert_mlp: weight dimension mismatch")
+        b = [_np_f32(b_up), _np_f32(b_gate), _np_f32(b_down)]
+        self._check(self._lib.csk_moe_load_expert_mxfp4(self._h, expert_id, *map(_p, arrs), *map(_p, b)))
+
+    def load_experts(self, experts: dict, ids=None):
+        """``experts``: lists as made by ``synth.all_experts`` (index i <-> ids[i])."""
+        ids = list(range(self.E)) if ids is None else list(ids)
+        for i, e in enumerate(ids):
+            b = [experts[n][i] if experts.get(n) is not None else None for n in ("b_up", "b_gate", "b_down")]
+            self.load_expert(e, experts["w_up"][i], experts["w_gate"][i], experts["w_down"][i], *b)
+
+    def unpack_expert(self, expert_id, which):
+        out = np.empty(self.H * self.F // 32 * 17, np.uint8)
+        self._check(self._lib.csk_moe_unpack_expert_mxfp4(self._h, expert_id, which, _p(out)))
+        return out
+
+    def expert_resident(self, expert_id) -> bool:
+        return bool(self._lib.csk_moe_expert_resident(self._h, expert_id))
+
+    # -- host-buffer calls ----------------------------------------------------
+    def route(self, hidden):
+        hidden = _np_f32(hidden).reshape(-1, self.H)
+        T = hidden.shape[0]
+        out = np.empty((T, self.k, 2), np.float32)
+        self._check(self._lib.csk_moe_route(self._h, _p(hidden), T, _p(out)))
+        return out
+
+    def forward(self, hidden, router_out=None, out=None, router_out_buf=None):
+        """(out[T,H], router_out[T,k,2]).  ``hidden``/``out`` may be pinned torch tensors."""
+        if isinstance(hidden, np.ndarray) or not hasattr(hidden, "data_ptr"):
+            hidden = _np_f32(hidden).reshape(-1, self.H)
+        T = hidden.shape[0]
+        if out is None:
+            out = np.empty((T, self.H), np.float32)
+        r_in = _np_f32(router_out)
+        r_out = router_out_buf if router_out_buf is not None else np.empty((T, self.k, 2), np.float32)
+        self._check(self._lib.csk_moe_forward(self._h, _p(hidden), T, _p(r_in), _p(r_out), _p(out)))
+        return out, r_out
+
+    def expert_forward(self, expert_id, hidden, router_out):
+        """Dense [T,H] output of one expert node, or None for the {0}-shaped empty tensor."""
+        hidden = _np_f32(hidden).reshape(-1, self.H)
+        router_out = _np_f32(router_out)
+        T = hidden.shape[0]
+        out = np.empty((T, self.H), np.float32)
+        sel = C.c_int32(0)
+        self._check(self._lib.csk_moe_expert_forward(self._h, expert_id, _p(hidden), T, _p(router_out),
+                                                     _p(out), C.byref(sel)))
+        return out if sel.value else None
+
+    def merge(self, router_out, expert_outs):
+        router_out = _np_f32(router_out)
+        T = router_out.shape[0]
+        keep = [None if a is None else _np_f32(a) for a in expert_outs]
+        ptrs = (C.c_void_p * self.E)(*[None if a is None else a.ctypes.data for a in keep])
+        out = np.empty((T, self.H), np.float32)
+        self._check(self._lib.csk_moe_merge(self._h, _p(router_out), T, ptrs, _p(out)))
+        return out
+
+    # -- device-buffer calls (torch CUDA tensors or raw addresses) -------------
+    def route_dev(self, d_hidden, T, d_router_out, stream=None):
+        self._check(self._lib.csk_moe_route_dev(self._h, _p(d_hidden), T, _p(d_router_out), stream))
+
+    def forward_dev(self, d_hidden, T, d_out, d_router_in=None, d_router_out=None, stream=None):
+        self._check(self._lib.csk_moe_forward_dev(self._h, _p(d_hidden), T, _p(d_router_in),
+                                                  _p(d_router_out), _p(d_out), stream))
+
+    def sync(self):
+        """Wait for the last device-buffer call and raise what its kernels reported."""
+        self._check(self._lib.csk_moe_sync(self._h))
+
+    def ep_row_pitch(self) -> int:
+        return self._lib.csk_moe_ep_row_pitch(self._h)
+
+    def ep_dispatch_dev(self, d_hidden, T, d_send, d_counts, d_router_in=None, stream=None):
+        self._check(self._lib.csk_moe_ep_dispatch_dev(self._h, _p(d_hidden), T, _p(d_router_in), _p(d_send),
+                                                      _p(d_counts), stream))
+
+    def ep_experts_dev(self, d_recv, d_recv_counts, n_src, total_rows, d_ret, stream=None):
+        self._check(self._lib.csk_moe_ep_experts_dev(self._h, _p(d_recv), _p(d_recv_counts), n_src,
+                                                     total_rows, _p(d_ret), stream))
+
+    def ep_combine_dev(self, d_back, T, d_out, d_router_out=None, stream=None):
+        self._check(self._lib.csk_moe_ep_combine_dev(self._h, _p(d_back), T, _p(d_out), _p(d_router_out),
+                                                     stream))
+
+    # -- knobs / observability ---------------------------------------------------
+    def set_path(self, path):
+        self._check(self._lib.csk_moe_set_path(self._h, path))
+
+    def enable_timing(self, on=True):
+        self._check(self._lib.csk_moe_enable_timing(self._h, int(on)))
+
+    def timings(self) -> dict:
+        t = Timings()
+        self._check(self._lib.csk_moe_get_timings(self._h, C.byref(t)))
+        return {n: getattr(t, n) for n, _ in Timings._fields_}
+
+    def counters(self):
+        rows = np.zeros(self.E, np.int64)
+        d, b = C.c_int64(0), C.c_int64(0)
+        self._check(self._lib.csk_moe_get_counters(self._h, _p(rows), C.byref(d), C.byref(b)))
+        return rows, d.value, b.value
+
+
+# ---------------------------------------------------------------------------
+# Operator classes with the reference's names and setters
+# ---------------------------------------------------------------------------
+class moe_router_node:
+    """moe_router_node (moe_router_node.h:22-124): ``set_config``, ``set_sigmoid_gating``,
+    ``compute_test(hidden_states[B,S,H], gate_weights[E,H][, gate_bias[E]]) -> [B,S,k,2]``."""
+
+    def __init__(self, device=0):
+        self.num_experts_, self.top_k_, self.use_sigmoid_gating_ = 0, 0, False
+        self.device = device
+        self._layer = None
+        self._key = None
+
+    def set_config(self, num_experts, top_k):
+        self.num_experts_, self.top_k_ = int(num_experts), int(top_k)
+
+    def set_sigmoid_gating(self, v):
+        self.use_sigmoid_gating_ = bool(v)
+
+    def compute_test(self, hidden_states, gate_weights, gate_bias=None):
+        hidden_states, gate_weights = np.asarray(hidden_states), np.asarray(gate_weights)
+        if hidden_states.ndim != 3:
+            raise RuntimeError("moe_router: hidden_states must be 3D [batch, seq_len, hidden_dim], got "
+                               f"{hidden_states.ndim}D")
+        if gate_weights.ndim != 2:
+            raise RuntimeError("moe_router: gate_weights must be 2D [num_experts, hidden_dim], got "
+                               f"{gate_weights.ndim}D")
+        if gate_bias is not None and np.asarray(gate_bias).ndim != 1:
+            raise RuntimeError(f"moe_router: gate_bias must be 1D [num_experts], got {np.asarray(gate_bias).ndim}D")
+        B, S, H = hidden_states.shape
+        if gate_weights.shape != (self.num_experts_, H):
+            raise RuntimeError(f"moe_router: gate_weights shape mismatch, expected [{self.num_experts_}, {H}], "
+                               f"got [{gate_weights.shape[0]}, {gate_weights.shape[1]}]")
+        if gate_bias is not None and np.asarray(gate_bias).shape[0] != self.num_experts_:
+            raise RuntimeError(f"moe_router: gate_bias must have num_experts={self.num_experts_} elements, "
+                               f"got {np.asarray(gate_bias).shape[0]}")
+        if hidden_states.dtype != np.float32:
+            raise RuntimeError("moe_router: only float32 supported on the GPU path")
+        T = B * S
+        Hp = (H + 31) // 32 * 32  # the layer handle wants H % 32 == 0; zero columns add exact zeros
+        key = (self.num_experts_, self.top_k_, Hp, self.use_sigmoid_gating_, T)
+        if self._key != key:
+            if self._layer is not None:
+                self._layer.close()
+            self._layer = MoeLayer(self.num_experts_, self.top_k_, Hp, 32, has_bias=False,
+                                   sigmoid_gating=self.use_sigmoid_gating_, device=self.device,
+                                   max_tokens=max(T, 1))
+            self._key = key
+        h2 = hidden_states.reshape(T, H)
+        if Hp != H:
+            h2 = np.concatenate([h2, np.zeros((T, Hp - H), np.float32)], axis=1)
+            gate_weights = np.concatenate([gate_weights, np.zeros((self.num_experts_, Hp - H), np.float32)], axis=1)
+        self._layer.set_router(gate_weights, gate_bias)
+        return self._layer.route(h2).reshape(B, S, self.top_k_, 2)
+
+
+class expert_mlp_node:
+    """expert_mlp_node (expert_mlp_node.h:25-148), MXFP4 weight path."""
+
+    class activation_type(enum.IntEnum):
+        MODIFIED_SWIGLU = 0
+        STANDARD_SWIGLU = 1
+
+    def __init__(self, expert_id=0, device=0):
+        self.expert_id_ = int(expert_id)
+        self.activation_type_ = expert_mlp_node.activation_type.MODIFIED_SWIGLU
+        self.weight_before_ffn_ = False
+        self.device = device
+        self._layer = None
+        self._key = None
+
+    def get_expert_id(self):
+        return self.expert_id_
+
+    def get_proc_name(self):
+        return "expert_mlp"
+
+    def set_activation_type(self, t):
+        self.activation_type_ = expert_mlp_node.activation_type(t)
+
+    def get_activation_type(self):
+        return self.activation_type_
+
+    def set_weight_before_ffn(self, v):
+        self.weight_before_ffn_ = bool(v)
+
+    def _get_layer(self, H, F, has_bias, k, T):
+        key = (H, F, has_bias, k, int(self.activation_type_), self.weight_before_ffn_, self.expert_id_)
+        if self._key != key or self._layer.max_tokens < T:
+            if self._layer is not None:
+                self._layer.close()
+            # a one-expert layer whose only resident expert carries this node's id
+            self._layer = MoeLayer(max(self.expert_id_ + 1, k), k, H, F,
+                                   int(self.activation_type_), has_bias,
+                                   weight_before_ffn=self.weight_before_ffn_, device=self.device,
+                                   expert_begin=self.expert_id_, expert_count=1, max_tokens=max(T, 64))
+            self._key = key
+        return self._layer
+
+    def compute_test_mxfp4(self, hidden_vec, w_up, w_gate, w_down, b_up, b_gate, b_down, hidden_dim,
+                           expert_ffn_dim):
+        """One token through this expert (expert_mlp_node.h:63-70)."""
+        if hidden_dim % 2 or expert_ffn_dim % 2:
+            raise RuntimeError("compute_token_mxfp4: dimensions must be even")
+        lay = self._get_layer(hidden_dim, expert_ffn_dim, b_up is not None, 1, 1)
+        lay.load_expert(self.expert_id_, w_up, w_gate, w_down, b_up, b_gate, b_down)
+        r = np.array([[[self.expert_id_, 1.0]]], np.float32)
+        out = lay.expert_forward(self.expert_id_, np.asarray(hidden_vec, np.float32).reshape(1, -1), r)
+        return out[0]
+
+    def compute_with_mxfp4(self, hidden_states, w_up, w_gate, w_down, b_up, b_gate, b_down, router_output,
+                           expert_ffn_dim):
+        """The node's MXFP4 branch (expert_mlp_node.h:392-485): dense [B,S,H] output with
+        zero rows for tokens that did not select this expert, or a {0}-shaped tensor."""
+        hidden_states, router_output = np.asarray(hidden_states), np.asarray(router_output)
+        if hidden_states.ndim != 3:
+            raise RuntimeError("expert_mlp: hidden_states must be 3D")
+        if router_output.ndim != 4 or router_output.shape[3] != 2:
+            raise RuntimeError("expert_mlp: router_output must be 4D [batch, seq_len, top_k, 2]")
+        B, S, H = hidden_states.shape
+        F = int(expert_ffn_dim)
+        if not np.any(router_output[..., 0].astype(np.int32) == self.expert_id_):
+            return np.zeros((0,), np.float32)
+        if H % 32:
+            raise RuntimeError(f"expert_mlp: hidden_dim must be a multiple of 32 for MXFP4, got {H}")
+        if F % 32:
+            raise RuntimeError(f"expert_mlp: expert_ffn_dim must be a multiple of 32 for MXFP4, got {F}")
+        k = router_output.shape[2]
+        lay = self._get_layer(H, F, b_up is not None, k, B * S)
+        lay.load_expert(self.expert_id_, w_up, w_gate, w_down, b_up, b_gate, b_down)
+        out = lay.expert_forward(self.expert_id_, hidden_states.reshape(B * S, H),
+                                 router_output.reshape(B * S, k, 2))
+        return out.reshape(B, S, H)
+
+
+class expert_merge_node:
+    """expert_merge_node (expert_merge_node.h:9-134)."""
+
+    def __init__(self, device=0):
+        self.num_experts_, self.top_k_, self.weight_before_ffn_ = 0, 0, False
+        self.device = device
+
+    def set_config(self, num_experts, top_k):
+        self.num_experts_, self.top_k_ = int(num_experts), int(top_k)
+
+    def set_weight_before_ffn(self, v):
+        self.weight_before_ffn_ = bool(v)
+
+    def compute_test(self, inputs):
+        if len(inputs) != self.num_experts_ + 1:
+            raise RuntimeError(f"expert_merge: expected {self.num_experts_ + 1} inputs, got {len(inputs)}")
+        router = np.asarray(inputs[0])
+        if router.ndim != 4 or router.shape[2] != self.top_k_ or router.shape[3] != 2:
+            raise RuntimeError(f"expert_merge: router output must have shape [batch, seq_len, {self.top_k_}, 2]")
+        B, S = router.shape[:2]
+        dense = [a for a in inputs[1:] if np.asarray(a).ndim == 3 and np.asarray(a).shape[0] > 0]
+        if not dense:
+            raise RuntimeError("expert_merge: no non-empty expert outputs found")
+        H = np.asarray(dense[0]).shape[2]
+        for a in dense:
+            if np.asarray(a).shape != (B, S, H):
+                raise RuntimeError("expert_merge: all non-empty expert outputs must have same shape")
+        if router.dtype != np.float32:
+            raise RuntimeError("expert_merge: only float32 supported")
+        Hp = (H + 31) // 32 * 32
+        lay = MoeLayer(self.num_experts_, self.top_k_, Hp, 32, has_bias=False,
+                       weight_before_ffn=self.weight_before_ffn_, device=self.device, max_tokens=B * S)
+        outs = []
+        for a in inputs[1:]:
+            a = np.asarray(a)
+            if a.ndim == 3 and a.shape[0] > 0:
+                a = a.reshape(B * S, H).astype(np.float32)
+                if Hp != H:
+                    a = np.concatenate([a, np.zeros((B * S, Hp - H), np.float32)], axis=1)
+                outs.append(a)
+            else:
+                outs.append(None)
+        try:
+            out = lay.merge(router.reshape(B * S, self.top_k_, 2), outs)
+        finally:
+            lay.close()
+        return out[:, :H].reshape(B, S, H)

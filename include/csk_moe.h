@@ -1,0 +1,197 @@
+/* csk_moe.h -- C ABI of the B200 (sm_100a) mixture-of-experts layer.
+ *
+ * One opaque handle per MoE layer and device.  The handle owns the repacked
+ * MXFP4 expert weights, the router weights and all scratch memory on that
+ * device.  Every function returns 0 on success or a negative csk_status; no
+ * C++ exception crosses this boundary and nothing here aborts the process.
+ * csk_moe_last_error() gives the text of the last failure.
+ *
+ * Calls on one handle must be serialised by the caller; calls on different
+ * handles may run concurrently from different host threads (the reference
+ * drives each layer from its own scheduler thread, one frame in flight:
+ * include/coalsack/nn/model_io_nodes.h:268-290, src/llm/llm_engine.cpp:904).
+ *
+ * "reference" below means the yoshou/coalsack source tree; paths are relative
+ * to its root.  Tensor conventions are the reference's:
+ *   hidden      [T, H] fp32 row-major   (the reference's [batch, seq, H], T = batch*seq)
+ *   router_out  [T, k, 2] fp32          (expert id stored as a float, routing weight)
+ *   MXFP4       row-major rows of cols/32 blocks of 17 bytes: one E8M0 scale
+ *               byte, then 16 bytes of E2M1 codes; byte j holds element j in
+ *               its low nibble and element j+16 in its high nibble
+ *               (include/coalsack/tensor/dynamic_mx_tensor.h:19-44,
+ *                include/coalsack/gguf/gguf_dequant.h:437-455).
+ */
+#ifndef CSK_MOE_H
+#define CSK_MOE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum csk_status {
+  CSK_OK = 0,
+  CSK_ERR_INVALID = -1,  /* bad argument, shape or state                         */
+  CSK_ERR_CUDA = -2,     /* a CUDA runtime/driver call failed                    */
+  CSK_ERR_DEVICE = -3,   /* a device-side check failed (bad expert id, bounded
+                            wait ran out); the handle stays usable              */
+  CSK_ERR_NOMEM = -4,    /* allocation failed or capacity exceeded               */
+  CSK_ERR_MISSING = -5   /* an expert needed by the call was never loaded        */
+} csk_status;
+
+/* expert_mlp_node::activation_type (include/coalsack/nn/nn_ops/expert_mlp_node.h:27-30) */
+enum { CSK_ACT_MODIFIED_SWIGLU = 0, CSK_ACT_STANDARD_SWIGLU = 1 };
+
+/* Which expert kernel serves a forward call. AUTO picks by the number of
+ * (token, expert) rows; the other two force one kernel (tests, benchmarks). */
+enum { CSK_PATH_AUTO = 0, CSK_PATH_STREAM = 1, CSK_PATH_TILE = 2 };
+
+/* Layer description: graph_builder::config num_experts / expert_top_k /
+ * use_sigmoid_gating / weight_before_ffn (include/coalsack/llm/graph_builder.h:29-44)
+ * plus the per-node settings (moe_router_node.h:27-34, expert_mlp_node.h:44-52,
+ * expert_merge_node.h:17-24). */
+typedef struct csk_moe_config {
+  int32_t num_experts;        /* E, experts of the whole layer                    */
+  int32_t top_k;              /* k                                                */
+  int32_t hidden;             /* H, multiple of 32                                */
+  int32_t ffn;                /* F, multiple of 32                                */
+  int32_t activation;         /* CSK_ACT_*                                        */
+  int32_t has_bias;           /* experts carry b_up/b_gate/b_down                 */
+  int32_t sigmoid_gating;     /* routing weight = sigmoid(logit) instead of softmax */
+  int32_t weight_before_ffn;  /* scale the expert INPUT by the routing weight     */
+  int32_t device;             /* CUDA device ordinal                              */
+  int32_t expert_begin;       /* first expert resident on this device ...         */
+  int32_t expert_count;       /* ... and how many (0 = all E); expert parallelism */
+  int32_t reserved0;
+  int64_t max_tokens;         /* largest T (and, under expert parallelism, the
+                                 largest number of received rows / k) of a call   */
+} csk_moe_config;
+
+typedef struct csk_moe_layer csk_moe_layer;
+
+/* ---- lifetime ---------------------------------------------------------- */
+int csk_moe_create(const csk_moe_config* cfg, csk_moe_layer** out);
+int csk_moe_destroy(csk_moe_layer* layer);
+/* Text of the last error on this handle (or of the last failed create when
+ * layer is NULL).  Valid until the next call on the handle. */
+const char* csk_moe_last_error(const csk_moe_layer* layer);
+/* 1 when a usable CUDA device with compute capability 10.x is present. */
+int csk_moe_device_ok(int device);
+
+/* ---- weights ------------------------------------------------------------ */
+/* Router weights Wg [E,H] fp32 row-major and optional bias [E] (host).
+ * Replaces inputs 1 and 2 of moe_router_node (moe_router_node.h:51-124). */
+int csk_moe_set_router(csk_moe_layer* layer, const float* gate_w, const float* gate_bias_or_null);
+
+/* One expert's three MXFP4 matrices exactly as dynamic_mx_tensor::data_ptr()
+ * holds them (w_up [F,H], w_gate [F,H], w_down [H,F]) and its fp32 biases (NULL
+ * when has_bias = 0), all host pointers.  The matrices are repacked once into
+ * the device tile layout.  Replaces what moe_weight_fetch_node hands to each
+ * expert_mlp_node per frame (moe_weight_fetch_node.h:187-206,
+ * src/llm/moe_weight_provider.cpp:160-188). */
+int csk_moe_load_expert_mxfp4(csk_moe_layer* layer, int32_t expert_id, const uint8_t* w_up,
+                              const uint8_t* w_gate, const uint8_t* w_down, const float* b_up,
+                              const float* b_gate, const float* b_down);
+/* Inverse of the repack: writes matrix `which` (0 up, 1 gate, 2 down) of a
+ * resident expert back as 17-byte blocks (host).  The repack is lossless iff
+ * this returns the loaded bytes. */
+int csk_moe_unpack_expert_mxfp4(csk_moe_layer* layer, int32_t expert_id, int32_t which,
+                                uint8_t* out_blocks);
+/* 1 if the expert's weights are resident on the device, 0 if not. */
+int csk_moe_expert_resident(const csk_moe_layer* layer, int32_t expert_id);
+
+/* ---- host-buffer entry points (what the reference nodes bind) ---------- */
+/* moe_router_node::compute (moe_router_node.h:51-124, 140-214):
+ * hidden [T,H] -> router_out [T,k,2]. */
+int csk_moe_route(csk_moe_layer* layer, const float* hidden, int64_t T, float* router_out);
+
+/* The whole layer: router (when router_out_in is NULL) -> dispatch by expert
+ * -> grouped MXFP4 gated MLP -> weighted combine in router order.  Equals
+ * moe_router_node + moe_weight_fetch_node + E x expert_mlp_node +
+ * expert_merge_node (src/llm/llm_engine.cpp:721-753).  router_out_out
+ * (optional) receives the routing actually used.  out is [T,H]. */
+int csk_moe_forward(csk_moe_layer* layer, const float* hidden, int64_t T,
+                    const float* router_out_in, float* router_out_out, float* out);
+
+/* One expert_mlp_node (expert_mlp_node.h:392-530): dense [T,H] output with
+ * zero rows for tokens that did not select expert_id.  *selected is set to 0
+ * and out is left untouched when no token selected it (the reference then
+ * emits a {0}-shaped tensor, :441-443), else to 1. */
+int csk_moe_expert_forward(csk_moe_layer* layer, int32_t expert_id, const float* hidden, int64_t T,
+                           const float* router_out, float* out, int32_t* selected);
+
+/* expert_merge_node::compute (expert_merge_node.h:30-134): expert_outs[e] is a
+ * dense [T,H] host buffer or NULL for an empty ({0}-shaped) input. */
+int csk_moe_merge(csk_moe_layer* layer, const float* router_out, int64_t T,
+                  const float* const* expert_outs, float* out);
+
+/* ---- device-buffer entry points (no host copies; `stream` is a
+ *      cudaStream_t passed as void*, NULL = the handle's own stream) ------- */
+int csk_moe_route_dev(csk_moe_layer* layer, const float* d_hidden, int64_t T, float* d_router_out,
+                      void* stream);
+int csk_moe_forward_dev(csk_moe_layer* layer, const float* d_hidden, int64_t T,
+                        const float* d_router_out_in, float* d_router_out_out, float* d_out,
+                        void* stream);
+/* The device-buffer calls only enqueue work.  csk_moe_sync waits for the last
+ * one on this handle and reports what its kernels found (an expert id out of
+ * range, rows routed to an expert that is not loaded, capacity exceeded). */
+int csk_moe_sync(csk_moe_layer* layer);
+
+/* ---- expert parallelism: the layer cut at its two exchange points -------
+ * Rank r holds experts [expert_begin, expert_begin+expert_count).  A step is
+ *   dispatch_dev  : route local tokens, group their (token, expert) rows by
+ *                   global expert id (which is by destination rank, then
+ *                   expert), write them as fp16 rows into d_send and the
+ *                   per-expert row counts into d_counts [E] (int32)
+ *   <all-to-all of counts, then of rows: the caller's NCCL>
+ *   experts_dev   : run the resident experts over received rows.  d_recv holds
+ *                   n_src segments (one per source rank), each ordered by local
+ *                   expert; d_recv_counts is [n_src, expert_count] int32.
+ *                   Output rows (fp32, [rows, H]) are written to d_ret in the
+ *                   same order as d_recv.
+ *   <all-to-all of output rows back>
+ *   combine_dev   : weighted sum over k in router order of the returned rows
+ *                   (d_back is in the order of d_send).
+ * The reference has no counterpart (it runs every expert serially on one host
+ * thread); the arithmetic per row is that of csk_moe_forward. */
+/* Row pitch, in fp16 elements, of d_send / d_recv (H rounded up to 64). */
+int csk_moe_ep_row_pitch(const csk_moe_layer* layer);
+int csk_moe_ep_dispatch_dev(csk_moe_layer* layer, const float* d_hidden, int64_t T,
+                            const float* d_router_out_in, void* d_send_f16, int32_t* d_counts,
+                            void* stream);
+int csk_moe_ep_experts_dev(csk_moe_layer* layer, const void* d_recv_f16,
+                           const int32_t* d_recv_counts, int32_t n_src, int64_t total_rows,
+                           float* d_ret, void* stream);
+int csk_moe_ep_combine_dev(csk_moe_layer* layer, const float* d_back, int64_t T, float* d_out,
+                           float* d_router_out_out, void* stream);
+
+/* ---- knobs and observability ------------------------------------------- */
+int csk_moe_set_path(csk_moe_layer* layer, int32_t path /* CSK_PATH_* */);
+
+/* Device time of the stages of the last forward call on this handle, in
+ * milliseconds (CUDA events on the stream the kernels ran on).  Collection is
+ * off by default; csk_moe_enable_timing(layer, 1) turns it on. */
+typedef struct csk_moe_timings {
+  float route_ms;    /* router kernel                                  */
+  float permute_ms;  /* histogram, scan, scatter + fp16 gather         */
+  float gate_up_ms;  /* first grouped contraction + activation         */
+  float down_ms;     /* second grouped contraction                     */
+  float combine_ms;  /* weighted sum over k                            */
+  float total_ms;    /* first to last kernel                           */
+  int32_t path;      /* CSK_PATH_STREAM or CSK_PATH_TILE actually used */
+  int32_t launches;  /* kernels launched by the call                   */
+} csk_moe_timings;
+int csk_moe_enable_timing(csk_moe_layer* layer, int32_t on);
+int csk_moe_get_timings(csk_moe_layer* layer, csk_moe_timings* out);
+
+/* Counters of the last forward call: rows routed to each expert (E int64,
+ * host), number of distinct experts hit, weight bytes those experts hold. */
+int csk_moe_get_counters(csk_moe_layer* layer, int64_t* rows_per_expert, int64_t* distinct_experts,
+                         int64_t* weight_bytes_streamed);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CSK_MOE_H */

@@ -1,0 +1,278 @@
+/* TEST INFRASTRUCTURE ONLY -- never part of the product path.
+ *
+ * CPU restatement, in plain C, of the reference's mixture-of-experts hot path:
+ * router, MXFP4 codec, per-token gated expert MLP and the weighted merge.  It
+ * exists to check the CUDA kernels; only tests, the smoke check and the
+ * benchmark's CPU arm may load it.
+ *
+ * Parity pin: every function here is compared against the reference's own
+ * code (oracle/_ref/libcsk_ref.so, built from the reference checkout by
+ * oracle/Makefile) and against the committed golden vectors that library
+ * produced (tests/golden/), including the reference's own known-answer tests
+ * (E8M0 127/128/129 -> 0.5/1/2, all-zero nibbles -> zeros, TopKSelection
+ * -> experts 5,4,3, routing weights summing to 1).
+ *
+ * Each function cites the reference file:line it follows (paths within the
+ * reference project).  Build: see oracle/Makefile (-O2 -ffp-contract=off so
+ * that a*b+c is never fused unless written as fmaf()).
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+/* include/coalsack/gguf/gguf_dequant.h:413-415 -- E2M1 code -> doubled value. */
+static const int8_t k_e2m1_x2[16] = {0, 1, 2, 3, 4, 6, 8, 12, 0, -1, -2, -3, -4, -6, -8, -12};
+
+/* include/coalsack/gguf/gguf_dequant.h:419-433 -- E8M0 byte -> 2^(x-128);
+ * x = 0 and x = 1 give the fp32 subnormals 2^-128 and 2^-127. */
+float orc_e8m0_half(uint8_t x) {
+  uint32_t bits = (x < 2) ? (0x00200000u << x) : ((uint32_t)(x - 1) << 23);
+  float f;
+  memcpy(&f, &bits, sizeof f);
+  return f;
+}
+
+/* include/coalsack/gguf/gguf_dequant.h:437-455 -- k elements (k % 32 == 0) of
+ * 17-byte blocks: byte 0 the scale, byte 1+j holds element j in its low nibble
+ * and element j+16 in its high nibble. */
+void orc_dequant_mxfp4(const uint8_t* src, float* dst, int64_t k) {
+  for (int64_t b = 0; b < k / 32; ++b) {
+    const uint8_t* blk = src + 17 * b;
+    const float s = orc_e8m0_half(blk[0]);
+    for (int j = 0; j < 16; ++j) {
+      dst[32 * b + j] = (float)k_e2m1_x2[blk[1 + j] & 0x0F] * s;
+      dst[32 * b + j + 16] = (float)k_e2m1_x2[blk[1 + j] >> 4] * s;
+    }
+  }
+}
+
+/* include/coalsack/nn/nn_ops/moe_router_node.h:140-214.
+ * logit[e] = (((0 + h0*w0) + h1*w1) + ...) + bias[e], all fp32, no fusing;
+ * top-k by descending logit (order among exactly equal logits is unspecified
+ * in the reference, here the lower expert id wins); weights = softmax over the
+ * k selected logits (max-subtracted, expf, sum in k order, times 1/sum) or a
+ * per-expert sigmoid.  out is [T,k,2] = (expert id as float, weight). */
+int orc_router(const float* hidden, int64_t T, int64_t H, const float* Wg, const float* bias,
+               int64_t E, int64_t k, int sigmoid, float* out, float* logits_out) {
+  if (k > E || k <= 0) return -1;
+  float* logit = (float*)malloc(sizeof(float) * (size_t)E);
+  int* order = (int*)malloc(sizeof(int) * (size_t)E);
+  float* w = (float*)malloc(sizeof(float) * (size_t)k);
+  if (!logit || !order || !w) return -2;
+  for (int64_t t = 0; t < T; ++t) {
+    const float* h = hidden + t * H;
+    for (int64_t e = 0; e < E; ++e) {
+      float sum = 0.0f;
+      const float* g = Wg + e * H;
+      for (int64_t d = 0; d < H; ++d) {
+        float p = h[d] * g[d];
+        sum = sum + p;
+      }
+      logit[e] = sum + (bias ? bias[e] : 0.0f);
+      if (logits_out) logits_out[t * E + e] = logit[e];
+    }
+    /* selection sort of the k largest: same result as partial_sort wherever
+     * the logits are distinct */
+    for (int64_t e = 0; e < E; ++e) order[e] = (int)e;
+    for (int64_t j = 0; j < k; ++j) {
+      int64_t best = j;
+      for (int64_t i = j + 1; i < E; ++i) {
+        float a = logit[order[i]], b = logit[order[best]];
+        if (a > b || (a == b && order[i] < order[best])) best = i;
+      }
+      int tmp = order[j];
+      order[j] = order[best];
+      order[best] = tmp;
+    }
+    if (sigmoid) {
+      for (int64_t j = 0; j < k; ++j) w[j] = 1.0f / (1.0f + expf(-logit[order[j]]));
+    } else {
+      float mx = logit[order[0]];
+      for (int64_t j = 1; j < k; ++j)
+        if (logit[order[j]] > mx) mx = logit[order[j]];
+      float se = 0.0f;
+      for (int64_t j = 0; j < k; ++j) {
+        w[j] = expf(logit[order[j]] - mx);
+        se += w[j];
+      }
+      const float inv = (se > 0.0f) ? (1.0f / se) : 0.0f;
+      for (int64_t j = 0; j < k; ++j) w[j] *= inv;
+    }
+    for (int64_t j = 0; j < k; ++j) {
+      out[(t * k + j) * 2 + 0] = (float)order[j];
+      out[(t * k + j) * 2 + 1] = w[j];
+    }
+  }
+  free(logit);
+  free(order);
+  free(w);
+  return 0;
+}
+
+/* One output row of an MXFP4 GEMV, in the reference's summation order
+ * (include/coalsack/nn/nn_ops/expert_mlp_node.h:194-206, 211-245, 259-266,
+ * 684-692): eight running lanes; within a 32-element block the four groups of
+ * eight consecutive elements are fused-multiply-added into the lanes in turn;
+ * the lanes are folded as (l0+l4)+(l1+l5) then (l2+l6)+(l3+l7), then added. */
+static float row_dot_mxfp4(const float* x, const uint8_t* row_blocks, int64_t nblk) {
+  float lane[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  float wv[32];
+  for (int64_t b = 0; b < nblk; ++b) {
+    orc_dequant_mxfp4(row_blocks + 17 * b, wv, 32);
+    const float* xb = x + 32 * b;
+    for (int g = 0; g < 4; ++g)
+      for (int l = 0; l < 8; ++l) lane[l] = fmaf(xb[8 * g + l], wv[8 * g + l], lane[l]);
+  }
+  float s0 = lane[0] + lane[4], s1 = lane[1] + lane[5];
+  float s2 = lane[2] + lane[6], s3 = lane[3] + lane[7];
+  return (s0 + s1) + (s2 + s3);
+}
+
+/* include/coalsack/nn/nn_ops/expert_mlp_node.h:651-732 -- one token through
+ * one expert.  act: 0 = clamped gpt-oss gate (alpha 1.702, limit 7, gate
+ * clamped above only, up clamped both sides, then +1), 1 = silu(gate)*up.
+ * Biases (may be NULL) are added before the activation and after the down
+ * projection. */
+int orc_expert_token_mxfp4(const float* x, const uint8_t* w_up, const uint8_t* w_gate,
+                           const uint8_t* w_down, const float* b_up, const float* b_gate,
+                           const float* b_down, float* out, int64_t H, int64_t F, int act) {
+  if (H % 32 || F % 32) return -1;
+  float* a = (float*)malloc(sizeof(float) * (size_t)F);
+  if (!a) return -2;
+  const int64_t nbh = H / 32, nbf = F / 32;
+  for (int64_t o = 0; o < F; ++o) {
+    float up = row_dot_mxfp4(x, w_up + o * nbh * 17, nbh) + (b_up ? b_up[o] : 0.0f);
+    float gate = row_dot_mxfp4(x, w_gate + o * nbh * 17, nbh) + (b_gate ? b_gate[o] : 0.0f);
+    if (act == 0) {
+      const float lim = 7.0f, alpha = 1.702f;
+      float g = gate < lim ? gate : lim;
+      float u = up < -lim ? -lim : (up > lim ? lim : up);
+      float glu = g / (1.0f + expf(alpha * (-g)));
+      a[o] = glu * (u + 1.0f);
+    } else {
+      float silu = gate / (1.0f + expf(-gate));
+      a[o] = silu * up;
+    }
+  }
+  for (int64_t o = 0; o < H; ++o)
+    out[o] = row_dot_mxfp4(a, w_down + o * nbf * 17, nbf) + (b_down ? b_down[o] : 0.0f);
+  free(a);
+  return 0;
+}
+
+/* include/coalsack/nn/nn_ops/expert_mlp_node.h:488-530 -- the expert node's
+ * dense output: [T,H] with zero rows for tokens that did not select it.
+ * Returns 0 when no token selected the expert (the reference then emits a
+ * {0}-shaped tensor, :441-443), 1 otherwise. */
+int orc_expert_node_mxfp4(int expert_id, const float* hidden, int64_t T, int64_t H, int64_t F,
+                          const uint8_t* w_up, const uint8_t* w_gate, const uint8_t* w_down,
+                          const float* b_up, const float* b_gate, const float* b_down,
+                          const float* router_out, int64_t k, int act, int weight_before_ffn,
+                          float* out) {
+  int any = 0;
+  for (int64_t i = 0; i < T * k; ++i)
+    if ((int)router_out[2 * i] == expert_id) any = 1;
+  if (!any) return 0;
+  float* scaled = (float*)malloc(sizeof(float) * (size_t)H);
+  for (int64_t t = 0; t < T; ++t) {
+    int sel = 0;
+    float w = 0.0f;
+    for (int64_t j = 0; j < k; ++j)
+      if ((int)router_out[(t * k + j) * 2] == expert_id) {
+        sel = 1;
+        w = router_out[(t * k + j) * 2 + 1];
+        break;
+      }
+    if (!sel) {
+      memset(out + t * H, 0, sizeof(float) * (size_t)H);
+      continue;
+    }
+    const float* x = hidden + t * H;
+    if (weight_before_ffn) {
+      for (int64_t d = 0; d < H; ++d) scaled[d] = x[d] * w;
+      x = scaled;
+    }
+    orc_expert_token_mxfp4(x, w_up, w_gate, w_down, b_up, b_gate, b_down, out + t * H, H, F, act);
+  }
+  free(scaled);
+  return 1;
+}
+
+/* include/coalsack/nn/nn_ops/expert_merge_node.h:88-131 -- out[t] = sum over
+ * k in router order of w[t,k] * expert_out[e(t,k)][t]; NULL entries of
+ * expert_outs stand for the {0}-shaped empty tensors and are skipped; with
+ * weight_before_ffn the rows are summed unweighted.  Returns -1 for an expert
+ * id out of range, -2 when every expert output is empty. */
+int orc_merge(const float* router_out, int64_t T, int64_t k, int64_t E, int64_t H,
+              const float* const* expert_outs, int weight_before_ffn, float* out) {
+  int any = 0;
+  for (int64_t e = 0; e < E; ++e)
+    if (expert_outs[e]) any = 1;
+  if (!any) return -2;
+  memset(out, 0, sizeof(float) * (size_t)(T * H));
+  for (int64_t t = 0; t < T; ++t)
+    for (int64_t j = 0; j < k; ++j) {
+      int e = (int)router_out[(t * k + j) * 2];
+      float w = router_out[(t * k + j) * 2 + 1];
+      if (e < 0 || e >= E) return -1;
+      const float* y = expert_outs[e];
+      if (!y) continue;
+      for (int64_t d = 0; d < H; ++d) {
+        if (weight_before_ffn) {
+          out[t * H + d] += y[t * H + d];
+        } else {
+          float p = w * y[t * H + d];
+          out[t * H + d] += p;
+        }
+      }
+    }
+  return 0;
+}
+
+/* The whole layer for tokens [t0, t1): router (unless router_out is given),
+ * one expert call per (token, selected expert), weighted sum in router order.
+ * Same value flow as orc_expert_node_mxfp4 + orc_merge without building the E
+ * dense intermediates. */
+int orc_moe_layer(const float* hidden, int64_t t0, int64_t t1, int64_t H, int64_t F, int64_t E,
+                  int64_t k, const float* Wg, const float* router_bias, int sigmoid,
+                  const uint8_t* const* w_up, const uint8_t* const* w_gate,
+                  const uint8_t* const* w_down, const float* const* b_up,
+                  const float* const* b_gate, const float* const* b_down, int act,
+                  int weight_before_ffn, int compute_router, float* router_out_io, float* out) {
+  float* y = (float*)malloc(sizeof(float) * (size_t)H);
+  float* scaled = (float*)malloc(sizeof(float) * (size_t)H);
+  if (!y || !scaled) return -2;
+  for (int64_t t = t0; t < t1; ++t) {
+    float* r = router_out_io + t * k * 2;
+    if (compute_router) {
+      int rc = orc_router(hidden + t * H, 1, H, Wg, router_bias, E, k, sigmoid, r, NULL);
+      if (rc) return rc;
+    }
+    float* o = out + t * H;
+    memset(o, 0, sizeof(float) * (size_t)H);
+    for (int64_t j = 0; j < k; ++j) {
+      int e = (int)r[2 * j];
+      float w = r[2 * j + 1];
+      if (e < 0 || e >= E) return -1;
+      const float* x = hidden + t * H;
+      if (weight_before_ffn) {
+        for (int64_t d = 0; d < H; ++d) scaled[d] = x[d] * w;
+        x = scaled;
+      }
+      orc_expert_token_mxfp4(x, w_up[e], w_gate[e], w_down[e], b_up ? b_up[e] : NULL,
+                             b_gate ? b_gate[e] : NULL, b_down ? b_down[e] : NULL, y, H, F, act);
+      for (int64_t d = 0; d < H; ++d) {
+        if (weight_before_ffn) {
+          o[d] += y[d];
+        } else {
+          float p = w * y[d];
+          o[d] += p;
+        }
+      }
+    }
+  }
+  free(y);
+  free(scaled);
+  return 0;
+}

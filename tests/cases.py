@@ -1,0 +1,105 @@
+"""Seeded problem instances shared by the golden-vector generator and the tests."""
+from __future__ import annotations
+
+import zlib
+
+import numpy as np
+
+from coalsack_b200 import synth
+
+
+def crc(*arrays) -> np.uint32:
+    c = 0
+    for a in arrays:
+        if a is not None:
+            c = zlib.crc32(np.ascontiguousarray(a).tobytes(), c)
+    return np.uint32(c)
+
+
+def layer_inputs(shape, tokens=None, router_scale=1.0, exp_lo=118, exp_hi=124):
+    """(hidden, Wg, router bias, experts) of a layer shape.  ``router_scale``
+    widens the logit spread of small layers so that top-k gaps are not tiny."""
+    h = synth.hidden_states(shape, tokens)
+    Wg = synth.router_weight(shape) * np.float32(router_scale)
+    rb = synth.router_bias(shape)
+    ex = synth.all_experts(shape)
+    if (exp_lo, exp_hi) != (118, 124):
+        for e in range(shape.num_experts):
+            ex["w_up"][e] = synth.mxfp4_matrix(shape.seed, synth._T_WUP, e, shape.ffn, shape.hidden, exp_lo, exp_hi)
+            ex["w_gate"][e] = synth.mxfp4_matrix(shape.seed, synth._T_WGATE, e, shape.ffn, shape.hidden, exp_lo, exp_hi)
+            ex["w_down"][e] = synth.mxfp4_matrix(shape.seed, synth._T_WDOWN, e, shape.hidden, shape.ffn, exp_lo, exp_hi)
+    return h, Wg, rb, ex
+
+
+def inputs_crc(h, Wg, rb, ex) -> np.uint32:
+    parts = [h, Wg, rb]
+    for name in ("w_up", "w_gate", "w_down", "b_up", "b_gate", "b_down"):
+        if ex.get(name) is not None:
+            parts += list(ex[name])
+    return crc(*parts)
+
+
+def expert_args(ex, e):
+    """(w_up, w_gate, w_down, b_up, b_gate, b_down) of expert e."""
+    b = [ex[n][e] if ex.get(n) is not None else None for n in ("b_up", "b_gate", "b_down")]
+    return (ex["w_up"][e], ex["w_gate"][e], ex["w_down"][e], *b)
+
+
+# tag -> (synth.tiny kwargs, weight_before_ffn, router scale, (exp_lo, exp_hi))
+TINY_CASES = {
+    "tiny_a": (dict(seed=11, E=4, k=2, H=64, F=64, T=3, has_bias=True, act=synth.MODIFIED_SWIGLU),
+               False, 50.0, (118, 124)),
+    "tiny_b": (dict(seed=12, E=8, k=2, H=96, F=160, T=9, has_bias=False, act=synth.STANDARD_SWIGLU),
+               False, 50.0, (118, 124)),
+    "tiny_c": (dict(seed=13, E=6, k=3, H=128, F=96, T=5, has_bias=True, act=synth.MODIFIED_SWIGLU),
+               True, 50.0, (118, 124)),
+    "tiny_d": (dict(seed=14, E=16, k=4, H=256, F=320, T=40, has_bias=True, act=synth.MODIFIED_SWIGLU),
+               False, 20.0, (112, 130)),
+}
+
+
+def tiny_case(tag):
+    """(shape, hidden, Wg, router bias, experts, weight_before_ffn)."""
+    kw, wbf, rscale, (lo, hi) = TINY_CASES[tag]
+    sh = synth.tiny(**kw)
+    h, Wg, rb, ex = layer_inputs(sh, router_scale=rscale, exp_lo=lo, exp_hi=hi)
+    return sh, h, Wg, rb, ex, wbf
+
+
+def router16_case():
+    """Router inputs at the size of the reference's own 32-expert / top-4 router test."""
+    sh = synth.LayerShape("router_gptoss_scale", 32, 4, 128, 32, True, "normal", 0, 21, 16)
+    return synth.hidden_states(sh), synth.router_weight(sh) * np.float32(10), synth.router_bias(sh)
+
+
+def topk_selection_case():
+    """The reference's TopKSelection test: hidden = 1, gate row e = e / H."""
+    H, E, k = 4, 6, 3
+    hid = np.ones((1, H), np.float32)
+    gw = np.repeat((np.arange(E, dtype=np.float32) / np.float32(H))[:, None], H, axis=1)
+    return hid, np.ascontiguousarray(gw, np.float32), np.zeros(E, np.float32), k
+
+
+def c4x8_case():
+    sh = synth.C4.with_(num_experts=8, tokens=4)
+    return (sh, *layer_inputs(sh, router_scale=10.0))
+
+
+def codec_blocks():
+    blk = np.zeros(17 * 3, np.uint8)
+    blk[0], blk[17], blk[34] = 128, 119, 0
+    blk[1:17] = np.arange(16) | (np.arange(16)[::-1] << 4)
+    blk[18:34] = (np.arange(16) * 17) & 0xFF
+    blk[35:51] = 0xF1
+    return blk
+
+
+def err_stats(got, ref):
+    """(max-abs error / output RMS, mean|err| / mean|ref|) -- the two parity statistics."""
+    got, ref = np.asarray(got, np.float64), np.asarray(ref, np.float64)
+    rms = np.sqrt(np.mean(ref ** 2))
+    return float(np.max(np.abs(got - ref)) / rms), float(np.mean(np.abs(got - ref)) / np.mean(np.abs(ref)))
+
+
+MAX_ABS_OVER_RMS = 2e-2   # parity tolerance: max-abs error <= 2e-2 x output RMS
+MEAN_REL = 5e-3           # parity tolerance: mean|err| / mean|ref| <= 5e-3

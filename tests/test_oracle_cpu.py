@@ -1,0 +1,113 @@
+"""The CPU checker itself: the plain-C restatement against the golden vectors
+the unmodified reference produced, against the reference's own known-answer
+tests, and (where the reference is compiled) against the reference directly."""
+import numpy as np
+import pytest
+
+from coalsack_b200 import synth
+from tests import cases
+
+
+def test_e8m0_known_answers(port, golden):
+    # reference test/test_gguf_dequant.cpp:266-280
+    assert port.e8m0(127) == 0.5 and port.e8m0(128) == 1.0 and port.e8m0(129) == 2.0
+    got = np.array([port.e8m0(x) for x in range(256)], np.float32)
+    assert np.array_equal(got.view(np.uint32), golden["e8m0_all"].view(np.uint32))
+
+
+def test_dequant_zero_block(port):
+    # reference test/test_gguf_dequant.cpp:244-263
+    blk = np.zeros(17, np.uint8)
+    blk[0] = 128
+    assert np.all(port.dequant(blk) == 0.0)
+
+
+def test_dequant_golden(port, golden):
+    got = port.dequant(cases.codec_blocks())
+    assert np.array_equal(got.view(np.uint32), golden["codec_values"].view(np.uint32))
+    # block 0 has scale 1 and every code once in the low nibbles: doubled E2M1 values
+    assert list(got[:16]) == [0, 1, 2, 3, 4, 6, 8, 12, 0, -1, -2, -3, -4, -6, -8, -12]
+
+
+def test_router_topk_selection(port, golden):
+    # reference test/test_moe_router.cpp:82-138: experts 5, 4, 3 in that order
+    hid, gw, gb, k = cases.topk_selection_case()
+    out = port.router(hid, gw, gb, k)
+    assert list(out[0, :, 0].astype(int)) == [5, 4, 3]
+    assert np.array_equal(out, golden["topk_selection"])
+
+
+def test_router_golden(port, golden):
+    hid, gw, rb = cases.router16_case()
+    assert cases.crc(hid, gw, rb) == golden["router16_crc"], "synthetic generator drifted"
+    for key, kw in (("router16", {}), ("router16_sigmoid", {"sigmoid": True})):
+        out = port.router(hid, gw, rb, 4, **kw)
+        assert np.array_equal(out, golden[key])
+    out = port.router(hid, gw, None, 4)
+    assert np.array_equal(out, golden["router16_nobias"])
+    # reference test/test_moe_router.cpp:77,199: weights positive, summing to 1
+    w = golden["router16"][..., 1]
+    assert np.all(w > 0) and np.allclose(w.sum(-1), 1.0, atol=1e-5)
+
+
+@pytest.mark.parametrize("tag", list(cases.TINY_CASES))
+def test_tiny_layers_golden(port, golden, tag):
+    sh, h, Wg, rb, ex, wbf = cases.tiny_case(tag)
+    assert cases.inputs_crc(h, Wg, rb, ex) == golden[f"{tag}_crc"], "synthetic generator drifted"
+    out, ro = port.moe_layer(h, Wg, rb, ex, sh.top_k, sh.act, weight_before_ffn=wbf)
+    assert np.array_equal(ro, golden[f"{tag}_router"])
+    assert np.array_equal(out, golden[f"{tag}_out"])
+    nodes = []
+    for e in range(sh.num_experts):
+        o = port.expert_node(e, h, *cases.expert_args(ex, e), ro, sh.ffn, sh.act, wbf)
+        assert (o is not None) == bool(golden[f"{tag}_selected"][e])
+        if o is not None:
+            assert np.array_equal(o, golden[f"{tag}_nodes"][e])
+            # rows of tokens that did not pick the expert are exactly zero
+            picked = (ro[:, :, 0].astype(int) == e).any(axis=1)
+            assert np.all(o[~picked] == 0.0)
+        nodes.append(o)
+    merged = port.merge(ro, nodes, sh.hidden, wbf)
+    assert np.array_equal(merged, golden[f"{tag}_merge"])
+    # merging the per-expert node outputs equals the fused layer evaluation
+    assert np.array_equal(merged, out)
+
+
+def test_c0_golden(port, golden):
+    sh = synth.C0
+    h, Wg, rb, ex = cases.layer_inputs(sh, 32)
+    assert cases.inputs_crc(h, Wg, rb, ex) == golden["c0_crc"], "synthetic generator drifted"
+    out1, ro1 = port.moe_layer(h[:1], Wg, rb, ex, sh.top_k, sh.act, nthreads=4)
+    assert np.array_equal(ro1, golden["c0_t1_router"])
+    assert np.array_equal(out1, golden["c0_t1_out"])
+    out4, ro4 = port.moe_layer(h[:4], Wg, rb, ex, sh.top_k, sh.act, nthreads=4)
+    assert np.array_equal(ro4, golden["c0_t32_router"][:4])
+    assert np.array_equal(out4, golden["c0_t32_out_first4"])
+
+
+def test_c4_golden(port, golden):
+    sh, h, Wg, rb, ex = cases.c4x8_case()
+    assert cases.inputs_crc(h, Wg, rb, ex) == golden["c4x8_crc"], "synthetic generator drifted"
+    out, ro = port.moe_layer(h, Wg, rb, ex, sh.top_k, sh.act, nthreads=4)
+    assert np.array_equal(ro, golden["c4x8_router"])
+    assert np.array_equal(out, golden["c4x8_out"])
+    assert np.allclose(ro[..., 1].sum(-1), 1.0, atol=1e-5)
+
+
+def test_merge_errors(port):
+    ro = np.array([[[7.0, 1.0]]], np.float32)
+    with pytest.raises(RuntimeError):
+        port.merge(ro, [np.zeros((1, 32), np.float32)] * 2, 32)       # expert id out of range
+    with pytest.raises(RuntimeError):
+        port.merge(np.array([[[0.0, 1.0]]], np.float32), [None, None], 32)  # all inputs empty
+
+
+def test_port_equals_reference_on_fresh_inputs(port, ref):
+    """Bit-for-bit agreement with the compiled reference on inputs that are not in the fixtures."""
+    sh = synth.tiny(seed=97, E=8, k=3, H=160, F=224, T=7, has_bias=True, act=synth.STANDARD_SWIGLU)
+    h, Wg, rb, ex = cases.layer_inputs(sh, router_scale=30.0, exp_lo=90, exp_hi=150)
+    a, ra = port.moe_layer(h, Wg, rb, ex, sh.top_k, sh.act)
+    b, rb_ = ref.moe_layer(h, Wg, rb, ex, sh.top_k, sh.act)
+    assert np.array_equal(ra, rb_) and np.array_equal(a, b)
+    for x in (0, 1, 2, 254, 255):
+        assert port.e8m0(x) == ref.e8m0(x)
