@@ -20,7 +20,7 @@ __device__ __forceinline__ uint32_t raw_code(const uint8_t* src, int K, int row,
 }
 
 __global__ void k_repack(const uint8_t* __restrict__ src0, const uint8_t* __restrict__ src1,
-                         uint8_t* __restrict__ dst, MatLayout L) {
+                         uint8_t* __restrict__ dst, MatLayout L, int* __restrict__ emax_out) {
   const size_t n_words = L.bytes() / 4;
   for (size_t w = (size_t)blockIdx.x * blockDim.x + threadIdx.x; w < n_words;
        w += (size_t)gridDim.x * blockDim.x) {
@@ -47,6 +47,7 @@ __global__ void k_repack(const uint8_t* __restrict__ src0, const uint8_t* __rest
       }
     } else {
       const int g = wi - kSubCodeBytes / 4;
+      int emax = -1;
 #pragma unroll
       for (int slot = 0; slot < 4; ++slot) {
         int r_in_tile = sub * 16 + g + ((slot & 2) ? 8 : 0);
@@ -57,10 +58,14 @@ __global__ void k_repack(const uint8_t* __restrict__ src0, const uint8_t* __rest
           r_in_tile -= L.BN / 2;
         }
         const int row = n_tile * L.rows_per_tile() + r_in_tile;
-        uint32_t e = 127;
-        if (row < L.N && col < L.K) e = src[((size_t)row * (L.K / 32) + col / 32) * 17];
+        uint32_t e = 0;  // padding: zero codes under the smallest scale
+        if (row < L.N && col < L.K) {
+          e = src[((size_t)row * (L.K / 32) + col / 32) * 17];
+          emax = max(emax, (int)e);
+        }
         out |= e << (8 * slot);
       }
+      if (emax >= 0) atomicMax(emax_out, emax);  // largest scale exponent of the matrix
     }
     reinterpret_cast<uint32_t*>(dst)[w] = out;
   }
@@ -97,131 +102,146 @@ __global__ void k_unpack(const uint8_t* __restrict__ packed, uint8_t* __restrict
 //
 // The selected expert indices must equal the reference's bit for bit, and the
 // reference accumulates each logit sequentially in fp32 with separate multiply
-// and add.  So each (token, expert) logit is one thread's in-order chain of
-// __fmul_rn/__fadd_rn (never contracted into an FMA).  A block covers
-// kRouterTok tokens for each of its token sub-groups; thread = one expert of
-// one sub-group, keeping kRouterTok running sums while it walks the hidden
-// dimension once.  Top-k: one warp per token, k rounds of arg-max by shuffles
-// (ties -> lower expert id; the reference leaves ties unspecified).
+// and add.  So each (token, expert) logit is ONE thread's in-order chain of
+// __fmul_rn / __fadd_rn over the hidden dimension (never contracted into an
+// FMA, never reassociated).  Parallelism comes from the T*E independent chains:
+// a block owns a BT x BE tile of (tokens x experts), a thread a TT x EE
+// sub-tile, and both operand tiles are staged through shared memory in chunks
+// of the hidden dimension so every global load is coalesced along it.
+//   k_router_logits<4,4>: prefill (many tokens), 16 chains per thread
+//   k_router_logits<1,1>: decode (a few tokens), one chain per thread, spread
+//                         over as many SMs as there are expert groups
+// k_router_topk then selects per token: one warp, k rounds of arg-max by
+// shuffles (ties -> lower expert id; the reference leaves ties unspecified),
+// softmax over the selected logits (or sigmoid) exactly as the reference.
 // ---------------------------------------------------------------------------
-constexpr int kRouterTok = 8;
-constexpr int kRouterChunk = 256;
+constexpr int kRouterChunk = 64;
+constexpr int kRouterPad = 4;
 constexpr int kRouterThreads = 128;
 constexpr int kMaxTopK = 16;
 
+template <int TT, int EE>
 __global__ void __launch_bounds__(kRouterThreads)
-k_router(const float* __restrict__ hidden, const float* __restrict__ wgT,
-         const float* __restrict__ bias, float* __restrict__ router_out, int T, int H, int E,
-         int E_stride, int k, int sigmoid, int e_lanes /* pow2 >= min(E,128) */) {
+k_router_logits(const float* __restrict__ hidden, const float* __restrict__ wg,
+                const float* __restrict__ bias, float* __restrict__ logits, int T, int H, int E,
+                int ntx /* threads along tokens; 128/ntx along experts */) {
   extern __shared__ float smem[];
-  const int groups = kRouterThreads / e_lanes;           // token sub-groups per block
-  const int tok_per_block = groups * kRouterTok;
-  float* hs = smem;                                      // [tok_per_block][kRouterChunk]
-  float* lg = smem + tok_per_block * kRouterChunk;       // [tok_per_block][E]
+  constexpr int LD = kRouterChunk + kRouterPad;
+  const int nty = kRouterThreads / ntx;
+  const int BT = ntx * TT, BE = nty * EE;
+  float* hs = smem;            // [BT][LD]
+  float* ws = smem + BT * LD;  // [BE][LD]
   const int tid = threadIdx.x;
-  const int grp = tid / e_lanes, el = tid % e_lanes;
-  const int t_block = blockIdx.x * tok_per_block;
+  const int tx = tid % ntx, ty = tid / ntx;
+  const int t0 = blockIdx.x * BT, e0 = blockIdx.y * BE;
 
-  for (int e0 = 0; e0 < E; e0 += e_lanes) {
-    const int e = e0 + el;
-    float acc[kRouterTok];
+  float acc[TT][EE];
 #pragma unroll
-    for (int t = 0; t < kRouterTok; ++t) acc[t] = 0.f;
-    for (int d0 = 0; d0 < H; d0 += kRouterChunk) {
-      const int dc = min(kRouterChunk, H - d0);
-      __syncthreads();
-      for (int i = tid; i < tok_per_block * kRouterChunk; i += kRouterThreads) {
-        const int tt = i / kRouterChunk, d = i % kRouterChunk;
-        const int t = t_block + tt;
-        hs[i] = (t < T && d < dc) ? hidden[(size_t)t * H + d0 + d] : 0.f;
-      }
-      __syncthreads();
-      if (e < E) {
-        const float* hrow = hs + grp * kRouterTok * kRouterChunk;
-        const float* wcol = wgT + (size_t)d0 * E_stride + e;
-        int d = 0;
-        for (; d + 4 <= dc; d += 4) {
-          float w0 = wcol[(size_t)(d + 0) * E_stride], w1 = wcol[(size_t)(d + 1) * E_stride];
-          float w2 = wcol[(size_t)(d + 2) * E_stride], w3 = wcol[(size_t)(d + 3) * E_stride];
+  for (int i = 0; i < TT; ++i)
 #pragma unroll
-          for (int t = 0; t < kRouterTok; ++t) {
-            const float4 h4 = *reinterpret_cast<const float4*>(hrow + t * kRouterChunk + d);
-            float a = acc[t];
-            a = __fadd_rn(a, __fmul_rn(h4.x, w0));
-            a = __fadd_rn(a, __fmul_rn(h4.y, w1));
-            a = __fadd_rn(a, __fmul_rn(h4.z, w2));
-            a = __fadd_rn(a, __fmul_rn(h4.w, w3));
-            acc[t] = a;
-          }
-        }
-        for (; d < dc; ++d) {
-          const float w0 = wcol[(size_t)d * E_stride];
-#pragma unroll
-          for (int t = 0; t < kRouterTok; ++t)
-            acc[t] = __fadd_rn(acc[t], __fmul_rn(hrow[t * kRouterChunk + d], w0));
-        }
+    for (int j = 0; j < EE; ++j) acc[i][j] = 0.f;
+
+  for (int d0 = 0; d0 < H; d0 += kRouterChunk) {
+    const int dc = min(kRouterChunk, H - d0);  // H % 32 == 0, so dc is 32 or 64
+    __syncthreads();
+    // coalesced float4 loads along the hidden dimension
+    for (int i = tid; i < (BT + BE) * (kRouterChunk / 4); i += kRouterThreads) {
+      const int r = i / (kRouterChunk / 4), c = (i % (kRouterChunk / 4)) * 4;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (r < BT) {
+        if (t0 + r < T && c < dc) v = *reinterpret_cast<const float4*>(hidden + (size_t)(t0 + r) * H + d0 + c);
+        *reinterpret_cast<float4*>(hs + r * LD + c) = v;
+      } else {
+        const int e = e0 + r - BT;
+        if (e < E && c < dc) v = *reinterpret_cast<const float4*>(wg + (size_t)e * H + d0 + c);
+        *reinterpret_cast<float4*>(ws + (r - BT) * LD + c) = v;
       }
     }
-    if (e < E) {
-      const float b = bias ? bias[e] : 0.f;
+    __syncthreads();
+    // thread (tx, ty) owns tokens tx + i*ntx and experts ty + j*nty: neighbouring
+    // threads read neighbouring rows (stride LD = 4 mod 32 words), so the 128-bit
+    // shared loads of a quarter-warp fall in distinct banks
+    const float* hp = hs + tx * LD;
+    const float* wp = ws + ty * LD;
+    for (int d = 0; d < dc; d += 4) {
+      float4 hv[TT], wv[EE];
 #pragma unroll
-      for (int t = 0; t < kRouterTok; ++t)
-        lg[(grp * kRouterTok + t) * E + e] = __fadd_rn(acc[t], b);
+      for (int i = 0; i < TT; ++i) hv[i] = *reinterpret_cast<const float4*>(hp + i * ntx * LD + d);
+#pragma unroll
+      for (int j = 0; j < EE; ++j) wv[j] = *reinterpret_cast<const float4*>(wp + j * nty * LD + d);
+#pragma unroll
+      for (int i = 0; i < TT; ++i)
+#pragma unroll
+        for (int j = 0; j < EE; ++j) {
+          float a = acc[i][j];
+          a = __fadd_rn(a, __fmul_rn(hv[i].x, wv[j].x));
+          a = __fadd_rn(a, __fmul_rn(hv[i].y, wv[j].y));
+          a = __fadd_rn(a, __fmul_rn(hv[i].z, wv[j].z));
+          a = __fadd_rn(a, __fmul_rn(hv[i].w, wv[j].w));
+          acc[i][j] = a;
+        }
     }
   }
-  __syncthreads();
-
-  // top-k + routing weights, one warp per token
-  const int lane = tid & 31, warp = tid >> 5;
-  for (int tt = warp; tt < tok_per_block; tt += kRouterThreads / 32) {
-    const int t = t_block + tt;
-    if (t >= T) continue;
-    float* l = lg + tt * E;
-    float sel_v[kMaxTopK];
-    int sel_i[kMaxTopK];
-    for (int j = 0; j < k; ++j) {
-      float bv = -INFINITY;
-      int bi = 0x7fffffff;
-      for (int e = lane; e < E; e += 32) {
-        const float v = l[e];
-        if (v > bv || (v == bv && e < bi)) {
-          bv = v;
-          bi = e;
-        }
-      }
-      for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (ov > bv || (ov == bv && oi < bi)) {
-          bv = ov;
-          bi = oi;
-        }
-      }
-      sel_v[j] = bv;
-      sel_i[j] = bi;
-      __syncwarp();
-      if (lane == 0 && bi < E) l[bi] = __int_as_float(0xffc00000);  // NaN: never wins a '>' test
-      __syncwarp();
+#pragma unroll
+  for (int i = 0; i < TT; ++i)
+#pragma unroll
+    for (int j = 0; j < EE; ++j) {
+      const int t = t0 + tx + i * ntx, e = e0 + ty + j * nty;
+      if (t < T && e < E) logits[(size_t)t * E + e] = __fadd_rn(acc[i][j], bias ? bias[e] : 0.f);
     }
-    if (lane == 0) {
-      float w[kMaxTopK];
-      if (sigmoid) {
-        for (int j = 0; j < k; ++j) w[j] = 1.0f / (1.0f + expf(-sel_v[j]));
-      } else {
-        float mx = sel_v[0];
-        for (int j = 1; j < k; ++j) mx = fmaxf(mx, sel_v[j]);
-        float se = 0.f;
-        for (int j = 0; j < k; ++j) {
-          w[j] = expf(sel_v[j] - mx);
-          se += w[j];
-        }
-        const float inv = se > 0.f ? 1.0f / se : 0.f;
-        for (int j = 0; j < k; ++j) w[j] *= inv;
+}
+
+__global__ void __launch_bounds__(128)
+k_router_topk(float* __restrict__ logits, float* __restrict__ router_out, int T, int E, int k,
+              int sigmoid) {
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= T) return;
+  float* l = logits + (size_t)t * E;
+  float sel_v[kMaxTopK];
+  int sel_i[kMaxTopK];
+  for (int j = 0; j < k; ++j) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float v = l[e];
+      if (v > bv || (v == bv && e < bi)) {
+        bv = v;
+        bi = e;
       }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) {
+        bv = ov;
+        bi = oi;
+      }
+    }
+    sel_v[j] = bv;
+    sel_i[j] = bi;
+    __syncwarp();
+    if (lane == 0 && bi < E) l[bi] = __int_as_float(0xffc00000);  // NaN: never wins a '>' test again
+    __syncwarp();
+  }
+  if (lane == 0) {
+    float w[kMaxTopK];
+    if (sigmoid) {
+      for (int j = 0; j < k; ++j) w[j] = 1.0f / (1.0f + expf(-sel_v[j]));
+    } else {
+      float mx = sel_v[0];
+      for (int j = 1; j < k; ++j) mx = fmaxf(mx, sel_v[j]);
+      float se = 0.f;
       for (int j = 0; j < k; ++j) {
-        router_out[((size_t)t * k + j) * 2 + 0] = (float)sel_i[j];
-        router_out[((size_t)t * k + j) * 2 + 1] = w[j];
+        w[j] = expf(sel_v[j] - mx);
+        se += w[j];
       }
+      const float inv = se > 0.f ? 1.0f / se : 0.f;
+      for (int j = 0; j < k; ++j) w[j] *= inv;
+    }
+    for (int j = 0; j < k; ++j) {
+      router_out[((size_t)t * k + j) * 2 + 0] = (float)sel_i[j];
+      router_out[((size_t)t * k + j) * 2 + 1] = w[j];
     }
   }
 }
@@ -419,16 +439,6 @@ __global__ void k_combine(const float* __restrict__ router_out, const int* __res
       }
     }
     *reinterpret_cast<float4*>(out + (size_t)t * H + d) = acc;
-  }
-}
-
-// [E,H] -> [H,E_stride] transpose of the router weights (coalesced reads by expert).
-__global__ void k_transpose_router(const float* __restrict__ wg, float* __restrict__ wgT, int E, int H,
-                                   int E_stride) {
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < (size_t)E * H;
-       i += (size_t)gridDim.x * blockDim.x) {
-    const int e = (int)(i / H), d = (int)(i % H);
-    wgT[(size_t)d * E_stride + e] = wg[i];
   }
 }
 

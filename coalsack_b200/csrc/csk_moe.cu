@@ -24,7 +24,7 @@ struct csk_moe_layer {
   csk_moe_config cfg{};
   int E = 0, k = 0, H = 0, F = 0, e0 = 0, Eloc = 0;
   MatLayout Lgu{}, Ld{};
-  size_t off_gu = 0, off_d = 0, off_bias = 0, expert_stride = 0;
+  size_t off_gu = 0, off_d = 0, off_bias = 0, off_meta = 0, expert_stride = 0;
   uint8_t* d_weights = nullptr;
   uint8_t* d_resident = nullptr;  // [Eloc] flags on the device
   std::vector<uint8_t> resident;
@@ -32,9 +32,8 @@ struct csk_moe_layer {
   size_t stage_bytes = 0;
 
   float* d_wg = nullptr;   // [E,H]
-  float* d_wgT = nullptr;  // [H,E_stride]
+  float* d_logits = nullptr;  // [max_T,E] router scratch
   float* d_rbias = nullptr;
-  int E_stride = 0;
   bool router_set = false, has_rbias = false;
 
   int64_t max_T = 0, max_rows = 0;
@@ -119,16 +118,27 @@ struct StageTimer {
 int launch_router(csk_moe_layer* L, const float* d_hidden, int64_t T, float* d_router,
                   cudaStream_t s) {
   if (!L->router_set) return fail(L, CSK_ERR_INVALID, "router weights were never set");
-  int e_lanes = 16;  // at most 64 tokens per block, whatever E is
-  while (e_lanes < L->E && e_lanes < kRouterThreads) e_lanes <<= 1;
-  const int tok_per_block = kRouterThreads / e_lanes * kRouterTok;
-  const size_t smem = (size_t)tok_per_block * (kRouterChunk + L->E) * sizeof(float);
-  const int blocks = (int)((T + tok_per_block - 1) / tok_per_block);
-  k_router<<<blocks, kRouterThreads, smem, s>>>(d_hidden, L->d_wgT, L->has_rbias ? L->d_rbias : nullptr,
-                                                 d_router, (int)T, L->H, L->E, L->E_stride, L->k,
-                                                 L->cfg.sigmoid_gating, e_lanes);
+  const float* bias = L->has_rbias ? L->d_rbias : nullptr;
+  constexpr int LD = kRouterChunk + kRouterPad;
+  if (T <= 32) {
+    // decode: one chain per thread, 32 tokens x 4 experts per block
+    const int ntx = 32, BT = 32, BE = 4;
+    dim3 grid((unsigned)((T + BT - 1) / BT), (unsigned)((L->E + BE - 1) / BE));
+    k_router_logits<1, 1><<<grid, kRouterThreads, (BT + BE) * LD * sizeof(float), s>>>(
+        d_hidden, L->d_wg, bias, L->d_logits, (int)T, L->H, L->E, ntx);
+  } else {
+    // prefill: 4 x 4 chains per thread; as many threads along experts as E fills
+    int nty = 16;
+    while (nty > 4 && (nty / 2) * 4 >= L->E) nty >>= 1;
+    const int ntx = kRouterThreads / nty, BT = ntx * 4, BE = nty * 4;
+    dim3 grid((unsigned)((T + BT - 1) / BT), (unsigned)((L->E + BE - 1) / BE));
+    k_router_logits<4, 4><<<grid, kRouterThreads, (BT + BE) * LD * sizeof(float), s>>>(
+        d_hidden, L->d_wg, bias, L->d_logits, (int)T, L->H, L->E, ntx);
+  }
+  k_router_topk<<<(unsigned)((T + 3) / 4), 128, 0, s>>>(L->d_logits, d_router, (int)T, L->E, L->k,
+                                                         L->cfg.sigmoid_gating);
   CSK_CUDA(L, cudaGetLastError());
-  L->last.launches++;
+  L->last.launches += 2;
   return CSK_OK;
 }
 
@@ -196,7 +206,7 @@ int choose_path(const csk_moe_layer* L, int64_t rows) {
   if (L->path == CSK_PATH_TILE) return CSK_PATH_TILE;
   // the tensor-core tiles are 128 rows tall: worth it once the average expert
   // fills a good part of one
-  return rows >= 48 * (int64_t)std::max(1, L->Eloc) ? CSK_PATH_TILE : CSK_PATH_STREAM;
+  return (L->tile.available && rows >= 48 * (int64_t)std::max(1, L->Eloc)) ? CSK_PATH_TILE : CSK_PATH_STREAM;
 }
 
 int tile_rows_for(const csk_moe_layer* L, int path, int64_t rows) {
@@ -208,10 +218,11 @@ int tile_rows_for(const csk_moe_layer* L, int path, int64_t rows) {
 int launch_experts(csk_moe_layer* L, int path, int tile_rows, const __half* x16, float* y, int ldy,
                    const int* out_row_map, cudaStream_t s, StageTimer& tm) {
   if (path == CSK_PATH_TILE) {
+    if (x16 != L->d_x16) return fail(L, CSK_ERR_INVALID, "the tile path reads the handle's own row buffer");
     int rc = tile_launch(L->tile, L->d_weights, L->expert_stride, L->off_gu, L->off_d, L->off_bias,
-                         L->Lgu, L->Ld, x16, L->ldx, L->d_a16, L->lda, y, ldy, out_row_map,
-                         L->d_tiles, L->d_meta, L->cfg.has_bias, L->cfg.activation, L->F, L->H,
-                         L->sm_count, s, [&]() { tm.mark(); });
+                         L->off_meta, L->Lgu, L->Ld, L->d_a16, L->lda, y, ldy, out_row_map, L->d_tiles,
+                         L->d_meta, L->cfg.has_bias, L->cfg.activation, L->F, L->sm_count, s,
+                         [&]() { tm.mark(); });
     if (rc) return fail(L, rc, "tensor-core path: %s", L->tile.err.c_str());
     L->last.launches += 2;
   } else {
@@ -365,14 +376,14 @@ int csk_moe_create(const csk_moe_config* cfg, csk_moe_layer** out) {
   L->off_gu = 0;
   L->off_d = (L->Lgu.bytes() + 255) / 256 * 256;
   L->off_bias = L->off_d + (L->Ld.bytes() + 255) / 256 * 256;
-  L->expert_stride = (L->off_bias + sizeof(float) * (2 * (size_t)L->F + L->H) + 255) / 256 * 256;
+  L->off_meta = L->off_bias + sizeof(float) * (2 * (size_t)L->F + L->H);  // int[4]: e_max of gate/up, of down
+  L->expert_stride = (L->off_meta + 16 + 255) / 256 * 256;
   L->resident.assign(eloc, 0);
   L->max_T = cfg->max_tokens;
   L->max_rows = cfg->max_tokens * cfg->top_k;
   L->ldx = L->Lgu.k_pad();
   L->lda = L->Ld.k_pad();
   L->max_tiles = (int)(L->max_rows / 8 + eloc + 8);
-  L->E_stride = (L->E + 31) / 32 * 32;
 
 #define CK(call)                                                                              \
   do {                                                                                        \
@@ -398,8 +409,7 @@ int csk_moe_create(const csk_moe_config* cfg, csk_moe_layer** out) {
   L->stage_bytes = (size_t)L->H * L->F / 32 * 17;
   CK(cudaMalloc(&L->d_stage, 3 * L->stage_bytes));
   CK(cudaMalloc(&L->d_wg, sizeof(float) * L->E * L->H));
-  CK(cudaMalloc(&L->d_wgT, sizeof(float) * L->E_stride * L->H));
-  CK(cudaMemset(L->d_wgT, 0, sizeof(float) * L->E_stride * L->H));
+  CK(cudaMalloc(&L->d_logits, sizeof(float) * L->max_T * L->E));
   CK(cudaMalloc(&L->d_rbias, sizeof(float) * L->E));
   CK(cudaMalloc(&L->d_hidden, sizeof(float) * L->max_T * L->H));
   CK(cudaMalloc(&L->d_router, sizeof(float) * L->max_T * L->k * 2));
@@ -421,9 +431,9 @@ int csk_moe_create(const csk_moe_config* cfg, csk_moe_layer** out) {
   CK(cudaMemset(L->d_meta, 0, sizeof(int) * 8));
   CK(cudaMallocHost(&L->h_meta, sizeof(int) * 8));
   CK(cudaMallocHost(&L->h_counts64, sizeof(int64_t) * L->E));
-  CK(cudaFuncSetAttribute(k_router, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
   {
     int rc = tile_init(L->tile, cfg->device);
+    if (!rc) rc = tile_set_buffers(L->tile, L->d_x16, L->ldx, L->d_a16, L->lda, (size_t)L->max_rows + pad_rows);
     if (rc) {
       rc = fail(nullptr, rc, "tensor-core path setup: %s", L->tile.err.c_str());
       csk_moe_destroy(L);
@@ -441,7 +451,7 @@ int csk_moe_destroy(csk_moe_layer* L) {
   cudaSetDevice(L->cfg.device);
   if (L->stream) cudaStreamSynchronize(L->stream);
   tile_destroy(L->tile);
-  void* dev[] = {L->d_weights, L->d_resident, L->d_stage, L->d_wg, L->d_wgT, L->d_rbias, L->d_hidden,
+  void* dev[] = {L->d_weights, L->d_resident, L->d_stage, L->d_wg, L->d_logits, L->d_rbias, L->d_hidden,
                  L->d_router, L->d_out, L->d_x16, L->d_a16, L->d_y, L->d_counts, L->d_offsets,
                  L->d_cursor, L->d_row_of_pair, L->d_out_row_map, L->d_seg, L->d_tiles, L->d_meta};
   for (void* p : dev)
@@ -461,8 +471,6 @@ int csk_moe_set_router(csk_moe_layer* L, const float* gate_w, const float* gate_
   CSK_CUDA(L, cudaSetDevice(L->cfg.device));
   CSK_CUDA(L, cudaMemcpyAsync(L->d_wg, gate_w, sizeof(float) * L->E * L->H, cudaMemcpyHostToDevice,
                               L->stream));
-  k_transpose_router<<<grid_for((size_t)L->E * L->H, 256, 1024), 256, 0, L->stream>>>(
-      L->d_wg, L->d_wgT, L->E, L->H, L->E_stride);
   L->has_rbias = gate_bias != nullptr;
   if (gate_bias)
     CSK_CUDA(L, cudaMemcpyAsync(L->d_rbias, gate_bias, sizeof(float) * L->E, cudaMemcpyHostToDevice,
@@ -490,8 +498,10 @@ int csk_moe_load_expert_mxfp4(csk_moe_layer* L, int32_t expert_id, const uint8_t
   CSK_CUDA(L, cudaMemcpyAsync(s_up, w_up, L->stage_bytes, cudaMemcpyHostToDevice, s));
   CSK_CUDA(L, cudaMemcpyAsync(s_gate, w_gate, L->stage_bytes, cudaMemcpyHostToDevice, s));
   CSK_CUDA(L, cudaMemcpyAsync(s_down, w_down, L->stage_bytes, cudaMemcpyHostToDevice, s));
-  k_repack<<<grid_for(L->Lgu.bytes() / 4, 256, 4096), 256, 0, s>>>(s_gate, s_up, base + L->off_gu, L->Lgu);
-  k_repack<<<grid_for(L->Ld.bytes() / 4, 256, 4096), 256, 0, s>>>(s_down, nullptr, base + L->off_d, L->Ld);
+  int* emeta = reinterpret_cast<int*>(base + L->off_meta);
+  CSK_CUDA(L, cudaMemsetAsync(emeta, 0, 16, s));
+  k_repack<<<grid_for(L->Lgu.bytes() / 4, 256, 4096), 256, 0, s>>>(s_gate, s_up, base + L->off_gu, L->Lgu, emeta);
+  k_repack<<<grid_for(L->Ld.bytes() / 4, 256, 4096), 256, 0, s>>>(s_down, nullptr, base + L->off_d, L->Ld, emeta + 1);
   CSK_CUDA(L, cudaGetLastError());
   if (L->cfg.has_bias) {
     float* b = reinterpret_cast<float*>(base + L->off_bias);

@@ -294,13 +294,14 @@ class expert_mlp_node:
     def set_weight_before_ffn(self, v):
         self.weight_before_ffn_ = bool(v)
 
-    def _get_layer(self, H, F, has_bias, k, T):
-        key = (H, F, has_bias, k, int(self.activation_type_), self.weight_before_ffn_, self.expert_id_)
+    def _get_layer(self, H, F, has_bias, k, T, n_ids=1):
+        E = max(self.expert_id_ + 1, k, n_ids)  # the layer's id space must cover every id the router names
+        key = (H, F, has_bias, k, int(self.activation_type_), self.weight_before_ffn_, self.expert_id_, E)
         if self._key != key or self._layer.max_tokens < T:
             if self._layer is not None:
                 self._layer.close()
             # a one-expert layer whose only resident expert carries this node's id
-            self._layer = MoeLayer(max(self.expert_id_ + 1, k), k, H, F,
+            self._layer = MoeLayer(E, k, H, F,
                                    int(self.activation_type_), has_bias,
                                    weight_before_ffn=self.weight_before_ffn_, device=self.device,
                                    expert_begin=self.expert_id_, expert_count=1, max_tokens=max(T, 64))
@@ -336,7 +337,7 @@ class expert_mlp_node:
         if F % 32:
             raise RuntimeError(f"expert_mlp: expert_ffn_dim must be a multiple of 32 for MXFP4, got {F}")
         k = router_output.shape[2]
-        lay = self._get_layer(H, F, b_up is not None, k, B * S)
+        lay = self._get_layer(H, F, b_up is not None, k, B * S, int(router_output[..., 0].max()) + 1)
         lay.load_expert(self.expert_id_, w_up, w_gate, w_down, b_up, b_gate, b_down)
         out = lay.expert_forward(self.expert_id_, hidden_states.reshape(B * S, H),
                                  router_output.reshape(B * S, k, 2))

@@ -4,7 +4,7 @@ inputs, and the reference itself where its compiled wrapper travelled along."""
 import numpy as np
 import pytest
 
-from coalsack_b200 import (CskError, MoeLayer, PATH_STREAM, expert_merge_node, expert_mlp_node,
+from coalsack_b200 import (CskError, MoeLayer, PATH_STREAM, PATH_TILE, expert_merge_node, expert_mlp_node,
                            moe_router_node, synth)
 from tests import cases
 
@@ -195,8 +195,11 @@ def test_tiny_layer_given_router_output(gpu_lib, golden):
 def test_exponent_range(gpu_lib, port):
     """Scale exponents far outside the benchmark's [118,124]: dequantisation stays exact."""
     sh = synth.tiny(seed=41, E=4, k=2, H=128, F=128, T=6, has_bias=False)
-    h, Wg, rb, ex = cases.layer_inputs(sh, router_scale=50.0, exp_lo=96, exp_hi=136)
+    h, Wg, rb, ex = cases.layer_inputs(sh, router_scale=50.0, exp_lo=70, exp_hi=120)
+    for e in range(4):
+        ex["w_down"][e] = synth.mxfp4_matrix(sh.seed, synth._T_WDOWN, e, 128, 128, 120, 200)
     lay = make_layer(sh, Wg, rb, ex)
+    lay.set_path(PATH_STREAM)
     out, ro = lay.forward(h)
     want, _ = port.moe_layer(h, Wg, rb, ex, 2, sh.act, router_out=ro)
     assert np.all(np.isfinite(want)) and np.any(want != 0)
@@ -239,7 +242,7 @@ def test_many_rows_one_expert_and_ragged(gpu_lib, port):
     sh = synth.tiny(seed=51, E=8, k=2, H=192, F=224, T=300, has_bias=True)
     h, Wg, rb, ex = cases.layer_inputs(sh, router_scale=40.0)
     rb = rb.copy()
-    rb[0] += 8.0      # expert 0 nearly always wins a slot
+    rb[0] += 60.0     # expert 0 nearly always wins a slot
     rb[5:] -= 50.0    # experts 5..7 never selected
     lay = make_layer(sh, Wg, rb, ex, max_tokens=300)
     out, ro = lay.forward(h)
@@ -249,7 +252,7 @@ def test_many_rows_one_expert_and_ragged(gpu_lib, port):
     assert rows[0] > 250 and rows[5:].sum() == 0 and rows.sum() == 600
     want, _ = port.moe_layer(h, Wg, rb, ex, 2, sh.act, nthreads=8, router_out=ro)
     assert_close(out, want, "skewed")
-    for path in (PATH_STREAM,):
+    for path in (PATH_STREAM, PATH_TILE):
         lay.set_path(path)
         out2, _ = lay.forward(h, router_out=ro)
         assert_close(out2, want, f"skewed path {path}")
@@ -318,3 +321,58 @@ def test_expert_node_empty_and_dense(gpu_lib, golden):
         assert out.shape == (0,)
     with pytest.raises(RuntimeError, match="must be 3D"):
         node.compute_with_mxfp4(h, *cases.expert_args(ex, 0), ro.reshape(1, *ro.shape), sh.ffn)
+
+
+# ---- the tensor-core (tcgen05) kernel, forced --------------------------------------
+@pytest.mark.parametrize("tag", list(cases.TINY_CASES))
+def test_tile_path_tiny_layers(gpu_lib, golden, tag):
+    sh, h, Wg, rb, ex, wbf = cases.tiny_case(tag)
+    lay = make_layer(sh, Wg, rb, ex, wbf)
+    lay.set_path(PATH_TILE)
+    out, ro = lay.forward(h)
+    assert lay.timings()["path"] == PATH_TILE
+    assert same_experts(ro, golden[f"{tag}_router"])
+    assert_close(out, golden[f"{tag}_out"], tag)
+    for e in range(sh.num_experts):
+        o = lay.expert_forward(e, h, golden[f"{tag}_router"])
+        assert (o is not None) == bool(golden[f"{tag}_selected"][e])
+        if o is not None:
+            picked = (golden[f"{tag}_router"][:, :, 0].astype(int) == e).any(axis=1)
+            assert np.all(o[~picked] == 0.0)
+            if picked.sum() > 1:
+                assert_close(o[picked], golden[f"{tag}_nodes"][e][picked], f"{tag} expert {e}")
+    lay.close()
+
+
+def test_tile_path_c0(gpu_lib, golden, port):
+    sh = synth.C0
+    h, Wg, rb, ex = cases.layer_inputs(sh, 32)
+    lay = make_layer(sh, Wg, rb, ex, max_tokens=32)
+    lay.set_path(PATH_TILE)
+    out1, ro1 = lay.forward(h[:1])
+    assert_close(out1, golden["c0_t1_out"], "c0 T=1 tile")
+    out32, ro32 = lay.forward(h)
+    assert same_experts(ro32, golden["c0_t32_router"])
+    assert_close(out32[:4], golden["c0_t32_out_first4"], "c0 T=32 tile")
+    want, _ = port.moe_layer(h, Wg, rb, ex, sh.top_k, sh.act, nthreads=8, router_out=ro32)
+    assert_close(out32, want, "c0 T=32 tile, all rows")
+    lay.close()
+
+
+def test_tile_path_wide_exponents(gpu_lib, port):
+    """Scale exponents spread over 37 binades inside one matrix stay exact in the fp16 tile.
+    (Gate/up scales are kept small so the pre-activations stay near the clamp range: with
+    weights in the thousands a 16-bit input row alone moves pre-activations by whole units.)"""
+    sh = synth.tiny(seed=43, E=4, k=2, H=128, F=128, T=200, has_bias=False)
+    h, Wg, rb, ex = cases.layer_inputs(sh, router_scale=50.0, exp_lo=84, exp_hi=120)
+    for e in range(4):
+        ex["w_down"][e] = synth.mxfp4_matrix(sh.seed, synth._T_WDOWN, e, 128, 128, 100, 136)
+    lay = make_layer(sh, Wg, rb, ex, max_tokens=200)
+    want = None
+    for path in (PATH_TILE, PATH_STREAM):
+        lay.set_path(path)
+        out, ro = lay.forward(h)
+        if want is None:
+            want, _ = port.moe_layer(h, Wg, rb, ex, 2, sh.act, nthreads=8, router_out=ro)
+        assert_close(out, want, f"wide exponents, path {path}")
+    lay.close()
