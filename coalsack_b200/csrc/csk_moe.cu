@@ -781,4 +781,68 @@ int csk_moe_ep_combine_dev(csk_moe_layer* L, const float* d_back, int64_t T, flo
   return CSK_OK;
 }
 
+// ---- routing without any allocation ---------------------------------------------
+// Scratch for csk_moe_route_static: the [T,E] logits between its two kernels.
+// File-scope device memory, so every GPU that loads this library carries these
+// 1 MiB until the process exits.  In host code `g_static_logits` is only a
+// stand-in for the symbol; the device address comes from cudaGetSymbolAddress.
+constexpr int64_t kStaticLogitsMax = 256 * 1024;  // floats: T * E may not exceed this
+static __device__ __align__(256) float g_static_logits[kStaticLogitsMax];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mu;
+float* g_static_logits_addr[kMaxDevices] = {nullptr};
+}  // namespace
+
+int csk_moe_route_static(const float* d_hidden, int64_t T, int32_t H, const float* d_gate_w,
+                         const float* d_gate_bias, int32_t E, int32_t k, int32_t sigmoid_gating,
+                         float* d_router_out, void* stream) {
+  if (!d_hidden || !d_gate_w || !d_router_out) return fail(nullptr, CSK_ERR_INVALID, "route_static: null argument");
+  if (T <= 0 || H <= 0 || H % 32 || E <= 0 || E > 1024 || k <= 0 || k > kMaxTopK || k > E)
+    return fail(nullptr, CSK_ERR_INVALID,
+                "route_static: need T > 0, H a positive multiple of 32, 1 <= E <= 1024, 1 <= k <= min(E, %d); "
+                "got T=%lld H=%d E=%d k=%d", kMaxTopK, (long long)T, H, E, k);
+  if (T * (int64_t)E > kStaticLogitsMax)
+    return fail(nullptr, CSK_ERR_NOMEM,
+                "route_static: T*E = %lld exceeds the built-in scratch of %lld logits; split the batch or use "
+                "csk_moe_route_dev on a handle", (long long)(T * (int64_t)E), (long long)kStaticLogitsMax);
+  int dev = -1;
+  cudaError_t ce = cudaGetDevice(&dev);
+  if (ce != cudaSuccess) return fail(nullptr, CSK_ERR_CUDA, "route_static: cudaGetDevice: %s", cudaGetErrorString(ce));
+  if (dev < 0 || dev >= kMaxDevices) return fail(nullptr, CSK_ERR_INVALID, "route_static: device ordinal %d not supported", dev);
+  float* logits = nullptr;
+  {
+    // once per device, with that device current: resolve the symbol to its address there
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    if (!g_static_logits_addr[dev]) {
+      void* p = nullptr;
+      ce = cudaGetSymbolAddress(&p, g_static_logits);
+      if (ce != cudaSuccess || !p)
+        return fail(nullptr, CSK_ERR_CUDA, "route_static: cudaGetSymbolAddress: %s", cudaGetErrorString(ce));
+      g_static_logits_addr[dev] = static_cast<float*>(p);
+    }
+    logits = g_static_logits_addr[dev];
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  constexpr int LD = kRouterChunk + kRouterPad;
+  if (T <= 32) {
+    const int ntx = 32, BT = 32, BE = 4;
+    dim3 grid((unsigned)((T + BT - 1) / BT), (unsigned)((E + BE - 1) / BE));
+    k_router_logits<1, 1><<<grid, kRouterThreads, (BT + BE) * LD * sizeof(float), s>>>(
+        d_hidden, d_gate_w, d_gate_bias, logits, (int)T, H, E, ntx);
+  } else {
+    int nty = 16;
+    while (nty > 4 && (nty / 2) * 4 >= E) nty >>= 1;
+    const int ntx = kRouterThreads / nty, BT = ntx * 4, BE = nty * 4;
+    dim3 grid((unsigned)((T + BT - 1) / BT), (unsigned)((E + BE - 1) / BE));
+    k_router_logits<4, 4><<<grid, kRouterThreads, (BT + BE) * LD * sizeof(float), s>>>(
+        d_hidden, d_gate_w, d_gate_bias, logits, (int)T, H, E, ntx);
+  }
+  k_router_topk<<<(unsigned)((T + 3) / 4), 128, 0, s>>>(logits, d_router_out, (int)T, E, k, sigmoid_gating);
+  ce = cudaGetLastError();
+  if (ce != cudaSuccess) return fail(nullptr, CSK_ERR_CUDA, "route_static: launch failed: %s", cudaGetErrorString(ce));
+  return CSK_OK;
+}
+
 }  // extern "C"

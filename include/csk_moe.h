@@ -139,6 +139,35 @@ int csk_moe_forward_dev(csk_moe_layer* layer, const float* d_hidden, int64_t T,
  * range, rows routed to an expert that is not loaded, capacity exceeded). */
 int csk_moe_sync(csk_moe_layer* layer);
 
+/* Routing for callers that must not allocate.  No counterpart in the reference
+ * (its router keeps its logits in a std::vector on the host).
+ *
+ * Same result as csk_moe_route_dev, but it needs no handle and calls no
+ * cudaMalloc/cudaFree or any other allocating routine: the [T,E] logits between
+ * its two kernels live in a 1 MiB array compiled into this library's device
+ * image.  Meant for hosts where device memory was handed out up front to one
+ * owner (a serving process that reserves the whole GPU for its own pool, so a
+ * later cudaMalloc simply fails) and for threads that may not block on the
+ * allocator's device-wide synchronisation, such as a per-layer scheduler
+ * thread that shares the GPU with other layers' streams.
+ *
+ * All pointers are device pointers on the CURRENT device: hidden [T,H] fp32,
+ * gate_w [E,H] fp32, gate_bias [E] or NULL, router_out [T,k,2].  `stream` is a
+ * cudaStream_t passed as void* (NULL = the default stream); the call only
+ * enqueues work.
+ * Limits: T*E <= 262144 logits (e.g. 2048 tokens at 128 experts), H a multiple
+ * of 32, E <= 1024, k <= 16; beyond them the call returns CSK_ERR_NOMEM /
+ * CSK_ERR_INVALID with a message in csk_moe_last_error(NULL) and launches nothing.
+ * The first call on each device resolves the array's device address
+ * (cudaGetSymbolAddress); make that first call before any stream capture.
+ * The array is shared by every call in the process and keeps the last call's
+ * logits; each call overwrites the part it reads, so nothing needs clearing,
+ * but two calls that overlap on the same GPU (different streams or threads)
+ * race on it: serialise them. */
+int csk_moe_route_static(const float* d_hidden, int64_t T, int32_t H, const float* d_gate_w,
+                         const float* d_gate_bias_or_null, int32_t E, int32_t k,
+                         int32_t sigmoid_gating, float* d_router_out, void* stream);
+
 /* ---- expert parallelism: the layer cut at its two exchange points -------
  * Rank r holds experts [expert_begin, expert_begin+expert_count).  A step is
  *   dispatch_dev  : route local tokens, group their (token, expert) rows by
