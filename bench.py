@@ -241,7 +241,7 @@ def run_ours(args):
                 "traffic": None, "ms_per_launch": gu_ms,
                 "layer_tflops": algorithmic_flops(sh, T * world) / (ms_per_step * 1e-3) / 1e12,
                 "stages_ms": {n: stage[n] for n in ("route_ms", "permute_ms", "gate_up_ms", "down_ms", "combine_ms", "total_ms")}}
-    cb, _ = time_reference(sh, 2, 1) if world == 1 else (None, None)
+    cb, _ = time_reference(sh, 2, 1) if (world == 1 and not args.skip_cpu) else (None, None)
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f16 operands (MXFP4 weights dequantised exactly), f32 accumulate; f32 router",
@@ -319,6 +319,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c1", choices=sorted(synth.CONFIGS))
     ap.add_argument("--tokens", type=int, default=None, help="override the workload's tokens per GPU")
+    ap.add_argument("--skip-cpu", action="store_true", help="leave out the cpu_baseline leg (profiling runs)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

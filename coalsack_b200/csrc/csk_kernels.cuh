@@ -120,17 +120,25 @@ constexpr int kRouterPad = 4;
 constexpr int kRouterThreads = 128;
 constexpr int kMaxTopK = 16;
 
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, bool valid) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  const int n = valid ? 16 : 0;  // src-size 0 -> the 16 bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gsrc), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 template <int TT, int EE>
 __global__ void __launch_bounds__(kRouterThreads)
 k_router_logits(const float* __restrict__ hidden, const float* __restrict__ wg,
                 const float* __restrict__ bias, float* __restrict__ logits, int T, int H, int E,
                 int ntx /* threads along tokens; 128/ntx along experts */) {
-  extern __shared__ float smem[];
+  extern __shared__ __align__(16) float smem[];
   constexpr int LD = kRouterChunk + kRouterPad;
   const int nty = kRouterThreads / ntx;
   const int BT = ntx * TT, BE = nty * EE;
-  float* hs = smem;            // [BT][LD]
-  float* ws = smem + BT * LD;  // [BE][LD]
+  const int tile_floats = (BT + BE) * LD;  // one stage: hs[BT][LD] then ws[BE][LD]
   const int tid = threadIdx.x;
   const int tx = tid % ntx, ty = tid / ntx;
   const int t0 = blockIdx.x * BT, e0 = blockIdx.y * BE;
@@ -141,28 +149,41 @@ k_router_logits(const float* __restrict__ hidden, const float* __restrict__ wg,
 #pragma unroll
     for (int j = 0; j < EE; ++j) acc[i][j] = 0.f;
 
-  for (int d0 = 0; d0 < H; d0 += kRouterChunk) {
+  // asynchronous, coalesced 16-byte copies along the hidden dimension into stage `st`
+  auto load_chunk = [&](int st, int d0) {
+    float* base = smem + st * tile_floats;
     const int dc = min(kRouterChunk, H - d0);  // H % 32 == 0, so dc is 32 or 64
-    __syncthreads();
-    // coalesced float4 loads along the hidden dimension
     for (int i = tid; i < (BT + BE) * (kRouterChunk / 4); i += kRouterThreads) {
       const int r = i / (kRouterChunk / 4), c = (i % (kRouterChunk / 4)) * 4;
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
       if (r < BT) {
-        if (t0 + r < T && c < dc) v = *reinterpret_cast<const float4*>(hidden + (size_t)(t0 + r) * H + d0 + c);
-        *reinterpret_cast<float4*>(hs + r * LD + c) = v;
+        const bool ok = t0 + r < T && c < dc;
+        cp_async16(base + r * LD + c, ok ? hidden + (size_t)(t0 + r) * H + d0 + c : hidden, ok);
       } else {
         const int e = e0 + r - BT;
-        if (e < E && c < dc) v = *reinterpret_cast<const float4*>(wg + (size_t)e * H + d0 + c);
-        *reinterpret_cast<float4*>(ws + (r - BT) * LD + c) = v;
+        const bool ok = e < E && c < dc;
+        cp_async16(base + r * LD + c, ok ? wg + (size_t)e * H + d0 + c : wg, ok);
       }
+    }
+    cp_async_commit();
+  };
+
+  const int n_chunks = (H + kRouterChunk - 1) / kRouterChunk;
+  load_chunk(0, 0);
+  for (int ch = 0; ch < n_chunks; ++ch) {
+    const int st = ch & 1;
+    if (ch + 1 < n_chunks) {
+      load_chunk(st ^ 1, (ch + 1) * kRouterChunk);  // stage st^1 was released by the barrier ending chunk ch-1
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
     }
     __syncthreads();
     // thread (tx, ty) owns tokens tx + i*ntx and experts ty + j*nty: neighbouring
     // threads read neighbouring rows (stride LD = 4 mod 32 words), so the 128-bit
     // shared loads of a quarter-warp fall in distinct banks
-    const float* hp = hs + tx * LD;
-    const float* wp = ws + ty * LD;
+    const float* hp = smem + st * tile_floats + tx * LD;
+    const float* wp = smem + st * tile_floats + BT * LD + ty * LD;
+    const int dc = min(kRouterChunk, H - ch * kRouterChunk);
     for (int d = 0; d < dc; d += 4) {
       float4 hv[TT], wv[EE];
 #pragma unroll
@@ -181,6 +202,7 @@ k_router_logits(const float* __restrict__ hidden, const float* __restrict__ wg,
           acc[i][j] = a;
         }
     }
+    __syncthreads();
   }
 #pragma unroll
   for (int i = 0; i < TT; ++i)
@@ -189,6 +211,50 @@ k_router_logits(const float* __restrict__ hidden, const float* __restrict__ wg,
       const int t = t0 + tx + i * ntx, e = e0 + ty + j * nty;
       if (t < T && e < E) logits[(size_t)t * E + e] = __fadd_rn(acc[i][j], bias ? bias[e] : 0.f);
     }
+}
+
+// Lets the router kernels use more than the default 48 KB of dynamic shared
+// memory (few experts and many tokens make tall token tiles).  Once per device.
+inline cudaError_t router_prepare_device() {
+  const int bytes = 100 * 1024;
+  cudaError_t e = cudaFuncSetAttribute(k_router_logits<4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(k_router_logits<2, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(k_router_logits<1, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(k_router_logits<1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  return e;
+}
+
+// Picks the chain tile per thread so that the grid fills the machine, and launches.
+inline void launch_router_logits(const float* d_hidden, const float* d_wg, const float* d_bias, float* d_logits,
+                                 int64_t T, int H, int E, int sm_count, cudaStream_t s) {
+  constexpr int LD = kRouterChunk + kRouterPad;
+  auto smem_of = [&](int BT, int BE) { return (size_t)2 * (BT + BE) * LD * sizeof(float); };
+  if (T <= 32) {
+    // decode: one chain per thread, 32 tokens x 4 experts per block, E/4 blocks
+    const int ntx = 32, BT = 32, BE = 4;
+    dim3 grid((unsigned)((T + BT - 1) / BT), (unsigned)((E + BE - 1) / BE));
+    k_router_logits<1, 1><<<grid, kRouterThreads, smem_of(BT, BE), s>>>(d_hidden, d_wg, d_bias, d_logits, (int)T, H, E, ntx);
+    return;
+  }
+  // threads along experts: as many as E fills with EE = 4 (E <= 16 -> 4)
+  int nty = 16;
+  while (nty > 4 && (nty / 2) * 4 >= E) nty >>= 1;
+  const int ntx = kRouterThreads / nty;
+  const long chains = (long)T * E;
+  const long want_blocks = 3L * sm_count;
+  if (chains / (16 * kRouterThreads) >= want_blocks) {
+    const int BT = ntx * 4, BE = nty * 4;
+    dim3 grid((unsigned)((T + BT - 1) / BT), (unsigned)((E + BE - 1) / BE));
+    k_router_logits<4, 4><<<grid, kRouterThreads, smem_of(BT, BE), s>>>(d_hidden, d_wg, d_bias, d_logits, (int)T, H, E, ntx);
+  } else if (chains / (8 * kRouterThreads) >= want_blocks) {
+    const int BT = ntx * 2, BE = nty * 4;
+    dim3 grid((unsigned)((T + BT - 1) / BT), (unsigned)((E + BE - 1) / BE));
+    k_router_logits<2, 4><<<grid, kRouterThreads, smem_of(BT, BE), s>>>(d_hidden, d_wg, d_bias, d_logits, (int)T, H, E, ntx);
+  } else {
+    const int BT = ntx, BE = nty * 4;
+    dim3 grid((unsigned)((T + BT - 1) / BT), (unsigned)((E + BE - 1) / BE));
+    k_router_logits<1, 4><<<grid, kRouterThreads, smem_of(BT, BE), s>>>(d_hidden, d_wg, d_bias, d_logits, (int)T, H, E, ntx);
+  }
 }
 
 __global__ void __launch_bounds__(128)

@@ -118,23 +118,8 @@ struct StageTimer {
 int launch_router(csk_moe_layer* L, const float* d_hidden, int64_t T, float* d_router,
                   cudaStream_t s) {
   if (!L->router_set) return fail(L, CSK_ERR_INVALID, "router weights were never set");
-  const float* bias = L->has_rbias ? L->d_rbias : nullptr;
-  constexpr int LD = kRouterChunk + kRouterPad;
-  if (T <= 32) {
-    // decode: one chain per thread, 32 tokens x 4 experts per block
-    const int ntx = 32, BT = 32, BE = 4;
-    dim3 grid((unsigned)((T + BT - 1) / BT), (unsigned)((L->E + BE - 1) / BE));
-    k_router_logits<1, 1><<<grid, kRouterThreads, (BT + BE) * LD * sizeof(float), s>>>(
-        d_hidden, L->d_wg, bias, L->d_logits, (int)T, L->H, L->E, ntx);
-  } else {
-    // prefill: 4 x 4 chains per thread; as many threads along experts as E fills
-    int nty = 16;
-    while (nty > 4 && (nty / 2) * 4 >= L->E) nty >>= 1;
-    const int ntx = kRouterThreads / nty, BT = ntx * 4, BE = nty * 4;
-    dim3 grid((unsigned)((T + BT - 1) / BT), (unsigned)((L->E + BE - 1) / BE));
-    k_router_logits<4, 4><<<grid, kRouterThreads, (BT + BE) * LD * sizeof(float), s>>>(
-        d_hidden, L->d_wg, bias, L->d_logits, (int)T, L->H, L->E, ntx);
-  }
+  launch_router_logits(d_hidden, L->d_wg, L->has_rbias ? L->d_rbias : nullptr, L->d_logits, T, L->H, L->E,
+                       L->sm_count, s);
   k_router_topk<<<(unsigned)((T + 3) / 4), 128, 0, s>>>(L->d_logits, d_router, (int)T, L->E, L->k,
                                                          L->cfg.sigmoid_gating);
   CSK_CUDA(L, cudaGetLastError());
@@ -431,6 +416,7 @@ int csk_moe_create(const csk_moe_config* cfg, csk_moe_layer** out) {
   CK(cudaMemset(L->d_meta, 0, sizeof(int) * 8));
   CK(cudaMallocHost(&L->h_meta, sizeof(int) * 8));
   CK(cudaMallocHost(&L->h_counts64, sizeof(int64_t) * L->E));
+  CK(router_prepare_device());
   {
     int rc = tile_init(L->tile, cfg->device);
     if (!rc) rc = tile_set_buffers(L->tile, L->d_x16, L->ldx, L->d_a16, L->lda, (size_t)L->max_rows + pad_rows);
@@ -820,25 +806,17 @@ int csk_moe_route_static(const float* d_hidden, int64_t T, int32_t H, const floa
       ce = cudaGetSymbolAddress(&p, g_static_logits);
       if (ce != cudaSuccess || !p)
         return fail(nullptr, CSK_ERR_CUDA, "route_static: cudaGetSymbolAddress: %s", cudaGetErrorString(ce));
+      ce = router_prepare_device();
+      if (ce != cudaSuccess)
+        return fail(nullptr, CSK_ERR_CUDA, "route_static: cudaFuncSetAttribute: %s", cudaGetErrorString(ce));
       g_static_logits_addr[dev] = static_cast<float*>(p);
     }
     logits = g_static_logits_addr[dev];
   }
   cudaStream_t s = (cudaStream_t)stream;
-  constexpr int LD = kRouterChunk + kRouterPad;
-  if (T <= 32) {
-    const int ntx = 32, BT = 32, BE = 4;
-    dim3 grid((unsigned)((T + BT - 1) / BT), (unsigned)((E + BE - 1) / BE));
-    k_router_logits<1, 1><<<grid, kRouterThreads, (BT + BE) * LD * sizeof(float), s>>>(
-        d_hidden, d_gate_w, d_gate_bias, logits, (int)T, H, E, ntx);
-  } else {
-    int nty = 16;
-    while (nty > 4 && (nty / 2) * 4 >= E) nty >>= 1;
-    const int ntx = kRouterThreads / nty, BT = ntx * 4, BE = nty * 4;
-    dim3 grid((unsigned)((T + BT - 1) / BT), (unsigned)((E + BE - 1) / BE));
-    k_router_logits<4, 4><<<grid, kRouterThreads, (BT + BE) * LD * sizeof(float), s>>>(
-        d_hidden, d_gate_w, d_gate_bias, logits, (int)T, H, E, ntx);
-  }
+  int sms = 148;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  launch_router_logits(d_hidden, d_gate_w, d_gate_bias, logits, T, H, E, sms, s);
   k_router_topk<<<(unsigned)((T + 3) / 4), 128, 0, s>>>(logits, d_router_out, (int)T, E, k, sigmoid_gating);
   ce = cudaGetLastError();
   if (ce != cudaSuccess) return fail(nullptr, CSK_ERR_CUDA, "route_static: launch failed: %s", cudaGetErrorString(ce));

@@ -10,9 +10,9 @@
 //               activation tile (128-byte swizzle) and one bulk copy of the
 //               packed weight tile (codes + E8M0 scales, one contiguous span)
 //   warp 1      issues the MMAs (one lane), owns the tensor-memory allocation
-//   warps 2-5   dequantise the packed tile into the K-major, 128-byte-swizzled
+//   warps 2-9   dequantise the packed tile into the K-major, 128-byte-swizzled
 //               fp16 operand tile (cvt.e2m1x2 -> half2, times 2^(e - e_max + 13))
-//   warps 6-9   epilogue: tcgen05.ld of the accumulator, scale by the matrix's
+//   warps 10-13 epilogue: tcgen05.ld of the accumulator, scale by the matrix's
 //               power of two, bias, activation, store
 // Two accumulators of BN columns alternate, so the epilogue of one work item
 // overlaps the contraction of the next.
@@ -38,7 +38,8 @@
 namespace csk {
 
 constexpr int kTileM = 128;          // rows of a tensor-core row tile
-constexpr int kTileThreads = 320;    // 10 warps
+constexpr int kDequantWarps = 8;
+constexpr int kTileThreads = (2 + kDequantWarps + 4) * 32;  // producer, MMA, dequantisers, epilogue
 constexpr long long kWaitBudget = 2000000000LL;  // clock cycles (~1 s) before a wait gives up
 
 struct TileState {
@@ -211,7 +212,7 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
   if (threadIdx.x == 0) {
     for (int s = 0; s < 6; ++s) {
       mbar_init(bar_full_raw(s), 1);
-      mbar_init(bar_full_b(s), 4);
+      mbar_init(bar_full_b(s), kDequantWarps);
       mbar_init(bar_empty(s), 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -320,7 +321,7 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
       while (!mbar_try(bar_drain, 0) && clock64() - t0 < kWaitBudget) {
       }
     }
-  } else if (warp < 6) {
+  } else if (warp < 2 + kDequantWarps) {
     // ------------------------------ dequantisers ------------------------------
     const int dw = warp - 2;
     const int g = lane >> 2, q = lane & 3;
@@ -339,7 +340,7 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
         uint8_t* st = smem + (size_t)s * stage_bytes;
         uint8_t* btile = st + a_bytes;
         const uint8_t* packed = st + a_bytes + b_bytes;
-        for (int sub = dw; sub < L.subs; sub += 4) {
+        for (int sub = dw; sub < L.subs; sub += kDequantWarps) {
           const uint4 c = *reinterpret_cast<const uint4*>(packed + sub * kSubBytes + lane * 16);
           const uint32_t sc = *reinterpret_cast<const uint32_t*>(packed + sub * kSubBytes + kSubCodeBytes + g * 4);
           // odd rows start with the other 32-column block: a quarter-warp's eight

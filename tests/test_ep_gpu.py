@@ -1,0 +1,76 @@
+"""The expert-parallel stages of the C ABI (dispatch / experts / combine) on ONE
+GPU: N ranks are N handles in one process and the two all-to-all exchanges are
+plain slice copies, run one after the other (nothing here waits on another
+kernel).  Result must match the single-device layer and the CPU checker."""
+import numpy as np
+import pytest
+
+from coalsack_b200 import MoeLayer, PATH_STREAM, PATH_TILE, synth
+from tests import cases
+
+pytestmark = pytest.mark.gpu
+
+
+def run_emulated_ep(torch, sh, N, tokens, Wg, rb, ex, path):
+    E, k, H = sh.num_experts, sh.top_k, sh.hidden
+    eloc = E // N
+    dev = torch.device("cuda", 0)
+    layers, hs = [], []
+    for r in range(N):
+        lay = MoeLayer.from_shape(sh, max_tokens=max(sum(tokens), 1), expert_begin=r * eloc, expert_count=eloc)
+        lay.set_router(Wg, rb)
+        lay.load_experts({n: (None if ex.get(n) is None else ex[n][r * eloc:(r + 1) * eloc])
+                          for n in ("w_up", "w_gate", "w_down", "b_up", "b_gate", "b_down")},
+                         ids=range(r * eloc, (r + 1) * eloc))
+        lay.set_path(path)
+        layers.append(lay)
+        hs.append(torch.from_numpy(synth.hidden_states(sh, tokens[r], rep=r)).to(dev))
+    pitch = layers[0].ep_row_pitch()
+    send = [torch.zeros((tokens[r] * k, pitch), dtype=torch.float16, device=dev) for r in range(N)]
+    counts = [torch.zeros(E, dtype=torch.int32, device=dev) for _ in range(N)]
+    for r in range(N):
+        layers[r].ep_dispatch_dev(hs[r], tokens[r], send[r], counts[r])
+    torch.cuda.synchronize()
+    cn = np.stack([c.cpu().numpy() for c in counts])             # [src, expert]
+    offs = np.concatenate([np.zeros((N, 1), np.int64), np.cumsum(cn, axis=1)], axis=1)
+    outs = []
+    rets = []
+    for d in range(N):                                            # destination rank d receives from every src
+        segs = [send[s][offs[s, d * eloc]:offs[s, (d + 1) * eloc]] for s in range(N)]
+        recv = torch.cat(segs) if segs else send[0][:0]
+        rc = torch.from_numpy(np.ascontiguousarray(cn[:, d * eloc:(d + 1) * eloc]).astype(np.int32)).to(dev)
+        total = recv.shape[0]
+        ret = torch.zeros((max(total, 1), H), dtype=torch.float32, device=dev)
+        if total:
+            layers[d].ep_experts_dev(recv.contiguous(), rc, N, total, ret)
+            layers[d].sync()
+        rets.append((ret, [s.shape[0] for s in segs]))
+    for s in range(N):                                            # rows travel back in the order they were sent
+        parts = []
+        for d in range(N):
+            ret, lens = rets[d]
+            start = sum(lens[:s])
+            parts.append(ret[start:start + lens[s]])
+        back = torch.cat(parts).contiguous()
+        assert back.shape[0] == tokens[s] * k
+        out = torch.empty((tokens[s], H), dtype=torch.float32, device=dev)
+        ro = torch.empty((tokens[s], k, 2), dtype=torch.float32, device=dev)
+        layers[s].ep_combine_dev(back, tokens[s], out, ro)
+        torch.cuda.synchronize()
+        outs.append((out.cpu().numpy(), ro.cpu().numpy(), hs[s].cpu().numpy()))
+    for lay in layers:
+        lay.close()
+    return outs
+
+
+@pytest.mark.parametrize("path", [PATH_STREAM, PATH_TILE])
+@pytest.mark.parametrize("N,tokens", [(2, (37, 64)), (4, (3, 0 + 1, 50, 9))])
+def test_emulated_ep_matches_checker(gpu_lib, port, path, N, tokens):
+    import torch
+    sh = synth.tiny(seed=81, E=8, k=3, H=192, F=160, T=1, has_bias=True)
+    _, Wg, rb, ex = cases.layer_inputs(sh, router_scale=40.0)
+    for out, ro, h in run_emulated_ep(torch, sh, N, tokens, Wg, rb, ex, path):
+        want, want_ro = port.moe_layer(h, Wg, rb, ex, sh.top_k, sh.act, nthreads=4)
+        assert np.array_equal(ro[..., 0], want_ro[..., 0])
+        mx, mr = cases.err_stats(out, want)
+        assert mx <= cases.MAX_ABS_OVER_RMS and mr <= cases.MEAN_REL, (path, N, mx, mr)
