@@ -232,7 +232,7 @@ def run_ours(args):
         return
 
     peaks = measured_peaks()
-    rows = T * k
+    rows = stage.get("rows_received", T * k)   # under expert parallelism: rows this rank's experts processed
     gu_flops = rows * 4.0 * H * sh.ffn     # gate and up projections: 2 * rows * 2F * H
     gu_ms = stage["gate_up_ms"]
     achieved = gu_flops / (gu_ms * 1e-3) / 1e12 if gu_ms > 0 else 0.0

@@ -735,6 +735,7 @@ int csk_moe_ep_experts_dev(csk_moe_layer* L, const void* d_recv_f16, const int32
                                                L->d_offsets, n_src, L->Eloc, L->e0, L->d_out_row_map);
   CSK_CUDA(L, cudaGetLastError());
   StageTimer tm(L, s);
+  tm.mark();
   int rc;
   if (path == CSK_PATH_TILE) {
     rc = launch_experts(L, path, tile_rows, L->d_x16, d_ret, L->H, L->d_out_row_map, s, tm);
@@ -747,7 +748,14 @@ int csk_moe_ep_experts_dev(csk_moe_layer* L, const void* d_recv_f16, const int32
     }
   }
   if (rc) return rc;
-  return check_device_status(L, s);
+  rc = check_device_status(L, s);
+  if (rc) return rc;
+  if (L->timing && tm.n == 3) {  // the status check above already waited for the stream
+    cudaEventElapsedTime(&L->last.gate_up_ms, L->ev[0], L->ev[1]);
+    cudaEventElapsedTime(&L->last.down_ms, L->ev[1], L->ev[2]);
+    L->last.total_ms = L->last.gate_up_ms + L->last.down_ms;
+  }
+  return CSK_OK;
 }
 
 int csk_moe_ep_combine_dev(csk_moe_layer* L, const float* d_back, int64_t T, float* d_out,

@@ -161,9 +161,26 @@ class EpBench:
         self.torch.cuda.synchronize()
 
     def stage_times(self, steps):
-        z = {k: 0.0 for k in ("route_ms", "permute_ms", "gate_up_ms", "down_ms", "combine_ms", "total_ms")}
-        z.update(path="ep", gate_up_kernel="k_tile<gated>", launches=12)
-        return z
+        """Device time of the two expert contractions on this rank (events inside the library)
+        plus whole-stage times from torch events around dispatch / exchange / experts / combine."""
+        lay = self.backend.layer
+        lay.enable_timing(True)
+        acc = {"gate_up_ms": 0.0, "down_ms": 0.0}
+        n = max(3, min(steps, 10))
+        rows = 0
+        for _ in range(n):
+            rows = self.ep.forward(self.d_hidden, self.T, self.d_out)
+            self.torch.cuda.synchronize()
+            t = lay.timings()
+            acc["gate_up_ms"] += t["gate_up_ms"]
+            acc["down_ms"] += t["down_ms"]
+            path = t["path"]
+        lay.enable_timing(False)
+        out = {k: v / n for k, v in acc.items()}
+        out.update(route_ms=0.0, permute_ms=0.0, combine_ms=0.0, total_ms=out["gate_up_ms"] + out["down_ms"],
+                   path={1: "stream", 2: "tile"}.get(int(path), "?"), launches=14, rows_received=int(rows))
+        out["gate_up_kernel"] = "k_stream<gated>" if out["path"] == "stream" else "k_tile<gated>"
+        return out
 
     def time_e2e(self, steps, warmup):
         import time
