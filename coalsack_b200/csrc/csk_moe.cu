@@ -23,8 +23,9 @@ std::string g_create_error;
 struct csk_moe_layer {
   csk_moe_config cfg{};
   int E = 0, k = 0, H = 0, F = 0, e0 = 0, Eloc = 0;
-  MatLayout Lgu{}, Ld{};
-  size_t off_gu = 0, off_d = 0, off_bias = 0, off_meta = 0, expert_stride = 0;
+  MatLayout Lgu{}, Ld{};    // streaming kernel's layout
+  TileLayout Tgu{}, Td{};   // tensor-core kernel's layout (a second copy of the codes)
+  size_t off_gu = 0, off_d = 0, off_tgu = 0, off_td = 0, off_bias = 0, off_meta = 0, expert_stride = 0;
   uint8_t* d_weights = nullptr;
   uint8_t* d_resident = nullptr;  // [Eloc] flags on the device
   std::vector<uint8_t> resident;
@@ -204,8 +205,8 @@ int launch_experts(csk_moe_layer* L, int path, int tile_rows, const __half* x16,
                    const int* out_row_map, cudaStream_t s, StageTimer& tm) {
   if (path == CSK_PATH_TILE) {
     if (x16 != L->d_x16) return fail(L, CSK_ERR_INVALID, "the tile path reads the handle's own row buffer");
-    int rc = tile_launch(L->tile, L->d_weights, L->expert_stride, L->off_gu, L->off_d, L->off_bias,
-                         L->off_meta, L->Lgu, L->Ld, L->d_a16, L->lda, y, ldy, out_row_map, L->d_tiles,
+    int rc = tile_launch(L->tile, L->d_weights, L->expert_stride, L->off_tgu, L->off_td, L->off_bias,
+                         L->off_meta, L->Tgu, L->Td, L->d_a16, L->lda, y, ldy, out_row_map, L->d_tiles,
                          L->d_meta, L->cfg.has_bias, L->cfg.activation, L->F, L->sm_count, s,
                          [&]() { tm.mark(); });
     if (rc) return fail(L, rc, "tensor-core path: %s", L->tile.err.c_str());
@@ -358,9 +359,14 @@ int csk_moe_create(const csk_moe_config* cfg, csk_moe_layer** out) {
   L->Eloc = eloc;
   L->Lgu = make_layout(L->F, L->H, true);
   L->Ld = make_layout(L->H, L->F, false);
+  L->Tgu = make_tile_layout(L->F, L->H, true);
+  L->Td = make_tile_layout(L->H, L->F, false);
+  auto up256 = [](size_t v) { return (v + 255) / 256 * 256; };
   L->off_gu = 0;
-  L->off_d = (L->Lgu.bytes() + 255) / 256 * 256;
-  L->off_bias = L->off_d + (L->Ld.bytes() + 255) / 256 * 256;
+  L->off_d = up256(L->Lgu.bytes());
+  L->off_tgu = L->off_d + up256(L->Ld.bytes());
+  L->off_td = L->off_tgu + up256(L->Tgu.bytes());
+  L->off_bias = L->off_td + up256(L->Td.bytes());
   L->off_meta = L->off_bias + sizeof(float) * (2 * (size_t)L->F + L->H);  // int[4]: e_max of gate/up, of down
   L->expert_stride = (L->off_meta + 16 + 255) / 256 * 256;
   L->resident.assign(eloc, 0);
@@ -488,6 +494,8 @@ int csk_moe_load_expert_mxfp4(csk_moe_layer* L, int32_t expert_id, const uint8_t
   CSK_CUDA(L, cudaMemsetAsync(emeta, 0, 16, s));
   k_repack<<<grid_for(L->Lgu.bytes() / 4, 256, 4096), 256, 0, s>>>(s_gate, s_up, base + L->off_gu, L->Lgu, emeta);
   k_repack<<<grid_for(L->Ld.bytes() / 4, 256, 4096), 256, 0, s>>>(s_down, nullptr, base + L->off_d, L->Ld, emeta + 1);
+  k_repack_tile<<<grid_for(L->Tgu.bytes() / 4, 256, 4096), 256, 0, s>>>(s_gate, s_up, base + L->off_tgu, L->Tgu);
+  k_repack_tile<<<grid_for(L->Td.bytes() / 4, 256, 4096), 256, 0, s>>>(s_down, nullptr, base + L->off_td, L->Td);
   CSK_CUDA(L, cudaGetLastError());
   if (L->cfg.has_bias) {
     float* b = reinterpret_cast<float*>(base + L->off_bias);
@@ -506,13 +514,21 @@ int csk_moe_unpack_expert_mxfp4(csk_moe_layer* L, int32_t expert_id, int32_t whi
   if (check_layer(L)) return CSK_ERR_INVALID;
   if (expert_id < L->e0 || expert_id >= L->e0 + L->Eloc || !L->resident[expert_id - L->e0])
     return fail(L, CSK_ERR_MISSING, "expert %d is not loaded", expert_id);
-  if (which < 0 || which > 2 || !out) return fail(L, CSK_ERR_INVALID, "bad argument");
+  if (which < 0 || which > 5 || !out) return fail(L, CSK_ERR_INVALID, "bad argument");
   CSK_CUDA(L, cudaSetDevice(L->cfg.device));
   const uint8_t* base = L->d_weights + (size_t)(expert_id - L->e0) * L->expert_stride;
-  const MatLayout& lay = which == 2 ? L->Ld : L->Lgu;
-  const uint8_t* packed = base + (which == 2 ? L->off_d : L->off_gu);
-  k_unpack<<<grid_for((size_t)lay.N * (lay.K / 32), 128, 4096), 128, 0, L->stream>>>(
-      packed, L->d_stage, lay, which == 0 ? 1 : 0);
+  if (which < 3) {
+    const MatLayout& lay = which == 2 ? L->Ld : L->Lgu;
+    const uint8_t* packed = base + (which == 2 ? L->off_d : L->off_gu);
+    k_unpack<<<grid_for((size_t)lay.N * (lay.K / 32), 128, 4096), 128, 0, L->stream>>>(
+        packed, L->d_stage, lay, which == 0 ? 1 : 0);
+  } else {
+    const int w = which - 3;
+    const TileLayout& lay = w == 2 ? L->Td : L->Tgu;
+    const uint8_t* packed = base + (w == 2 ? L->off_td : L->off_tgu);
+    k_unpack_tile<<<grid_for((size_t)lay.N * (lay.K / 32), 128, 4096), 128, 0, L->stream>>>(
+        packed, L->d_stage, lay, w == 0 ? 1 : 0);
+  }
   CSK_CUDA(L, cudaGetLastError());
   CSK_CUDA(L, cudaMemcpyAsync(out, L->d_stage, L->stage_bytes, cudaMemcpyDeviceToHost, L->stream));
   CSK_CUDA(L, cudaStreamSynchronize(L->stream));

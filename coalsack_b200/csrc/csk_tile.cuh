@@ -1,31 +1,41 @@
 // Tensor-core grouped contraction over repacked MXFP4 weights (the prefill-side
-// kernel), written for sm_100a: TMA-staged operands, MXFP4 tiles dequantised in
-// shared memory to fp16, tcgen05.mma (kind::f16) with fp32 accumulators in
-// tensor memory, and a fused epilogue (bias + gated activation -> fp16 rows, or
-// bias -> fp32 rows).
+// kernel), written for sm_100a.
 //
-// One persistent CTA per SM walks work items (row tile of 128 grouped rows x
-// weight tile of BN rows).  Warp roles:
-//   warp 0      producer: per k-tile one TMA tensor load of the 128 x 64 fp16
-//               activation tile (128-byte swizzle) and one bulk copy of the
-//               packed weight tile (codes + E8M0 scales, one contiguous span)
-//   warp 1      issues the MMAs (one lane), owns the tensor-memory allocation
-//   warps 2-9   dequantise the packed tile into the K-major, 128-byte-swizzled
-//               fp16 operand tile (cvt.e2m1x2 -> half2, times 2^(e - e_max + 13))
-//   warps 10-13 epilogue: tcgen05.ld of the accumulator, scale by the matrix's
-//               power of two, bias, activation, store
-// Two accumulators of BN columns alternate, so the epilogue of one work item
-// overlaps the contraction of the next.
+// The contraction is computed transposed, D[weight row, token] = W · Xᵀ, so that
+// the WEIGHTS are the tensor-memory operand of tcgen05.mma and only the token
+// rows go through shared memory:
+//
+//   * a work item is (row tile of up to 192 grouped token rows of one expert) x
+//     (weight tile of 128 rows); the MMA's N is the item's own row count rounded
+//     up to 16, so ragged expert sizes cost no padded tensor work;
+//   * per 64-column k-step the producer warp issues one TMA tensor load of the
+//     192 x 64 fp16 token tile (128-byte swizzle) and one bulk copy of the packed
+//     weight tile (4352 bytes: codes + E8M0 scales, one contiguous span);
+//   * eight dequantiser warps turn the packed tile into fp16 (cvt.e2m1x2 ->
+//     half2, times 2^(e - e_max + 13)) and write it straight into tensor memory
+//     with tcgen05.st: thread = one weight row, 32 columns of one 32-element
+//     block = 16 registers.  The dequantised weights never touch shared memory;
+//   * one lane issues four tcgen05.mma (kind::f16, A from tensor memory, B = the
+//     token tile via a shared-memory descriptor) per k-step, fp32 accumulators
+//     in tensor memory, two accumulators so the epilogue of one item overlaps
+//     the contraction of the next;
+//   * four epilogue warps read the accumulator (lane = weight row, column =
+//     token), scale by the matrix's power of two, add the bias and either apply
+//     the gated activation (gate and up rows are interleaved on adjacent lanes
+//     and meet by one shuffle) and store fp16 rows, or store fp32 output rows.
+//
+// Tensor memory (512 columns): [0,384) two accumulators of 192 columns,
+// [384,512) a ring of four dequantised weight tiles of 32 columns (64 fp16).
 //
 // fp16 operands: every MXFP4 value is value(E2M1) * 2^(e-127).  Within a matrix
-// the tile is held as value * 2^(e - e_max + 13) (at most 6 * 2^13, exact in
-// fp16 while e_max - e <= 36; smaller blocks lose low bits below 2^-24 of that
-// range), and the accumulator is multiplied by 2^(e_max - 140) afterwards.
+// the tile holds value * 2^(e - e_max + 13) (at most 6 * 2^13; exact in fp16
+// while e_max - e <= 36, smaller blocks lose bits below 2^-24 of that range) and
+// the accumulator is multiplied by 2^(e_max - 140) afterwards.
 //
 // Every wait on an mbarrier is bounded: past a clock budget the CTA records
 // kDevErrWaitTimeout in the status word, all roles leave their loops, copies in
-// flight are waited for (bounded again), tensor memory is freed and the kernel
-// returns.
+// flight are waited for (bounded again), outstanding MMAs are drained, tensor
+// memory is freed and the kernel returns.
 #pragma once
 
 #include <cuda.h>
@@ -37,10 +47,115 @@
 
 namespace csk {
 
-constexpr int kTileM = 128;          // rows of a tensor-core row tile
+constexpr int kTileM = 192;          // token rows of a row tile (TMA box height, MMA N <= 192)
+constexpr int kTileW = 128;          // weight rows of a weight tile (tensor-memory lanes, MMA M)
 constexpr int kDequantWarps = 8;
 constexpr int kTileThreads = (2 + kDequantWarps + 4) * 32;  // producer, MMA, dequantisers, epilogue
-constexpr long long kWaitBudget = 2000000000LL;  // clock cycles (~1 s) before a wait gives up
+constexpr int kTileABytes = kTileM * 128;                   // token tile in shared memory
+constexpr int kTilePacked = 4352;                           // packed weight tile: 4096 codes + 256 scales
+constexpr int kTileRawBytes = kTileABytes + 5120;           // one shared-memory stage (1024-byte multiple)
+constexpr int kTileStages = 7;
+constexpr int kTileAStages = 4;                             // weight tiles resident in tensor memory
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kTmemABase = 2 * kTileM;                 // first column of the weight ring
+constexpr long long kWaitBudget = 2000000000LL;             // clock cycles (~1 s) before a wait gives up
+
+// Device layout of a matrix for this kernel: tiles of 128 rows x 64 columns,
+// stored [n_tile][k_tile], 4352 bytes each:
+//   bytes    0..4095  codes: [column block 0/1][row 0..127][16 bytes = 32 codes, nibble i of
+//                     word w = column 8w + i]
+//   bytes 4096..4351  E8M0 scales: [column block][row]
+// For the fused gate/up matrix tile row 2i is gate feature 64*n_tile + i and row
+// 2i+1 the up row of the same feature.
+struct TileLayout {
+  int N, K, paired, n_tiles, k_tiles;
+  __host__ __device__ int feats_per_tile() const { return paired ? kTileW / 2 : kTileW; }
+  __host__ __device__ size_t bytes() const { return (size_t)n_tiles * k_tiles * kTilePacked; }
+  __host__ __device__ int k_pad() const { return k_tiles * kTileK; }
+};
+inline TileLayout make_tile_layout(int N, int K, bool paired) {
+  TileLayout L{};
+  L.N = N;
+  L.K = K;
+  L.paired = paired ? 1 : 0;
+  L.n_tiles = ceil_div(N, L.feats_per_tile());
+  L.k_tiles = ceil_div(K, kTileK);
+  return L;
+}
+
+// Repack of 17-byte blocks into the layout above (src1 = up matrix when paired).
+__global__ void k_repack_tile(const uint8_t* __restrict__ src0, const uint8_t* __restrict__ src1,
+                              uint8_t* __restrict__ dst, TileLayout L) {
+  const size_t n_words = L.bytes() / 4;
+  constexpr int WPT = kTilePacked / 4;  // 1088 words per tile
+  for (size_t w = (size_t)blockIdx.x * blockDim.x + threadIdx.x; w < n_words; w += (size_t)gridDim.x * blockDim.x) {
+    const size_t tile = w / WPT;
+    const int wi = (int)(w % WPT);
+    const int kt = (int)(tile % L.k_tiles), nt = (int)(tile / L.k_tiles);
+    uint32_t out = 0;
+    auto source = [&](int trow, const uint8_t*& src, int& feat) {
+      if (L.paired) {
+        src = (trow & 1) ? src1 : src0;
+        feat = nt * (kTileW / 2) + (trow >> 1);
+      } else {
+        src = src0;
+        feat = nt * kTileW + trow;
+      }
+    };
+    if (wi < 1024) {
+      const int blk = wi >> 9, trow = (wi & 511) >> 2, q = wi & 3;
+      const int col = kt * kTileK + blk * 32 + q * 8;
+      const uint8_t* src;
+      int feat;
+      source(trow, src, feat);
+      if (feat < L.N && col < L.K) {
+        const uint8_t* b = src + ((size_t)feat * (L.K / 32) + col / 32) * 17;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int j = q * 8 + i;
+          const uint32_t code = j < 16 ? (b[1 + j] & 0xF) : (b[1 + j - 16] >> 4);
+          out |= code << (4 * i);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const int bi = (wi - 1024) * 4 + t;
+        const int blk = bi >> 7, trow = bi & 127;
+        const int col = kt * kTileK + blk * 32;
+        const uint8_t* src;
+        int feat;
+        source(trow, src, feat);
+        uint32_t e = 0;  // padding: zero codes under the smallest scale
+        if (feat < L.N && col < L.K) e = src[((size_t)feat * (L.K / 32) + col / 32) * 17];
+        out |= e << (8 * t);
+      }
+    }
+    reinterpret_cast<uint32_t*>(dst)[w] = out;
+  }
+}
+
+// Inverse of k_repack_tile for one source matrix (which_half: 0 = the matrix
+// itself or the gate rows, 1 = the up rows).  One thread per 17-byte block.
+__global__ void k_unpack_tile(const uint8_t* __restrict__ packed, uint8_t* __restrict__ out, TileLayout L,
+                              int which_half) {
+  const int kb = L.K / 32;
+  const size_t n_blocks = (size_t)L.N * kb;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_blocks; i += (size_t)gridDim.x * blockDim.x) {
+    const int feat = (int)(i / kb), blk_g = (int)(i % kb);
+    const int nt = feat / L.feats_per_tile();
+    const int trow = L.paired ? (feat % (kTileW / 2)) * 2 + which_half : feat % kTileW;
+    const int kt = blk_g / 2, blk = blk_g & 1;
+    const uint8_t* tile = packed + ((size_t)nt * L.k_tiles + kt) * kTilePacked;
+    uint8_t* o = out + i * 17;
+    o[0] = tile[4096 + blk * 128 + trow];
+    const uint32_t* words = reinterpret_cast<const uint32_t*>(tile + ((size_t)blk * 128 + trow) * 16);
+    uint32_t codes[32];
+    for (int q = 0; q < 4; ++q)
+      for (int t = 0; t < 8; ++t) codes[q * 8 + t] = (words[q] >> (4 * t)) & 0xF;
+    for (int j = 0; j < 16; ++j) o[1 + j] = (uint8_t)(codes[j] | (codes[j + 16] << 4));
+  }
+}
 
 struct TileState {
   bool available = false;
@@ -52,9 +167,7 @@ struct TileState {
 };
 
 // ---- small PTX wrappers -----------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
 }
@@ -81,7 +194,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   if (mbar_try(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
-    for (int i = 0; i < 64; ++i)
+    for (int i = 0; i < 32; ++i)
       if (mbar_try(bar, parity)) return true;
     if (*abort_flag) return false;
     if (clock64() - t0 > kWaitBudget) {
@@ -90,7 +203,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
   }
 }
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -119,13 +231,15 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
 }
 // kind::f16, fp16 x fp16 -> fp32, both operands K-major, M = 128, N = n.
 __device__ __forceinline__ uint32_t umma_idesc_f16(int n) {
-  return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+  return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kTileW >> 4) << 24);
 }
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+// D[tmem] (+)= A[tmem] * B[smem]^T
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc,
+                                            uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
-      "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
@@ -143,6 +257,14 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // fp16 bit pattern (in both halves) of 2^s for s in [-24, 15]; 0 below, 2^15 above.
 __device__ __forceinline__ uint32_t h2_pow2(int s) {
@@ -159,7 +281,7 @@ __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
 struct TileArgs {
   const uint8_t* weights;
   size_t expert_stride, mat_offset, bias_offset, meta_offset;
-  MatLayout L;
+  TileLayout L;
   __half* a_out;          // GATED: activated rows [rows, lda]
   int lda;
   float* y_out;           // !GATED: output rows [rows, ldy]
@@ -168,52 +290,44 @@ struct TileArgs {
   const RowTile* tiles;
   const int* n_tiles_ptr;
   int* meta;              // meta[3] = device status word
-  int has_bias, act, F, meta_slot, stages;
+  int has_bias, act, F, meta_slot;
 };
 
-inline size_t tile_stage_bytes(const MatLayout& L) {
-  const size_t packed = ((size_t)L.subs * kSubBytes + 1023) / 1024 * 1024;  // keeps every stage 1024-byte aligned
-  return (size_t)kTileM * 128 + (size_t)L.BN * 128 + packed;
-}
-inline int tile_stages(const MatLayout& L) {
-  const size_t budget = 227 * 1024 - 2048;
-  int s = (int)(budget / tile_stage_bytes(L));
-  return s > 6 ? 6 : s;
-}
+inline size_t tile_smem_bytes() { return (size_t)kTileStages * kTileRawBytes + 1024 + 512; }
 
 template <bool GATED>
 __global__ void __launch_bounds__(kTileThreads, 1)
 k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  const MatLayout& L = A.L;
-  const int BN = L.BN, KT = L.k_tiles, NS = A.stages;
-  const uint32_t tile_bytes = (uint32_t)L.tile_bytes();
-  const uint32_t a_bytes = kTileM * 128, b_bytes = (uint32_t)BN * 128;
-  const uint32_t packed_bytes = (tile_bytes + 1023) / 1024 * 1024;
-  const uint32_t stage_bytes = a_bytes + b_bytes + packed_bytes;
+  const TileLayout& L = A.L;
+  const int KT = L.k_tiles;
+  constexpr int NR = kTileStages, NA = kTileAStages;
 
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  const uint32_t smem_base = smem_u32(smem);
-  uint8_t* ctrl = smem + (size_t)NS * stage_bytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(ctrl);  // full_raw[6], full_b[6], empty[6], tmem_full[2], tmem_empty[2], drain
+  const uint32_t smem_base = smem_u32(smem);  // ring of [token tile | packed weight tile]
+  uint8_t* ctrl = smem + (size_t)NR * kTileRawBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ctrl);
   const uint32_t bar_base = smem_u32(bars);
-  auto bar_full_raw = [&](int s) { return bar_base + 8u * s; };
-  auto bar_full_b = [&](int s) { return bar_base + 8u * (6 + s); };
-  auto bar_empty = [&](int s) { return bar_base + 8u * (12 + s); };
-  auto bar_tmem_full = [&](int b) { return bar_base + 8u * (18 + b); };
-  auto bar_tmem_empty = [&](int b) { return bar_base + 8u * (20 + b); };
-  const uint32_t bar_drain = bar_base + 8u * 22;
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(ctrl + 8 * 24);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl + 8 * 24 + 8);
+  auto bar_full_raw = [&](int s) { return bar_base + 8u * s; };               // TMA landed
+  auto bar_empty_raw = [&](int s) { return bar_base + 8u * (8 + s); };        // MMAs of that k-step retired
+  auto bar_full_a = [&](int s) { return bar_base + 8u * (16 + s); };          // weight tile written to tensor memory
+  auto bar_empty_a = [&](int s) { return bar_base + 8u * (20 + s); };
+  auto bar_tmem_full = [&](int b) { return bar_base + 8u * (24 + b); };
+  auto bar_tmem_empty = [&](int b) { return bar_base + 8u * (26 + b); };
+  const uint32_t bar_drain = bar_base + 8u * 28;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(ctrl + 8 * 32);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl + 8 * 32 + 8);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t tmem_cols = BN * 2 <= 256 ? 256u : 512u;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < 6; ++s) {
+    for (int s = 0; s < 8; ++s) {
       mbar_init(bar_full_raw(s), 1);
-      mbar_init(bar_full_b(s), kDequantWarps);
-      mbar_init(bar_empty(s), 1);
+      mbar_init(bar_empty_raw(s), 1);
+    }
+    for (int s = 0; s < 4; ++s) {
+      mbar_init(bar_full_a(s), kDequantWarps);
+      mbar_init(bar_empty_a(s), 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar_tmem_full(b), 1);
@@ -225,7 +339,7 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)),
-                 "r"(tmem_cols)
+                 "r"(kTmemCols)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -247,18 +361,19 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
       for (long item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
         const RowTile rt = A.tiles[item / L.n_tiles];
         const int nt = (int)(item % L.n_tiles);
-        const uint8_t* wsrc = A.weights + (size_t)rt.expert * A.expert_stride + A.mat_offset + (size_t)nt * KT * tile_bytes;
+        const uint8_t* wsrc =
+            A.weights + (size_t)rt.expert * A.expert_stride + A.mat_offset + (size_t)nt * KT * kTilePacked;
         for (int kt = 0; kt < KT; ++kt) {
-          if (!mbar_wait(bar_empty(s), ph ^ 1, abort_flag)) {
+          if (!mbar_wait(bar_empty_raw(s), ph ^ 1, abort_flag)) {
             ok = false;
             break;
           }
-          const uint32_t st = smem_base + (uint32_t)s * stage_bytes;
-          mbar_expect_tx(bar_full_raw(s), a_bytes + tile_bytes);
+          const uint32_t st = smem_base + (uint32_t)s * kTileRawBytes;
+          mbar_expect_tx(bar_full_raw(s), kTileABytes + kTilePacked);
           tma_load_2d(st, &tmap, kt * kTileK, rt.row0, bar_full_raw(s));
-          bulk_load(st + a_bytes + b_bytes, wsrc + (size_t)kt * tile_bytes, tile_bytes, bar_full_raw(s));
+          bulk_load(st + kTileABytes, wsrc + (size_t)kt * kTilePacked, kTilePacked, bar_full_raw(s));
           ++issued;
-          if (++s == NS) {
+          if (++s == NR) {
             s = 0;
             ph ^= 1;
           }
@@ -268,9 +383,9 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
         // let the copies still in flight land before the CTA goes away
         int s2 = s;
         uint32_t ph2 = ph;
-        for (int i = 0; i < NS && i < issued; ++i) {
+        for (int i = 0; i < NR && i < issued; ++i) {
           if (--s2 < 0) {
-            s2 = NS - 1;
+            s2 = NR - 1;
             ph2 ^= 1;
           }
           const long long t0 = clock64();
@@ -282,12 +397,14 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
     if (lane == 0) {
-      const uint32_t idesc = umma_idesc_f16(BN);
-      int s = 0;
-      uint32_t ph = 0;
+      int s = 0, sa = 0;
+      uint32_t ph = 0, pha = 0;
       long it = 0;
       bool ok = true;
       for (long item = blockIdx.x; ok && item < n_items; item += gridDim.x, ++it) {
+        const RowTile rt = A.tiles[item / L.n_tiles];
+        const int n_mma = max(16, (rt.rows + 15) & ~15);
+        const uint32_t idesc = umma_idesc_f16(n_mma);
         const int buf = (int)(it & 1);
         const uint32_t use_ph = (uint32_t)((it >> 1) & 1);
         if (!mbar_wait(bar_tmem_empty(buf), use_ph ^ 1, abort_flag)) {
@@ -295,22 +412,27 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
           break;
         }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)buf * BN;
+        const uint32_t d_tmem = tmem_base + (uint32_t)buf * kTileM;
         for (int kt = 0; kt < KT; ++kt) {
-          if (!mbar_wait(bar_full_raw(s), ph, abort_flag) || !mbar_wait(bar_full_b(s), ph, abort_flag)) {
+          if (!mbar_wait(bar_full_raw(s), ph, abort_flag) || !mbar_wait(bar_full_a(sa), pha, abort_flag)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint32_t st = smem_base + (uint32_t)s * stage_bytes;
-          const uint64_t da = umma_desc_sw128(st), db = umma_desc_sw128(st + a_bytes);
+          const uint64_t db = umma_desc_sw128(smem_base + (uint32_t)s * kTileRawBytes);
+          const uint32_t a_tmem = tmem_base + kTmemABase + (uint32_t)sa * 32;
 #pragma unroll
           for (int k4 = 0; k4 < kTileK / 16; ++k4)
-            umma_f16(d_tmem, da + (uint64_t)(k4 * 2), db + (uint64_t)(k4 * 2), idesc, (kt | k4) ? 1u : 0u);
-          umma_commit(bar_empty(s));
-          if (++s == NS) {
+            umma_f16_ts(d_tmem, a_tmem + (uint32_t)k4 * 8, db + (uint64_t)(k4 * 2), idesc, (kt | k4) ? 1u : 0u);
+          umma_commit(bar_empty_raw(s));
+          umma_commit(bar_empty_a(sa));
+          if (++s == NR) {
             s = 0;
             ph ^= 1;
+          }
+          if (++sa == NA) {
+            sa = 0;
+            pha ^= 1;
           }
         }
         if (ok) umma_commit(bar_tmem_full(buf));
@@ -323,65 +445,60 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
     }
   } else if (warp < 2 + kDequantWarps) {
     // ------------------------------ dequantisers ------------------------------
-    const int dw = warp - 2;
-    const int g = lane >> 2, q = lane & 3;
-    int s = 0;
-    uint32_t ph = 0;
+    // thread = weight row (tensor-memory lane) x one 32-column block of the k-step
+    const int quarter = warp & 3;            // lanes 32*quarter .. +31 are this warp's
+    const int blk = (warp - 2) >> 2;         // which 32-column block
+    const int trow = quarter * 32 + lane;
+    int s = 0, sa = 0;
+    uint32_t ph = 0, pha = 0;
     bool ok = true;
     for (long item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
       const RowTile rt = A.tiles[item / L.n_tiles];
       const int* emeta = reinterpret_cast<const int*>(A.weights + (size_t)rt.expert * A.expert_stride + A.meta_offset);
       const int emax = emeta[A.meta_slot];
       for (int kt = 0; kt < KT; ++kt) {
-        if (!mbar_wait(bar_full_raw(s), ph, abort_flag)) {
+        if (!mbar_wait(bar_full_raw(s), ph, abort_flag) || !mbar_wait(bar_empty_a(sa), pha ^ 1, abort_flag)) {
           ok = false;
           break;
         }
-        uint8_t* st = smem + (size_t)s * stage_bytes;
-        uint8_t* btile = st + a_bytes;
-        const uint8_t* packed = st + a_bytes + b_bytes;
-        for (int sub = dw; sub < L.subs; sub += kDequantWarps) {
-          const uint4 c = *reinterpret_cast<const uint4*>(packed + sub * kSubBytes + lane * 16);
-          const uint32_t sc = *reinterpret_cast<const uint32_t*>(packed + sub * kSubBytes + kSubCodeBytes + g * 4);
-          // odd rows start with the other 32-column block: a quarter-warp's eight
-          // 16-byte stores then hit eight different bank groups
-          const int b_first = g & 1;
-#pragma unroll
-          for (int hi = 0; hi < 2; ++hi) {
-            const uint32_t w_b0 = hi ? c.z : c.x, w_b1 = hi ? c.w : c.y;  // row g + 8*hi, column blocks 0 / 1
-            const int row = sub * 16 + g + hi * 8;
-            uint8_t* rowp = btile + (row >> 3) * 1024 + (row & 7) * 128;
-#pragma unroll
-            for (int ord = 0; ord < 2; ++ord) {
-              const int b = b_first ^ ord;
-              const uint32_t w = b ? w_b1 : w_b0;
-              const int e = (int)((sc >> (8 * (hi * 2 + b))) & 0xFF);
-              const uint32_t sh2 = h2_pow2(e - emax + 13);
-              uint32_t h[4];
-              dequant_word(w, h);
-              uint4 o;
-              o.x = hmul2_u32(h[0], sh2);
-              o.y = hmul2_u32(h[1], sh2);
-              o.z = hmul2_u32(h[2], sh2);
-              o.w = hmul2_u32(h[3], sh2);
-              const int chunk = (b * 4 + q) ^ (row & 7);
-              *reinterpret_cast<uint4*>(rowp + chunk * 16) = o;
-            }
-          }
+        const uint8_t* packed = smem + (size_t)s * kTileRawBytes + kTileABytes;
+        const uint4 c = *reinterpret_cast<const uint4*>(packed + (blk * 128 + trow) * 16);
+        const int e = packed[4096 + blk * 128 + trow];
+        const uint32_t sh2 = h2_pow2(e - emax + 13);
+        uint32_t h[16];
+        {
+          uint32_t t[4];
+          dequant_word(c.x, t);
+          h[0] = t[0]; h[1] = t[1]; h[2] = t[2]; h[3] = t[3];
+          dequant_word(c.y, t);
+          h[4] = t[0]; h[5] = t[1]; h[6] = t[2]; h[7] = t[3];
+          dequant_word(c.z, t);
+          h[8] = t[0]; h[9] = t[1]; h[10] = t[2]; h[11] = t[3];
+          dequant_word(c.w, t);
+          h[12] = t[0]; h[13] = t[1]; h[14] = t[2]; h[15] = t[3];
         }
-        fence_proxy_async();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) h[i] = hmul2_u32(h[i], sh2);
+        tc_fence_after();
+        tmem_st16(tmem_base + ((uint32_t)(quarter * 32) << 16) + kTmemABase + (uint32_t)sa * 32 + (uint32_t)blk * 16, h);
+        tmem_st_wait();
+        tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_full_b(s));
-        if (++s == NS) {
+        if (lane == 0) mbar_arrive(bar_full_a(sa));
+        if (++s == NR) {
           s = 0;
           ph ^= 1;
+        }
+        if (++sa == NA) {
+          sa = 0;
+          pha ^= 1;
         }
       }
     }
   } else {
     // ------------------------------ epilogue ------------------------------
     const int quarter = warp & 3;  // tensor-memory lanes 32*quarter .. +31 belong to this warp
-    const int m = quarter * 32 + lane;
+    const int trow = quarter * 32 + lane;
     long it = 0;
     bool ok = true;
     for (long item = blockIdx.x; ok && item < n_items; item += gridDim.x, ++it) {
@@ -398,71 +515,47 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
         break;
       }
       tc_fence_after();
-      const uint32_t t_acc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * BN;
-      const bool row_ok = m < rt.rows;
+      const uint32_t t_acc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * kTileM;
       if (GATED) {
-        const int half = BN / 2;
-        __half* orow = A.a_out + (size_t)(rt.row0 + m) * A.lda;
-        for (int c0 = 0; c0 < half; c0 += 32) {
-          uint32_t rg[32], ru[32];
-          tmem_ld32(t_acc + c0, rg);
-          tmem_ld32(t_acc + half + c0, ru);
-          tmem_ld_wait();
-          const int n0 = nt * half + c0;
-          if (row_ok) {
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              uint32_t packed[4];
-#pragma unroll
-              for (int p = 0; p < 4; ++p) {
-                float a2[2];
-#pragma unroll
-                for (int u = 0; u < 2; ++u) {
-                  const int i = v * 8 + p * 2 + u, n = n0 + i;
-                  float gate = __uint_as_float(rg[i]) * oscale, up = __uint_as_float(ru[i]) * oscale;
-                  if (A.has_bias && n < L.N) {
-                    up += bias[n];
-                    gate += bias[A.F + n];
-                  }
-                  a2[u] = gated_act(gate, up, A.act);
-                }
-                __half2 h2 = __floats2half2_rn(a2[0], a2[1]);
-                packed[p] = *reinterpret_cast<uint32_t*>(&h2);
-              }
-              const int n = n0 + v * 8;
-              if (n + 8 <= L.N) {
-                *reinterpret_cast<uint4*>(orow + n) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-              } else {
-                for (int i = 0; i < 8 && n + i < L.N; ++i)
-                  orow[n + i] = reinterpret_cast<const __half*>(packed)[i];
-              }
-            }
-          }
-        }
-      } else {
-        const int orow_i = A.out_row_map ? (row_ok ? A.out_row_map[rt.row0 + m] : 0) : rt.row0 + m;
-        float* orow = A.y_out + (size_t)orow_i * A.ldy;
-        for (int c0 = 0; c0 < BN; c0 += 32) {
+        // even lane = gate row, odd lane = up row of feature `feat`
+        const int feat = nt * (kTileW / 2) + (trow >> 1);
+        const bool feat_ok = feat < L.N;
+        const bool odd = trow & 1;
+        float my_bias = 0.f;
+        if (A.has_bias && feat_ok) my_bias = odd ? bias[feat] : bias[A.F + feat];
+        for (int c0 = 0; c0 < rt.rows; c0 += 32) {
           uint32_t r[32];
           tmem_ld32(t_acc + c0, r);
           tmem_ld_wait();
-          const int n0 = nt * BN + c0;
-          if (row_ok) {
 #pragma unroll
-            for (int v = 0; v < 8; ++v) {
-              float o[4];
+          for (int jj = 0; jj < 16; ++jj) {
+            // the pair exchanges both tokens; the even lane finishes token 2jj, the odd lane token 2jj+1
+            const float v0 = __uint_as_float(r[2 * jj]) * oscale + my_bias;
+            const float v1 = __uint_as_float(r[2 * jj + 1]) * oscale + my_bias;
+            const float p0 = __shfl_xor_sync(0xffffffffu, v0, 1);
+            const float p1 = __shfl_xor_sync(0xffffffffu, v1, 1);
+            const float gate = odd ? p1 : v0, up = odd ? v1 : p0;
+            const int tok = c0 + 2 * jj + (odd ? 1 : 0);
+            if (feat_ok && tok < rt.rows)
+              A.a_out[(size_t)(rt.row0 + tok) * A.lda + feat] = __float2half_rn(gated_act(gate, up, A.act));
+          }
+        }
+      } else {
+        const int n = nt * kTileW + trow;
+        const bool n_ok = n < L.N;
+        const float my_bias = (A.has_bias && n_ok) ? bias[2 * A.F + n] : 0.f;
+        for (int c0 = 0; c0 < rt.rows; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld32(t_acc + c0, r);
+          tmem_ld_wait();
+          // lane j fetches the output row of token c0 + j once; every lane then reads it by shuffle
+          int my_orow = rt.row0 + c0 + lane;
+          if (A.out_row_map) my_orow = (c0 + lane < rt.rows) ? A.out_row_map[rt.row0 + c0 + lane] : 0;
 #pragma unroll
-              for (int u = 0; u < 4; ++u) {
-                const int n = n0 + v * 4 + u;
-                o[u] = __uint_as_float(r[v * 4 + u]) * oscale + ((A.has_bias && n < L.N) ? bias[2 * A.F + n] : 0.f);
-              }
-              const int n = n0 + v * 4;
-              if (n + 4 <= L.N) {
-                *reinterpret_cast<float4*>(orow + n) = make_float4(o[0], o[1], o[2], o[3]);
-              } else {
-                for (int i = 0; i < 4 && n + i < L.N; ++i) orow[n + i] = o[i];
-              }
-            }
+          for (int j = 0; j < 32; ++j) {
+            const int orow = __shfl_sync(0xffffffffu, my_orow, j);
+            if (n_ok && c0 + j < rt.rows)
+              A.y_out[(size_t)orow * A.ldy + n] = __uint_as_float(r[j]) * oscale + my_bias;
           }
         }
       }
@@ -478,7 +571,7 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
   if (threadIdx.x == 0 && *abort_flag) atomicOr(&A.meta[3], kDevErrWaitTimeout);
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
   }
 }
 
@@ -499,7 +592,7 @@ inline int tile_init(TileState& st, int device) {
   }
   st.encode_fn = fn;
   for (auto* f : {(const void*)k_tile<true>, (const void*)k_tile<false>}) {
-    if (cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) {
+    if (cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tile_smem_bytes()) != cudaSuccess) {
       st.err = std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(cudaGetLastError());
       return CSK_ERR_CUDA;
     }
@@ -509,7 +602,7 @@ inline int tile_init(TileState& st, int device) {
 }
 inline void tile_destroy(TileState&) {}
 
-// [rows, ld] fp16 row-major, boxes of 128 rows x 64 columns, 128-byte swizzle.
+// [rows, ld] fp16 row-major, boxes of kTileM rows x 64 columns, 128-byte swizzle.
 inline int tile_make_map(TileState& st, CUtensorMap* map, const __half* base, size_t rows, int ld) {
   const cuuint64_t dims[2] = {(cuuint64_t)ld, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(__half)};
@@ -536,9 +629,9 @@ inline int tile_set_buffers(TileState& st, const __half* x16, int ldx, const __h
 }
 
 inline int tile_launch(TileState& st, const uint8_t* weights, size_t expert_stride, size_t off_gu, size_t off_d,
-                       size_t off_bias, size_t off_meta, const MatLayout& Lgu, const MatLayout& Ld, __half* a16, int lda,
-                       float* y, int ldy, const int* out_row_map, const RowTile* tiles, int* meta, int has_bias,
-                       int act, int F, int sm_count, cudaStream_t s, const std::function<void()>& mark) {
+                       size_t off_bias, size_t off_meta, const TileLayout& Lgu, const TileLayout& Ld, __half* a16,
+                       int lda, float* y, int ldy, const int* out_row_map, const RowTile* tiles, int* meta,
+                       int has_bias, int act, int F, int sm_count, cudaStream_t s, const std::function<void()>& mark) {
   if (!st.available || !st.maps_ready) {
     st.err = "tensor-core path is not initialised";
     return CSK_ERR_INVALID;
@@ -554,14 +647,13 @@ inline int tile_launch(TileState& st, const uint8_t* weights, size_t expert_stri
   a.has_bias = has_bias;
   a.act = act;
   a.F = F;
+  const size_t smem = tile_smem_bytes();
   // gate/up + activation
   a.mat_offset = off_gu;
   a.L = Lgu;
   a.a_out = a16;
   a.lda = lda;
   a.meta_slot = 0;
-  a.stages = tile_stages(Lgu);
-  size_t smem = (size_t)a.stages * tile_stage_bytes(Lgu) + 1024 + 256;
   k_tile<true><<<sm_count, kTileThreads, smem, s>>>(st.tmap_x, a);
   mark();
   // down
@@ -571,8 +663,6 @@ inline int tile_launch(TileState& st, const uint8_t* weights, size_t expert_stri
   a.ldy = ldy;
   a.out_row_map = out_row_map;
   a.meta_slot = 1;
-  a.stages = tile_stages(Ld);
-  smem = (size_t)a.stages * tile_stage_bytes(Ld) + 1024 + 256;
   k_tile<false><<<sm_count, kTileThreads, smem, s>>>(st.tmap_a, a);
   mark();
   cudaError_t e = cudaGetLastError();

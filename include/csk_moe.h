@@ -94,9 +94,10 @@ int csk_moe_set_router(csk_moe_layer* layer, const float* gate_w, const float* g
 int csk_moe_load_expert_mxfp4(csk_moe_layer* layer, int32_t expert_id, const uint8_t* w_up,
                               const uint8_t* w_gate, const uint8_t* w_down, const float* b_up,
                               const float* b_gate, const float* b_down);
-/* Inverse of the repack: writes matrix `which` (0 up, 1 gate, 2 down) of a
- * resident expert back as 17-byte blocks (host).  The repack is lossless iff
- * this returns the loaded bytes. */
+/* Inverse of the repack: writes matrix `which` (0 up, 1 gate, 2 down from the
+ * streaming kernel's layout; 3 up, 4 gate, 5 down from the tensor-core
+ * kernel's layout) of a resident expert back as 17-byte blocks (host).  The
+ * repack is lossless iff this returns the loaded bytes. */
 int csk_moe_unpack_expert_mxfp4(csk_moe_layer* layer, int32_t expert_id, int32_t which,
                                 uint8_t* out_blocks);
 /* 1 if the expert's weights are resident on the device, 0 if not. */

@@ -36,7 +36,8 @@ def test_repack_is_lossless(gpu_lib, tag):
     lay = make_layer(sh, Wg, rb, ex)
     for e in range(sh.num_experts):
         for which, name in enumerate(("w_up", "w_gate", "w_down")):
-            assert np.array_equal(lay.unpack_expert(e, which), ex[name][e]), (e, name)
+            assert np.array_equal(lay.unpack_expert(e, which), ex[name][e]), (e, name)          # streaming layout
+            assert np.array_equal(lay.unpack_expert(e, which + 3), ex[name][e]), (e, name, "T")  # tensor-core layout
     lay.close()
 
 
@@ -48,6 +49,7 @@ def test_repack_is_lossless_full_size(gpu_lib):
     for e in range(2):
         for which, name in enumerate(("w_up", "w_gate", "w_down")):
             assert np.array_equal(lay.unpack_expert(e, which), ex[name][e])
+            assert np.array_equal(lay.unpack_expert(e, which + 3), ex[name][e])
     lay.close()
 
 
