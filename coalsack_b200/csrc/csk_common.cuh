@@ -115,6 +115,19 @@ __device__ __forceinline__ void dequant_word(uint32_t w, uint32_t (&h)[4]) {
       : "r"(w));
 }
 
+// The same activations with the hardware's approximate exp2 / reciprocal (relative
+// error around 2^-21, far below the fp16 rounding of the stored result).  Used in
+// the tensor-core kernel's epilogue, which sits on the critical path.
+__device__ __forceinline__ float gated_act_fast(float gate, float up, int act) {
+  if (act == CSK_ACT_MODIFIED_SWIGLU) {
+    const float lim = 7.0f, alpha = 1.702f;
+    const float g = fminf(gate, lim);
+    const float u = fminf(fmaxf(up, -lim), lim);
+    return g * __frcp_rn(1.0f + __expf(-alpha * g)) * (u + 1.0f);
+  }
+  return gate * __frcp_rn(1.0f + __expf(-gate)) * up;
+}
+
 // Gated activations of the reference (expert_mlp_node.h:657-658, 699-707).
 __device__ __forceinline__ float gated_act(float gate, float up, int act) {
   if (act == CSK_ACT_MODIFIED_SWIGLU) {

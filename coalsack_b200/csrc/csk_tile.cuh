@@ -6,26 +6,27 @@
 // rows go through shared memory:
 //
 //   * a work item is (row tile of up to 192 grouped token rows of one expert) x
-//     (weight tile of 128 rows); the MMA's N is the item's own row count rounded
-//     up to 16, so ragged expert sizes cost no padded tensor work;
+//     (weight tile of 256 rows, as two halves of 128); the MMA's N is the item's
+//     own row count rounded up to 16, so ragged expert sizes cost no padded
+//     tensor work, and every token tile fetched from L2 feeds 256 weight rows;
 //   * per 64-column k-step the producer warp issues one TMA tensor load of the
 //     192 x 64 fp16 token tile (128-byte swizzle) and one bulk copy of the packed
-//     weight tile (4352 bytes: codes + E8M0 scales, one contiguous span);
+//     weight tile (2 x 4352 bytes: codes + E8M0 scales, one contiguous span);
 //   * eight dequantiser warps turn the packed tile into fp16 (cvt.e2m1x2 ->
 //     half2, times 2^(e - e_max + 13)) and write it straight into tensor memory
 //     with tcgen05.st: thread = one weight row, 32 columns of one 32-element
 //     block = 16 registers.  The dequantised weights never touch shared memory;
-//   * one lane issues four tcgen05.mma (kind::f16, A from tensor memory, B = the
-//     token tile via a shared-memory descriptor) per k-step, fp32 accumulators
-//     in tensor memory, two accumulators so the epilogue of one item overlaps
-//     the contraction of the next;
-//   * four epilogue warps read the accumulator (lane = weight row, column =
+//   * one lane issues eight tcgen05.mma (kind::f16, A from tensor memory, B = the
+//     token tile via a shared-memory descriptor) per k-step, four per half, into
+//     two fp32 accumulators in tensor memory;
+//   * sixteen epilogue warps (per half: four lane quarters x two column ranges) read the accumulator (lane = weight row, column =
 //     token), scale by the matrix's power of two, add the bias and either apply
 //     the gated activation (gate and up rows are interleaved on adjacent lanes
 //     and meet by one shuffle) and store fp16 rows, or store fp32 output rows.
 //
-// Tensor memory (512 columns): [0,384) two accumulators of 192 columns,
-// [384,512) a ring of four dequantised weight tiles of 32 columns (64 fp16).
+// Tensor memory (512 columns): [0,384) the accumulators of the two halves, 192
+// columns each; [384,512) a ring of two dequantised weight tiles, 2 x 32 columns
+// (2 x 64 fp16 per row) each.
 //
 // fp16 operands: every MXFP4 value is value(E2M1) * 2^(e-127).  Within a matrix
 // the tile holds value * 2^(e - e_max + 13) (at most 6 * 2^13; exact in fp16
@@ -48,28 +49,33 @@
 namespace csk {
 
 constexpr int kTileM = 192;          // token rows of a row tile (TMA box height, MMA N <= 192)
-constexpr int kTileW = 128;          // weight rows of a weight tile (tensor-memory lanes, MMA M)
+constexpr int kTileW = 128;          // weight rows of half a weight tile (tensor-memory lanes, MMA M)
 constexpr int kDequantWarps = 8;
-constexpr int kTileThreads = (2 + kDequantWarps + 4) * 32;  // producer, MMA, dequantisers, epilogue
+constexpr int kEpilogueWarps = 16;
+constexpr int kTileThreads = (2 + kDequantWarps + kEpilogueWarps) * 32;  // producer, MMA, dequantisers, epilogue
 constexpr int kTileABytes = kTileM * 128;                   // token tile in shared memory
-constexpr int kTilePacked = 4352;                           // packed weight tile: 4096 codes + 256 scales
-constexpr int kTileRawBytes = kTileABytes + 5120;           // one shared-memory stage (1024-byte multiple)
-constexpr int kTileStages = 7;
-constexpr int kTileAStages = 4;                             // weight tiles resident in tensor memory
+constexpr int kHalfPacked = 4352;                           // packed half tile: 4096 codes + 256 scales
+constexpr int kTilePacked = 2 * kHalfPacked;                // packed weight tile (two halves)
+constexpr int kTileRawBytes = kTileABytes + 9216;           // one shared-memory stage (1024-byte multiple)
+constexpr int kTileStages = 6;
+constexpr int kTileAStages = 2;                             // weight tiles resident in tensor memory
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kTmemABase = 2 * kTileM;                 // first column of the weight ring
 constexpr long long kWaitBudget = 2000000000LL;             // clock cycles (~1 s) before a wait gives up
 
-// Device layout of a matrix for this kernel: tiles of 128 rows x 64 columns,
-// stored [n_tile][k_tile], 4352 bytes each:
+// Device layout of a matrix for this kernel: tiles of 256 rows x 64 columns,
+// stored [n_tile][k_tile]; a tile is two halves of 128 rows, 4352 bytes each:
 //   bytes    0..4095  codes: [column block 0/1][row 0..127][16 bytes = 32 codes, nibble i of
 //                     word w = column 8w + i]
 //   bytes 4096..4351  E8M0 scales: [column block][row]
-// For the fused gate/up matrix tile row 2i is gate feature 64*n_tile + i and row
-// 2i+1 the up row of the same feature.
+// For the fused gate/up matrix row 2i of half h is gate feature 128*n_tile + 64*h + i
+// and row 2i+1 the up row of the same feature.
 struct TileLayout {
   int N, K, paired, n_tiles, k_tiles;
-  __host__ __device__ int feats_per_tile() const { return paired ? kTileW / 2 : kTileW; }
+  __host__ __device__ int feats_per_half() const { return paired ? kTileW / 2 : kTileW; }
+  __host__ __device__ int feats_per_tile() const { return 2 * feats_per_half(); }
+  // halves of tile nt that hold any real row (the last tile may need only one)
+  __host__ __device__ int halves(int nt) const { return nt * feats_per_tile() + feats_per_half() < N ? 2 : 1; }
   __host__ __device__ size_t bytes() const { return (size_t)n_tiles * k_tiles * kTilePacked; }
   __host__ __device__ int k_pad() const { return k_tiles * kTileK; }
 };
@@ -87,19 +93,21 @@ inline TileLayout make_tile_layout(int N, int K, bool paired) {
 __global__ void k_repack_tile(const uint8_t* __restrict__ src0, const uint8_t* __restrict__ src1,
                               uint8_t* __restrict__ dst, TileLayout L) {
   const size_t n_words = L.bytes() / 4;
-  constexpr int WPT = kTilePacked / 4;  // 1088 words per tile
+  constexpr int WPT = kHalfPacked / 4;  // 1088 words per half tile
   for (size_t w = (size_t)blockIdx.x * blockDim.x + threadIdx.x; w < n_words; w += (size_t)gridDim.x * blockDim.x) {
-    const size_t tile = w / WPT;
+    const size_t half_idx = w / WPT;
     const int wi = (int)(w % WPT);
+    const int half = (int)(half_idx & 1);
+    const size_t tile = half_idx >> 1;
     const int kt = (int)(tile % L.k_tiles), nt = (int)(tile / L.k_tiles);
     uint32_t out = 0;
     auto source = [&](int trow, const uint8_t*& src, int& feat) {
       if (L.paired) {
         src = (trow & 1) ? src1 : src0;
-        feat = nt * (kTileW / 2) + (trow >> 1);
+        feat = nt * kTileW + half * (kTileW / 2) + (trow >> 1);
       } else {
         src = src0;
-        feat = nt * kTileW + trow;
+        feat = nt * 2 * kTileW + half * kTileW + trow;
       }
     };
     if (wi < 1024) {
@@ -144,9 +152,10 @@ __global__ void k_unpack_tile(const uint8_t* __restrict__ packed, uint8_t* __res
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_blocks; i += (size_t)gridDim.x * blockDim.x) {
     const int feat = (int)(i / kb), blk_g = (int)(i % kb);
     const int nt = feat / L.feats_per_tile();
+    const int half = (feat % L.feats_per_tile()) / L.feats_per_half();
     const int trow = L.paired ? (feat % (kTileW / 2)) * 2 + which_half : feat % kTileW;
     const int kt = blk_g / 2, blk = blk_g & 1;
-    const uint8_t* tile = packed + ((size_t)nt * L.k_tiles + kt) * kTilePacked;
+    const uint8_t* tile = packed + ((size_t)nt * L.k_tiles + kt) * kTilePacked + (size_t)half * kHalfPacked;
     uint8_t* o = out + i * 17;
     o[0] = tile[4096 + blk * 128 + trow];
     const uint32_t* words = reinterpret_cast<const uint32_t*>(tile + ((size_t)blk * 128 + trow) * 16);
@@ -312,8 +321,8 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
   auto bar_empty_raw = [&](int s) { return bar_base + 8u * (8 + s); };        // MMAs of that k-step retired
   auto bar_full_a = [&](int s) { return bar_base + 8u * (16 + s); };          // weight tile written to tensor memory
   auto bar_empty_a = [&](int s) { return bar_base + 8u * (20 + s); };
-  auto bar_tmem_full = [&](int b) { return bar_base + 8u * (24 + b); };
-  auto bar_tmem_empty = [&](int b) { return bar_base + 8u * (26 + b); };
+  const uint32_t bar_tmem_full = bar_base + 8u * 24;    // both accumulators complete
+  const uint32_t bar_tmem_empty = bar_base + 8u * 26;   // all epilogue warps done reading them
   const uint32_t bar_drain = bar_base + 8u * 28;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(ctrl + 8 * 32);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl + 8 * 32 + 8);
@@ -329,10 +338,8 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
       mbar_init(bar_full_a(s), kDequantWarps);
       mbar_init(bar_empty_a(s), 1);
     }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(bar_tmem_full(b), 1);
-      mbar_init(bar_tmem_empty(b), 4);
-    }
+    mbar_init(bar_tmem_full, 1);
+    mbar_init(bar_tmem_empty, kEpilogueWarps);
     mbar_init(bar_drain, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -363,15 +370,16 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
         const int nt = (int)(item % L.n_tiles);
         const uint8_t* wsrc =
             A.weights + (size_t)rt.expert * A.expert_stride + A.mat_offset + (size_t)nt * KT * kTilePacked;
+        const uint32_t w_bytes = (uint32_t)L.halves(nt) * kHalfPacked;
         for (int kt = 0; kt < KT; ++kt) {
           if (!mbar_wait(bar_empty_raw(s), ph ^ 1, abort_flag)) {
             ok = false;
             break;
           }
           const uint32_t st = smem_base + (uint32_t)s * kTileRawBytes;
-          mbar_expect_tx(bar_full_raw(s), kTileABytes + kTilePacked);
+          mbar_expect_tx(bar_full_raw(s), kTileABytes + w_bytes);
           tma_load_2d(st, &tmap, kt * kTileK, rt.row0, bar_full_raw(s));
-          bulk_load(st + kTileABytes, wsrc + (size_t)kt * kTilePacked, kTilePacked, bar_full_raw(s));
+          bulk_load(st + kTileABytes, wsrc + (size_t)kt * kTilePacked, w_bytes, bar_full_raw(s));
           ++issued;
           if (++s == NR) {
             s = 0;
@@ -403,16 +411,14 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
       bool ok = true;
       for (long item = blockIdx.x; ok && item < n_items; item += gridDim.x, ++it) {
         const RowTile rt = A.tiles[item / L.n_tiles];
+        const int halves = L.halves((int)(item % L.n_tiles));
         const int n_mma = max(16, (rt.rows + 15) & ~15);
         const uint32_t idesc = umma_idesc_f16(n_mma);
-        const int buf = (int)(it & 1);
-        const uint32_t use_ph = (uint32_t)((it >> 1) & 1);
-        if (!mbar_wait(bar_tmem_empty(buf), use_ph ^ 1, abort_flag)) {
+        if (!mbar_wait(bar_tmem_empty, (uint32_t)(it & 1) ^ 1, abort_flag)) {
           ok = false;
           break;
         }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)buf * kTileM;
         for (int kt = 0; kt < KT; ++kt) {
           if (!mbar_wait(bar_full_raw(s), ph, abort_flag) || !mbar_wait(bar_full_a(sa), pha, abort_flag)) {
             ok = false;
@@ -420,10 +426,13 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
           }
           tc_fence_after();
           const uint64_t db = umma_desc_sw128(smem_base + (uint32_t)s * kTileRawBytes);
-          const uint32_t a_tmem = tmem_base + kTmemABase + (uint32_t)sa * 32;
+          for (int h = 0; h < halves; ++h) {
+            const uint32_t d_tmem = tmem_base + (uint32_t)h * kTileM;
+            const uint32_t a_tmem = tmem_base + kTmemABase + (uint32_t)sa * 64 + (uint32_t)h * 32;
 #pragma unroll
-          for (int k4 = 0; k4 < kTileK / 16; ++k4)
-            umma_f16_ts(d_tmem, a_tmem + (uint32_t)k4 * 8, db + (uint64_t)(k4 * 2), idesc, (kt | k4) ? 1u : 0u);
+            for (int k4 = 0; k4 < kTileK / 16; ++k4)
+              umma_f16_ts(d_tmem, a_tmem + (uint32_t)k4 * 8, db + (uint64_t)(k4 * 2), idesc, (kt | k4) ? 1u : 0u);
+          }
           umma_commit(bar_empty_raw(s));
           umma_commit(bar_empty_a(sa));
           if (++s == NR) {
@@ -435,7 +444,7 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
             pha ^= 1;
           }
         }
-        if (ok) umma_commit(bar_tmem_full(buf));
+        if (ok) umma_commit(bar_tmem_full);
       }
       // everything issued has to retire before tensor memory is freed
       umma_commit(bar_drain);
@@ -449,42 +458,61 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
     const int quarter = warp & 3;            // lanes 32*quarter .. +31 are this warp's
     const int blk = (warp - 2) >> 2;         // which 32-column block
     const int trow = quarter * 32 + lane;
-    int s = 0, sa = 0;
+    int s = 0, sa = 0, pending = -1;
     uint32_t ph = 0, pha = 0;
     bool ok = true;
     for (long item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
       const RowTile rt = A.tiles[item / L.n_tiles];
+      const int halves = L.halves((int)(item % L.n_tiles));
       const int* emeta = reinterpret_cast<const int*>(A.weights + (size_t)rt.expert * A.expert_stride + A.meta_offset);
       const int emax = emeta[A.meta_slot];
       for (int kt = 0; kt < KT; ++kt) {
-        if (!mbar_wait(bar_full_raw(s), ph, abort_flag) || !mbar_wait(bar_empty_a(sa), pha ^ 1, abort_flag)) {
+        if (!mbar_wait(bar_full_raw(s), ph, abort_flag)) {
           ok = false;
           break;
         }
-        const uint8_t* packed = smem + (size_t)s * kTileRawBytes + kTileABytes;
-        const uint4 c = *reinterpret_cast<const uint4*>(packed + (blk * 128 + trow) * 16);
-        const int e = packed[4096 + blk * 128 + trow];
-        const uint32_t sh2 = h2_pow2(e - emax + 13);
-        uint32_t h[16];
-        {
-          uint32_t t[4];
-          dequant_word(c.x, t);
-          h[0] = t[0]; h[1] = t[1]; h[2] = t[2]; h[3] = t[3];
-          dequant_word(c.y, t);
-          h[4] = t[0]; h[5] = t[1]; h[6] = t[2]; h[7] = t[3];
-          dequant_word(c.z, t);
-          h[8] = t[0]; h[9] = t[1]; h[10] = t[2]; h[11] = t[3];
-          dequant_word(c.w, t);
-          h[12] = t[0]; h[13] = t[1]; h[14] = t[2]; h[15] = t[3];
-        }
+        // convert first (shared memory -> registers), so that the tensor-memory store of
+        // the previous k-step retires while this one is being prepared
+        uint32_t h[2][16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) h[i] = hmul2_u32(h[i], sh2);
+        for (int hf = 0; hf < 2; ++hf) {
+          if (hf < halves) {
+            const uint8_t* packed = smem + (size_t)s * kTileRawBytes + kTileABytes + hf * kHalfPacked;
+            const uint4 c = *reinterpret_cast<const uint4*>(packed + (blk * 128 + trow) * 16);
+            const int e = packed[4096 + blk * 128 + trow];
+            const uint32_t sh2 = h2_pow2(e - emax + 13);
+            uint32_t t[4];
+            dequant_word(c.x, t);
+            h[hf][0] = t[0]; h[hf][1] = t[1]; h[hf][2] = t[2]; h[hf][3] = t[3];
+            dequant_word(c.y, t);
+            h[hf][4] = t[0]; h[hf][5] = t[1]; h[hf][6] = t[2]; h[hf][7] = t[3];
+            dequant_word(c.z, t);
+            h[hf][8] = t[0]; h[hf][9] = t[1]; h[hf][10] = t[2]; h[hf][11] = t[3];
+            dequant_word(c.w, t);
+            h[hf][12] = t[0]; h[hf][13] = t[1]; h[hf][14] = t[2]; h[hf][15] = t[3];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) h[hf][i] = hmul2_u32(h[hf][i], sh2);
+          }
+        }
+        if (pending >= 0) {  // publish the tile stored in the previous iteration
+          tmem_st_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_full_a(pending));
+          pending = -1;
+        }
+        if (!mbar_wait(bar_empty_a(sa), pha ^ 1, abort_flag)) {
+          ok = false;
+          break;
+        }
         tc_fence_after();
-        tmem_st16(tmem_base + ((uint32_t)(quarter * 32) << 16) + kTmemABase + (uint32_t)sa * 32 + (uint32_t)blk * 16, h);
-        tmem_st_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_full_a(sa));
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf)
+          if (hf < halves)
+            tmem_st16(tmem_base + ((uint32_t)(quarter * 32) << 16) + kTmemABase + (uint32_t)sa * 64 + (uint32_t)hf * 32 +
+                          (uint32_t)blk * 16,
+                      h[hf]);
+        pending = sa;
         if (++s == NR) {
           s = 0;
           ph ^= 1;
@@ -495,35 +523,45 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
         }
       }
     }
+    if (pending >= 0) {
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_full_a(pending));
+    }
   } else {
     // ------------------------------ epilogue ------------------------------
     const int quarter = warp & 3;  // tensor-memory lanes 32*quarter .. +31 belong to this warp
+    const int half = ((warp - 2 - kDequantWarps) >> 2) & 1;  // which half of the weight tile this warp finishes
+    const int c_begin = ((warp - 2 - kDequantWarps) >> 3) * (kTileM / 2);  // ... and which 96 token columns
+    const int c_end = c_begin + kTileM / 2;
     const int trow = quarter * 32 + lane;
     long it = 0;
     bool ok = true;
     for (long item = blockIdx.x; ok && item < n_items; item += gridDim.x, ++it) {
       const RowTile rt = A.tiles[item / L.n_tiles];
       const int nt = (int)(item % L.n_tiles);
-      const int buf = (int)(it & 1);
-      const uint32_t use_ph = (uint32_t)((it >> 1) & 1);
+      const bool active = half < L.halves(nt);
       const uint8_t* ebase = A.weights + (size_t)rt.expert * A.expert_stride;
       const float* bias = reinterpret_cast<const float*>(ebase + A.bias_offset);
       const int emax = reinterpret_cast<const int*>(ebase + A.meta_offset)[A.meta_slot];
       const float oscale = ldexpf(1.0f, emax - 140);
-      if (!mbar_wait(bar_tmem_full(buf), use_ph, abort_flag)) {
+      if (!mbar_wait(bar_tmem_full, (uint32_t)(it & 1), abort_flag)) {
         ok = false;
         break;
       }
       tc_fence_after();
-      const uint32_t t_acc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * kTileM;
-      if (GATED) {
+      const uint32_t t_acc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)half * kTileM;
+      if (!active) {
+        // this half of the last weight tile is padding: nothing to finish
+      } else if (GATED) {
         // even lane = gate row, odd lane = up row of feature `feat`
-        const int feat = nt * (kTileW / 2) + (trow >> 1);
+        const int feat = nt * kTileW + half * (kTileW / 2) + (trow >> 1);
         const bool feat_ok = feat < L.N;
         const bool odd = trow & 1;
         float my_bias = 0.f;
         if (A.has_bias && feat_ok) my_bias = odd ? bias[feat] : bias[A.F + feat];
-        for (int c0 = 0; c0 < rt.rows; c0 += 32) {
+        for (int c0 = c_begin; c0 < min(rt.rows, c_end); c0 += 32) {
           uint32_t r[32];
           tmem_ld32(t_acc + c0, r);
           tmem_ld_wait();
@@ -537,14 +575,14 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
             const float gate = odd ? p1 : v0, up = odd ? v1 : p0;
             const int tok = c0 + 2 * jj + (odd ? 1 : 0);
             if (feat_ok && tok < rt.rows)
-              A.a_out[(size_t)(rt.row0 + tok) * A.lda + feat] = __float2half_rn(gated_act(gate, up, A.act));
+              A.a_out[(size_t)(rt.row0 + tok) * A.lda + feat] = __float2half_rn(gated_act_fast(gate, up, A.act));
           }
         }
       } else {
-        const int n = nt * kTileW + trow;
+        const int n = nt * 2 * kTileW + half * kTileW + trow;
         const bool n_ok = n < L.N;
         const float my_bias = (A.has_bias && n_ok) ? bias[2 * A.F + n] : 0.f;
-        for (int c0 = 0; c0 < rt.rows; c0 += 32) {
+        for (int c0 = c_begin; c0 < min(rt.rows, c_end); c0 += 32) {
           uint32_t r[32];
           tmem_ld32(t_acc + c0, r);
           tmem_ld_wait();
@@ -561,7 +599,7 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_tmem_empty(buf));
+      if (lane == 0) mbar_arrive(bar_tmem_empty);
     }
   }
 
