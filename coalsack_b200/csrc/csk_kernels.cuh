@@ -554,8 +554,10 @@ k_ep_plan(const int* __restrict__ recv_counts, int n_src, int e_count, int e_beg
   }
 }
 
-// One block per (src, expert) segment: copy its rows to their expert-major
-// place and remember where each came from.
+// Blocks (x = segment, y = row slice): copy the segment's rows to their
+// expert-major place and remember where each came from.  A row is ldx/8 16-byte
+// words, so every thread has only a couple of independent loads per row and
+// many rows are in flight across the y dimension.
 __global__ void k_ep_regroup(const __half* __restrict__ recv, __half* __restrict__ x16, int ldx,
                              const int* __restrict__ seg, const int* __restrict__ offsets, int n_src,
                              int e_count, int e_begin, int* __restrict__ out_row_map) {
@@ -563,11 +565,13 @@ __global__ void k_ep_regroup(const __half* __restrict__ recv, __half* __restrict
   const int e = b % e_count;
   const int src_row0 = seg[b], n = seg[b + 1] - seg[b];
   const int dst_row0 = offsets[e_begin + e] + seg[1025 + b];
-  const uint4* s = reinterpret_cast<const uint4*>(recv + (size_t)src_row0 * ldx);
-  uint4* d = reinterpret_cast<uint4*>(x16 + (size_t)dst_row0 * ldx);
-  const size_t n16 = (size_t)n * ldx / 8;
-  for (size_t i = threadIdx.x; i < n16; i += blockDim.x) d[i] = s[i];
-  for (int r = threadIdx.x; r < n; r += blockDim.x) out_row_map[dst_row0 + r] = src_row0 + r;
+  const int w16 = ldx / 8;
+  for (int r = blockIdx.y; r < n; r += gridDim.y) {
+    const uint4* s = reinterpret_cast<const uint4*>(recv + (size_t)(src_row0 + r) * ldx);
+    uint4* d = reinterpret_cast<uint4*>(x16 + (size_t)(dst_row0 + r) * ldx);
+    for (int i = threadIdx.x; i < w16; i += blockDim.x) d[i] = s[i];
+    if (threadIdx.x == 0) out_row_map[dst_row0 + r] = src_row0 + r;
+  }
 }
 
 // Stream path only: rows computed in expert-major order go back to arrival order.

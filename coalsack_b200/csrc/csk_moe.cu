@@ -747,7 +747,7 @@ int csk_moe_ep_experts_dev(csk_moe_layer* L, const void* d_recv_f16, const int32
   k_ep_plan<<<1, 1024, 0, s>>>(d_recv_counts, n_src, L->Eloc, L->e0, L->d_counts, L->d_seg);
   k_scan<<<1, 1024, 0, s>>>(L->d_counts, L->E, L->e0, L->Eloc, tile_rows, (int)L->max_rows, L->max_tiles,
                             L->d_resident, L->d_offsets, L->d_cursor, L->d_tiles, L->d_meta);
-  k_ep_regroup<<<n_src * L->Eloc, 256, 0, s>>>((const __half*)d_recv_f16, L->d_x16, L->ldx, L->d_seg,
+  k_ep_regroup<<<dim3((unsigned)(n_src * L->Eloc), (unsigned)std::max(1, 16 * L->sm_count / (n_src * L->Eloc))), 128, 0, s>>>((const __half*)d_recv_f16, L->d_x16, L->ldx, L->d_seg,
                                                L->d_offsets, n_src, L->Eloc, L->e0, L->d_out_row_map);
   CSK_CUDA(L, cudaGetLastError());
   StageTimer tm(L, s);
@@ -764,9 +764,11 @@ int csk_moe_ep_experts_dev(csk_moe_layer* L, const void* d_recv_f16, const int32
     }
   }
   if (rc) return rc;
+  L->last_stream = s;
+  if (!L->timing) return CSK_OK;  // enqueue only; csk_moe_sync reports what the kernels found
   rc = check_device_status(L, s);
   if (rc) return rc;
-  if (L->timing && tm.n == 3) {  // the status check above already waited for the stream
+  if (tm.n == 3) {  // the status check above already waited for the stream
     cudaEventElapsedTime(&L->last.gate_up_ms, L->ev[0], L->ev[1]);
     cudaEventElapsedTime(&L->last.down_ms, L->ev[1], L->ev[2]);
     L->last.total_ms = L->last.gate_up_ms + L->last.down_ms;
