@@ -108,9 +108,9 @@ __global__ void k_unpack(const uint8_t* __restrict__ packed, uint8_t* __restrict
 // a block owns a BT x BE tile of (tokens x experts), a thread a TT x EE
 // sub-tile, and both operand tiles are staged through shared memory in chunks
 // of the hidden dimension so every global load is coalesced along it.
-//   k_router_logits<4,4>: prefill (many tokens), 16 chains per thread
-//   k_router_logits<1,1>: decode (a few tokens), one chain per thread, spread
-//                         over as many SMs as there are expert groups
+//   k_router_logits<4,4,64>:  prefill (many tokens), 16 chains per thread
+//   k_router_logits<1,1,480>: decode (a few tokens), one chain per thread, spread
+//                             over the expert groups, long chunks of the hidden dimension
 // k_router_topk then selects per token: one warp, k rounds of arg-max by
 // shuffles (ties -> lower expert id; the reference leaves ties unspecified),
 // softmax over the selected logits (or sigmoid) exactly as the reference.
@@ -129,13 +129,13 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-template <int TT, int EE>
+template <int TT, int EE, int CH>
 __global__ void __launch_bounds__(kRouterThreads)
 k_router_logits(const float* __restrict__ hidden, const float* __restrict__ wg,
                 const float* __restrict__ bias, float* __restrict__ logits, int T, int H, int E,
                 int ntx /* threads along tokens; 128/ntx along experts */) {
   extern __shared__ __align__(16) float smem[];
-  constexpr int LD = kRouterChunk + kRouterPad;
+  constexpr int LD = CH + kRouterPad;
   const int nty = kRouterThreads / ntx;
   const int BT = ntx * TT, BE = nty * EE;
   const int tile_floats = (BT + BE) * LD;  // one stage: hs[BT][LD] then ws[BE][LD]
@@ -152,9 +152,9 @@ k_router_logits(const float* __restrict__ hidden, const float* __restrict__ wg,
   // asynchronous, coalesced 16-byte copies along the hidden dimension into stage `st`
   auto load_chunk = [&](int st, int d0) {
     float* base = smem + st * tile_floats;
-    const int dc = min(kRouterChunk, H - d0);  // H % 32 == 0, so dc is 32 or 64
-    for (int i = tid; i < (BT + BE) * (kRouterChunk / 4); i += kRouterThreads) {
-      const int r = i / (kRouterChunk / 4), c = (i % (kRouterChunk / 4)) * 4;
+    const int dc = min(CH, H - d0);  // H % 32 == 0, so dc is a multiple of 32
+    for (int i = tid; i < (BT + BE) * (CH / 4); i += kRouterThreads) {
+      const int r = i / (CH / 4), c = (i % (CH / 4)) * 4;
       if (r < BT) {
         const bool ok = t0 + r < T && c < dc;
         cp_async16(base + r * LD + c, ok ? hidden + (size_t)(t0 + r) * H + d0 + c : hidden, ok);
@@ -167,12 +167,12 @@ k_router_logits(const float* __restrict__ hidden, const float* __restrict__ wg,
     cp_async_commit();
   };
 
-  const int n_chunks = (H + kRouterChunk - 1) / kRouterChunk;
+  const int n_chunks = (H + CH - 1) / CH;
   load_chunk(0, 0);
   for (int ch = 0; ch < n_chunks; ++ch) {
     const int st = ch & 1;
     if (ch + 1 < n_chunks) {
-      load_chunk(st ^ 1, (ch + 1) * kRouterChunk);  // stage st^1 was released by the barrier ending chunk ch-1
+      load_chunk(st ^ 1, (ch + 1) * CH);  // stage st^1 was released by the barrier ending chunk ch-1
       cp_async_wait<1>();
     } else {
       cp_async_wait<0>();
@@ -183,7 +183,10 @@ k_router_logits(const float* __restrict__ hidden, const float* __restrict__ wg,
     // shared loads of a quarter-warp fall in distinct banks
     const float* hp = smem + st * tile_floats + tx * LD;
     const float* wp = smem + st * tile_floats + BT * LD + ty * LD;
-    const int dc = min(kRouterChunk, H - ch * kRouterChunk);
+    const int dc = min(CH, H - ch * CH);
+    // unrolled so the shared-memory loads of later steps are in flight while the
+    // (serial) add chain of the current one retires
+#pragma unroll 8
     for (int d = 0; d < dc; d += 4) {
       float4 hv[TT], wv[EE];
 #pragma unroll
@@ -213,27 +216,32 @@ k_router_logits(const float* __restrict__ hidden, const float* __restrict__ wg,
     }
 }
 
+constexpr int kRouterChunkDecode = 480;  // long chunks for few tokens: six round trips to L2 instead of 45
+
 // Lets the router kernels use more than the default 48 KB of dynamic shared
-// memory (few experts and many tokens make tall token tiles).  Once per device.
+// memory (few experts and many tokens make tall token tiles; the decode variant
+// stages long chunks).  Once per device.
 inline cudaError_t router_prepare_device() {
   const int bytes = 100 * 1024;
-  cudaError_t e = cudaFuncSetAttribute(k_router_logits<4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-  if (e == cudaSuccess) e = cudaFuncSetAttribute(k_router_logits<2, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-  if (e == cudaSuccess) e = cudaFuncSetAttribute(k_router_logits<1, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-  if (e == cudaSuccess) e = cudaFuncSetAttribute(k_router_logits<1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  cudaError_t e = cudaFuncSetAttribute(k_router_logits<4, 4, kRouterChunk>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(k_router_logits<2, 4, kRouterChunk>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(k_router_logits<1, 4, kRouterChunk>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(k_router_logits<1, 1, kRouterChunkDecode>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
   return e;
 }
 
 // Picks the chain tile per thread so that the grid fills the machine, and launches.
 inline void launch_router_logits(const float* d_hidden, const float* d_wg, const float* d_bias, float* d_logits,
                                  int64_t T, int H, int E, int sm_count, cudaStream_t s) {
-  constexpr int LD = kRouterChunk + kRouterPad;
-  auto smem_of = [&](int BT, int BE) { return (size_t)2 * (BT + BE) * LD * sizeof(float); };
-  if (T <= 32) {
-    // decode: one chain per thread, 32 tokens x 4 experts per block, E/4 blocks
-    const int ntx = 32, BT = 32, BE = 4;
+  auto smem_of = [&](int BT, int BE, int ch) { return (size_t)2 * (BT + BE) * (ch + kRouterPad) * sizeof(float); };
+  if (T <= 256) {
+    // few tokens: one chain per thread, T*E/128 blocks.  8 tokens x 16 experts per block.
+    const int ntx = 8;
+    const int BT = ntx, BE = kRouterThreads / ntx;
     dim3 grid((unsigned)((T + BT - 1) / BT), (unsigned)((E + BE - 1) / BE));
-    k_router_logits<1, 1><<<grid, kRouterThreads, smem_of(BT, BE), s>>>(d_hidden, d_wg, d_bias, d_logits, (int)T, H, E, ntx);
+    k_router_logits<1, 1, kRouterChunkDecode><<<grid, kRouterThreads, smem_of(BT, BE, kRouterChunkDecode), s>>>(
+        d_hidden, d_wg, d_bias, d_logits, (int)T, H, E, ntx);
     return;
   }
   // threads along experts: as many as E fills with EE = 4 (E <= 16 -> 4)
@@ -242,18 +250,19 @@ inline void launch_router_logits(const float* d_hidden, const float* d_wg, const
   const int ntx = kRouterThreads / nty;
   const long chains = (long)T * E;
   const long want_blocks = 3L * sm_count;
+  constexpr int CH = kRouterChunk;
   if (chains / (16 * kRouterThreads) >= want_blocks) {
     const int BT = ntx * 4, BE = nty * 4;
     dim3 grid((unsigned)((T + BT - 1) / BT), (unsigned)((E + BE - 1) / BE));
-    k_router_logits<4, 4><<<grid, kRouterThreads, smem_of(BT, BE), s>>>(d_hidden, d_wg, d_bias, d_logits, (int)T, H, E, ntx);
+    k_router_logits<4, 4, CH><<<grid, kRouterThreads, smem_of(BT, BE, CH), s>>>(d_hidden, d_wg, d_bias, d_logits, (int)T, H, E, ntx);
   } else if (chains / (8 * kRouterThreads) >= want_blocks) {
     const int BT = ntx * 2, BE = nty * 4;
     dim3 grid((unsigned)((T + BT - 1) / BT), (unsigned)((E + BE - 1) / BE));
-    k_router_logits<2, 4><<<grid, kRouterThreads, smem_of(BT, BE), s>>>(d_hidden, d_wg, d_bias, d_logits, (int)T, H, E, ntx);
+    k_router_logits<2, 4, CH><<<grid, kRouterThreads, smem_of(BT, BE, CH), s>>>(d_hidden, d_wg, d_bias, d_logits, (int)T, H, E, ntx);
   } else {
     const int BT = ntx, BE = nty * 4;
     dim3 grid((unsigned)((T + BT - 1) / BT), (unsigned)((E + BE - 1) / BE));
-    k_router_logits<1, 4><<<grid, kRouterThreads, smem_of(BT, BE), s>>>(d_hidden, d_wg, d_bias, d_logits, (int)T, H, E, ntx);
+    k_router_logits<1, 4, CH><<<grid, kRouterThreads, smem_of(BT, BE, CH), s>>>(d_hidden, d_wg, d_bias, d_logits, (int)T, H, E, ntx);
   }
 }
 
@@ -346,18 +355,38 @@ __global__ void k_hist(const float* __restrict__ router_out, int n_pairs, int E,
 // counts are indexed by GLOBAL expert id; tiles carry the id local to this
 // device (e - e_begin); rows of experts outside [e_begin, e_begin+e_count) get
 // offsets but no tiles (under expert parallelism they belong to other devices).
+//
+// With router_out given (small batches) the block first builds the histogram
+// itself -- counts and the status word then need no clearing beforehand and the
+// whole plan is one launch.
 __global__ void __launch_bounds__(1024)
-k_scan(const int* __restrict__ counts, int E, int e_begin, int e_count, int tile_rows, int max_rows,
+k_scan(int* __restrict__ counts, int E, int e_begin, int e_count, int tile_rows, int max_rows,
        int max_tiles, const uint8_t* __restrict__ resident, int* __restrict__ offsets,
-       int* __restrict__ cursor, RowTile* __restrict__ tiles, int* __restrict__ meta) {
+       int* __restrict__ cursor, RowTile* __restrict__ tiles, int* __restrict__ meta,
+       const float* __restrict__ router_out, int n_pairs, int only_expert) {
   __shared__ int s_row_off[1025];
   __shared__ int s_tile_off[1025];
   __shared__ int s_warp[2][32];
   __shared__ int s_distinct;
   const int e = threadIdx.x, lane = e & 31, warp = e >> 5;
   if (e == 0) s_distinct = 0;
+  if (router_out) {
+    s_tile_off[e] = 0;  // serves as the histogram until the scan below overwrites it
+    if (e == 0) meta[3] = 0;
+    __syncthreads();
+    for (int i = e; i < n_pairs; i += 1024) {
+      const int x = (int)router_out[2 * (size_t)i];
+      if (x < 0 || x >= E) {
+        atomicOr(&meta[3], kDevErrExpertRange);
+      } else if (only_expert < 0 || x == only_expert) {
+        atomicAdd(&s_tile_off[x], 1);
+      }
+    }
+  }
   __syncthreads();
-  const int c = e < E ? counts[e] : 0;
+  const int c = router_out ? s_tile_off[e] : (e < E ? counts[e] : 0);
+  if (router_out && e < E) counts[e] = c;
+  __syncthreads();  // every thread holds its count before s_tile_off is reused
   const bool local = e >= e_begin && e < e_begin + e_count;
   const int nt = local ? (c + tile_rows - 1) / tile_rows : 0;
   if (c > 0) {

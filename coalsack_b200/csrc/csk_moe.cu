@@ -65,6 +65,18 @@ struct csk_moe_layer {
   int sm_count = 148;
   TileState tile;  // tensor maps and launch state of the tensor-core path
 
+  // Small batches are launch-bound: their kernel sequence is captured once per
+  // (T, buffers, stream) into a CUDA graph and replayed.
+  struct GraphEntry {
+    int64_t T;
+    const void *hidden, *router_in;
+    void *router_out, *out;
+    cudaStream_t stream;
+    cudaGraphExec_t exec;
+  };
+  std::vector<GraphEntry> graphs;
+  bool use_graphs = true;
+
   std::string err;
   int64_t last_T = 0;
   int n_marks = 0;
@@ -133,18 +145,26 @@ int launch_permute(csk_moe_layer* L, const float* d_hidden, const float* d_route
                    int only_expert, int tile_rows, int e_begin, int e_count, __half* x16, int ldx,
                    int64_t max_rows, cudaStream_t s) {
   const int n_pairs = (int)(T * L->k);
-  CSK_CUDA(L, cudaMemsetAsync(L->d_counts, 0, sizeof(int) * L->E, s));
-  CSK_CUDA(L, cudaMemsetAsync(L->d_meta, 0, sizeof(int) * 8, s));
-  k_hist<<<grid_for(n_pairs, 256, 2 * L->sm_count), 256, sizeof(int) * L->E, s>>>(
-      d_router, n_pairs, L->E, only_expert, L->d_counts, L->d_meta);
-  k_scan<<<1, 1024, 0, s>>>(L->d_counts, L->E, e_begin, e_count, tile_rows, (int)max_rows,
-                            L->max_tiles, e_count ? L->d_resident : nullptr, L->d_offsets,
-                            L->d_cursor, L->d_tiles, L->d_meta);
+  const uint8_t* res = e_count ? L->d_resident : nullptr;
+  if (n_pairs <= 8192) {
+    // small batch: histogram, scan and tile list in one single-block launch
+    k_scan<<<1, 1024, 0, s>>>(L->d_counts, L->E, e_begin, e_count, tile_rows, (int)max_rows, L->max_tiles, res,
+                              L->d_offsets, L->d_cursor, L->d_tiles, L->d_meta, d_router, n_pairs, only_expert);
+    L->last.launches += 1;
+  } else {
+    CSK_CUDA(L, cudaMemsetAsync(L->d_counts, 0, sizeof(int) * L->E, s));
+    CSK_CUDA(L, cudaMemsetAsync(L->d_meta, 0, sizeof(int) * 8, s));
+    k_hist<<<grid_for(n_pairs, 256, 2 * L->sm_count), 256, sizeof(int) * L->E, s>>>(
+        d_router, n_pairs, L->E, only_expert, L->d_counts, L->d_meta);
+    k_scan<<<1, 1024, 0, s>>>(L->d_counts, L->E, e_begin, e_count, tile_rows, (int)max_rows, L->max_tiles, res,
+                              L->d_offsets, L->d_cursor, L->d_tiles, L->d_meta, nullptr, 0, -1);
+    L->last.launches += 2;
+  }
   k_scatter<<<grid_for(n_pairs, 8, 8 * L->sm_count), 256, 0, s>>>(
       d_router, d_hidden, n_pairs, L->k, L->H, L->E, only_expert, L->d_offsets, L->d_cursor,
       L->d_row_of_pair, x16, ldx, (int)max_rows, L->cfg.weight_before_ffn);
   CSK_CUDA(L, cudaGetLastError());
-  L->last.launches += 3;
+  L->last.launches += 1;
   return CSK_OK;
 }
 
@@ -442,6 +462,8 @@ int csk_moe_destroy(csk_moe_layer* L) {
   if (!L) return CSK_OK;
   cudaSetDevice(L->cfg.device);
   if (L->stream) cudaStreamSynchronize(L->stream);
+  for (auto& g : L->graphs)
+    if (g.exec) cudaGraphExecDestroy(g.exec);
   tile_destroy(L->tile);
   void* dev[] = {L->d_weights, L->d_resident, L->d_stage, L->d_wg, L->d_logits, L->d_rbias, L->d_hidden,
                  L->d_router, L->d_out, L->d_x16, L->d_a16, L->d_y, L->d_counts, L->d_offsets,
@@ -544,6 +566,9 @@ int csk_moe_set_path(csk_moe_layer* L, int32_t path) {
   if (check_layer(L)) return CSK_ERR_INVALID;
   if (path < CSK_PATH_AUTO || path > CSK_PATH_TILE) return fail(L, CSK_ERR_INVALID, "unknown path %d", path);
   L->path = path;
+  for (auto& g : L->graphs)
+    if (g.exec) cudaGraphExecDestroy(g.exec);
+  L->graphs.clear();  // captured sequences embed the old choice
   return CSK_OK;
 }
 
@@ -603,7 +628,54 @@ int csk_moe_forward_dev(csk_moe_layer* L, const float* d_hidden, int64_t T, cons
   if (check_layer(L)) return CSK_ERR_INVALID;
   if (!d_hidden || !d_out) return fail(L, CSK_ERR_INVALID, "null argument");
   CSK_CUDA(L, cudaSetDevice(L->cfg.device));
-  return forward_dev(L, d_hidden, T, d_router_in, d_router_out, d_out, -1, pick(L, stream), false);
+  cudaStream_t s = pick(L, stream);
+  constexpr int64_t kGraphMaxTokens = 512;
+  if (!L->use_graphs || L->timing || T > kGraphMaxTokens || T <= 0 || T > L->max_T)
+    return forward_dev(L, d_hidden, T, d_router_in, d_router_out, d_out, -1, s, false);
+  for (auto& g : L->graphs)
+    if (g.T == T && g.hidden == d_hidden && g.router_in == d_router_in && g.router_out == d_router_out &&
+        g.out == d_out && g.stream == s) {
+      CSK_CUDA(L, cudaGraphLaunch(g.exec, s));
+      L->last_T = T;
+      L->last_stream = s;
+      L->n_marks = 0;
+      return CSK_OK;
+    }
+  // first call with these arguments: capture the sequence, then replay it
+  cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(s, &st) != cudaSuccess || st != cudaStreamCaptureStatusNone) {
+    cudaGetLastError();  // the caller is capturing this stream itself: just enqueue
+    return forward_dev(L, d_hidden, T, d_router_in, d_router_out, d_out, -1, s, false);
+  }
+  if (cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+    cudaGetLastError();
+    return forward_dev(L, d_hidden, T, d_router_in, d_router_out, d_out, -1, s, false);
+  }
+  int rc = forward_dev(L, d_hidden, T, d_router_in, d_router_out, d_out, -1, s, false);
+  cudaGraph_t graph = nullptr;
+  cudaError_t ce = cudaStreamEndCapture(s, &graph);
+  if (rc || ce != cudaSuccess || !graph) {
+    cudaGetLastError();
+    if (graph) cudaGraphDestroy(graph);
+    if (rc) return rc;
+    L->use_graphs = false;  // capture is not possible here: fall back to plain launches for good
+    return forward_dev(L, d_hidden, T, d_router_in, d_router_out, d_out, -1, s, false);
+  }
+  cudaGraphExec_t exec = nullptr;
+  ce = cudaGraphInstantiate(&exec, graph, 0);
+  cudaGraphDestroy(graph);
+  if (ce != cudaSuccess || !exec) {
+    cudaGetLastError();
+    L->use_graphs = false;
+    return forward_dev(L, d_hidden, T, d_router_in, d_router_out, d_out, -1, s, false);
+  }
+  if (L->graphs.size() >= 32) {
+    cudaGraphExecDestroy(L->graphs.front().exec);
+    L->graphs.erase(L->graphs.begin());
+  }
+  L->graphs.push_back({T, d_hidden, d_router_in, d_router_out, d_out, s, exec});
+  CSK_CUDA(L, cudaGraphLaunch(exec, s));
+  return CSK_OK;
 }
 
 // ---- host-buffer entry points ----------------------------------------------
@@ -632,8 +704,11 @@ int csk_moe_forward(csk_moe_layer* L, const float* hidden, int64_t T, const floa
   CSK_CUDA(L, cudaMemcpyAsync(L->d_hidden, hidden, sizeof(float) * T * L->H, cudaMemcpyHostToDevice, s));
   if (router_in)
     CSK_CUDA(L, cudaMemcpyAsync(L->d_router, router_in, sizeof(float) * T * L->k * 2, cudaMemcpyHostToDevice, s));
-  int rc = forward_dev(L, L->d_hidden, T, router_in ? L->d_router : nullptr, nullptr, L->d_out, -1, s, true);
+  int rc = csk_moe_forward_dev(L, L->d_hidden, T, router_in ? L->d_router : nullptr, nullptr, L->d_out, s);
   if (rc) return rc;
+  rc = check_device_status(L, s);
+  if (rc) return rc;
+  if (L->timing && L->n_marks > 1) finish_timings(L, L->n_marks, L->last_routed);
   CSK_CUDA(L, cudaMemcpyAsync(out, L->d_out, sizeof(float) * T * L->H, cudaMemcpyDeviceToHost, s));
   if (router_out)
     CSK_CUDA(L, cudaMemcpyAsync(router_out, L->d_router, sizeof(float) * T * L->k * 2, cudaMemcpyDeviceToHost, s));
@@ -746,7 +821,7 @@ int csk_moe_ep_experts_dev(csk_moe_layer* L, const void* d_recv_f16, const int32
   CSK_CUDA(L, cudaMemsetAsync(L->d_counts, 0, sizeof(int) * L->E, s));
   k_ep_plan<<<1, 1024, 0, s>>>(d_recv_counts, n_src, L->Eloc, L->e0, L->d_counts, L->d_seg);
   k_scan<<<1, 1024, 0, s>>>(L->d_counts, L->E, L->e0, L->Eloc, tile_rows, (int)L->max_rows, L->max_tiles,
-                            L->d_resident, L->d_offsets, L->d_cursor, L->d_tiles, L->d_meta);
+                            L->d_resident, L->d_offsets, L->d_cursor, L->d_tiles, L->d_meta, nullptr, 0, -1);
   k_ep_regroup<<<dim3((unsigned)(n_src * L->Eloc), (unsigned)std::max(1, 16 * L->sm_count / (n_src * L->Eloc))), 128, 0, s>>>((const __half*)d_recv_f16, L->d_x16, L->ldx, L->d_seg,
                                                L->d_offsets, n_src, L->Eloc, L->e0, L->d_out_row_map);
   CSK_CUDA(L, cudaGetLastError());

@@ -1,0 +1,110 @@
+"""The benchmark configurations at their full sizes.  The CPU checker cannot run
+whole batches of this size in seconds, so parity is shown three ways: router
+indices for EVERY token against the restatement (bit-exact), layer outputs for
+a seeded sample of tokens against the restatement, and size-independent
+properties over the whole batch (routing weights sum to one; permuting the
+tokens permutes the outputs bit for bit; the two expert kernels agree)."""
+import numpy as np
+import pytest
+
+from coalsack_b200 import MoeLayer, PATH_STREAM, PATH_TILE, synth
+from tests import cases
+
+pytestmark = pytest.mark.gpu
+
+
+def _load(sh, max_tokens):
+    lay = MoeLayer.from_shape(sh, max_tokens=max_tokens)
+    lay.set_router(synth.router_weight(sh), synth.router_bias(sh))
+    cache = {}
+    for e in range(sh.num_experts):
+        w = synth.expert_weights(sh, e)
+        lay.load_expert(e, w["w_up"], w["w_gate"], w["w_down"], w["b_up"], w["b_gate"], w["b_down"])
+        cache[e] = w
+    return lay, cache
+
+
+def _experts_dict(sh, cache):
+    ex = {k: [cache[e][k] for e in range(sh.num_experts)] for k in ("w_up", "w_gate", "w_down")}
+    for k in ("b_up", "b_gate", "b_down"):
+        ex[k] = [cache[e][k] for e in range(sh.num_experts)] if sh.has_bias else None
+    return ex
+
+
+def _check_config(sh, port, sample=48, also_stream=True):
+    T = sh.tokens
+    lay, cache = _load(sh, T)
+    h = synth.hidden_states(sh)
+    Wg, rb = synth.router_weight(sh), synth.router_bias(sh)
+    lay.set_path(PATH_TILE)
+    out, ro = lay.forward(h)
+    assert lay.timings()["path"] == PATH_TILE
+
+    # routing: every token, bit-exact indices
+    want_ro = port.router(h, Wg, rb, sh.top_k)
+    assert np.array_equal(ro[..., 0], want_ro[..., 0]), "router indices differ from the CPU checker"
+    assert np.allclose(ro[..., 1], want_ro[..., 1], atol=2e-6)
+    assert np.all(ro[..., 1] > 0) and np.allclose(ro[..., 1].sum(-1), 1.0, atol=1e-5)
+    ids = ro[..., 0].astype(int)
+    assert ids.min() >= 0 and ids.max() < sh.num_experts
+    assert all(len(set(r)) == sh.top_k for r in ids[:256])  # k distinct experts per token
+    rows, distinct, _ = lay.counters()
+    assert rows.sum() == T * sh.top_k and np.array_equal(rows, np.bincount(ids.ravel(), minlength=sh.num_experts))
+
+    # a seeded sample of tokens against the CPU restatement of the reference
+    pick = np.sort(np.random.default_rng(sh.seed).choice(T, size=min(sample, T), replace=False))
+    want, _ = port.moe_layer(h[pick], Wg, rb, _experts_dict(sh, cache), sh.top_k, sh.act, nthreads=16,
+                             router_out=ro[pick])
+    mx, mr = cases.err_stats(out[pick], want)
+    assert mx <= cases.MAX_ABS_OVER_RMS and mr <= cases.MEAN_REL, (sh.name, mx, mr)
+    assert np.all(np.isfinite(out))
+
+    # permuting the tokens permutes the outputs, bit for bit (row placement never changes a row's value)
+    perm = np.random.default_rng(sh.seed + 100).permutation(T)
+    out_p, ro_p = lay.forward(h[perm])
+    assert np.array_equal(ro_p, ro[perm])
+    assert np.array_equal(out_p, out[perm])
+
+    # the streaming kernel and the tensor-core kernel are independent implementations of the same rows
+    if also_stream:
+        lay.set_path(PATH_STREAM)
+        out_s, _ = lay.forward(h, router_out=ro)
+        mx, mr = cases.err_stats(out_s, out)
+        assert mx <= 1e-2 and mr <= 2e-3, ("stream vs tile", mx, mr)
+        mx, mr = cases.err_stats(out_s[pick], want)
+        assert mx <= cases.MAX_ABS_OVER_RMS and mr <= cases.MEAN_REL
+    lay.close()
+    return mx, mr
+
+
+def test_config1_prefill_4096_zipf(gpu_lib, port):
+    _check_config(synth.C1, port)
+
+
+def test_config4_qwen_shape_2048(gpu_lib, port):
+    _check_config(synth.C4, port)
+
+
+def test_config2_prefill_8192_128_experts(gpu_lib, port):
+    _check_config(synth.C2, port, sample=32, also_stream=False)
+
+
+def test_config3_decode_batches(gpu_lib, port):
+    """Decode sweep batches on the 128-expert layer: fresh activations per repetition."""
+    sh = synth.C3
+    lay, cache = _load(sh, 256)
+    Wg, rb = synth.router_weight(sh), synth.router_bias(sh)
+    ex = _experts_dict(sh, cache)
+    for T, rep in ((1, 0), (2, 1), (4, 2), (16, 3), (64, 4), (256, 5)):
+        h = synth.hidden_states(sh, T, rep=rep)
+        out, ro = lay.forward(h)
+        want_ro = port.router(h, Wg, rb, sh.top_k)
+        assert np.array_equal(ro[..., 0], want_ro[..., 0]), T
+        n = min(T, 24)
+        want, _ = port.moe_layer(h[:n], Wg, rb, ex, sh.top_k, sh.act, nthreads=16, router_out=ro[:n])
+        mx, mr = cases.err_stats(out[:n], want)
+        assert mx <= cases.MAX_ABS_OVER_RMS and mr <= cases.MEAN_REL, (T, mx, mr)
+        # twice in a row (the second call replays the captured launch sequence)
+        out2, _ = lay.forward(h)
+        assert np.array_equal(out, out2)
+    lay.close()
