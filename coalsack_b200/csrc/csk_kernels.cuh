@@ -108,9 +108,9 @@ __global__ void k_unpack(const uint8_t* __restrict__ packed, uint8_t* __restrict
 // a block owns a BT x BE tile of (tokens x experts), a thread a TT x EE
 // sub-tile, and both operand tiles are staged through shared memory in chunks
 // of the hidden dimension so every global load is coalesced along it.
-//   k_router_logits<4,4,64>:  prefill (many tokens), 16 chains per thread
-//   k_router_logits<1,1,480>: decode (a few tokens), one chain per thread, spread
-//                             over the expert groups, long chunks of the hidden dimension
+//   k_router_logits<4,4>: prefill (many tokens), 16 chains per thread, 64-column chunks
+//   k_router_logits<1,1>: decode (a few tokens), one chain per thread, 4 experts per block,
+//                         the block's rows staged whole where they fit
 // k_router_topk then selects per token: one warp, k rounds of arg-max by
 // shuffles (ties -> lower expert id; the reference leaves ties unspecified),
 // softmax over the selected logits (or sigmoid) exactly as the reference.
@@ -129,18 +129,21 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-template <int TT, int EE, int CH>
+template <int TT, int EE>
 __global__ void __launch_bounds__(kRouterThreads)
 k_router_logits(const float* __restrict__ hidden, const float* __restrict__ wg,
                 const float* __restrict__ bias, float* __restrict__ logits, int T, int H, int E,
-                int ntx /* threads along tokens; 128/ntx along experts */) {
+                int ntx /* threads along tokens; 128/ntx along experts */,
+                int nty_used /* thread rows along experts that hold chains (<= 128/ntx) */,
+                int ch /* columns of the hidden dimension staged per step */) {
   extern __shared__ __align__(16) float smem[];
-  constexpr int LD = CH + kRouterPad;
-  const int nty = kRouterThreads / ntx;
-  const int BT = ntx * TT, BE = nty * EE;
+  const int LD = ch + kRouterPad;
+  const int BT = ntx * TT, BE = nty_used * EE;
   const int tile_floats = (BT + BE) * LD;  // one stage: hs[BT][LD] then ws[BE][LD]
   const int tid = threadIdx.x;
   const int tx = tid % ntx, ty = tid / ntx;
+  const bool has_chains = ty < nty_used;
+  const int nty = nty_used;
   const int t0 = blockIdx.x * BT, e0 = blockIdx.y * BE;
 
   float acc[TT][EE];
@@ -152,9 +155,10 @@ k_router_logits(const float* __restrict__ hidden, const float* __restrict__ wg,
   // asynchronous, coalesced 16-byte copies along the hidden dimension into stage `st`
   auto load_chunk = [&](int st, int d0) {
     float* base = smem + st * tile_floats;
-    const int dc = min(CH, H - d0);  // H % 32 == 0, so dc is a multiple of 32
-    for (int i = tid; i < (BT + BE) * (CH / 4); i += kRouterThreads) {
-      const int r = i / (CH / 4), c = (i % (CH / 4)) * 4;
+    const int dc = min(ch, H - d0);  // H % 32 == 0 and ch % 32 == 0, so dc is a multiple of 32
+    const int w = ch / 4;
+    for (int i = tid; i < (BT + BE) * w; i += kRouterThreads) {
+      const int r = i / w, c = (i % w) * 4;
       if (r < BT) {
         const bool ok = t0 + r < T && c < dc;
         cp_async16(base + r * LD + c, ok ? hidden + (size_t)(t0 + r) * H + d0 + c : hidden, ok);
@@ -167,12 +171,12 @@ k_router_logits(const float* __restrict__ hidden, const float* __restrict__ wg,
     cp_async_commit();
   };
 
-  const int n_chunks = (H + CH - 1) / CH;
+  const int n_chunks = (H + ch - 1) / ch;  // one chunk: everything is requested at once, one stage
   load_chunk(0, 0);
-  for (int ch = 0; ch < n_chunks; ++ch) {
-    const int st = ch & 1;
-    if (ch + 1 < n_chunks) {
-      load_chunk(st ^ 1, (ch + 1) * CH);  // stage st^1 was released by the barrier ending chunk ch-1
+  for (int c_i = 0; c_i < n_chunks; ++c_i) {
+    const int st = c_i & 1;
+    if (c_i + 1 < n_chunks) {
+      load_chunk(st ^ 1, (c_i + 1) * ch);  // stage st^1 was released by the barrier ending chunk c_i-1
       cp_async_wait<1>();
     } else {
       cp_async_wait<0>();
@@ -183,65 +187,79 @@ k_router_logits(const float* __restrict__ hidden, const float* __restrict__ wg,
     // shared loads of a quarter-warp fall in distinct banks
     const float* hp = smem + st * tile_floats + tx * LD;
     const float* wp = smem + st * tile_floats + BT * LD + ty * LD;
-    const int dc = min(CH, H - ch * CH);
-    // unrolled so the shared-memory loads of later steps are in flight while the
-    // (serial) add chain of the current one retires
+    const int dc = min(ch, H - c_i * ch);
+    if (has_chains) {
+      // unrolled so the shared-memory loads of later steps are in flight while the
+      // (serial) add chain of the current one retires
 #pragma unroll 8
-    for (int d = 0; d < dc; d += 4) {
-      float4 hv[TT], wv[EE];
+      for (int d = 0; d < dc; d += 4) {
+        float4 hv[TT], wv[EE];
 #pragma unroll
-      for (int i = 0; i < TT; ++i) hv[i] = *reinterpret_cast<const float4*>(hp + i * ntx * LD + d);
+        for (int i = 0; i < TT; ++i) hv[i] = *reinterpret_cast<const float4*>(hp + i * ntx * LD + d);
 #pragma unroll
-      for (int j = 0; j < EE; ++j) wv[j] = *reinterpret_cast<const float4*>(wp + j * nty * LD + d);
+        for (int j = 0; j < EE; ++j) wv[j] = *reinterpret_cast<const float4*>(wp + j * nty * LD + d);
 #pragma unroll
-      for (int i = 0; i < TT; ++i)
+        for (int i = 0; i < TT; ++i)
 #pragma unroll
-        for (int j = 0; j < EE; ++j) {
-          float a = acc[i][j];
-          a = __fadd_rn(a, __fmul_rn(hv[i].x, wv[j].x));
-          a = __fadd_rn(a, __fmul_rn(hv[i].y, wv[j].y));
-          a = __fadd_rn(a, __fmul_rn(hv[i].z, wv[j].z));
-          a = __fadd_rn(a, __fmul_rn(hv[i].w, wv[j].w));
-          acc[i][j] = a;
-        }
+          for (int j = 0; j < EE; ++j) {
+            float a = acc[i][j];
+            a = __fadd_rn(a, __fmul_rn(hv[i].x, wv[j].x));
+            a = __fadd_rn(a, __fmul_rn(hv[i].y, wv[j].y));
+            a = __fadd_rn(a, __fmul_rn(hv[i].z, wv[j].z));
+            a = __fadd_rn(a, __fmul_rn(hv[i].w, wv[j].w));
+            acc[i][j] = a;
+          }
+      }
     }
     __syncthreads();
   }
+  if (has_chains) {
 #pragma unroll
-  for (int i = 0; i < TT; ++i)
+    for (int i = 0; i < TT; ++i)
 #pragma unroll
-    for (int j = 0; j < EE; ++j) {
-      const int t = t0 + tx + i * ntx, e = e0 + ty + j * nty;
-      if (t < T && e < E) logits[(size_t)t * E + e] = __fadd_rn(acc[i][j], bias ? bias[e] : 0.f);
-    }
+      for (int j = 0; j < EE; ++j) {
+        const int t = t0 + tx + i * ntx, e = e0 + ty + j * nty;
+        if (t < T && e < E) logits[(size_t)t * E + e] = __fadd_rn(acc[i][j], bias ? bias[e] : 0.f);
+      }
+  }
 }
 
-constexpr int kRouterChunkDecode = 480;  // long chunks for few tokens: six round trips to L2 instead of 45
+constexpr int kRouterSmemMax = 200 * 1024;
 
 // Lets the router kernels use more than the default 48 KB of dynamic shared
-// memory (few experts and many tokens make tall token tiles; the decode variant
-// stages long chunks).  Once per device.
+// memory.  Once per device.
 inline cudaError_t router_prepare_device() {
-  const int bytes = 100 * 1024;
-  cudaError_t e = cudaFuncSetAttribute(k_router_logits<4, 4, kRouterChunk>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-  if (e == cudaSuccess) e = cudaFuncSetAttribute(k_router_logits<2, 4, kRouterChunk>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-  if (e == cudaSuccess) e = cudaFuncSetAttribute(k_router_logits<1, 4, kRouterChunk>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-  if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(k_router_logits<1, 1, kRouterChunkDecode>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+  cudaError_t e = cudaFuncSetAttribute(k_router_logits<4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRouterSmemMax);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(k_router_logits<2, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRouterSmemMax);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(k_router_logits<1, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRouterSmemMax);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(k_router_logits<1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRouterSmemMax);
   return e;
 }
 
 // Picks the chain tile per thread so that the grid fills the machine, and launches.
 inline void launch_router_logits(const float* d_hidden, const float* d_wg, const float* d_bias, float* d_logits,
                                  int64_t T, int H, int E, int sm_count, cudaStream_t s) {
-  auto smem_of = [&](int BT, int BE, int ch) { return (size_t)2 * (BT + BE) * (ch + kRouterPad) * sizeof(float); };
+  auto smem_of = [&](int BT, int BE, int ch, int stages) {
+    return (size_t)stages * (BT + BE) * (ch + kRouterPad) * sizeof(float);
+  };
   if (T <= 256) {
-    // few tokens: one chain per thread, T*E/128 blocks.  8 tokens x 16 experts per block.
-    const int ntx = 8;
-    const int BT = ntx, BE = kRouterThreads / ntx;
+    // few tokens: one chain per thread and only 4 experts per block, so even a single
+    // token spreads its E chains (and the loads of the router weights) over E/4 SMs;
+    // threads without a chain still help with the copies.  When the block's rows fit
+    // in shared memory whole, everything is requested at once (one round trip to L2
+    // instead of one per chunk); else long double-buffered chunks.
+    int ntx = 1;
+    while (ntx < T && ntx < 32) ntx <<= 1;
+    const int BT = ntx, BE = 4;
+    int ch = (H + 31) / 32 * 32, stages = 1;
+    if (smem_of(BT, BE, ch, 1) > (size_t)kRouterSmemMax) {
+      stages = 2;
+      ch = 480;
+      while (smem_of(BT, BE, ch, 2) > (size_t)kRouterSmemMax) ch -= 32;
+    }
     dim3 grid((unsigned)((T + BT - 1) / BT), (unsigned)((E + BE - 1) / BE));
-    k_router_logits<1, 1, kRouterChunkDecode><<<grid, kRouterThreads, smem_of(BT, BE, kRouterChunkDecode), s>>>(
-        d_hidden, d_wg, d_bias, d_logits, (int)T, H, E, ntx);
+    k_router_logits<1, 1><<<grid, kRouterThreads, smem_of(BT, BE, ch, stages), s>>>(
+        d_hidden, d_wg, d_bias, d_logits, (int)T, H, E, ntx, BE, ch);
     return;
   }
   // threads along experts: as many as E fills with EE = 4 (E <= 16 -> 4)
@@ -250,19 +268,19 @@ inline void launch_router_logits(const float* d_hidden, const float* d_wg, const
   const int ntx = kRouterThreads / nty;
   const long chains = (long)T * E;
   const long want_blocks = 3L * sm_count;
-  constexpr int CH = kRouterChunk;
+  const int CH = kRouterChunk;
   if (chains / (16 * kRouterThreads) >= want_blocks) {
     const int BT = ntx * 4, BE = nty * 4;
     dim3 grid((unsigned)((T + BT - 1) / BT), (unsigned)((E + BE - 1) / BE));
-    k_router_logits<4, 4, CH><<<grid, kRouterThreads, smem_of(BT, BE, CH), s>>>(d_hidden, d_wg, d_bias, d_logits, (int)T, H, E, ntx);
+    k_router_logits<4, 4><<<grid, kRouterThreads, smem_of(BT, BE, CH, 2), s>>>(d_hidden, d_wg, d_bias, d_logits, (int)T, H, E, ntx, nty, CH);
   } else if (chains / (8 * kRouterThreads) >= want_blocks) {
     const int BT = ntx * 2, BE = nty * 4;
     dim3 grid((unsigned)((T + BT - 1) / BT), (unsigned)((E + BE - 1) / BE));
-    k_router_logits<2, 4, CH><<<grid, kRouterThreads, smem_of(BT, BE, CH), s>>>(d_hidden, d_wg, d_bias, d_logits, (int)T, H, E, ntx);
+    k_router_logits<2, 4><<<grid, kRouterThreads, smem_of(BT, BE, CH, 2), s>>>(d_hidden, d_wg, d_bias, d_logits, (int)T, H, E, ntx, nty, CH);
   } else {
     const int BT = ntx, BE = nty * 4;
     dim3 grid((unsigned)((T + BT - 1) / BT), (unsigned)((E + BE - 1) / BE));
-    k_router_logits<1, 4, CH><<<grid, kRouterThreads, smem_of(BT, BE, CH), s>>>(d_hidden, d_wg, d_bias, d_logits, (int)T, H, E, ntx);
+    k_router_logits<1, 4><<<grid, kRouterThreads, smem_of(BT, BE, CH, 2), s>>>(d_hidden, d_wg, d_bias, d_logits, (int)T, H, E, ntx, nty, CH);
   }
 }
 

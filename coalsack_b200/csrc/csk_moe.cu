@@ -168,7 +168,7 @@ int launch_permute(csk_moe_layer* L, const float* d_hidden, const float* d_route
   return CSK_OK;
 }
 
-template <int NT8>
+template <int NT8, int KSPLIT>
 void launch_stream_pair(csk_moe_layer* L, const __half* x16, float* y, int ldy, cudaStream_t s,
                         StageTimer& tm) {
   StreamArgs a{};
@@ -180,7 +180,9 @@ void launch_stream_pair(csk_moe_layer* L, const __half* x16, float* y, int ldy, 
   a.has_bias = L->cfg.has_bias;
   a.act = L->cfg.activation;
   a.F = L->F;
-  const int grid = L->sm_count * 8;
+  a.meta = L->d_meta;
+  // every CTA takes one contiguous range of work units; as many CTAs as fit at once
+  auto grid_for_smem = [&](size_t smem) { return L->sm_count * (int)std::max<size_t>(1, std::min<size_t>(4, (227 * 1024) / smem)); };
   // gate/up + activation
   a.mat_offset = L->off_gu;
   a.L = L->Lgu;
@@ -188,7 +190,8 @@ void launch_stream_pair(csk_moe_layer* L, const __half* x16, float* y, int ldy, 
   a.ldx = L->ldx;
   a.a_out = L->d_a16;
   a.lda = L->lda;
-  k_stream<NT8, true><<<grid, 128, 0, s>>>(a);
+  size_t smem = stream_smem_bytes(NT8, L->Lgu.k_pad(), KSPLIT, true);
+  k_stream<NT8, true, KSPLIT><<<grid_for_smem(smem), kStreamThreads, smem, s>>>(a);
   tm.mark();
   // down
   a.mat_offset = L->off_d;
@@ -197,14 +200,29 @@ void launch_stream_pair(csk_moe_layer* L, const __half* x16, float* y, int ldy, 
   a.ldx = L->lda;
   a.y_out = y;
   a.ldy = ldy;
-  k_stream<NT8, false><<<grid, 128, 0, s>>>(a);
+  smem = stream_smem_bytes(NT8, L->Ld.k_pad(), KSPLIT, false);
+  k_stream<NT8, false, KSPLIT><<<grid_for_smem(smem), kStreamThreads, smem, s>>>(a);
   tm.mark();
   L->last.launches += 2;
 }
 
+template <int NT8, int KSPLIT>
+cudaError_t stream_prepare_one() {
+  cudaError_t e = cudaFuncSetAttribute(k_stream<NT8, true, KSPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(k_stream<NT8, false, KSPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+  return e;
+}
+cudaError_t stream_prepare_device() {
+  cudaError_t e = stream_prepare_one<1, 1>();
+  if (e == cudaSuccess) e = stream_prepare_one<1, 8>();
+  if (e == cudaSuccess) e = stream_prepare_one<2, 1>();
+  return e;
+}
+
 int stream_tile_rows(const csk_moe_layer* L, int64_t rows) {
-  // short row tiles while most experts see a couple of rows, taller ones after
-  return rows <= 2 * (int64_t)std::max(1, L->Eloc) ? 8 : 32;
+  // 8-row tiles while the average expert sees at most eight rows, 16-row tiles after
+  return rows <= 8 * (int64_t)std::max(1, L->Eloc) ? 8 : 16;
 }
 
 int choose_path(const csk_moe_layer* L, int64_t rows) {
@@ -221,8 +239,8 @@ int tile_rows_for(const csk_moe_layer* L, int path, int64_t rows) {
 
 // grouped gate/up + activation + down over the row tiles listed in d_tiles;
 // x16 holds the grouped rows; output rows go to y (through out_row_map if set)
-int launch_experts(csk_moe_layer* L, int path, int tile_rows, const __half* x16, float* y, int ldy,
-                   const int* out_row_map, cudaStream_t s, StageTimer& tm) {
+int launch_experts(csk_moe_layer* L, int path, int tile_rows, int64_t n_rows_hint, const __half* x16, float* y,
+                   int ldy, const int* out_row_map, cudaStream_t s, StageTimer& tm) {
   if (path == CSK_PATH_TILE) {
     if (x16 != L->d_x16) return fail(L, CSK_ERR_INVALID, "the tile path reads the handle's own row buffer");
     int rc = tile_launch(L->tile, L->d_weights, L->expert_stride, L->off_tgu, L->off_td, L->off_bias,
@@ -233,10 +251,18 @@ int launch_experts(csk_moe_layer* L, int path, int tile_rows, const __half* x16,
     L->last.launches += 2;
   } else {
     if (out_row_map) return fail(L, CSK_ERR_INVALID, "row map needs the tile path");
+    const size_t need = std::max(stream_smem_bytes(tile_rows / 8, L->Lgu.k_pad(), 8, true),
+                                 stream_smem_bytes(tile_rows / 8, L->Ld.k_pad(), 8, false));
+    if (need > 200 * 1024)
+      return fail(L, CSK_ERR_NOMEM, "hidden/ffn dimension too large for the streaming kernel's row buffer");
     if (tile_rows == 8) {
-      launch_stream_pair<1>(L, x16, y, ldy, s, tm);
+      if (n_rows_hint <= 32) {
+        launch_stream_pair<1, 8>(L, x16, y, ldy, s, tm);  // a handful of rows: split the contraction over the warps
+      } else {
+        launch_stream_pair<1, 1>(L, x16, y, ldy, s, tm);
+      }
     } else {
-      launch_stream_pair<4>(L, x16, y, ldy, s, tm);
+      launch_stream_pair<2, 1>(L, x16, y, ldy, s, tm);
     }
   }
   CSK_CUDA(L, cudaGetLastError());
@@ -300,7 +326,7 @@ int forward_dev(csk_moe_layer* L, const float* d_hidden, int64_t T, const float*
                           L->ldx, L->max_rows, s);
   if (rc) return rc;
   tm.mark();
-  rc = launch_experts(L, path, tile_rows, L->d_x16, L->d_y, L->H, nullptr, s, tm);
+  rc = launch_experts(L, path, tile_rows, rows, L->d_x16, L->d_y, L->H, nullptr, s, tm);
   if (rc) return rc;
   k_combine<<<(unsigned)T, 256, 0, s>>>(router, L->d_row_of_pair, L->d_y, L->H, d_out, (int)T, L->k,
                                         L->H, L->cfg.weight_before_ffn, only_expert >= 0);
@@ -443,6 +469,7 @@ int csk_moe_create(const csk_moe_config* cfg, csk_moe_layer** out) {
   CK(cudaMallocHost(&L->h_meta, sizeof(int) * 8));
   CK(cudaMallocHost(&L->h_counts64, sizeof(int64_t) * L->E));
   CK(router_prepare_device());
+  CK(stream_prepare_device());
   {
     int rc = tile_init(L->tile, cfg->device);
     if (!rc) rc = tile_set_buffers(L->tile, L->d_x16, L->ldx, L->d_a16, L->lda, (size_t)L->max_rows + pad_rows);
@@ -829,9 +856,9 @@ int csk_moe_ep_experts_dev(csk_moe_layer* L, const void* d_recv_f16, const int32
   tm.mark();
   int rc;
   if (path == CSK_PATH_TILE) {
-    rc = launch_experts(L, path, tile_rows, L->d_x16, d_ret, L->H, L->d_out_row_map, s, tm);
+    rc = launch_experts(L, path, tile_rows, total_rows, L->d_x16, d_ret, L->H, L->d_out_row_map, s, tm);
   } else {
-    rc = launch_experts(L, path, tile_rows, L->d_x16, L->d_y, L->H, nullptr, s, tm);
+    rc = launch_experts(L, path, tile_rows, total_rows, L->d_x16, L->d_y, L->H, nullptr, s, tm);
     if (!rc) {
       k_ep_ungroup<<<grid_for((size_t)total_rows, 8, 8 * L->sm_count), 256, 0, s>>>(
           L->d_y, d_ret, L->H, L->d_out_row_map, (int)total_rows);

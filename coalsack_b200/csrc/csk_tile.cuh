@@ -61,7 +61,6 @@ constexpr int kTileStages = 6;
 constexpr int kTileAStages = 2;                             // weight tiles resident in tensor memory
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kTmemABase = 2 * kTileM;                 // first column of the weight ring
-constexpr long long kWaitBudget = 2000000000LL;             // clock cycles (~1 s) before a wait gives up
 
 // Device layout of a matrix for this kernel: tiles of 256 rows x 64 columns,
 // stored [n_tile][k_tile]; a tile is two halves of 128 rows, 4352 bytes each:
@@ -175,43 +174,7 @@ struct TileState {
   void* encode_fn = nullptr;
 };
 
-// ---- small PTX wrappers -----------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait.  Returns false (and raises the CTA's abort flag) when the clock
-// budget ran out or another role already aborted.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try(bar, parity)) return true;
-  const long long t0 = clock64();
-  for (;;) {
-    for (int i = 0; i < 32; ++i)
-      if (mbar_try(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitBudget) {
-      *abort_flag = 1;
-      return false;
-    }
-  }
-}
+// ---- tensor-core PTX wrappers (mbarrier / bulk-copy helpers live in csk_common.cuh) ----
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -221,12 +184,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       "l"(map), "r"(x), "r"(y), "r"(bar)
       : "memory");
 }
-__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-               "l"(src), "r"(bytes), "r"(bar)
-               : "memory");
-}
-
 // K-major operand tile with 128-byte swizzle: rows of 128 bytes, groups of 8
 // rows 1024 bytes apart.
 __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
