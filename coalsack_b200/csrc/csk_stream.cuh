@@ -97,18 +97,18 @@ __global__ void __launch_bounds__(kStreamThreads) k_stream(const StreamArgs A) {
   constexpr int NACC = GATED ? 2 : 1;
   constexpr int REC = NACC * kSubBytes;          // bytes of one stage
   constexpr int NSTG = kStreamRingBytes / REC;   // 3 (gated) or 6 stages per warp
-  extern __shared__ __align__(128) uint8_t smem_raw[];
+  extern __shared__ __align__(128) uint8_t stream_smem[];
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, q = lane & 3;
   const MatLayout& L = A.L;
   const int ldxs = L.k_pad() + kStreamXPad;
-  __half* xs = reinterpret_cast<__half*>(smem_raw);
-  uint8_t* ring = smem_raw + stream_x_bytes(NT8, L.k_pad()) + (size_t)warp * kStreamRingBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + stream_x_bytes(NT8, L.k_pad()) +
+  __half* xs = reinterpret_cast<__half*>(stream_smem);
+  uint8_t* ring = stream_smem + stream_x_bytes(NT8, L.k_pad()) + (size_t)warp * kStreamRingBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stream_smem + stream_x_bytes(NT8, L.k_pad()) +
                                                (size_t)kStreamWarps * kStreamRingBytes) + warp * 12;
   float(*red)[NACC * NT8 * 4][32] = reinterpret_cast<float(*)[NACC * NT8 * 4][32]>(
-      smem_raw + stream_x_bytes(NT8, L.k_pad()) + (size_t)kStreamWarps * (kStreamRingBytes + 12 * 8));
+      stream_smem + stream_x_bytes(NT8, L.k_pad()) + (size_t)kStreamWarps * (kStreamRingBytes + 12 * 8));
   const uint32_t ring_u32 = smem_u32(ring), bar_u32 = smem_u32(bars);
 
   if (lane == 0)

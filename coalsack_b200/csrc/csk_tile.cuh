@@ -264,12 +264,12 @@ inline size_t tile_smem_bytes() { return (size_t)kTileStages * kTileRawBytes + 1
 template <bool GATED>
 __global__ void __launch_bounds__(kTileThreads, 1)
 k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
-  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  extern __shared__ __align__(1024) uint8_t tile_smem[];
   const TileLayout& L = A.L;
   const int KT = L.k_tiles;
   constexpr int NR = kTileStages, NA = kTileAStages;
 
-  uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)tile_smem + 1023) & ~(uintptr_t)1023);
   const uint32_t smem_base = smem_u32(smem);  // ring of [token tile | packed weight tile]
   uint8_t* ctrl = smem + (size_t)NR * kTileRawBytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(ctrl);
