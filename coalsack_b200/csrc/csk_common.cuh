@@ -15,11 +15,12 @@
 namespace csk {
 
 // ---------------------------------------------------------------------------
-// Device layout of one repacked MXFP4 matrix W[N, K] (K = contraction dim).
+// Device layout of one repacked MXFP4 matrix W[N, K] (K = contraction dim) for
+// the streaming kernel.
 //
-// The matrix is cut into tiles of BN rows x 64 columns, stored tile after tile
-// as [n_tile][k_tile]; a tile is BN/16 records ("sub-tiles") of 16 rows x 64
-// columns, 544 bytes each:
+// The rows are cut into groups of 16; a group is stored as one contiguous run
+// of records along K: [group][k_tile][record], a record being 16 rows x 64
+// columns in 544 bytes:
 //
 //   bytes   0..511  codes, lane-major for a warp: lane l = 4*g + q owns 16 bytes
 //                   = four 32-bit words
@@ -32,15 +33,10 @@ namespace csk {
 //   bytes 512..543  E8M0 scales: for g = 0..7 four bytes
 //                     (row g blk 0, row g blk 1, row g+8 blk 0, row g+8 blk 1)
 //
-// One warp reads a sub-tile with a single 128-bit load per lane (plus one
-// 32-bit scale load); a whole tile is one contiguous span, so the tensor-core
-// kernel fetches it with one bulk copy.  Rows >= N and columns >= K are padded
-// with zero codes.
-//
-// For the fused gate/up matrix the tile's first BN/2 rows are gate features
-// [n_tile*BN/2, (n_tile+1)*BN/2) and its last BN/2 rows the same up features,
-// so one tile (and one warp's pair of sub-tiles) sees both operands of the
-// gated activation.
+// One warp reads a record with a single 128-bit load per lane (plus one 32-bit
+// scale load).  For the fused gate/up matrix a group is 16 FEATURES and every
+// k-tile has two records, gate then up, so one warp sees both operands of the
+// gated activation.  Rows >= N and columns >= K are padded with zero codes.
 // ---------------------------------------------------------------------------
 constexpr int kSubBytes = 544;
 constexpr int kSubCodeBytes = 512;
@@ -49,38 +45,23 @@ constexpr int kTileK = 64;
 struct MatLayout {
   int N;        // logical rows (for gate/up: F features, stored as 2 x F rows)
   int K;        // logical columns
-  int BN;       // tile rows
   int paired;   // 1 = fused gate/up
-  int n_tiles;  // tiles along N
-  int k_tiles;  // tiles along K
-  int subs;     // BN / 16
-  __host__ __device__ int rows_per_tile() const { return paired ? BN / 2 : BN; }
-  __host__ __device__ size_t tile_bytes() const { return (size_t)subs * kSubBytes; }
-  __host__ __device__ size_t bytes() const { return (size_t)n_tiles * k_tiles * tile_bytes(); }
+  int groups;   // 16-row groups
+  int k_tiles;  // 64-column tiles along K
+  __host__ __device__ int recs() const { return paired ? 2 : 1; }
+  __host__ __device__ size_t group_bytes() const { return (size_t)k_tiles * recs() * kSubBytes; }
+  __host__ __device__ size_t bytes() const { return (size_t)groups * group_bytes(); }
   __host__ __device__ int k_pad() const { return k_tiles * kTileK; }
-  __host__ __device__ int n_pad() const { return n_tiles * rows_per_tile(); }
 };
 
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
-// Tile height that wastes the least padding (ties -> the larger tile).
 inline MatLayout make_layout(int N, int K, bool paired) {
   MatLayout L{};
   L.N = N;
   L.K = K;
   L.paired = paired ? 1 : 0;
-  int best = 0, best_pad = 1 << 30;
-  for (int bn : {128, 192, 256}) {
-    int rows = paired ? bn / 2 : bn;
-    int pad = ceil_div(N, rows) * rows;
-    if (pad < best_pad || (pad == best_pad && bn > best)) {
-      best = bn;
-      best_pad = pad;
-    }
-  }
-  L.BN = best;
-  L.subs = best / 16;
-  L.n_tiles = ceil_div(N, L.rows_per_tile());
+  L.groups = ceil_div(N, 16);
   L.k_tiles = ceil_div(K, kTileK);
   return L;
 }

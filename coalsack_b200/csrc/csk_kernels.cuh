@@ -26,21 +26,16 @@ __global__ void k_repack(const uint8_t* __restrict__ src0, const uint8_t* __rest
        w += (size_t)gridDim.x * blockDim.x) {
     const size_t rec = w / (kSubBytes / 4);
     const int wi = (int)(w % (kSubBytes / 4));
-    const int sub = (int)(rec % L.subs);
-    const int kt = (int)((rec / L.subs) % L.k_tiles);
-    const int n_tile = (int)(rec / ((size_t)L.subs * L.k_tiles));
+    const int m = (int)(rec % L.recs());  // 0 = the matrix itself / gate, 1 = up
+    const int kt = (int)((rec / L.recs()) % L.k_tiles);
+    const int grp = (int)(rec / ((size_t)L.recs() * L.k_tiles));
+    const uint8_t* src = m ? src1 : src0;
     uint32_t out = 0;
     if (wi < kSubCodeBytes / 4) {
       const int lane = wi >> 2, word = wi & 3;
       const int g = lane >> 2, q = lane & 3;
-      int r_in_tile = sub * 16 + g + ((word & 2) ? 8 : 0);
+      const int row = grp * 16 + g + ((word & 2) ? 8 : 0);
       const int col = kt * kTileK + (word & 1) * 32 + q * 8;
-      const uint8_t* src = src0;
-      if (L.paired && r_in_tile >= L.BN / 2) {
-        src = src1;
-        r_in_tile -= L.BN / 2;
-      }
-      const int row = n_tile * L.rows_per_tile() + r_in_tile;
       if (row < L.N && col < L.K) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) out |= raw_code(src, L.K, row, col + i) << (4 * i);
@@ -50,14 +45,8 @@ __global__ void k_repack(const uint8_t* __restrict__ src0, const uint8_t* __rest
       int emax = -1;
 #pragma unroll
       for (int slot = 0; slot < 4; ++slot) {
-        int r_in_tile = sub * 16 + g + ((slot & 2) ? 8 : 0);
+        const int row = grp * 16 + g + ((slot & 2) ? 8 : 0);
         const int col = kt * kTileK + (slot & 1) * 32;
-        const uint8_t* src = src0;
-        if (L.paired && r_in_tile >= L.BN / 2) {
-          src = src1;
-          r_in_tile -= L.BN / 2;
-        }
-        const int row = n_tile * L.rows_per_tile() + r_in_tile;
         uint32_t e = 0;  // padding: zero codes under the smallest scale
         if (row < L.N && col < L.K) {
           e = src[((size_t)row * (L.K / 32) + col / 32) * 17];
@@ -80,12 +69,10 @@ __global__ void k_unpack(const uint8_t* __restrict__ packed, uint8_t* __restrict
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_blocks;
        i += (size_t)gridDim.x * blockDim.x) {
     const int row = (int)(i / kb), blk = (int)(i % kb);
-    const int n_tile = row / L.rows_per_tile();
-    int r_in_tile = row % L.rows_per_tile() + (which_half ? L.BN / 2 : 0);
-    const int sub = r_in_tile / 16, r16 = r_in_tile % 16;
+    const int grp = row / 16, r16 = row % 16;
     const int g = r16 & 7, hi = r16 >> 3;
     const int kt = blk / 2, b = blk & 1;
-    const uint8_t* rec = packed + (((size_t)n_tile * L.k_tiles + kt) * L.subs + sub) * kSubBytes;
+    const uint8_t* rec = packed + (((size_t)grp * L.k_tiles + kt) * L.recs() + which_half) * kSubBytes;
     uint8_t* o = out + i * 17;
     o[0] = rec[kSubCodeBytes + g * 4 + hi * 2 + b];
     uint32_t codes[32];
@@ -104,203 +91,71 @@ __global__ void k_unpack(const uint8_t* __restrict__ packed, uint8_t* __restrict
 // reference accumulates each logit sequentially in fp32 with separate multiply
 // and add.  So each (token, expert) logit is ONE thread's in-order chain of
 // __fmul_rn / __fadd_rn over the hidden dimension (never contracted into an
-// FMA, never reassociated).  Parallelism comes from the T*E independent chains:
-// a block owns a BT x BE tile of (tokens x experts), a thread a TT x EE
-// sub-tile, and both operand tiles are staged through shared memory in chunks
-// of the hidden dimension so every global load is coalesced along it.
-//   k_router_logits<4,4>: prefill (many tokens), 16 chains per thread, 64-column chunks
-//   k_router_logits<1,1>: decode (a few tokens), one chain per thread, 4 experts per block,
-//                         the block's rows staged whole where they fit
+// FMA, never reassociated).  Parallelism comes from the T*E independent chains.
 // k_router_topk then selects per token: one warp, k rounds of arg-max by
 // shuffles (ties -> lower expert id; the reference leaves ties unspecified),
 // softmax over the selected logits (or sigmoid) exactly as the reference.
 // ---------------------------------------------------------------------------
-constexpr int kRouterChunk = 64;
-constexpr int kRouterPad = 4;
-constexpr int kRouterThreads = 128;
+constexpr int kRouterPad = 4;       // row stride 4 mod 32 words: a quarter-warp's 128-bit loads hit distinct banks
+constexpr int kRouterStages = 4;
 constexpr int kMaxTopK = 16;
+constexpr int kMaxExperts = 1024;
 
-__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, bool valid) {
-  const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
-  const int n = valid ? 16 : 0;  // src-size 0 -> the 16 bytes are zero-filled
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gsrc), "r"(n) : "memory");
+// ch = columns of the hidden dimension per pipeline stage
+inline size_t router_smem_bytes(int tokens_per_block, int ch) {
+  return (size_t)kRouterStages * (32 + tokens_per_block) * (ch + kRouterPad) * sizeof(float) + 128;
+}
+
+__device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gsrc) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-template <int TT, int EE>
-__global__ void __launch_bounds__(kRouterThreads)
-k_router_logits(const float* __restrict__ hidden, const float* __restrict__ wg,
-                const float* __restrict__ bias, float* __restrict__ logits, int T, int H, int E,
-                int ntx /* threads along tokens; 128/ntx along experts */,
-                int nty_used /* thread rows along experts that hold chains (<= 128/ntx) */,
-                int ch /* columns of the hidden dimension staged per step */) {
-  extern __shared__ __align__(16) float smem[];
-  const int LD = ch + kRouterPad;
-  const int BT = ntx * TT, BE = nty_used * EE;
-  const int tile_floats = (BT + BE) * LD;  // one stage: hs[BT][LD] then ws[BE][LD]
-  const int tid = threadIdx.x;
-  const int tx = tid % ntx, ty = tid / ntx;
-  const bool has_chains = ty < nty_used;
-  const int nty = nty_used;
-  const int t0 = blockIdx.x * BT, e0 = blockIdx.y * BE;
-
-  float acc[TT][EE];
-#pragma unroll
-  for (int i = 0; i < TT; ++i)
-#pragma unroll
-    for (int j = 0; j < EE; ++j) acc[i][j] = 0.f;
-
-  // asynchronous, coalesced 16-byte copies along the hidden dimension into stage `st`
-  auto load_chunk = [&](int st, int d0) {
-    float* base = smem + st * tile_floats;
-    const int dc = min(ch, H - d0);  // H % 32 == 0 and ch % 32 == 0, so dc is a multiple of 32
-    const int w = ch / 4;
-    for (int i = tid; i < (BT + BE) * w; i += kRouterThreads) {
-      const int r = i / w, c = (i % w) * 4;
-      if (r < BT) {
-        const bool ok = t0 + r < T && c < dc;
-        cp_async16(base + r * LD + c, ok ? hidden + (size_t)(t0 + r) * H + d0 + c : hidden, ok);
-      } else {
-        const int e = e0 + r - BT;
-        const bool ok = e < E && c < dc;
-        cp_async16(base + r * LD + c, ok ? wg + (size_t)e * H + d0 + c : wg, ok);
-      }
-    }
-    cp_async_commit();
-  };
-
-  const int n_chunks = (H + ch - 1) / ch;  // one chunk: everything is requested at once, one stage
-  load_chunk(0, 0);
-  for (int c_i = 0; c_i < n_chunks; ++c_i) {
-    const int st = c_i & 1;
-    if (c_i + 1 < n_chunks) {
-      load_chunk(st ^ 1, (c_i + 1) * ch);  // stage st^1 was released by the barrier ending chunk c_i-1
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
-    __syncthreads();
-    // thread (tx, ty) owns tokens tx + i*ntx and experts ty + j*nty: neighbouring
-    // threads read neighbouring rows (stride LD = 4 mod 32 words), so the 128-bit
-    // shared loads of a quarter-warp fall in distinct banks
-    const float* hp = smem + st * tile_floats + tx * LD;
-    const float* wp = smem + st * tile_floats + BT * LD + ty * LD;
-    const int dc = min(ch, H - c_i * ch);
-    if (has_chains) {
-      // unrolled so the shared-memory loads of later steps are in flight while the
-      // (serial) add chain of the current one retires
-#pragma unroll 8
-      for (int d = 0; d < dc; d += 4) {
-        float4 hv[TT], wv[EE];
-#pragma unroll
-        for (int i = 0; i < TT; ++i) hv[i] = *reinterpret_cast<const float4*>(hp + i * ntx * LD + d);
-#pragma unroll
-        for (int j = 0; j < EE; ++j) wv[j] = *reinterpret_cast<const float4*>(wp + j * nty * LD + d);
-#pragma unroll
-        for (int i = 0; i < TT; ++i)
-#pragma unroll
-          for (int j = 0; j < EE; ++j) {
-            float a = acc[i][j];
-            a = __fadd_rn(a, __fmul_rn(hv[i].x, wv[j].x));
-            a = __fadd_rn(a, __fmul_rn(hv[i].y, wv[j].y));
-            a = __fadd_rn(a, __fmul_rn(hv[i].z, wv[j].z));
-            a = __fadd_rn(a, __fmul_rn(hv[i].w, wv[j].w));
-            acc[i][j] = a;
-          }
-      }
-    }
-    __syncthreads();
-  }
-  if (has_chains) {
-#pragma unroll
-    for (int i = 0; i < TT; ++i)
-#pragma unroll
-      for (int j = 0; j < EE; ++j) {
-        const int t = t0 + tx + i * ntx, e = e0 + ty + j * nty;
-        if (t < T && e < E) logits[(size_t)t * E + e] = __fadd_rn(acc[i][j], bias ? bias[e] : 0.f);
-      }
+// Router weights repacked for the logits kernel: [group of 32 experts][chunk of
+// CH columns][32 rows][CH + pad] floats, so that a stage of the kernel's ring
+// is ONE contiguous span (one bulk copy).  Rows past E and columns past H are 0.
+inline size_t router_packed_floats(int E, int H, int ch) {
+  return (size_t)((E + 31) / 32) * ((H + ch - 1) / ch) * 32 * (ch + kRouterPad);
+}
+__global__ void k_pack_router(const float* __restrict__ wg, float* __restrict__ packed, int E, int H, int ch) {
+  const int ld = ch + kRouterPad, n_chunks = (H + ch - 1) / ch;
+  const size_t n = (size_t)((E + 31) / 32) * n_chunks * 32 * ld;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const int c = (int)(i % ld);
+    const int r = (int)((i / ld) % 32);
+    const int ci = (int)((i / ((size_t)ld * 32)) % n_chunks);
+    const int g = (int)(i / ((size_t)ld * 32 * n_chunks));
+    const int e = g * 32 + r, d = ci * ch + c;
+    packed[i] = (c < ch && e < E && d < H) ? wg[(size_t)e * H + d] : 0.f;
   }
 }
 
-constexpr int kRouterSmemMax = 200 * 1024;
-
-// Lets the router kernels use more than the default 48 KB of dynamic shared
-// memory.  Once per device.
-inline cudaError_t router_prepare_device() {
-  cudaError_t e = cudaFuncSetAttribute(k_router_logits<4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRouterSmemMax);
-  if (e == cudaSuccess) e = cudaFuncSetAttribute(k_router_logits<2, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRouterSmemMax);
-  if (e == cudaSuccess) e = cudaFuncSetAttribute(k_router_logits<1, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRouterSmemMax);
-  if (e == cudaSuccess) e = cudaFuncSetAttribute(k_router_logits<1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRouterSmemMax);
-  return e;
-}
-
-// Picks the chain tile per thread so that the grid fills the machine, and launches.
-inline void launch_router_logits(const float* d_hidden, const float* d_wg, const float* d_bias, float* d_logits,
-                                 int64_t T, int H, int E, int sm_count, cudaStream_t s) {
-  auto smem_of = [&](int BT, int BE, int ch, int stages) {
-    return (size_t)stages * (BT + BE) * (ch + kRouterPad) * sizeof(float);
-  };
-  if (T <= 256) {
-    // few tokens: one chain per thread and only 4 experts per block, so even a single
-    // token spreads its E chains (and the loads of the router weights) over E/4 SMs;
-    // threads without a chain still help with the copies.  When the block's rows fit
-    // in shared memory whole, everything is requested at once (one round trip to L2
-    // instead of one per chunk); else long double-buffered chunks.
-    int ntx = 1;
-    while (ntx < T && ntx < 32) ntx <<= 1;
-    const int BT = ntx, BE = 4;
-    int ch = (H + 31) / 32 * 32, stages = 1;
-    if (smem_of(BT, BE, ch, 1) > (size_t)kRouterSmemMax) {
-      stages = 2;
-      ch = 480;
-      while (smem_of(BT, BE, ch, 2) > (size_t)kRouterSmemMax) ch -= 32;
-    }
-    dim3 grid((unsigned)((T + BT - 1) / BT), (unsigned)((E + BE - 1) / BE));
-    k_router_logits<1, 1><<<grid, kRouterThreads, smem_of(BT, BE, ch, stages), s>>>(
-        d_hidden, d_wg, d_bias, d_logits, (int)T, H, E, ntx, BE, ch);
-    return;
-  }
-  // threads along experts: as many as E fills with EE = 4 (E <= 16 -> 4)
-  int nty = 16;
-  while (nty > 4 && (nty / 2) * 4 >= E) nty >>= 1;
-  const int ntx = kRouterThreads / nty;
-  const long chains = (long)T * E;
-  const long want_blocks = 3L * sm_count;
-  const int CH = kRouterChunk;
-  if (chains / (16 * kRouterThreads) >= want_blocks) {
-    const int BT = ntx * 4, BE = nty * 4;
-    dim3 grid((unsigned)((T + BT - 1) / BT), (unsigned)((E + BE - 1) / BE));
-    k_router_logits<4, 4><<<grid, kRouterThreads, smem_of(BT, BE, CH, 2), s>>>(d_hidden, d_wg, d_bias, d_logits, (int)T, H, E, ntx, nty, CH);
-  } else if (chains / (8 * kRouterThreads) >= want_blocks) {
-    const int BT = ntx * 2, BE = nty * 4;
-    dim3 grid((unsigned)((T + BT - 1) / BT), (unsigned)((E + BE - 1) / BE));
-    k_router_logits<2, 4><<<grid, kRouterThreads, smem_of(BT, BE, CH, 2), s>>>(d_hidden, d_wg, d_bias, d_logits, (int)T, H, E, ntx, nty, CH);
-  } else {
-    const int BT = ntx, BE = nty * 4;
-    dim3 grid((unsigned)((T + BT - 1) / BT), (unsigned)((E + BE - 1) / BE));
-    k_router_logits<1, 4><<<grid, kRouterThreads, smem_of(BT, BE, CH, 2), s>>>(d_hidden, d_wg, d_bias, d_logits, (int)T, H, E, ntx, nty, CH);
-  }
-}
-
-__global__ void __launch_bounds__(128)
-k_router_topk(float* __restrict__ logits, float* __restrict__ router_out, int T, int E, int k,
-              int sigmoid) {
+// Top-k of one token's logits by one warp, then softmax over the selected
+// logits (or sigmoid) exactly as the reference (moe_router_node.h:165-214).
+// The logits sit in registers (lane l holds experts l, l+32, ...); each of the
+// k rounds is an arg-max by shuffles (ties -> lower expert id; the reference
+// leaves ties unspecified).
+__device__ __forceinline__ void warp_topk(const float* __restrict__ l, int E, int k, int sigmoid,
+                                          float* __restrict__ out /* [k][2] */) {
   const int lane = threadIdx.x & 31;
-  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (t >= T) return;
-  float* l = logits + (size_t)t * E;
+  float v[kMaxExperts / 32];
+#pragma unroll
+  for (int i = 0; i < kMaxExperts / 32; ++i) v[i] = (i * 32 < E && i * 32 + lane < E) ? __ldcg(l + i * 32 + lane) : -INFINITY;
   float sel_v[kMaxTopK];
   int sel_i[kMaxTopK];
   for (int j = 0; j < k; ++j) {
     float bv = -INFINITY;
     int bi = 0x7fffffff;
-    for (int e = lane; e < E; e += 32) {
-      const float v = l[e];
-      if (v > bv || (v == bv && e < bi)) {
-        bv = v;
-        bi = e;
+#pragma unroll
+    for (int i = 0; i < kMaxExperts / 32; ++i) {
+      if (i * 32 < E) {  // warp-uniform
+        const float x = v[i];
+        if (x > bv) {  // ascending expert id within the lane: '>' keeps the lowest on ties
+          bv = x;
+          bi = i * 32 + lane;
+        }
       }
     }
     for (int o = 16; o > 0; o >>= 1) {
@@ -313,9 +168,10 @@ k_router_topk(float* __restrict__ logits, float* __restrict__ router_out, int T,
     }
     sel_v[j] = bv;
     sel_i[j] = bi;
-    __syncwarp();
-    if (lane == 0 && bi < E) l[bi] = __int_as_float(0xffc00000);  // NaN: never wins a '>' test again
-    __syncwarp();
+    // the winner leaves the pool: NaN never wins a '>' test again
+#pragma unroll
+    for (int i = 0; i < kMaxExperts / 32; ++i)
+      if (i * 32 < E && bi == i * 32 + lane) v[i] = __int_as_float(0xffc00000);
   }
   if (lane == 0) {
     float w[kMaxTopK];
@@ -333,10 +189,329 @@ k_router_topk(float* __restrict__ logits, float* __restrict__ router_out, int T,
       for (int j = 0; j < k; ++j) w[j] *= inv;
     }
     for (int j = 0; j < k; ++j) {
-      router_out[((size_t)t * k + j) * 2 + 0] = (float)sel_i[j];
-      router_out[((size_t)t * k + j) * 2 + 1] = w[j];
+      out[j * 2 + 0] = (float)sel_i[j];
+      out[j * 2 + 1] = w[j];
     }
   }
+}
+
+struct RouterArgs {
+  const float* hidden;   // [T,H], 16-byte aligned
+  const float* wg;       // PACKED: router_packed layout for this CH; else [E,H], 16-byte aligned
+  const float* bias;     // [E] or null
+  float* logits;         // [T,E] scratch
+  float* router_out;     // [T,k,2]; written when `counters` is given
+  int* counters;         // one per token block, all zero between launches; null = logits only
+  int* status;           // device status word or null
+  int T, H, E, k, sigmoid;
+};
+
+// A block is one producer warp (four with plain weights) plus TW consumer warps.  A
+// consumer warp owns TT tokens, its lanes 32 neighbouring experts: a thread runs TT chains.
+//   * expert rows: a four-stage ring of CH-column chunks filled by bulk copies
+//     (cp.async.bulk, completion counted on the stage's mbarrier).  An SM starts
+//     only about one bulk copy per 70-100 cycles, so with PACKED weights a stage
+//     is one copy issued by one thread; with plain [E,H] weights the producers'
+//     lanes issue one copy per row;
+//   * token rows: each consumer warp keeps its own TT rows in a ring of the same
+//     depth, filled with cp.async by the warp itself (nobody else reads them);
+//   * a lane reads its own expert row with 128-bit loads (conflict-free by the
+//     row padding) and the token rows by broadcast.  A chain costs one dependent
+//     add per column, so a logit takes about H x (add latency) cycles however
+//     many run at once: TT = 1 keeps two 32-column register blocks in flight to
+//     run one chain at that speed (few tokens), larger TT trades latency for
+//     fewer shared-memory reads per chain (many tokens);
+//   * with `counters`, the last block to finish a token block's logits (an
+//     atomic ticket after a fence) also selects the top-k for those tokens.
+// Waits are bounded; a wait that runs out sets kDevErrWaitTimeout in *status
+// (when given) and the block leaves.
+// Bounded wait that naps between polls, for a warp that shares its scheduler with a
+// warp doing the real work.
+__device__ __forceinline__ bool mbar_wait_nap(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+    __nanosleep(64);
+    if (mbar_try(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitBudget) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+
+__host__ __device__ constexpr int router_producer_warps(bool packed) { return packed ? 1 : 4; }
+
+template <int TW, int TT, int CH, bool PACKED>
+__global__ void __launch_bounds__((TW + router_producer_warps(PACKED)) * 32)
+k_router_logits(const RouterArgs A) {
+  extern __shared__ __align__(128) uint8_t router_smem_raw[];
+  constexpr int LD = CH + kRouterPad;
+  constexpr int NS = kRouterStages, NP = router_producer_warps(PACKED);
+  constexpr int BT = TW * TT;                   // tokens of the block
+  constexpr int stage_floats = (32 + BT) * LD;  // ws[32][LD] then hs[BT][LD]
+  float* stages = reinterpret_cast<float*>(router_smem_raw);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(router_smem_raw + (size_t)NS * stage_floats * sizeof(float));
+  const uint32_t bar_base = smem_u32(bars);
+  auto bar_full = [&](int s) { return bar_base + 8u * s; };
+  auto bar_empty = [&](int s) { return bar_base + 8u * (NS + s); };
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * NS);
+  volatile int* ticket = abort_flag + 1;
+
+  const int T = A.T, H = A.H, E = A.E;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int t0 = blockIdx.x * BT, e0 = blockIdx.y * 32;
+  const int n_chunks = (H + CH - 1) / CH;
+
+  if (tid == 0) {
+    for (int s = 0; s < NS; ++s) {
+      mbar_init(bar_full(s), PACKED ? 1 : NP);
+      mbar_init(bar_empty(s), TW);
+    }
+    *abort_flag = 0;
+    *ticket = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  if (warp < NP) {
+    // ------------------------------ producers ------------------------------
+    const int n_e = min(32, E - e0);
+    const bool mine = PACKED ? (warp == 0 && lane == 0) : (warp + NP * lane < n_e);
+    const int row = warp + NP * lane;  // !PACKED: producer p moves expert rows p, p+NP, ...
+    const int n_mine = __popc(__ballot_sync(0xffffffffu, mine));  // !PACKED: may be 0, the warp still posts its arrival
+    const float* src = PACKED ? A.wg + (size_t)blockIdx.y * n_chunks * 32 * LD : A.wg + (size_t)(e0 + row) * H;
+    int issued = 0;
+    bool ok = true;
+    if (!PACKED || n_mine) {
+      for (int ci = 0; ci < n_chunks; ++ci) {
+        const int st = ci % NS;
+        if (ci >= NS && !mbar_wait_nap(bar_empty(st), (uint32_t)((ci / NS - 1) & 1), abort_flag)) {
+          ok = false;
+          break;
+        }
+        const uint32_t dst = smem_u32(stages + (size_t)st * stage_floats);
+        if (PACKED) {
+          if (mine) {
+            mbar_expect_tx(bar_full(st), 32 * LD * 4);
+            bulk_load(dst, src + (size_t)ci * 32 * LD, 32 * LD * 4, bar_full(st));
+          }
+        } else {
+          const int d0 = ci * CH;
+          const uint32_t row_bytes = (uint32_t)min(CH, H - d0) * sizeof(float);  // H % 32 == 0: a multiple of 128
+          if (lane == 0) mbar_expect_tx(bar_full(st), (uint32_t)n_mine * row_bytes);
+          __syncwarp();
+          if (mine) bulk_load(dst + (uint32_t)row * LD * 4, src + d0, row_bytes, bar_full(st));
+        }
+        ++issued;
+      }
+    }
+    if (!ok) {
+      // let the copies still in flight land before the block goes away
+      for (int i = 0; i < NS && i < issued; ++i) {
+        const int ci = issued - 1 - i;
+        const long long tb = clock64();
+        while (!mbar_try(bar_full(ci % NS), (uint32_t)((ci / NS) & 1)) && clock64() - tb < kWaitBudget) {
+        }
+      }
+    }
+  } else {
+    // ------------------------------ consumers ------------------------------
+    const int w = warp - NP;
+    float acc[TT];
+#pragma unroll
+    for (int i = 0; i < TT; ++i) acc[i] = 0.f;
+    // this warp's token rows of chunk ci -> its rows of stage ci % NS
+    auto load_tokens = [&](int ci) {
+      const int d0 = ci * CH;
+      const int dc = min(CH, H - d0);
+      const uint32_t dst = smem_u32(stages + (size_t)(ci % NS) * stage_floats + (32 + w * TT) * LD);
+#pragma unroll
+      for (int i = 0; i < TT; ++i) {
+        const int t = t0 + w * TT + i;
+        if (t < T)
+          for (int c = lane * 4; c < dc; c += 128)
+            cp_async16(dst + (uint32_t)(i * LD + c) * 4, A.hidden + (size_t)t * H + d0 + c);
+      }
+    };
+    for (int i = 0; i < NS - 1; ++i) {
+      if (i < n_chunks) load_tokens(i);
+      cp_async_commit();
+    }
+    bool ok = true;
+    for (int ci = 0; ci < n_chunks; ++ci) {
+      const int st = ci % NS;
+      cp_async_wait<NS - 2>();  // this lane's part of the token rows of chunk ci has landed ...
+      __syncwarp();             // ... and the other lanes'; the rows used in the last iteration are free
+      if (ci + NS - 1 < n_chunks) load_tokens(ci + NS - 1);
+      cp_async_commit();
+      if (!mbar_wait(bar_full(st), (uint32_t)((ci / NS) & 1), abort_flag)) {
+        ok = false;
+        break;
+      }
+      const float* wp = stages + (size_t)st * stage_floats + lane * LD;
+      const float* hp = stages + (size_t)st * stage_floats + (32 + w * TT) * LD;
+      const int dc = min(CH, H - ci * CH);
+      if (TT == 1) {
+        // 32-column blocks.  The add chain issues one instruction per four cycles; the loads
+        // and the (independent) products of the NEXT block are written between its adds so
+        // they go into those idle issue slots.
+        const int nblk = dc / 32;
+        float pa[32], pb[32];
+        auto products = [&](int blk, float (&p)[32]) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float4 wv = *reinterpret_cast<const float4*>(wp + blk * 32 + i * 4);
+            const float4 hv = *reinterpret_cast<const float4*>(hp + blk * 32 + i * 4);
+            p[4 * i] = __fmul_rn(hv.x, wv.x);
+            p[4 * i + 1] = __fmul_rn(hv.y, wv.y);
+            p[4 * i + 2] = __fmul_rn(hv.z, wv.z);
+            p[4 * i + 3] = __fmul_rn(hv.w, wv.w);
+          }
+        };
+        // adds of block `p`, products of block `nblk_next` (if any) into `q`
+        auto chain = [&](const float (&p)[32], int next, float (&q)[32]) {
+          float a = acc[0];
+          const bool more = next < nblk;
+          float4 wv[8], hv[8];
+          if (more) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              wv[i] = *reinterpret_cast<const float4*>(wp + next * 32 + i * 4);
+              hv[i] = *reinterpret_cast<const float4*>(hp + next * 32 + i * 4);
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            a = __fadd_rn(a, p[4 * i]);
+            if (more) q[4 * i] = __fmul_rn(hv[i].x, wv[i].x);
+            a = __fadd_rn(a, p[4 * i + 1]);
+            if (more) q[4 * i + 1] = __fmul_rn(hv[i].y, wv[i].y);
+            a = __fadd_rn(a, p[4 * i + 2]);
+            if (more) q[4 * i + 2] = __fmul_rn(hv[i].z, wv[i].z);
+            a = __fadd_rn(a, p[4 * i + 3]);
+            if (more) q[4 * i + 3] = __fmul_rn(hv[i].w, wv[i].w);
+          }
+          acc[0] = a;
+        };
+        products(0, pa);
+        for (int blk = 0; blk < nblk; blk += 2) {
+          chain(pa, blk + 1, pb);
+          if (blk + 1 < nblk) chain(pb, blk + 2, pa);
+        }
+      } else {
+#pragma unroll 2
+        for (int d = 0; d < dc; d += 4) {
+          const float4 wv = *reinterpret_cast<const float4*>(wp + d);
+          float4 hv[TT];
+#pragma unroll
+          for (int i = 0; i < TT; ++i) hv[i] = *reinterpret_cast<const float4*>(hp + i * LD + d);
+#pragma unroll
+          for (int i = 0; i < TT; ++i) {
+            float a = acc[i];
+            a = __fadd_rn(a, __fmul_rn(hv[i].x, wv.x));
+            a = __fadd_rn(a, __fmul_rn(hv[i].y, wv.y));
+            a = __fadd_rn(a, __fmul_rn(hv[i].z, wv.z));
+            a = __fadd_rn(a, __fmul_rn(hv[i].w, wv.w));
+            acc[i] = a;
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_empty(st));
+    }
+    cp_async_wait<0>();
+    if (ok) {
+      const int e = e0 + lane;
+      const float b = (A.bias && e < E) ? A.bias[e] : 0.f;
+#pragma unroll
+      for (int i = 0; i < TT; ++i) {
+        const int t = t0 + w * TT + i;
+        if (t < T && e < E) A.logits[(size_t)t * E + e] = __fadd_rn(acc[i], b);
+      }
+      __threadfence();  // the logits before the block's ticket below
+    }
+  }
+  __syncthreads();
+  if (tid == 0 && *abort_flag && A.status) atomicOr(A.status, kDevErrWaitTimeout);
+  if (A.counters == nullptr) return;
+
+  // ---- the last block of this token block selects the top-k ----
+  if (tid == 0) {
+    int last = 1;
+    if (gridDim.y > 1) {
+      __threadfence();  // this block's logits before its ticket
+      last = atomicAdd(&A.counters[blockIdx.x], 1) == (int)gridDim.y - 1;
+      if (last) {
+        A.counters[blockIdx.x] = 0;  // ready for the next launch
+        __threadfence();             // the other blocks' logits after their tickets
+      }
+    }
+    *ticket = last;
+  }
+  __syncthreads();
+  if (!*ticket) return;
+  for (int i = warp; i < BT; i += TW + NP) {
+    const int t = t0 + i;
+    if (t < T) warp_topk(A.logits + (size_t)t * E, E, A.k, A.sigmoid, A.router_out + (size_t)t * A.k * 2);
+  }
+}
+
+template <int TW, int TT, int CH, bool PACKED>
+cudaError_t router_prepare_one() {
+  return cudaFuncSetAttribute(k_router_logits<TW, TT, CH, PACKED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              (int)router_smem_bytes(TW * TT, CH));
+}
+constexpr int kRouterChunkFew = 256, kRouterChunkMany = 128;  // columns per stage: few / many tokens
+// Lets the router kernels use more than the default 48 KB of dynamic shared
+// memory.  Once per device.
+inline cudaError_t router_prepare_device() {
+  cudaError_t e = router_prepare_one<1, 1, kRouterChunkFew, true>();
+  if (e == cudaSuccess) e = router_prepare_one<2, 1, kRouterChunkFew, true>();
+  if (e == cudaSuccess) e = router_prepare_one<4, 1, kRouterChunkFew, true>();
+  if (e == cudaSuccess) e = router_prepare_one<4, 2, kRouterChunkMany, true>();
+  if (e == cudaSuccess) e = router_prepare_one<4, 4, kRouterChunkMany, true>();
+  if (e == cudaSuccess) e = router_prepare_one<1, 1, kRouterChunkFew, false>();
+  if (e == cudaSuccess) e = router_prepare_one<2, 1, kRouterChunkFew, false>();
+  if (e == cudaSuccess) e = router_prepare_one<4, 1, kRouterChunkFew, false>();
+  if (e == cudaSuccess) e = router_prepare_one<4, 2, kRouterChunkMany, false>();
+  if (e == cudaSuccess) e = router_prepare_one<4, 4, kRouterChunkMany, false>();
+  return e;
+}
+
+template <int TW, int TT, int CH, bool PACKED>
+void launch_router_one(const RouterArgs& a, cudaStream_t s) {
+  const dim3 grid((unsigned)((a.T + TW * TT - 1) / (TW * TT)), (unsigned)((a.E + 31) / 32));
+  k_router_logits<TW, TT, CH, PACKED><<<grid, (TW + router_producer_warps(PACKED)) * 32, router_smem_bytes(TW * TT, CH), s>>>(a);
+}
+
+// Few tokens per block while that still leaves SMs idle (a block's speed is bounded by its
+// shared-memory reads: one 16-byte word per lane per four columns and chain), more chains per
+// thread once the machine is full.  wg_few / wg_many: the weights packed for the two chunk
+// widths (PACKED) or both the plain [E,H] matrix.  Returns the number of token blocks.
+template <bool PACKED>
+inline int launch_router_logits(RouterArgs a, const float* wg_few, const float* wg_many, int sm_count,
+                                cudaStream_t s) {
+  const int64_t token_blocks = (int64_t)a.T * ((a.E + 31) / 32);  // blocks if every block held one token
+  if (token_blocks <= 4 * (int64_t)sm_count) {
+    a.wg = wg_few;
+    if (token_blocks <= sm_count) launch_router_one<1, 1, kRouterChunkFew, PACKED>(a, s);
+    else if (token_blocks <= 2 * (int64_t)sm_count) launch_router_one<2, 1, kRouterChunkFew, PACKED>(a, s);
+    else launch_router_one<4, 1, kRouterChunkFew, PACKED>(a, s);
+  } else {
+    a.wg = wg_many;
+    if (token_blocks <= 8 * (int64_t)sm_count) launch_router_one<4, 2, kRouterChunkMany, PACKED>(a, s);
+    else launch_router_one<4, 4, kRouterChunkMany, PACKED>(a, s);
+  }
+  return 0;
+}
+
+__global__ void __launch_bounds__(128)
+k_router_topk(const float* __restrict__ logits, float* __restrict__ router_out, int T, int E, int k, int sigmoid) {
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= T) return;
+  warp_topk(logits + (size_t)t * E, E, k, sigmoid, router_out + (size_t)t * k * 2);
 }
 
 // ---------------------------------------------------------------------------

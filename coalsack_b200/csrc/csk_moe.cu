@@ -33,6 +33,9 @@ struct csk_moe_layer {
   size_t stage_bytes = 0;
 
   float* d_wg = nullptr;   // [E,H]
+  float* d_wg_few = nullptr;   // the same repacked for the router kernel's two chunk widths
+  float* d_wg_many = nullptr;
+  int* d_route_cnt = nullptr;  // [max_T] tickets of the router's token blocks (zero between launches)
   float* d_logits = nullptr;  // [max_T,E] router scratch
   float* d_rbias = nullptr;
   bool router_set = false, has_rbias = false;
@@ -53,7 +56,7 @@ struct csk_moe_layer {
   int* d_out_row_map = nullptr;  // [max_rows] (expert-parallel receive side)
   int* d_seg = nullptr;          // [2*1024+2] segment plan (expert-parallel receive side)
   RowTile* d_tiles = nullptr;
-  int* d_meta = nullptr;  // 8 ints
+  int* d_meta = nullptr;  // 16 ints: [0..7] rewritten by every permutation, [8] the router's status word
   int* h_meta = nullptr;  // pinned mirror
   int64_t* h_counts64 = nullptr;
 
@@ -131,12 +134,23 @@ struct StageTimer {
 int launch_router(csk_moe_layer* L, const float* d_hidden, int64_t T, float* d_router,
                   cudaStream_t s) {
   if (!L->router_set) return fail(L, CSK_ERR_INVALID, "router weights were never set");
-  launch_router_logits(d_hidden, L->d_wg, L->has_rbias ? L->d_rbias : nullptr, L->d_logits, T, L->H, L->E,
-                       L->sm_count, s);
-  k_router_topk<<<(unsigned)((T + 3) / 4), 128, 0, s>>>(L->d_logits, d_router, (int)T, L->E, L->k,
-                                                         L->cfg.sigmoid_gating);
+  if (reinterpret_cast<uintptr_t>(d_hidden) % 16)
+    return fail(L, CSK_ERR_INVALID, "hidden states must be 16-byte aligned");
+  RouterArgs a{};
+  a.hidden = d_hidden;
+  a.bias = L->has_rbias ? L->d_rbias : nullptr;
+  a.logits = L->d_logits;
+  a.router_out = d_router;
+  a.counters = L->d_route_cnt;
+  a.status = L->d_meta + 8;
+  a.T = (int)T;
+  a.H = L->H;
+  a.E = L->E;
+  a.k = L->k;
+  a.sigmoid = L->cfg.sigmoid_gating;
+  launch_router_logits<true>(a, L->d_wg_few, L->d_wg_many, L->sm_count, s);
   CSK_CUDA(L, cudaGetLastError());
-  L->last.launches += 2;
+  L->last.launches += 1;
   return CSK_OK;
 }
 
@@ -168,8 +182,18 @@ int launch_permute(csk_moe_layer* L, const float* d_hidden, const float* d_route
   return CSK_OK;
 }
 
-template <int NT8, int KSPLIT>
-void launch_stream_pair(csk_moe_layer* L, const __half* x16, float* y, int ldy, cudaStream_t s,
+// warps per CTA and ring stages of the streaming kernel: whole-contraction variant, split-contraction variant
+#ifndef CSK_STREAM_W
+#define CSK_STREAM_W 10
+#endif
+#ifndef CSK_STREAM_S
+#define CSK_STREAM_S 3
+#endif
+#ifndef CSK_STREAM_KS
+#define CSK_STREAM_KS 3
+#endif
+template <int NT8, int KSPLIT, int W, int NSTG>
+void launch_stream_pair(csk_moe_layer* L, const __half* x16, float* y, int ldy, int x_rows, cudaStream_t s,
                         StageTimer& tm) {
   StreamArgs a{};
   a.weights = L->d_weights;
@@ -181,8 +205,12 @@ void launch_stream_pair(csk_moe_layer* L, const __half* x16, float* y, int ldy, 
   a.act = L->cfg.activation;
   a.F = L->F;
   a.meta = L->d_meta;
+  a.x_rows = x_rows;
   // every CTA takes one contiguous range of work units; as many CTAs as fit at once
-  auto grid_for_smem = [&](size_t smem) { return L->sm_count * (int)std::max<size_t>(1, std::min<size_t>(4, (227 * 1024) / smem)); };
+  const size_t per_sm_limit = W > 8 ? 2 : 3;
+  auto grid_for_smem = [&](size_t smem) {
+    return L->sm_count * (int)std::max<size_t>(1, std::min<size_t>(per_sm_limit, (227 * 1024) / (smem + 1024)));
+  };
   // gate/up + activation
   a.mat_offset = L->off_gu;
   a.L = L->Lgu;
@@ -190,8 +218,8 @@ void launch_stream_pair(csk_moe_layer* L, const __half* x16, float* y, int ldy, 
   a.ldx = L->ldx;
   a.a_out = L->d_a16;
   a.lda = L->lda;
-  size_t smem = stream_smem_bytes(NT8, L->Lgu.k_pad(), KSPLIT, true);
-  k_stream<NT8, true, KSPLIT><<<grid_for_smem(smem), kStreamThreads, smem, s>>>(a);
+  size_t smem = stream_smem_bytes(x_rows, NT8, L->Lgu.k_pad(), KSPLIT, true, W, NSTG);
+  k_stream<NT8, true, KSPLIT, W, NSTG><<<grid_for_smem(smem), W * 32, smem, s>>>(a);
   tm.mark();
   // down
   a.mat_offset = L->off_d;
@@ -200,23 +228,23 @@ void launch_stream_pair(csk_moe_layer* L, const __half* x16, float* y, int ldy, 
   a.ldx = L->lda;
   a.y_out = y;
   a.ldy = ldy;
-  smem = stream_smem_bytes(NT8, L->Ld.k_pad(), KSPLIT, false);
-  k_stream<NT8, false, KSPLIT><<<grid_for_smem(smem), kStreamThreads, smem, s>>>(a);
+  smem = stream_smem_bytes(x_rows, NT8, L->Ld.k_pad(), KSPLIT, false, W, NSTG);
+  k_stream<NT8, false, KSPLIT, W, NSTG><<<grid_for_smem(smem), W * 32, smem, s>>>(a);
   tm.mark();
   L->last.launches += 2;
 }
 
-template <int NT8, int KSPLIT>
+template <int NT8, int KSPLIT, int W, int NSTG>
 cudaError_t stream_prepare_one() {
-  cudaError_t e = cudaFuncSetAttribute(k_stream<NT8, true, KSPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+  cudaError_t e = cudaFuncSetAttribute(k_stream<NT8, true, KSPLIT, W, NSTG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
   if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(k_stream<NT8, false, KSPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    e = cudaFuncSetAttribute(k_stream<NT8, false, KSPLIT, W, NSTG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
   return e;
 }
 cudaError_t stream_prepare_device() {
-  cudaError_t e = stream_prepare_one<1, 1>();
-  if (e == cudaSuccess) e = stream_prepare_one<1, 8>();
-  if (e == cudaSuccess) e = stream_prepare_one<2, 1>();
+  cudaError_t e = stream_prepare_one<1, 1, CSK_STREAM_W, CSK_STREAM_S>();
+  if (e == cudaSuccess) e = stream_prepare_one<1, 8, 8, CSK_STREAM_KS>();
+  if (e == cudaSuccess) e = stream_prepare_one<2, 1, 8, 3>();
   return e;
 }
 
@@ -239,8 +267,8 @@ int tile_rows_for(const csk_moe_layer* L, int path, int64_t rows) {
 
 // grouped gate/up + activation + down over the row tiles listed in d_tiles;
 // x16 holds the grouped rows; output rows go to y (through out_row_map if set)
-int launch_experts(csk_moe_layer* L, int path, int tile_rows, int64_t n_rows_hint, const __half* x16, float* y,
-                   int ldy, const int* out_row_map, cudaStream_t s, StageTimer& tm) {
+int launch_experts(csk_moe_layer* L, int path, int tile_rows, int64_t n_rows_hint, int64_t rows_per_expert_max,
+                   const __half* x16, float* y, int ldy, const int* out_row_map, cudaStream_t s, StageTimer& tm) {
   if (path == CSK_PATH_TILE) {
     if (x16 != L->d_x16) return fail(L, CSK_ERR_INVALID, "the tile path reads the handle's own row buffer");
     int rc = tile_launch(L->tile, L->d_weights, L->expert_stride, L->off_tgu, L->off_td, L->off_bias,
@@ -251,18 +279,22 @@ int launch_experts(csk_moe_layer* L, int path, int tile_rows, int64_t n_rows_hin
     L->last.launches += 2;
   } else {
     if (out_row_map) return fail(L, CSK_ERR_INVALID, "row map needs the tile path");
-    const size_t need = std::max(stream_smem_bytes(tile_rows / 8, L->Lgu.k_pad(), 8, true),
-                                 stream_smem_bytes(tile_rows / 8, L->Ld.k_pad(), 8, false));
+    // no tile holds more rows than its expert received
+    const int x_rows = (int)std::max<int64_t>(1, std::min<int64_t>(tile_rows, rows_per_expert_max));
+    const int kp = std::max(L->Lgu.k_pad(), L->Ld.k_pad());
+    const size_t need = tile_rows == 8 ? std::max(stream_smem_bytes(x_rows, 1, kp, 8, true, 8, CSK_STREAM_KS),
+                                                  stream_smem_bytes(x_rows, 1, kp, 1, true, CSK_STREAM_W, CSK_STREAM_S))
+                                       : stream_smem_bytes(x_rows, 2, kp, 1, true, 8, 3);
     if (need > 200 * 1024)
       return fail(L, CSK_ERR_NOMEM, "hidden/ffn dimension too large for the streaming kernel's row buffer");
     if (tile_rows == 8) {
       if (n_rows_hint <= 32) {
-        launch_stream_pair<1, 8>(L, x16, y, ldy, s, tm);  // a handful of rows: split the contraction over the warps
+        launch_stream_pair<1, 8, 8, CSK_STREAM_KS>(L, x16, y, ldy, x_rows, s, tm);  // a handful of rows: split the contraction over the warps
       } else {
-        launch_stream_pair<1, 1>(L, x16, y, ldy, s, tm);
+        launch_stream_pair<1, 1, CSK_STREAM_W, CSK_STREAM_S>(L, x16, y, ldy, x_rows, s, tm);
       }
     } else {
-      launch_stream_pair<2, 1>(L, x16, y, ldy, s, tm);
+      launch_stream_pair<2, 1, 8, 3>(L, x16, y, ldy, x_rows, s, tm);
     }
   }
   CSK_CUDA(L, cudaGetLastError());
@@ -271,9 +303,10 @@ int launch_experts(csk_moe_layer* L, int path, int tile_rows, int64_t n_rows_hin
 }
 
 int check_device_status(csk_moe_layer* L, cudaStream_t s) {
-  CSK_CUDA(L, cudaMemcpyAsync(L->h_meta, L->d_meta, sizeof(int) * 8, cudaMemcpyDeviceToHost, s));
+  CSK_CUDA(L, cudaMemcpyAsync(L->h_meta, L->d_meta, sizeof(int) * 16, cudaMemcpyDeviceToHost, s));
   CSK_CUDA(L, cudaStreamSynchronize(s));
-  const int st = L->h_meta[3];
+  const int st = L->h_meta[3] | L->h_meta[8];
+  if (L->h_meta[8]) cudaMemsetAsync(L->d_meta + 8, 0, sizeof(int), s);
   if (st & kDevErrExpertRange)
     return fail(L, CSK_ERR_INVALID, "expert_idx out of range in router output");
   if (st & kDevErrCapacity)
@@ -326,7 +359,7 @@ int forward_dev(csk_moe_layer* L, const float* d_hidden, int64_t T, const float*
                           L->ldx, L->max_rows, s);
   if (rc) return rc;
   tm.mark();
-  rc = launch_experts(L, path, tile_rows, rows, L->d_x16, L->d_y, L->H, nullptr, s, tm);
+  rc = launch_experts(L, path, tile_rows, rows, T, L->d_x16, L->d_y, L->H, nullptr, s, tm);
   if (rc) return rc;
   k_combine<<<(unsigned)T, 256, 0, s>>>(router, L->d_row_of_pair, L->d_y, L->H, d_out, (int)T, L->k,
                                         L->H, L->cfg.weight_before_ffn, only_expert >= 0);
@@ -446,6 +479,10 @@ int csk_moe_create(const csk_moe_config* cfg, csk_moe_layer** out) {
   L->stage_bytes = (size_t)L->H * L->F / 32 * 17;
   CK(cudaMalloc(&L->d_stage, 3 * L->stage_bytes));
   CK(cudaMalloc(&L->d_wg, sizeof(float) * L->E * L->H));
+  CK(cudaMalloc(&L->d_wg_few, sizeof(float) * router_packed_floats(L->E, L->H, kRouterChunkFew)));
+  CK(cudaMalloc(&L->d_wg_many, sizeof(float) * router_packed_floats(L->E, L->H, kRouterChunkMany)));
+  CK(cudaMalloc(&L->d_route_cnt, sizeof(int) * L->max_T));
+  CK(cudaMemset(L->d_route_cnt, 0, sizeof(int) * L->max_T));
   CK(cudaMalloc(&L->d_logits, sizeof(float) * L->max_T * L->E));
   CK(cudaMalloc(&L->d_rbias, sizeof(float) * L->E));
   CK(cudaMalloc(&L->d_hidden, sizeof(float) * L->max_T * L->H));
@@ -464,9 +501,9 @@ int csk_moe_create(const csk_moe_config* cfg, csk_moe_layer** out) {
   CK(cudaMalloc(&L->d_out_row_map, sizeof(int) * L->max_rows));
   CK(cudaMalloc(&L->d_seg, sizeof(int) * (3 * 1024 + 8)));
   CK(cudaMalloc(&L->d_tiles, sizeof(RowTile) * L->max_tiles));
-  CK(cudaMalloc(&L->d_meta, sizeof(int) * 8));
-  CK(cudaMemset(L->d_meta, 0, sizeof(int) * 8));
-  CK(cudaMallocHost(&L->h_meta, sizeof(int) * 8));
+  CK(cudaMalloc(&L->d_meta, sizeof(int) * 16));
+  CK(cudaMemset(L->d_meta, 0, sizeof(int) * 16));
+  CK(cudaMallocHost(&L->h_meta, sizeof(int) * 16));
   CK(cudaMallocHost(&L->h_counts64, sizeof(int64_t) * L->E));
   CK(router_prepare_device());
   CK(stream_prepare_device());
@@ -492,7 +529,7 @@ int csk_moe_destroy(csk_moe_layer* L) {
   for (auto& g : L->graphs)
     if (g.exec) cudaGraphExecDestroy(g.exec);
   tile_destroy(L->tile);
-  void* dev[] = {L->d_weights, L->d_resident, L->d_stage, L->d_wg, L->d_logits, L->d_rbias, L->d_hidden,
+  void* dev[] = {L->d_weights, L->d_resident, L->d_stage, L->d_wg, L->d_wg_few, L->d_wg_many, L->d_route_cnt, L->d_logits, L->d_rbias, L->d_hidden,
                  L->d_router, L->d_out, L->d_x16, L->d_a16, L->d_y, L->d_counts, L->d_offsets,
                  L->d_cursor, L->d_row_of_pair, L->d_out_row_map, L->d_seg, L->d_tiles, L->d_meta};
   for (void* p : dev)
@@ -512,6 +549,11 @@ int csk_moe_set_router(csk_moe_layer* L, const float* gate_w, const float* gate_
   CSK_CUDA(L, cudaSetDevice(L->cfg.device));
   CSK_CUDA(L, cudaMemcpyAsync(L->d_wg, gate_w, sizeof(float) * L->E * L->H, cudaMemcpyHostToDevice,
                               L->stream));
+  k_pack_router<<<grid_for(router_packed_floats(L->E, L->H, kRouterChunkFew), 256, 1024), 256, 0, L->stream>>>(
+      L->d_wg, L->d_wg_few, L->E, L->H, kRouterChunkFew);
+  k_pack_router<<<grid_for(router_packed_floats(L->E, L->H, kRouterChunkMany), 256, 1024), 256, 0, L->stream>>>(
+      L->d_wg, L->d_wg_many, L->E, L->H, kRouterChunkMany);
+  CSK_CUDA(L, cudaGetLastError());
   L->has_rbias = gate_bias != nullptr;
   if (gate_bias)
     CSK_CUDA(L, cudaMemcpyAsync(L->d_rbias, gate_bias, sizeof(float) * L->E, cudaMemcpyHostToDevice,
@@ -856,9 +898,9 @@ int csk_moe_ep_experts_dev(csk_moe_layer* L, const void* d_recv_f16, const int32
   tm.mark();
   int rc;
   if (path == CSK_PATH_TILE) {
-    rc = launch_experts(L, path, tile_rows, total_rows, L->d_x16, d_ret, L->H, L->d_out_row_map, s, tm);
+    rc = launch_experts(L, path, tile_rows, total_rows, total_rows, L->d_x16, d_ret, L->H, L->d_out_row_map, s, tm);
   } else {
-    rc = launch_experts(L, path, tile_rows, total_rows, L->d_x16, L->d_y, L->H, nullptr, s, tm);
+    rc = launch_experts(L, path, tile_rows, total_rows, total_rows, L->d_x16, L->d_y, L->H, nullptr, s, tm);
     if (!rc) {
       k_ep_ungroup<<<grid_for((size_t)total_rows, 8, 8 * L->sm_count), 256, 0, s>>>(
           L->d_y, d_ret, L->H, L->d_out_row_map, (int)total_rows);
@@ -944,7 +986,16 @@ int csk_moe_route_static(const float* d_hidden, int64_t T, int32_t H, const floa
   cudaStream_t s = (cudaStream_t)stream;
   int sms = 148;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  launch_router_logits(d_hidden, d_gate_w, d_gate_bias, logits, T, H, E, sms, s);
+  if (reinterpret_cast<uintptr_t>(d_hidden) % 16 || reinterpret_cast<uintptr_t>(d_gate_w) % 16)
+    return fail(nullptr, CSK_ERR_INVALID, "route_static: hidden states and gate weights must be 16-byte aligned");
+  RouterArgs a{};
+  a.hidden = d_hidden;
+  a.bias = d_gate_bias;
+  a.logits = logits;
+  a.T = (int)T;
+  a.H = H;
+  a.E = E;
+  launch_router_logits<false>(a, d_gate_w, d_gate_w, sms, s);
   k_router_topk<<<(unsigned)((T + 3) / 4), 128, 0, s>>>(logits, d_router_out, (int)T, E, k, sigmoid_gating);
   ce = cudaGetLastError();
   if (ce != cudaSuccess) return fail(nullptr, CSK_ERR_CUDA, "route_static: launch failed: %s", cudaGetErrorString(ce));

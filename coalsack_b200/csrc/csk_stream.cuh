@@ -2,22 +2,28 @@
 // kernel).  Memory-bound by design: every weight byte of every expert that
 // received rows is read once per row tile.
 //
-//   * weights: each warp owns a ring of shared-memory stages; lane 0 keeps it
-//     full with bulk copies (cp.async.bulk, one 544-byte record per copy, an
-//     mbarrier per stage), so the bytes in flight cost no registers.  A stage is
-//     consumed with one conflict-free 128-bit shared load per lane, dequantised
-//     in registers (cvt.e2m1x2 -> half2) and multiplied against the tile's
-//     8*NT8 token rows on the tensor cores (mma.sync m16n8k16, fp16 in, fp32
-//     out).  The E8M0 block scale is applied in fp32 to each 32-column partial
-//     sum, so dequantisation is exact for every scale exponent (a block with
-//     scale byte 0, i.e. 2^-127, contributes zero);
+//   * weights: the records of one 16-row group lie one after the other along
+//     the contraction dimension, so a warp's work is ONE contiguous byte stream.
+//     Each warp owns a ring of 2176-byte shared-memory stages; lane 0 keeps it
+//     full with one bulk copy per stage (cp.async.bulk, an mbarrier per stage),
+//     so the bytes in flight cost no registers, and the copies are large because
+//     an SM starts only about one bulk copy per 70-100 cycles.  A stage holds
+//     four records: gate and up of two k-tiles, or (plain matrix) the records of
+//     four consecutive k-tiles.  A record is consumed with one
+//     conflict-free 128-bit shared load per lane, dequantised in registers
+//     (cvt.e2m1x2 -> half2) and multiplied against the tile's 8*NT8 token rows
+//     on the tensor cores (mma.sync m16n8k16, fp16 in, fp32 out).  The E8M0
+//     block scale is applied in fp32 to each 32-column partial sum, so
+//     dequantisation is exact for every scale exponent (a block with scale
+//     byte 0, i.e. 2^-127, contributes zero);
 //   * token rows: the current row tile sits in shared memory (fp16, copied once
-//     per tile with cp.async); a CTA works through a contiguous range of work
-//     units, so it changes tile rarely and its weight reads are one long stream;
-//   * KSPLIT = 1: a unit is eight neighbouring 16-row groups of a weight matrix,
+//     per tile with cp.async; only as many rows as the batch can put in a tile);
+//     a CTA works through a contiguous range of work units, so it changes tile
+//     rarely and its weight reads are long streams;
+//   * KSPLIT = 1: a unit is W neighbouring 16-row groups of a weight matrix,
 //     one per warp, each warp walking the whole contraction dimension;
-//     KSPLIT = 8: a unit is one group whose contraction dimension is split over
-//     the eight warps (a handful of rows in the batch: more units, more loads in
+//     KSPLIT = W: a unit is one group whose contraction dimension is split over
+//     the warps (a handful of rows in the batch: more units, more loads in
 //     flight), partial sums meet in shared memory.
 //
 // Every wait on a stage's mbarrier is bounded; when one runs out the warp
@@ -75,55 +81,88 @@ struct StreamArgs {
   int has_bias;
   int act;
   int F;                      // ffn dim (bias block: b_up[F], b_gate[F], b_down[H])
+  int x_rows;                 // token rows staged per tile: >= the rows of every tile, <= 8*NT8
 };
 
-constexpr int kStreamWarps = 8;
-constexpr int kStreamThreads = kStreamWarps * 32;
-constexpr int kStreamXPad = 32;  // halves: staggers consecutive token rows by 64 bytes in shared memory
-constexpr int kStreamRingBytes = 3 * 2 * kSubBytes;  // per warp: 3 stages of a gate+up record pair, or 6 of one record
+constexpr int kStreamXPad = 32;      // halves: staggers consecutive token rows by 64 bytes in shared memory
+#ifndef CSK_STREAM_RPS
+#define CSK_STREAM_RPS 4
+#endif
+constexpr int kStreamRecsPerStage = CSK_STREAM_RPS;  // records per ring stage = per bulk copy
+constexpr int kStreamStageBytes = kStreamRecsPerStage * kSubBytes;
 
-__host__ __device__ inline size_t stream_x_bytes(int nt8, int k_pad) {
-  return ((size_t)8 * nt8 * (k_pad + kStreamXPad) * sizeof(__half) + 127) / 128 * 128;
+__host__ __device__ inline size_t stream_x_bytes(int x_rows, int k_pad) {
+  return ((size_t)x_rows * (k_pad + kStreamXPad) * sizeof(__half) + 127) / 128 * 128;
 }
-inline size_t stream_smem_bytes(int nt8, int k_pad, int ksplit, bool gated) {
-  const size_t ring = (size_t)kStreamWarps * kStreamRingBytes;
-  const size_t bars = (size_t)kStreamWarps * 12 * 8;
-  const size_t red = ksplit > 1 ? (size_t)(kStreamWarps - 1) * (gated ? 2 : 1) * nt8 * 4 * 32 * sizeof(float) : 0;
-  return stream_x_bytes(nt8, k_pad) + ring + bars + red + 128;
+inline size_t stream_smem_bytes(int x_rows, int nt8, int k_pad, int ksplit, bool gated, int warps, int stages) {
+  const size_t ring = (size_t)warps * stages * kStreamStageBytes;
+  const size_t bars = (size_t)warps * stages * 8;
+  const size_t red = ksplit > 1 ? (size_t)(warps - 1) * (gated ? 2 : 1) * nt8 * 4 * 32 * sizeof(float) : 0;
+  return stream_x_bytes(x_rows, k_pad) + ring + bars + red + 128;
 }
 
-template <int NT8, bool GATED, int KSPLIT>
-__global__ void __launch_bounds__(kStreamThreads) k_stream(const StreamArgs A) {
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+
+// W warps per CTA.  KSPLIT = 1: a unit is W neighbouring 16-row groups, one per warp;
+// KSPLIT = W: a unit is one group, its k-tiles split over the warps.
+// NSTG = ring stages per warp.
+template <int NT8, bool GATED, int KSPLIT, int W, int NSTG>
+__global__ void __launch_bounds__(W * 32, W > 8 ? 2 : 3) k_stream(const StreamArgs A) {
   constexpr int NACC = GATED ? 2 : 1;
-  constexpr int REC = NACC * kSubBytes;          // bytes of one stage
-  constexpr int NSTG = kStreamRingBytes / REC;   // 3 (gated) or 6 stages per warp
+  constexpr int KPS = kStreamRecsPerStage / NACC;  // k-tiles per stage
+  constexpr int SB = kStreamStageBytes;
+  static_assert(KSPLIT == 1 || KSPLIT == W, "split over all warps or not at all");
   extern __shared__ __align__(128) uint8_t stream_smem[];
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, q = lane & 3;
-  const MatLayout& L = A.L;
+  const MatLayout L = A.L;
+  const int k_tiles = L.k_tiles;
   const int ldxs = L.k_pad() + kStreamXPad;
+  const int x_rows = A.x_rows;
+  const size_t x_bytes = stream_x_bytes(x_rows, L.k_pad());
   __half* xs = reinterpret_cast<__half*>(stream_smem);
-  uint8_t* ring = stream_smem + stream_x_bytes(NT8, L.k_pad()) + (size_t)warp * kStreamRingBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(stream_smem + stream_x_bytes(NT8, L.k_pad()) +
-                                               (size_t)kStreamWarps * kStreamRingBytes) + warp * 12;
+  const uint32_t xs_u32 = smem_u32(xs);
+  const uint32_t ring_u32 = smem_u32(stream_smem + x_bytes) + (uint32_t)warp * (NSTG * SB);
+  const uint32_t bar_u32 = smem_u32(stream_smem + x_bytes + (size_t)W * NSTG * SB) + (uint32_t)warp * (NSTG * 8);
   float(*red)[NACC * NT8 * 4][32] = reinterpret_cast<float(*)[NACC * NT8 * 4][32]>(
-      stream_smem + stream_x_bytes(NT8, L.k_pad()) + (size_t)kStreamWarps * (kStreamRingBytes + 12 * 8));
-  const uint32_t ring_u32 = smem_u32(ring), bar_u32 = smem_u32(bars);
+      stream_smem + x_bytes + (size_t)W * (NSTG * SB + NSTG * 8));
 
   if (lane == 0)
     for (int i = 0; i < NSTG; ++i) mbar_init(bar_u32 + 8u * i, 1);
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   __syncthreads();
 
-  const int groups = L.n_pad() / 16;  // 16-row groups (feature pairs when gated)
-  const int subs_half = GATED ? L.subs / 2 : L.subs;
-  const int units_per_tile = KSPLIT == 1 ? (groups + kStreamWarps - 1) / kStreamWarps : groups;
+  const int groups = L.groups;  // 16-row groups (16 features, gate and up, when GATED)
+  const int units_per_tile = KSPLIT == 1 ? (groups + W - 1) / W : groups;
   const long n_units = (long)(*A.n_tiles_ptr) * units_per_tile;
   // balanced contiguous ranges
   const long u_begin = n_units * blockIdx.x / gridDim.x;
   const long u_end = n_units * (blockIdx.x + 1) / gridDim.x;
-  const size_t kt_stride = L.tile_bytes();
+  const size_t group_bytes = L.group_bytes();
+  const int n_stages = (k_tiles + KPS - 1) / KPS;  // stages of a whole group
+  const int sb = KSPLIT == 1 ? 0 : (int)((long)n_stages * warp / KSPLIT);
+  const int se = KSPLIT == 1 ? n_stages : (int)((long)n_stages * (warp + 1) / KSPLIT);
+
+  // per-lane shared-memory addresses: code words, scale word, token fragments
+  const uint32_t rec_lane = ring_u32 + (uint32_t)lane * 16;
+  const uint32_t scl_lane = ring_u32 + kSubCodeBytes + (uint32_t)g * 4;
+  uint32_t x_lane[NT8];
+#pragma unroll
+  for (int j = 0; j < NT8; ++j) {
+    // lanes whose token row does not exist read the last staged row: their result columns are never stored
+    const int r = min(j * 8 + g, x_rows - 1);
+    x_lane[j] = xs_u32 + (uint32_t)(r * ldxs + q * 8) * 2;
+  }
 
   uint32_t stage_phase = 0;  // bit i = parity to wait for on stage i
   bool waits_ok = true;
@@ -133,29 +172,25 @@ __global__ void __launch_bounds__(kStreamThreads) k_stream(const StreamArgs A) {
     const int tile_i = (int)(u / units_per_tile);
     const int uq = (int)(u % units_per_tile);
     if (tile_i != cur_tile) {
-      // bring the tile's token rows into shared memory (rows beyond the tile's count read as zero)
+      // bring the tile's token rows into shared memory
       __syncthreads();
       rt = A.tiles[tile_i];
       cur_tile = tile_i;
       const int w16 = L.k_pad() / 8;
-      for (int i = threadIdx.x; i < 8 * NT8 * w16; i += kStreamThreads) {
+      const int n_rows = min(rt.rows, x_rows);
+      for (int i = threadIdx.x; i < n_rows * w16; i += W * 32) {
         const int r = i / w16, c = (i % w16) * 8;
-        const bool ok = r < rt.rows;
-        const __half* src = ok ? A.x + (size_t)(rt.row0 + r) * A.ldx + c : A.x;
-        const uint32_t dst = smem_u32(xs + (size_t)r * ldxs + c);
-        const int nbytes = ok ? 16 : 0;
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(nbytes) : "memory");
+        const __half* src = A.x + (size_t)(rt.row0 + r) * A.ldx + c;
+        const uint32_t dst = xs_u32 + (uint32_t)(r * ldxs + c) * 2;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
       }
       asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
       __syncthreads();
     }
-    const int grp = KSPLIT == 1 ? uq * kStreamWarps + warp : uq;
+    const int grp = KSPLIT == 1 ? uq * W + warp : uq;
     const bool active = grp < groups;
-    const int n_tile = grp / subs_half, s = grp % subs_half;
-    const uint8_t* wbase = A.weights + (size_t)rt.expert * A.expert_stride + A.mat_offset +
-                           (size_t)n_tile * L.k_tiles * L.tile_bytes();
-    const uint8_t* p0 = wbase + (size_t)s * kSubBytes;                  // gate (or the only) record
-    const uint8_t* p1 = wbase + (size_t)(s + subs_half) * kSubBytes;    // up record
+    const uint8_t* wsrc =
+        A.weights + (size_t)rt.expert * A.expert_stride + A.mat_offset + (size_t)grp * group_bytes;
 
     float acc[NACC][NT8][4];
 #pragma unroll
@@ -165,82 +200,84 @@ __global__ void __launch_bounds__(kStreamThreads) k_stream(const StreamArgs A) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) acc[m][j][c] = 0.f;
 
-    const int kt_begin = KSPLIT == 1 ? 0 : (int)((long)L.k_tiles * warp / KSPLIT);
-    const int kt_end = KSPLIT == 1 ? L.k_tiles : (int)((long)L.k_tiles * (warp + 1) / KSPLIT);
-
-    if (active && kt_begin < kt_end) {
-      // lane 0 is this warp's producer: stage st <- k-tile kt
-      auto fill = [&](int st, int kt) {
-        const uint32_t bar = bar_u32 + 8u * st, dst = ring_u32 + (uint32_t)st * REC;
-        const size_t o = (size_t)kt * kt_stride;
-        mbar_expect_tx(bar, REC);
-        bulk_load(dst, p0 + o, kSubBytes, bar);
-        if (GATED) bulk_load(dst + kSubBytes, p1 + o, kSubBytes, bar);
+    if (active && sb < se) {
+      // lane 0 is this warp's producer: ring stage st <- stage i of the group's stream
+      auto fill = [&](int st, int i) {
+        const uint32_t bar = bar_u32 + 8u * st;
+        const size_t off = (size_t)i * SB;
+        const uint32_t bytes = (uint32_t)min((size_t)SB, group_bytes - off);
+        mbar_expect_tx(bar, bytes);
+        bulk_load(ring_u32 + (uint32_t)st * SB, wsrc + off, bytes, bar);
       };
       if (lane == 0)
-        for (int i = 0; i < NSTG && kt_begin + i < kt_end; ++i) fill(i, kt_begin + i);
+        for (int i = 0; i < NSTG && sb + i < se; ++i) fill(i, sb + i);
       __syncwarp();
 
-      int st = 0;
-      for (int kt = kt_begin; kt < kt_end; ++kt) {
-        if (waits_ok) {
-          const uint32_t bar = bar_u32 + 8u * st, par = (stage_phase >> st) & 1u;
-          if (!mbar_try(bar, par)) {
-            const long long t0 = clock64();
-            while (!mbar_try(bar, par)) {
-              if (clock64() - t0 > kWaitBudget) {
-                waits_ok = false;
-                if (lane == 0) atomicOr(&A.meta[3], kDevErrWaitTimeout);
-                break;
+      for (int i0 = sb; i0 < se; i0 += NSTG) {
+#pragma unroll
+        for (int st = 0; st < NSTG; ++st) {
+          const int i = i0 + st;
+          if (i >= se) break;
+          if (waits_ok) {
+            const uint32_t bar = bar_u32 + 8u * st, par = (stage_phase >> st) & 1u;
+            if (!mbar_try(bar, par)) {
+              const long long t0 = clock64();
+              while (!mbar_try(bar, par)) {
+                if (clock64() - t0 > kWaitBudget) {
+                  waits_ok = false;
+                  if (lane == 0) atomicOr(&A.meta[3], kDevErrWaitTimeout);
+                  break;
+                }
               }
             }
           }
-        }
-        stage_phase ^= 1u << st;
-        const uint8_t* rec = ring + (size_t)st * REC;
-        uint4 c[NACC];
-        uint32_t sc[NACC];
+          stage_phase ^= 1u << st;
 #pragma unroll
-        for (int m = 0; m < NACC; ++m) {
-          c[m] = *reinterpret_cast<const uint4*>(rec + m * kSubBytes + lane * 16);
-          sc[m] = *reinterpret_cast<const uint32_t*>(rec + m * kSubBytes + kSubCodeBytes + g * 4);
-        }
+          for (int kk = 0; kk < KPS; ++kk) {
+            const int kt = i * KPS + kk;
+            if (kt >= k_tiles) break;  // the last stage of a group may hold fewer k-tiles
+            const uint32_t xk = (uint32_t)kt * (kTileK * 2);  // byte offset of the k-tile in a token row
+            uint4 c[NACC];
+            uint32_t sc[NACC];
 #pragma unroll
-        for (int b = 0; b < 2; ++b) {
-          uint32_t af[NACC][2][4];  // [matrix][k16 step][a0..a3]
-          float s_lo[NACC], s_hi[NACC];
+            for (int m = 0; m < NACC; ++m) {
+              c[m] = lds128(rec_lane + st * SB + (kk * NACC + m) * kSubBytes);
+              sc[m] = lds32(scl_lane + st * SB + (kk * NACC + m) * kSubBytes);
+            }
 #pragma unroll
-          for (int m = 0; m < NACC; ++m) {
-            uint32_t hlo[4], hhi[4];
-            dequant_word(b ? c[m].y : c[m].x, hlo);  // row g
-            dequant_word(b ? c[m].w : c[m].z, hhi);  // row g+8
-            af[m][0][0] = hlo[0]; af[m][0][1] = hhi[0]; af[m][0][2] = hlo[1]; af[m][0][3] = hhi[1];
-            af[m][1][0] = hlo[2]; af[m][1][1] = hhi[2]; af[m][1][2] = hlo[3]; af[m][1][3] = hhi[3];
-            s_lo[m] = b ? scale_of<1>(sc[m]) : scale_of<0>(sc[m]);
-            s_hi[m] = b ? scale_of<3>(sc[m]) : scale_of<2>(sc[m]);
-          }
+            for (int b = 0; b < 2; ++b) {
+              // the gate and the up record of a k-tile share the token fragments
+              uint4 xb[NT8];
 #pragma unroll
-          for (int j = 0; j < NT8; ++j) {
-            if (j * 8 < rt.rows) {  // warp-uniform: skip row groups the tile does not have
-              const uint4 xb =
-                  *reinterpret_cast<const uint4*>(xs + (size_t)(j * 8 + g) * ldxs + kt * kTileK + b * 32 + q * 8);
+              for (int j = 0; j < NT8; ++j)
+                if (j == 0 || j * 8 < rt.rows) xb[j] = lds128(x_lane[j] + xk + b * 64);
 #pragma unroll
               for (int m = 0; m < NACC; ++m) {
-                float t[4];
-                mma16816_first(t, af[m][0], xb.x, xb.y);
-                mma16816(t, af[m][1], xb.z, xb.w);
-                acc[m][j][0] = fmaf(t[0], s_lo[m], acc[m][j][0]);
-                acc[m][j][1] = fmaf(t[1], s_lo[m], acc[m][j][1]);
-                acc[m][j][2] = fmaf(t[2], s_hi[m], acc[m][j][2]);
-                acc[m][j][3] = fmaf(t[3], s_hi[m], acc[m][j][3]);
+                uint32_t lo[4], hi[4];
+                dequant_word(b ? c[m].y : c[m].x, lo);  // row g
+                dequant_word(b ? c[m].w : c[m].z, hi);  // row g+8
+                const uint32_t a0[4] = {lo[0], hi[0], lo[1], hi[1]}, a1[4] = {lo[2], hi[2], lo[3], hi[3]};
+                const float s_lo = b ? scale_of<1>(sc[m]) : scale_of<0>(sc[m]);
+                const float s_hi = b ? scale_of<3>(sc[m]) : scale_of<2>(sc[m]);
+#pragma unroll
+                for (int j = 0; j < NT8; ++j) {
+                  if (j == 0 || j * 8 < rt.rows) {  // warp-uniform: skip row groups the tile does not have
+                    float t[4];
+                    mma16816_first(t, a0, xb[j].x, xb[j].y);
+                    mma16816(t, a1, xb[j].z, xb[j].w);
+                    acc[m][j][0] = fmaf(t[0], s_lo, acc[m][j][0]);
+                    acc[m][j][1] = fmaf(t[1], s_lo, acc[m][j][1]);
+                    acc[m][j][2] = fmaf(t[2], s_hi, acc[m][j][2]);
+                    acc[m][j][3] = fmaf(t[3], s_hi, acc[m][j][3]);
+                  }
+                }
               }
             }
           }
+          // the stage's bytes are in registers: refill it (every lane has read before lane 0 goes on)
+          __syncwarp();
+          if (lane == 0 && i + NSTG < se) fill(st, i + NSTG);
         }
-        // the stage's bytes are in registers: refill it (every lane has read before lane 0 goes on)
-        __syncwarp();
-        if (lane == 0 && kt + NSTG < kt_end) fill(st, kt + NSTG);
-        if (++st == NSTG) st = 0;
       }
     }
 
@@ -266,7 +303,7 @@ __global__ void __launch_bounds__(kStreamThreads) k_stream(const StreamArgs A) {
               const int r = (m * NT8 + j) * 4 + c;
               float v = acc[m][j][c];
 #pragma unroll
-              for (int w = 0; w < kStreamWarps - 1; ++w) v += red[w][r][lane];
+              for (int w = 0; w < W - 1; ++w) v += red[w][r][lane];
               acc[m][j][c] = v;
             }
       }
@@ -276,7 +313,7 @@ __global__ void __launch_bounds__(kStreamThreads) k_stream(const StreamArgs A) {
           reinterpret_cast<const float*>(A.weights + (size_t)rt.expert * A.expert_stride + A.bias_offset);
 #pragma unroll
       for (int hrow = 0; hrow < 2; ++hrow) {
-        const int n = n_tile * L.rows_per_tile() + s * 16 + g + hrow * 8;  // feature / output index
+        const int n = grp * 16 + g + hrow * 8;  // feature / output index
         if (n >= L.N) continue;
         float bu = 0.f, bg = 0.f, bd = 0.f;
         if (A.has_bias) {
