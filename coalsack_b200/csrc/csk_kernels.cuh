@@ -730,6 +730,24 @@ __global__ void k_combine(const float* __restrict__ router_out, const int* __res
   }
 }
 
+// Router output with the rows of odd-numbered tokens that chose a replicated
+// expert redirected to the slot of its second copy.
+__global__ void k_ep_replicas(const float* __restrict__ router, float* __restrict__ out, int n_pairs, int k, int E,
+                              const int* __restrict__ replica_of) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_pairs; i += gridDim.x * blockDim.x) {
+    const float ef = router[2 * i];
+    const int e = (int)ef;
+    const int t = i / k;
+    float o = ef;
+    if (e >= 0 && e < E && (t & 1)) {
+      const int s = replica_of[e];
+      if (s >= 0) o = (float)s;
+    }
+    out[2 * i] = o;
+    out[2 * i + 1] = router[2 * i + 1];
+  }
+}
+
 // ---------------------------------------------------------------------------
 // Expert-parallel receive side.  Rows arrive as n_src segments (one per source
 // device), each ordered by local expert; the contractions want them grouped by

@@ -44,6 +44,9 @@ struct csk_moe_layer {
   int max_tiles = 0;
   float* d_hidden = nullptr;  // [max_T,H] staging for the host entry points
   float* d_router = nullptr;  // [max_T,k,2]
+  float* d_router_phys = nullptr;  // the same with replicated experts' odd tokens redirected (expert-parallel dispatch)
+  int* d_replica_of = nullptr;     // [E] slot of an expert's second copy or -1
+  bool has_replicas = false;
   float* d_out = nullptr;     // [max_T,H]
   __half* d_x16 = nullptr;    // [max_rows+pad, ldx]
   __half* d_a16 = nullptr;    // [max_rows+pad, lda]
@@ -487,6 +490,8 @@ int csk_moe_create(const csk_moe_config* cfg, csk_moe_layer** out) {
   CK(cudaMalloc(&L->d_rbias, sizeof(float) * L->E));
   CK(cudaMalloc(&L->d_hidden, sizeof(float) * L->max_T * L->H));
   CK(cudaMalloc(&L->d_router, sizeof(float) * L->max_T * L->k * 2));
+  CK(cudaMalloc(&L->d_router_phys, sizeof(float) * L->max_T * L->k * 2));
+  CK(cudaMalloc(&L->d_replica_of, sizeof(int) * L->E));
   CK(cudaMalloc(&L->d_out, sizeof(float) * L->max_T * L->H));
   const size_t pad_rows = kTileM;
   CK(cudaMalloc(&L->d_x16, sizeof(__half) * (L->max_rows + pad_rows) * L->ldx));
@@ -529,7 +534,7 @@ int csk_moe_destroy(csk_moe_layer* L) {
   for (auto& g : L->graphs)
     if (g.exec) cudaGraphExecDestroy(g.exec);
   tile_destroy(L->tile);
-  void* dev[] = {L->d_weights, L->d_resident, L->d_stage, L->d_wg, L->d_wg_few, L->d_wg_many, L->d_route_cnt, L->d_logits, L->d_rbias, L->d_hidden,
+  void* dev[] = {L->d_router_phys, L->d_replica_of, L->d_weights, L->d_resident, L->d_stage, L->d_wg, L->d_wg_few, L->d_wg_many, L->d_route_cnt, L->d_logits, L->d_rbias, L->d_hidden,
                  L->d_router, L->d_out, L->d_x16, L->d_a16, L->d_y, L->d_counts, L->d_offsets,
                  L->d_cursor, L->d_row_of_pair, L->d_out_row_map, L->d_seg, L->d_tiles, L->d_meta};
   for (void* p : dev)
@@ -864,11 +869,40 @@ int csk_moe_ep_dispatch_dev(csk_moe_layer* L, const float* d_hidden, int64_t T, 
     CSK_CUDA(L, cudaMemcpyAsync(L->d_router, d_router_in, sizeof(float) * T * L->k * 2,
                                 cudaMemcpyDeviceToDevice, s));
   }
+  const float* router = L->d_router;
+  if (L->has_replicas) {
+    k_ep_replicas<<<grid_for((size_t)T * L->k, 256, 4 * L->sm_count), 256, 0, s>>>(
+        L->d_router, L->d_router_phys, (int)(T * L->k), L->k, L->E, L->d_replica_of);
+    CSK_CUDA(L, cudaGetLastError());
+    router = L->d_router_phys;
+  }
   // group by global expert id; no tiles are built here (e_count = 0)
-  int rc = launch_permute(L, d_hidden, L->d_router, T, -1, 8, 0, 0, (__half*)d_send_f16, L->ldx,
+  int rc = launch_permute(L, d_hidden, router, T, -1, 8, 0, 0, (__half*)d_send_f16, L->ldx,
                           T * L->k, s);
   if (rc) return rc;
   CSK_CUDA(L, cudaMemcpyAsync(d_counts, L->d_counts, sizeof(int) * L->E, cudaMemcpyDeviceToDevice, s));
+  return CSK_OK;
+}
+
+int csk_moe_ep_set_replicas(csk_moe_layer* L, const int32_t* replica_of) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  CSK_CUDA(L, cudaSetDevice(L->cfg.device));
+  if (!replica_of) {
+    L->has_replicas = false;
+    return CSK_OK;
+  }
+  bool any = false;
+  for (int e = 0; e < L->E; ++e) {
+    const int s = replica_of[e];
+    if (s < -1 || s >= L->E || s == e)
+      return fail(L, CSK_ERR_INVALID, "replica_of[%d] = %d is not -1 or another expert slot below %d", e, s, L->E);
+    if (s >= 0 && replica_of[s] >= 0)
+      return fail(L, CSK_ERR_INVALID, "slot %d is a replica of expert %d and cannot have a replica itself", s, e);
+    any = any || s >= 0;
+  }
+  CSK_CUDA(L, cudaMemcpyAsync(L->d_replica_of, replica_of, sizeof(int) * L->E, cudaMemcpyHostToDevice, L->stream));
+  CSK_CUDA(L, cudaStreamSynchronize(L->stream));
+  L->has_replicas = any;
   return CSK_OK;
 }
 

@@ -31,6 +31,91 @@ def strided_placement(E: int, world: int) -> np.ndarray:
     return np.array([(p % per) * world + p // per for p in range(E)], dtype=np.int64)
 
 
+def _lpt(items, world, cap):
+    """items: (load, expert, copy).  Longest-processing-time packing into `world` bins of
+    `cap` slots, the two copies of an expert never in one bin."""
+    bins = [[] for _ in range(world)]
+    tot = np.zeros(world)
+    for it in sorted(items, key=lambda x: (-x[0], x[1], x[2])):
+        ok = [i for i in range(world) if len(bins[i]) < cap and all(o[1] != it[1] for o in bins[i])]
+        r = min(ok, key=lambda i: (tot[i], i))
+        bins[r].append(it)
+        tot[r] += it[0]
+    return bins, float(tot.max())
+
+
+class Placement:
+    """slots[p] = logical expert held by physical slot p (-1: empty); replica_of[p] = slot
+    of the second copy of the expert whose first copy is slot p, else -1."""
+
+    def __init__(self, slots, replica_of, world):
+        self.slots = np.asarray(slots, dtype=np.int64)
+        self.replica_of = np.asarray(replica_of, dtype=np.int32)
+        self.world = world
+        self.per_rank = len(self.slots) // world
+
+    @property
+    def n_slots(self):
+        return len(self.slots)
+
+    def is_primary(self):
+        """mask of the slots the router may select"""
+        rep = set(int(s) for s in self.replica_of if s >= 0)
+        return np.array([e >= 0 and p not in rep for p, e in enumerate(self.slots)])
+
+
+def plan_placement(load, world: int, extra_slots: int = 0) -> Placement:
+    """Placement of E experts on `world` ranks from a measured load per expert (rows it
+    received in a calibration batch).  E/world (+ extra_slots) slots per rank; the heaviest
+    experts get a second copy on another rank while that lowers the most loaded rank (each
+    copy then serves every other token).  Deterministic: every rank computes the same plan."""
+    load = np.asarray(load, dtype=np.float64)
+    E = load.shape[0]
+    cap = E // world + extra_slots
+    items = [(load[e], e, 0) for e in range(E)]
+    bins, worst = _lpt(items, world, cap)
+    free = world * extra_slots
+    split = set()
+    while free > 0:
+        cand = [e for e in np.argsort(-load, kind="stable") if int(e) not in split]
+        if not cand:
+            break
+        e = int(cand[0])
+        trial = [it for it in items if it[1] != e] + [(load[e] / 2, e, 0), (load[e] / 2, e, 1)]
+        tb, tw = _lpt(trial, world, cap)
+        if tw >= worst:
+            break
+        items, bins, worst = trial, tb, tw
+        split.add(e)
+        free -= 1
+    slots = -np.ones(world * cap, dtype=np.int64)
+    where = {}
+    for r, b in enumerate(bins):
+        for j, it in enumerate(sorted(b, key=lambda x: (x[1], x[2]))):
+            slots[r * cap + j] = it[1]
+            where[(it[1], it[2])] = r * cap + j
+    replica_of = -np.ones(world * cap, dtype=np.int32)
+    for e in split:
+        replica_of[where[(e, 0)]] = where[(e, 1)]
+    return Placement(slots, replica_of, world)
+
+
+def balanced_placement(load, world: int) -> np.ndarray:
+    """physical slot -> logical expert, E/world experts per rank, no replicas."""
+    return plan_placement(load, world, 0).slots
+
+
+def calibration_load(shape, hidden: np.ndarray) -> np.ndarray:
+    """Rows per expert that `hidden` [T,H] would route (host arithmetic, ordinary matmul:
+    good enough to size a placement, not used for results)."""
+    Wg, rb = synth.router_weight(shape), synth.router_bias(shape)
+    logits = hidden.astype(np.float32) @ Wg.T
+    if rb is not None:
+        logits = logits + rb
+    top = np.argpartition(-logits, shape.top_k - 1, axis=1)[:, :shape.top_k]
+    return np.bincount(top.ravel(), minlength=shape.num_experts).astype(np.int64)
+
+
 class GpuBackend:
     """The three compute stages on one GPU (torch CUDA tensors in and out)."""
 
@@ -40,26 +125,45 @@ class GpuBackend:
         self.torch = torch
         self.sh = shape
         E = shape.num_experts
-        assert E % world == 0, "experts must divide evenly over the ranks"
-        self.eloc = E // world
+        if placement is None:
+            assert E % world == 0, "experts must divide evenly over the ranks"
+            placement = Placement(np.arange(E), -np.ones(E, dtype=np.int32), world)
+        elif not isinstance(placement, Placement):
+            placement = Placement(np.asarray(placement), -np.ones(len(placement), dtype=np.int32), world)
+        self.placement = placement
+        self.eloc = placement.per_rank
         self.e0 = rank * self.eloc
         self.dev = torch.device("cuda", device_index)
-        self.place = np.arange(E) if placement is None else np.asarray(placement)
-        # under expert parallelism a rank can receive more rows than it sends; size for the worst
-        # case the benchmark configurations produce (all rows of every rank landing here is 8x)
-        self.layer = MoeLayer.from_shape(shape, device=device_index, max_tokens=max_tokens,
-                                         expert_begin=self.e0, expert_count=self.eloc)
+        # the layer sees physical slots as its experts
+        self.layer = MoeLayer.from_shape(shape.with_(num_experts=placement.n_slots), device=device_index,
+                                         max_tokens=max_tokens, expert_begin=self.e0, expert_count=self.eloc)
         self.pitch = self.layer.ep_row_pitch()
         self.row_dtype = torch.float16
         self.H, self.k = shape.hidden, shape.top_k
 
+    def physical_router(self, Wg, rb):
+        """Router rows in slot order; replica and empty slots get a zero row and a bias no
+        token's logit can beat."""
+        pl = self.placement
+        prim = pl.is_primary()
+        W = np.zeros((pl.n_slots, Wg.shape[1]), dtype=np.float32)
+        b = np.full(pl.n_slots, -1e30, dtype=np.float32)
+        W[prim] = Wg[pl.slots[prim]]
+        b[prim] = 0.0 if rb is None else rb[pl.slots[prim]]
+        return W, (b if (rb is not None or not prim.all()) else None)
+
     def load_synthetic(self):
         sh = self.sh
-        Wg, rb = synth.router_weight(sh), synth.router_bias(sh)
-        self.layer.set_router(Wg[self.place], None if rb is None else rb[self.place])
+        W, b = self.physical_router(synth.router_weight(sh), synth.router_bias(sh))
+        self.layer.set_router(W, b)
         for p in range(self.e0, self.e0 + self.eloc):
-            w = synth.expert_weights(sh, int(self.place[p]))
+            e = int(self.placement.slots[p])
+            if e < 0:
+                continue
+            w = synth.expert_weights(sh, e)
             self.layer.load_expert(p, w["w_up"], w["w_gate"], w["w_down"], w["b_up"], w["b_gate"], w["b_down"])
+        if (self.placement.replica_of >= 0).any():
+            self.layer.ep_set_replicas(self.placement.replica_of)
 
     def stream(self):
         return self.torch.cuda.current_stream(self.dev).cuda_stream
@@ -141,12 +245,16 @@ class EpBench:
         self.torch = torch
         self.sh, self.rank, self.world = sh, rank, world
         self.dev = torch.device("cuda", local)
-        place = strided_placement(sh.num_experts, world) if sh.router_bias == "zipf" else None
+        # expert placement from the load of one calibration batch (every rank's own tokens, summed)
+        h = synth.hidden_states(sh, rep=rank)
+        load = torch.from_numpy(calibration_load(sh, h)).to(self.dev)
+        import torch.distributed as dist
+        dist.all_reduce(load)
+        place = plan_placement(load.cpu().numpy(), world, extra_slots=1 if world > 1 else 0)
         # a rank may receive more rows than it sends when routing is uneven: leave 3x head-room
         self.backend = GpuBackend(sh, rank, world, local, max_tokens=3 * sh.tokens, placement=place)
         self.backend.load_synthetic()
         self.ep = EpLayer(self.backend, world)
-        h = synth.hidden_states(sh, rep=rank)
         self.h_host = torch.from_numpy(h).pin_memory()
         self.out_host = torch.empty_like(self.h_host).pin_memory()
         self.d_hidden = self.h_host.to(self.dev)

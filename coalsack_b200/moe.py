@@ -189,6 +189,16 @@ class MoeLayer:
         self._check(self._lib.csk_moe_ep_combine_dev(self._h, _p(d_back), T, _p(d_out), _p(d_router_out),
                                                      stream))
 
+    def ep_set_replicas(self, replica_of):
+        """replica_of[e] = slot holding a second copy of expert e's weights, or -1 (None: off)."""
+        if replica_of is None:
+            self._check(self._lib.csk_moe_ep_set_replicas(self._h, None))
+            return
+        a = np.ascontiguousarray(replica_of, dtype=np.int32)
+        if a.shape != (self.E,):
+            raise ValueError(f"replica_of must have shape ({self.E},)")
+        self._check(self._lib.csk_moe_ep_set_replicas(self._h, _p(a)))
+
     # -- knobs / observability ---------------------------------------------------
     def set_path(self, path):
         self._check(self._lib.csk_moe_set_path(self._h, path))

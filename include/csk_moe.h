@@ -196,6 +196,14 @@ int csk_moe_ep_experts_dev(csk_moe_layer* layer, const void* d_recv_f16,
                            float* d_ret, void* stream);
 int csk_moe_ep_combine_dev(csk_moe_layer* layer, const float* d_back, int64_t T, float* d_out,
                            float* d_router_out_out, void* stream);
+/* Replicas of heavily loaded experts.  replica_of is [num_experts] int32 (host):
+ * replica_of[e] = s >= 0 says that expert slot s holds a second copy of expert e's
+ * weights; csk_moe_ep_dispatch_dev then sends the rows of every odd-numbered token
+ * that chose e to slot s instead (the router output it reports keeps e).  -1 = no
+ * replica; a null pointer switches the feature off.  The router must never select
+ * a replica slot itself (give it a zero weight row and a very negative bias).
+ * Affects only the csk_moe_ep_* stages.  No counterpart in the reference. */
+int csk_moe_ep_set_replicas(csk_moe_layer* layer, const int32_t* replica_of);
 
 /* ---- knobs and observability ------------------------------------------- */
 int csk_moe_set_path(csk_moe_layer* layer, int32_t path /* CSK_PATH_* */);

@@ -62,3 +62,19 @@ def test_strided_placement_is_a_permutation():
         per = E // N
         for r in range(N):
             assert all(int(e) % N == r for e in p[r * per:(r + 1) * per])
+
+
+def test_balanced_placement_spreads_a_skewed_load():
+    from coalsack_b200.ep import balanced_placement
+    rng = np.random.default_rng(7)
+    for E, N in ((32, 8), (128, 8), (32, 2), (8, 1)):
+        load = (1000.0 / np.sqrt(np.arange(E) + 1.0) + rng.integers(0, 20, E)).round()
+        p = balanced_placement(load, N)
+        assert sorted(p.tolist()) == list(range(E))
+        per = E // N
+        worst = max(load[p[r * per:(r + 1) * per]].sum() for r in range(N))
+        strided = strided_placement(E, N)
+        worst_strided = max(load[strided[r * per:(r + 1) * per]].sum() for r in range(N))
+        assert worst <= worst_strided
+        # no rank can do better than the mean, nor than the single heaviest expert plus the lightest others
+        assert worst >= load.sum() / N - 1e-9

@@ -11,7 +11,7 @@ from tests import cases
 pytestmark = pytest.mark.gpu
 
 
-def run_emulated_ep(torch, sh, N, tokens, Wg, rb, ex, path):
+def run_emulated_ep(torch, sh, N, tokens, Wg, rb, ex, path, replica_of=None):
     E, k, H = sh.num_experts, sh.top_k, sh.hidden
     eloc = E // N
     dev = torch.device("cuda", 0)
@@ -23,6 +23,8 @@ def run_emulated_ep(torch, sh, N, tokens, Wg, rb, ex, path):
                           for n in ("w_up", "w_gate", "w_down", "b_up", "b_gate", "b_down")},
                          ids=range(r * eloc, (r + 1) * eloc))
         lay.set_path(path)
+        if replica_of is not None:
+            lay.ep_set_replicas(replica_of)
         layers.append(lay)
         hs.append(torch.from_numpy(synth.hidden_states(sh, tokens[r], rep=r)).to(dev))
     pitch = layers[0].ep_row_pitch()
@@ -74,3 +76,30 @@ def test_emulated_ep_matches_checker(gpu_lib, port, path, N, tokens):
         assert np.array_equal(ro[..., 0], want_ro[..., 0])
         mx, mr = cases.err_stats(out, want)
         assert mx <= cases.MAX_ABS_OVER_RMS and mr <= cases.MEAN_REL, (path, N, mx, mr)
+
+
+@pytest.mark.parametrize("path", [PATH_STREAM, PATH_TILE])
+def test_emulated_ep_with_replicated_experts(gpu_lib, port, path):
+    """Two ranks, five slots each for eight experts: the planner gives the heaviest experts a
+    second copy; odd tokens go there.  Output and (logical) routing must match the checker."""
+    import torch
+    from coalsack_b200.ep import plan_placement
+    sh = synth.tiny(seed=83, E=8, k=3, H=192, F=160, T=1, has_bias=True)
+    _, Wg, rb, ex = cases.layer_inputs(sh, router_scale=40.0)
+    load = np.array([900, 100, 90, 80, 70, 60, 50, 40])
+    pl = plan_placement(load, 2, extra_slots=1)
+    assert (pl.replica_of >= 0).any() and pl.n_slots == 10
+    prim = pl.is_primary()
+    Wp = np.zeros((pl.n_slots, sh.hidden), dtype=np.float32)
+    bp = np.full(pl.n_slots, -1e30, dtype=np.float32)
+    Wp[prim] = Wg[pl.slots[prim]]
+    bp[prim] = rb[pl.slots[prim]]
+    src = np.where(pl.slots >= 0, pl.slots, 0)           # empty slots carry some expert's weights, never routed
+    exp = {n: (None if ex.get(n) is None else [ex[n][e] for e in src]) for n in ex}
+    shp = sh.with_(num_experts=pl.n_slots)
+    tokens = (37, 64)
+    for out, ro, h in run_emulated_ep(torch, shp, 2, tokens, Wp, bp, exp, path, replica_of=pl.replica_of):
+        want, want_ro = port.moe_layer(h, Wg, rb, ex, sh.top_k, sh.act, nthreads=4)
+        assert np.array_equal(pl.slots[ro[..., 0].astype(np.int64)], want_ro[..., 0].astype(np.int64))
+        mx, mr = cases.err_stats(out, want)
+        assert mx <= cases.MAX_ABS_OVER_RMS and mr <= cases.MEAN_REL, (path, mx, mr)
