@@ -45,6 +45,18 @@ def measured_peaks():
     return {"hbm_gbs": 6650.0, "tflops": 1590.0, "tflops_sustained": 1400.0, "source": "fallback"}
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the dominant kernel, from the ncu captures
+# summarised under profiles/ (single GPU; key = workload name, tokens, kernel)
+MEASURED_TRAFFIC = {
+    ("c1_gptoss20b_prefill4096_zipf", 4096, "k_tile<gated>"): 476.3e6,     # profiles/k_tile_c1_prefill.md
+    ("c3_gptoss120b_decode", 64, "k_stream<gated>"): 953.8e6,             # profiles/k_stream_c3_decode64.md
+}
+
+
+def measured_traffic(sh, kernel, world):
+    return MEASURED_TRAFFIC.get((sh.name, sh.tokens, kernel)) if world == 1 else None
+
+
 class ClockSampler:
     """nvidia-smi samples of SM clock and throttle reasons while the timed region runs."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
@@ -57,7 +69,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.gpu)], stdout=subprocess.PIPE, text=True)
+                                          "-lms", "50", "-i", str(self.gpu)], stdout=subprocess.PIPE, text=True)
             self.th = threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True)
             self.th.start()
         except Exception:
@@ -210,7 +222,21 @@ def run_ours(args):
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
+    # the timed region of a small workload is shorter than nvidia-smi's sampling period: keep the same
+    # steps running (untimed, every rank: the steps are collective under expert parallelism) until the sampler
+    # has seen the GPU under this load for about half a second
+    extra = 0
+    if ms < 600.0:  # ms is the same on every rank (max over ranks)
+        n_extra = int(min(2000, max(0.0, 600.0 - ms) / max(ms / args.steps, 1e-3)))
+        for i in range(n_extra):
+            runner.step_dev()
+            if i % 64 == 63:
+                runner.sync()
+        extra = n_extra
+    torch.cuda.synchronize()
     clocks = sampler.stop() if rank == 0 else None
+    if clocks is not None:
+        clocks["window"] = f"timed region + {extra} more identical steps (untimed)"
     runner.sync()
     ms_per_step = ms / args.steps
     value = T * world / (ms_per_step * 1e-3)
@@ -233,14 +259,27 @@ def run_ours(args):
 
     peaks = measured_peaks()
     rows = stage.get("rows_received", T * k)   # under expert parallelism: rows this rank's experts processed
-    gu_flops = rows * 4.0 * H * sh.ffn     # gate and up projections: 2 * rows * 2F * H
     gu_ms = stage["gate_up_ms"]
-    achieved = gu_flops / (gu_ms * 1e-3) / 1e12 if gu_ms > 0 else 0.0
-    roofline = {"bound": "tensor", "kernel": stage["gate_up_kernel"], "achieved": achieved, "peak": peaks["tflops"],
-                "unit": "TFLOP/s", "frac": achieved / peaks["tflops"], "peak_source": peaks["source"] + " (burst bf16 cuBLAS)",
-                "traffic": None, "ms_per_launch": gu_ms,
-                "layer_tflops": algorithmic_flops(sh, T * world) / (ms_per_step * 1e-3) / 1e12,
-                "stages_ms": {n: stage[n] for n in ("route_ms", "permute_ms", "gate_up_ms", "down_ms", "combine_ms", "total_ms")}}
+    if stage["path"] == "tile":
+        # dense contraction: algorithmic FLOP of the gate and up projections, 2 * rows * 2F * H
+        gu_flops = rows * 4.0 * H * sh.ffn
+        achieved = gu_flops / (gu_ms * 1e-3) / 1e12 if gu_ms > 0 else 0.0
+        roofline = {"bound": "tensor", "kernel": stage["gate_up_kernel"], "achieved": achieved, "peak": peaks["tflops"],
+                    "unit": "TFLOP/s", "frac": achieved / peaks["tflops"],
+                    "peak_source": peaks["source"] + " (burst bf16 cuBLAS)"}
+    else:
+        # weight streaming: algorithmic bytes = the packed gate/up records of every expert that received rows
+        # (544 bytes per 16 features x 64 columns, gate and up), read once per 8- or 16-row tile
+        recs = -(-sh.ffn // 16) * -(-H // 64) * 2
+        gu_bytes = stage.get("row_tiles", 0) * recs * 544.0
+        achieved = gu_bytes / (gu_ms * 1e-3) / 1e9 if gu_ms > 0 else 0.0
+        roofline = {"bound": "hbm", "kernel": stage["gate_up_kernel"], "achieved": achieved, "peak": peaks["hbm_gbs"],
+                    "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+                    "peak_source": peaks["source"] + " (copy bandwidth)"}
+    roofline.update({"traffic": measured_traffic(sh, stage["gate_up_kernel"], world), "ms_per_launch": gu_ms,
+                     "layer_tflops": algorithmic_flops(sh, T * world) / (ms_per_step * 1e-3) / 1e12,
+                     "stages_ms": {n: stage[n] for n in ("route_ms", "permute_ms", "gate_up_ms", "down_ms",
+                                                        "combine_ms", "total_ms")}})
     cb, _ = time_reference(sh, 2, 1) if (world == 1 and not args.skip_cpu) else (None, None)
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -299,6 +338,9 @@ class SingleGpu:
         self.layer.enable_timing(False)
         out = {k: acc[k] / n for k in acc}
         out["path"] = {1: "stream", 2: "tile"}.get(int(round(out["path"])), "?")
+        rows_per_expert, _, _ = self.layer.counters()
+        tr = 16 if self.T * self.sh.top_k > 8 * self.sh.num_experts else 8
+        out["row_tiles"] = int(sum(-(-int(r) // tr) for r in rows_per_expert))
         out["gate_up_kernel"] = "k_stream<gated>" if out["path"] == "stream" else "k_tile<gated>"
         return out
 
