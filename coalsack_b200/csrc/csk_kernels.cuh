@@ -353,56 +353,60 @@ k_router_logits(const RouterArgs A) {
       const float* wp = stages + (size_t)st * stage_floats + lane * LD;
       const float* hp = stages + (size_t)st * stage_floats + (32 + w * TT) * LD;
       const int dc = min(CH, H - ci * CH);
+      if (dc < CH) {
+        // last, partial chunk: the code below always walks CH columns, so the missing ones must
+        // multiply to zero.  Every lane clears the tail of its own expert row (stale but written
+        // only with zeros by anyone) and of the warp's token rows.
+        float* wrow = stages + (size_t)st * stage_floats + lane * LD;
+        for (int c = dc; c < CH; ++c) wrow[c] = 0.f;
+        float* hrow = stages + (size_t)st * stage_floats + (32 + w * TT) * LD;
+        for (int i = 0; i < TT; ++i)
+          for (int c = dc + lane; c < CH; c += 32) hrow[i * LD + c] = 0.f;
+        __syncwarp();
+      }
       if (TT == 1) {
-        // 32-column blocks.  The add chain issues one instruction per four cycles; the loads
-        // and the (independent) products of the NEXT block are written between its adds so
-        // they go into those idle issue slots.
-        const int nblk = dc / 32;
-        float pa[32], pb[32];
-        auto products = [&](int blk, float (&p)[32]) {
+        // 32-column blocks, straight-line code for the whole chunk.  The add chain issues one
+        // instruction per four cycles; the loads and the (independent) products of the NEXT block
+        // are written between its adds so they go into those idle issue slots.
+        constexpr int NBLK = CH / 32;
+        float p[2][32];
+        float a = acc[0];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float4 wv = *reinterpret_cast<const float4*>(wp + blk * 32 + i * 4);
-            const float4 hv = *reinterpret_cast<const float4*>(hp + blk * 32 + i * 4);
-            p[4 * i] = __fmul_rn(hv.x, wv.x);
-            p[4 * i + 1] = __fmul_rn(hv.y, wv.y);
-            p[4 * i + 2] = __fmul_rn(hv.z, wv.z);
-            p[4 * i + 3] = __fmul_rn(hv.w, wv.w);
-          }
-        };
-        // adds of block `p`, products of block `nblk_next` (if any) into `q`
-        auto chain = [&](const float (&p)[32], int next, float (&q)[32]) {
-          float a = acc[0];
-          const bool more = next < nblk;
+        for (int i = 0; i < 8; ++i) {
+          const float4 wv = *reinterpret_cast<const float4*>(wp + i * 4);
+          const float4 hv = *reinterpret_cast<const float4*>(hp + i * 4);
+          p[0][4 * i] = __fmul_rn(hv.x, wv.x);
+          p[0][4 * i + 1] = __fmul_rn(hv.y, wv.y);
+          p[0][4 * i + 2] = __fmul_rn(hv.z, wv.z);
+          p[0][4 * i + 3] = __fmul_rn(hv.w, wv.w);
+        }
+#pragma unroll
+        for (int blk = 0; blk < NBLK; ++blk) {
+          const int cur = blk & 1, nxt = cur ^ 1;
           float4 wv[8], hv[8];
-          if (more) {
+          if (blk + 1 < NBLK) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-              wv[i] = *reinterpret_cast<const float4*>(wp + next * 32 + i * 4);
-              hv[i] = *reinterpret_cast<const float4*>(hp + next * 32 + i * 4);
+              wv[i] = *reinterpret_cast<const float4*>(wp + (blk + 1) * 32 + i * 4);
+              hv[i] = *reinterpret_cast<const float4*>(hp + (blk + 1) * 32 + i * 4);
             }
           }
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            a = __fadd_rn(a, p[4 * i]);
-            if (more) q[4 * i] = __fmul_rn(hv[i].x, wv[i].x);
-            a = __fadd_rn(a, p[4 * i + 1]);
-            if (more) q[4 * i + 1] = __fmul_rn(hv[i].y, wv[i].y);
-            a = __fadd_rn(a, p[4 * i + 2]);
-            if (more) q[4 * i + 2] = __fmul_rn(hv[i].z, wv[i].z);
-            a = __fadd_rn(a, p[4 * i + 3]);
-            if (more) q[4 * i + 3] = __fmul_rn(hv[i].w, wv[i].w);
+            a = __fadd_rn(a, p[cur][4 * i]);
+            if (blk + 1 < NBLK) p[nxt][4 * i] = __fmul_rn(hv[i].x, wv[i].x);
+            a = __fadd_rn(a, p[cur][4 * i + 1]);
+            if (blk + 1 < NBLK) p[nxt][4 * i + 1] = __fmul_rn(hv[i].y, wv[i].y);
+            a = __fadd_rn(a, p[cur][4 * i + 2]);
+            if (blk + 1 < NBLK) p[nxt][4 * i + 2] = __fmul_rn(hv[i].z, wv[i].z);
+            a = __fadd_rn(a, p[cur][4 * i + 3]);
+            if (blk + 1 < NBLK) p[nxt][4 * i + 3] = __fmul_rn(hv[i].w, wv[i].w);
           }
-          acc[0] = a;
-        };
-        products(0, pa);
-        for (int blk = 0; blk < nblk; blk += 2) {
-          chain(pa, blk + 1, pb);
-          if (blk + 1 < nblk) chain(pb, blk + 2, pa);
         }
+        acc[0] = a;
       } else {
-#pragma unroll 2
-        for (int d = 0; d < dc; d += 4) {
+#pragma unroll 4
+        for (int d = 0; d < CH; d += 4) {
           const float4 wv = *reinterpret_cast<const float4*>(wp + d);
           float4 hv[TT];
 #pragma unroll
