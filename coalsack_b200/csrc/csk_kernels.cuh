@@ -274,6 +274,8 @@ k_router_logits(const RouterArgs A) {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  griddep_wait();
+  griddep_launch();
 
   if (warp < NP) {
     // ------------------------------ producers ------------------------------
@@ -485,9 +487,10 @@ inline cudaError_t router_prepare_device() {
 }
 
 template <int TW, int TT, int CH, bool PACKED>
-void launch_router_one(const RouterArgs& a, cudaStream_t s) {
+void launch_router_one(const RouterArgs& a, cudaStream_t s, bool pdl) {
   const dim3 grid((unsigned)((a.T + TW * TT - 1) / (TW * TT)), (unsigned)((a.E + 31) / 32));
-  k_router_logits<TW, TT, CH, PACKED><<<grid, (TW + router_producer_warps(PACKED)) * 32, router_smem_bytes(TW * TT, CH), s>>>(a);
+  launch_k(k_router_logits<TW, TT, CH, PACKED>, grid, dim3((TW + router_producer_warps(PACKED)) * 32),
+           router_smem_bytes(TW * TT, CH), s, pdl, a);
 }
 
 // Few tokens per block while that still leaves SMs idle (a block's speed is bounded by its
@@ -496,17 +499,17 @@ void launch_router_one(const RouterArgs& a, cudaStream_t s) {
 // widths (PACKED) or both the plain [E,H] matrix.  Returns the number of token blocks.
 template <bool PACKED>
 inline int launch_router_logits(RouterArgs a, const float* wg_few, const float* wg_many, int sm_count,
-                                cudaStream_t s) {
+                                cudaStream_t s, bool pdl = false) {
   const int64_t token_blocks = (int64_t)a.T * ((a.E + 31) / 32);  // blocks if every block held one token
   if (token_blocks <= 4 * (int64_t)sm_count) {
     a.wg = wg_few;
-    if (token_blocks <= sm_count) launch_router_one<1, 1, kRouterChunkFew, PACKED>(a, s);
-    else if (token_blocks <= 2 * (int64_t)sm_count) launch_router_one<2, 1, kRouterChunkFew, PACKED>(a, s);
-    else launch_router_one<4, 1, kRouterChunkFew, PACKED>(a, s);
+    if (token_blocks <= sm_count) launch_router_one<1, 1, kRouterChunkFew, PACKED>(a, s, pdl);
+    else if (token_blocks <= 2 * (int64_t)sm_count) launch_router_one<2, 1, kRouterChunkFew, PACKED>(a, s, pdl);
+    else launch_router_one<4, 1, kRouterChunkFew, PACKED>(a, s, pdl);
   } else {
     a.wg = wg_many;
-    if (token_blocks <= 8 * (int64_t)sm_count) launch_router_one<4, 2, kRouterChunkMany, PACKED>(a, s);
-    else launch_router_one<4, 4, kRouterChunkMany, PACKED>(a, s);
+    if (token_blocks <= 8 * (int64_t)sm_count) launch_router_one<4, 2, kRouterChunkMany, PACKED>(a, s, pdl);
+    else launch_router_one<4, 4, kRouterChunkMany, PACKED>(a, s, pdl);
   }
   return 0;
 }
@@ -567,6 +570,8 @@ k_scan(int* __restrict__ counts, int E, int e_begin, int e_count, int tile_rows,
   __shared__ int s_distinct;
   const int e = threadIdx.x, lane = e & 31, warp = e >> 5;
   if (e == 0) s_distinct = 0;
+  griddep_wait();
+  griddep_launch();
   if (router_out) {
     s_tile_off[e] = 0;  // serves as the histogram until the scan below overwrites it
     if (e == 0) meta[3] = 0;
@@ -668,6 +673,8 @@ __global__ void k_scatter(const float* __restrict__ router_out, const float* __r
                           int max_rows, int weight_before_ffn) {
   const int lane = threadIdx.x & 31;
   const int warps_per_block = blockDim.x >> 5;
+  griddep_wait();
+  griddep_launch();
   for (int i = blockIdx.x * warps_per_block + (threadIdx.x >> 5); i < n_pairs;
        i += gridDim.x * warps_per_block) {
     const int e = (int)router_out[2 * (size_t)i];
@@ -706,6 +713,8 @@ __global__ void k_combine(const float* __restrict__ router_out, const int* __res
                           const float* __restrict__ y, int ldy, float* __restrict__ out, int T,
                           int k, int H, int unweighted, int dense_single) {
   const int t = blockIdx.x;
+  griddep_wait();
+  griddep_launch();
   if (t >= T) return;
   for (int d = threadIdx.x * 4; d < H; d += blockDim.x * 4) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);

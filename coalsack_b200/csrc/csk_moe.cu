@@ -39,6 +39,7 @@ struct csk_moe_layer {
   float* d_logits = nullptr;  // [max_T,E] router scratch
   float* d_rbias = nullptr;
   bool router_set = false, has_rbias = false;
+  bool pdl = false;  // launch the layer's kernels with programmatic dependent launch (small batches)
 
   int64_t max_T = 0, max_rows = 0;
   int max_tiles = 0;
@@ -151,7 +152,7 @@ int launch_router(csk_moe_layer* L, const float* d_hidden, int64_t T, float* d_r
   a.E = L->E;
   a.k = L->k;
   a.sigmoid = L->cfg.sigmoid_gating;
-  launch_router_logits<true>(a, L->d_wg_few, L->d_wg_many, L->sm_count, s);
+  launch_router_logits<true>(a, L->d_wg_few, L->d_wg_many, L->sm_count, s, L->pdl);
   CSK_CUDA(L, cudaGetLastError());
   L->last.launches += 1;
   return CSK_OK;
@@ -165,8 +166,8 @@ int launch_permute(csk_moe_layer* L, const float* d_hidden, const float* d_route
   const uint8_t* res = e_count ? L->d_resident : nullptr;
   if (n_pairs <= 8192) {
     // small batch: histogram, scan and tile list in one single-block launch
-    k_scan<<<1, 1024, 0, s>>>(L->d_counts, L->E, e_begin, e_count, tile_rows, (int)max_rows, L->max_tiles, res,
-                              L->d_offsets, L->d_cursor, L->d_tiles, L->d_meta, d_router, n_pairs, only_expert);
+    launch_k(k_scan, dim3(1), dim3(1024), 0, s, L->pdl, L->d_counts, L->E, e_begin, e_count, tile_rows, (int)max_rows,
+             L->max_tiles, res, L->d_offsets, L->d_cursor, L->d_tiles, L->d_meta, d_router, n_pairs, only_expert);
     L->last.launches += 1;
   } else {
     CSK_CUDA(L, cudaMemsetAsync(L->d_counts, 0, sizeof(int) * L->E, s));
@@ -177,9 +178,9 @@ int launch_permute(csk_moe_layer* L, const float* d_hidden, const float* d_route
                               L->d_offsets, L->d_cursor, L->d_tiles, L->d_meta, nullptr, 0, -1);
     L->last.launches += 2;
   }
-  k_scatter<<<grid_for(n_pairs, 8, 8 * L->sm_count), 256, 0, s>>>(
-      d_router, d_hidden, n_pairs, L->k, L->H, L->E, only_expert, L->d_offsets, L->d_cursor,
-      L->d_row_of_pair, x16, ldx, (int)max_rows, L->cfg.weight_before_ffn);
+  launch_k(k_scatter, dim3(grid_for(n_pairs, 8, 8 * L->sm_count)), dim3(256), 0, s, L->pdl, d_router, d_hidden,
+           n_pairs, L->k, L->H, L->E, only_expert, L->d_offsets, L->d_cursor, L->d_row_of_pair, x16, ldx, (int)max_rows,
+           L->cfg.weight_before_ffn);
   CSK_CUDA(L, cudaGetLastError());
   L->last.launches += 1;
   return CSK_OK;
@@ -222,7 +223,7 @@ void launch_stream_pair(csk_moe_layer* L, const __half* x16, float* y, int ldy, 
   a.a_out = L->d_a16;
   a.lda = L->lda;
   size_t smem = stream_smem_bytes(x_rows, NT8, L->Lgu.k_pad(), KSPLIT, true, W, NSTG);
-  k_stream<NT8, true, KSPLIT, W, NSTG><<<grid_for_smem(smem), W * 32, smem, s>>>(a);
+  launch_k(k_stream<NT8, true, KSPLIT, W, NSTG>, dim3(grid_for_smem(smem)), dim3(W * 32), smem, s, L->pdl, a);
   tm.mark();
   // down
   a.mat_offset = L->off_d;
@@ -232,7 +233,7 @@ void launch_stream_pair(csk_moe_layer* L, const __half* x16, float* y, int ldy, 
   a.y_out = y;
   a.ldy = ldy;
   smem = stream_smem_bytes(x_rows, NT8, L->Ld.k_pad(), KSPLIT, false, W, NSTG);
-  k_stream<NT8, false, KSPLIT, W, NSTG><<<grid_for_smem(smem), W * 32, smem, s>>>(a);
+  launch_k(k_stream<NT8, false, KSPLIT, W, NSTG>, dim3(grid_for_smem(smem)), dim3(W * 32), smem, s, L->pdl, a);
   tm.mark();
   L->last.launches += 2;
 }
@@ -342,6 +343,12 @@ int forward_dev(csk_moe_layer* L, const float* d_hidden, int64_t T, const float*
                                           (long long)T, (long long)L->max_T);
   L->last = csk_moe_timings{};
   L->last_T = T;
+  // small batches are launch-bound: let each kernel become resident while its predecessor drains
+  struct PdlScope {
+    csk_moe_layer* l;
+    ~PdlScope() { l->pdl = false; }
+  } pdl_scope{L};
+  L->pdl = T <= 512 && !L->timing;
   StageTimer tm(L, s);
   tm.mark();
   const float* router = d_router_in;
@@ -364,8 +371,8 @@ int forward_dev(csk_moe_layer* L, const float* d_hidden, int64_t T, const float*
   tm.mark();
   rc = launch_experts(L, path, tile_rows, rows, T, L->d_x16, L->d_y, L->H, nullptr, s, tm);
   if (rc) return rc;
-  k_combine<<<(unsigned)T, 256, 0, s>>>(router, L->d_row_of_pair, L->d_y, L->H, d_out, (int)T, L->k,
-                                        L->H, L->cfg.weight_before_ffn, only_expert >= 0);
+  launch_k(k_combine, dim3((unsigned)T), dim3(256), 0, s, L->pdl, router, L->d_row_of_pair, (const float*)L->d_y, L->H,
+           d_out, (int)T, L->k, L->H, (int)L->cfg.weight_before_ffn, (int)(only_expert >= 0));
   CSK_CUDA(L, cudaGetLastError());
   L->last.launches++;
   tm.mark();

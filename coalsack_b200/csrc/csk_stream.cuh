@@ -141,6 +141,8 @@ __global__ void __launch_bounds__(W * 32, W > 8 ? 2 : 3) k_stream(const StreamAr
     for (int i = 0; i < NSTG; ++i) mbar_init(bar_u32 + 8u * i, 1);
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   __syncthreads();
+  griddep_wait();
+  griddep_launch();
 
   const int groups = L.groups;  // 16-row groups (16 features, gate and up, when GATED)
   const int units_per_tile = KSPLIT == 1 ? (groups + W - 1) / W : groups;
