@@ -292,7 +292,10 @@ int launch_experts(csk_moe_layer* L, int path, int tile_rows, int64_t n_rows_hin
     if (need > 200 * 1024)
       return fail(L, CSK_ERR_NOMEM, "hidden/ffn dimension too large for the streaming kernel's row buffer");
     if (tile_rows == 8) {
-      if (n_rows_hint <= 32) {
+#ifndef CSK_KSPLIT_ROWS
+#define CSK_KSPLIT_ROWS 8
+#endif
+      if (n_rows_hint <= CSK_KSPLIT_ROWS) {  // measured: the split pays only while the whole batch is a handful of rows
         launch_stream_pair<1, 8, 8, CSK_STREAM_KS>(L, x16, y, ldy, x_rows, s, tm);  // a handful of rows: split the contraction over the warps
       } else {
         launch_stream_pair<1, 1, CSK_STREAM_W, CSK_STREAM_S>(L, x16, y, ldy, x_rows, s, tm);
