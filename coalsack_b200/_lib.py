@@ -49,7 +49,7 @@ SYMBOLS = {
     "csk_moe_ep_experts_dev": (C.c_int, [_vp, _vp, _vp, _i32, _i64, _vp, _vp]),
     "csk_moe_ep_combine_dev": (C.c_int, [_vp, _vp, _i64, _vp, _vp, _vp]),
     "csk_moe_ep_row_pitch": (C.c_int, [_vp]),
-    "csk_moe_ep_set_replicas": (C.c_int, [_vp, _vp]),
+    "csk_moe_ep_set_slot_map": (C.c_int, [_vp, _i32, _vp, _vp]),
     "csk_moe_set_path": (C.c_int, [_vp, _i32]),
     "csk_moe_enable_timing": (C.c_int, [_vp, _i32]),
     "csk_moe_get_timings": (C.c_int, [_vp, C.POINTER(Timings)]),

@@ -97,13 +97,14 @@ __global__ void k_unpack(const uint8_t* __restrict__ packed, uint8_t* __restrict
 // softmax over the selected logits (or sigmoid) exactly as the reference.
 // ---------------------------------------------------------------------------
 constexpr int kRouterPad = 4;       // row stride 4 mod 32 words: a quarter-warp's 128-bit loads hit distinct banks
-constexpr int kRouterStages = 4;
+// ring depth: four stages, three for the widest blocks (shared memory for two blocks per SM)
+__host__ __device__ constexpr int router_stages(int tokens_per_block) { return tokens_per_block >= 32 ? 3 : 4; }
 constexpr int kMaxTopK = 16;
 constexpr int kMaxExperts = 1024;
 
 // ch = columns of the hidden dimension per pipeline stage
 inline size_t router_smem_bytes(int tokens_per_block, int ch) {
-  return (size_t)kRouterStages * (32 + tokens_per_block) * (ch + kRouterPad) * sizeof(float) + 128;
+  return (size_t)router_stages(tokens_per_block) * (32 + tokens_per_block) * (ch + kRouterPad) * sizeof(float) + 128;
 }
 
 __device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void* gsrc) {
@@ -248,7 +249,7 @@ __global__ void __launch_bounds__((TW + router_producer_warps(PACKED)) * 32)
 k_router_logits(const RouterArgs A) {
   extern __shared__ __align__(128) uint8_t router_smem_raw[];
   constexpr int LD = CH + kRouterPad;
-  constexpr int NS = kRouterStages, NP = router_producer_warps(PACKED);
+  constexpr int NS = router_stages(TW * TT), NP = router_producer_warps(PACKED);
   constexpr int BT = TW * TT;                   // tokens of the block
   constexpr int stage_floats = (32 + BT) * LD;  // ws[32][LD] then hs[BT][LD]
   float* stages = reinterpret_cast<float*>(router_smem_raw);
@@ -478,11 +479,13 @@ inline cudaError_t router_prepare_device() {
   if (e == cudaSuccess) e = router_prepare_one<4, 1, kRouterChunkFew, true>();
   if (e == cudaSuccess) e = router_prepare_one<4, 2, kRouterChunkMany, true>();
   if (e == cudaSuccess) e = router_prepare_one<4, 4, kRouterChunkMany, true>();
+  if (e == cudaSuccess) e = router_prepare_one<8, 4, kRouterChunkMany, true>();
   if (e == cudaSuccess) e = router_prepare_one<1, 1, kRouterChunkFew, false>();
   if (e == cudaSuccess) e = router_prepare_one<2, 1, kRouterChunkFew, false>();
   if (e == cudaSuccess) e = router_prepare_one<4, 1, kRouterChunkFew, false>();
   if (e == cudaSuccess) e = router_prepare_one<4, 2, kRouterChunkMany, false>();
   if (e == cudaSuccess) e = router_prepare_one<4, 4, kRouterChunkMany, false>();
+  if (e == cudaSuccess) e = router_prepare_one<8, 4, kRouterChunkMany, false>();
   return e;
 }
 
@@ -509,7 +512,11 @@ inline int launch_router_logits(RouterArgs a, const float* wg_few, const float* 
   } else {
     a.wg = wg_many;
     if (token_blocks <= 8 * (int64_t)sm_count) launch_router_one<4, 2, kRouterChunkMany, PACKED>(a, s, pdl);
-    else launch_router_one<4, 4, kRouterChunkMany, PACKED>(a, s, pdl);
+#ifndef CSK_ROUTER_WIDE
+#define CSK_ROUTER_WIDE 64
+#endif
+    else if (token_blocks <= CSK_ROUTER_WIDE * (int64_t)sm_count) launch_router_one<4, 4, kRouterChunkMany, PACKED>(a, s, pdl);
+    else launch_router_one<8, 4, kRouterChunkMany, PACKED>(a, s, pdl);
   }
   return 0;
 }
@@ -743,18 +750,18 @@ __global__ void k_combine(const float* __restrict__ router_out, const int* __res
   }
 }
 
-// Router output with the rows of odd-numbered tokens that chose a replicated
-// expert redirected to the slot of its second copy.
-__global__ void k_ep_replicas(const float* __restrict__ router, float* __restrict__ out, int n_pairs, int k, int E,
-                              const int* __restrict__ replica_of) {
+// Router output with logical expert ids replaced by the slots their rows are grouped
+// under: the primary slot, or for odd-numbered tokens the slot of the expert's second copy.
+__global__ void k_ep_slots(const float* __restrict__ router, float* __restrict__ out, int n_pairs, int k, int E_logical,
+                           const int* __restrict__ primary, const int* __restrict__ replica) {
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_pairs; i += gridDim.x * blockDim.x) {
     const float ef = router[2 * i];
     const int e = (int)ef;
     const int t = i / k;
-    float o = ef;
-    if (e >= 0 && e < E && (t & 1)) {
-      const int s = replica_of[e];
-      if (s >= 0) o = (float)s;
+    float o = -1.f;  // an id the permutation reports as out of range
+    if (e >= 0 && e < E_logical) {
+      const int r = replica[e];
+      o = (float)((r >= 0 && (t & 1)) ? r : primary[e]);
     }
     out[2 * i] = o;
     out[2 * i + 1] = router[2 * i + 1];

@@ -45,9 +45,10 @@ struct csk_moe_layer {
   int max_tiles = 0;
   float* d_hidden = nullptr;  // [max_T,H] staging for the host entry points
   float* d_router = nullptr;  // [max_T,k,2]
-  float* d_router_phys = nullptr;  // the same with replicated experts' odd tokens redirected (expert-parallel dispatch)
-  int* d_replica_of = nullptr;     // [E] slot of an expert's second copy or -1
-  bool has_replicas = false;
+  float* d_router_phys = nullptr;  // the same with logical expert ids replaced by slots (expert-parallel dispatch)
+  int* d_slot_map = nullptr;       // [2][E]: primary slot, replica slot (or -1) of each logical expert
+  bool has_slot_map = false;
+  int E_router = 0;                // experts the router scores (= E without a slot map)
   float* d_out = nullptr;     // [max_T,H]
   __half* d_x16 = nullptr;    // [max_rows+pad, ldx]
   __half* d_a16 = nullptr;    // [max_rows+pad, lda]
@@ -149,7 +150,7 @@ int launch_router(csk_moe_layer* L, const float* d_hidden, int64_t T, float* d_r
   a.status = L->d_meta + 8;
   a.T = (int)T;
   a.H = L->H;
-  a.E = L->E;
+  a.E = L->E_router;
   a.k = L->k;
   a.sigmoid = L->cfg.sigmoid_gating;
   launch_router_logits<true>(a, L->d_wg_few, L->d_wg_many, L->sm_count, s, L->pdl);
@@ -344,6 +345,8 @@ int forward_dev(csk_moe_layer* L, const float* d_hidden, int64_t T, const float*
                 float* d_router_out, float* d_out, int only_expert, cudaStream_t s, bool sync_check) {
   if (T <= 0 || T > L->max_T) return fail(L, CSK_ERR_NOMEM, "T=%lld outside (0, max_tokens=%lld]",
                                           (long long)T, (long long)L->max_T);
+  if (L->has_slot_map)
+    return fail(L, CSK_ERR_INVALID, "the layer has an expert-parallel slot map: use the csk_moe_ep_* stages");
   L->last = csk_moe_timings{};
   L->last_T = T;
   // small batches are launch-bound: let each kernel become resident while its predecessor drains
@@ -501,7 +504,8 @@ int csk_moe_create(const csk_moe_config* cfg, csk_moe_layer** out) {
   CK(cudaMalloc(&L->d_hidden, sizeof(float) * L->max_T * L->H));
   CK(cudaMalloc(&L->d_router, sizeof(float) * L->max_T * L->k * 2));
   CK(cudaMalloc(&L->d_router_phys, sizeof(float) * L->max_T * L->k * 2));
-  CK(cudaMalloc(&L->d_replica_of, sizeof(int) * L->E));
+  CK(cudaMalloc(&L->d_slot_map, sizeof(int) * 2 * L->E));
+  L->E_router = L->E;
   CK(cudaMalloc(&L->d_out, sizeof(float) * L->max_T * L->H));
   const size_t pad_rows = kTileM;
   CK(cudaMalloc(&L->d_x16, sizeof(__half) * (L->max_rows + pad_rows) * L->ldx));
@@ -544,7 +548,7 @@ int csk_moe_destroy(csk_moe_layer* L) {
   for (auto& g : L->graphs)
     if (g.exec) cudaGraphExecDestroy(g.exec);
   tile_destroy(L->tile);
-  void* dev[] = {L->d_router_phys, L->d_replica_of, L->d_weights, L->d_resident, L->d_stage, L->d_wg, L->d_wg_few, L->d_wg_many, L->d_route_cnt, L->d_logits, L->d_rbias, L->d_hidden,
+  void* dev[] = {L->d_router_phys, L->d_slot_map, L->d_weights, L->d_resident, L->d_stage, L->d_wg, L->d_wg_few, L->d_wg_many, L->d_route_cnt, L->d_logits, L->d_rbias, L->d_hidden,
                  L->d_router, L->d_out, L->d_x16, L->d_a16, L->d_y, L->d_counts, L->d_offsets,
                  L->d_cursor, L->d_row_of_pair, L->d_out_row_map, L->d_seg, L->d_tiles, L->d_meta};
   for (void* p : dev)
@@ -562,16 +566,16 @@ int csk_moe_set_router(csk_moe_layer* L, const float* gate_w, const float* gate_
   if (check_layer(L)) return CSK_ERR_INVALID;
   if (!gate_w) return fail(L, CSK_ERR_INVALID, "gate_weights is null");
   CSK_CUDA(L, cudaSetDevice(L->cfg.device));
-  CSK_CUDA(L, cudaMemcpyAsync(L->d_wg, gate_w, sizeof(float) * L->E * L->H, cudaMemcpyHostToDevice,
+  CSK_CUDA(L, cudaMemcpyAsync(L->d_wg, gate_w, sizeof(float) * L->E_router * L->H, cudaMemcpyHostToDevice,
                               L->stream));
-  k_pack_router<<<grid_for(router_packed_floats(L->E, L->H, kRouterChunkFew), 256, 1024), 256, 0, L->stream>>>(
-      L->d_wg, L->d_wg_few, L->E, L->H, kRouterChunkFew);
-  k_pack_router<<<grid_for(router_packed_floats(L->E, L->H, kRouterChunkMany), 256, 1024), 256, 0, L->stream>>>(
-      L->d_wg, L->d_wg_many, L->E, L->H, kRouterChunkMany);
+  k_pack_router<<<grid_for(router_packed_floats(L->E_router, L->H, kRouterChunkFew), 256, 1024), 256, 0, L->stream>>>(
+      L->d_wg, L->d_wg_few, L->E_router, L->H, kRouterChunkFew);
+  k_pack_router<<<grid_for(router_packed_floats(L->E_router, L->H, kRouterChunkMany), 256, 1024), 256, 0, L->stream>>>(
+      L->d_wg, L->d_wg_many, L->E_router, L->H, kRouterChunkMany);
   CSK_CUDA(L, cudaGetLastError());
   L->has_rbias = gate_bias != nullptr;
   if (gate_bias)
-    CSK_CUDA(L, cudaMemcpyAsync(L->d_rbias, gate_bias, sizeof(float) * L->E, cudaMemcpyHostToDevice,
+    CSK_CUDA(L, cudaMemcpyAsync(L->d_rbias, gate_bias, sizeof(float) * L->E_router, cudaMemcpyHostToDevice,
                                 L->stream));
   CSK_CUDA(L, cudaStreamSynchronize(L->stream));
   L->router_set = true;
@@ -880,9 +884,9 @@ int csk_moe_ep_dispatch_dev(csk_moe_layer* L, const float* d_hidden, int64_t T, 
                                 cudaMemcpyDeviceToDevice, s));
   }
   const float* router = L->d_router;
-  if (L->has_replicas) {
-    k_ep_replicas<<<grid_for((size_t)T * L->k, 256, 4 * L->sm_count), 256, 0, s>>>(
-        L->d_router, L->d_router_phys, (int)(T * L->k), L->k, L->E, L->d_replica_of);
+  if (L->has_slot_map) {
+    k_ep_slots<<<grid_for((size_t)T * L->k, 256, 4 * L->sm_count), 256, 0, s>>>(
+        L->d_router, L->d_router_phys, (int)(T * L->k), L->k, L->E_router, L->d_slot_map, L->d_slot_map + L->E);
     CSK_CUDA(L, cudaGetLastError());
     router = L->d_router_phys;
   }
@@ -894,25 +898,36 @@ int csk_moe_ep_dispatch_dev(csk_moe_layer* L, const float* d_hidden, int64_t T, 
   return CSK_OK;
 }
 
-int csk_moe_ep_set_replicas(csk_moe_layer* L, const int32_t* replica_of) {
+int csk_moe_ep_set_slot_map(csk_moe_layer* L, int32_t n_logical, const int32_t* primary_slot,
+                            const int32_t* replica_slot) {
   if (check_layer(L)) return CSK_ERR_INVALID;
   CSK_CUDA(L, cudaSetDevice(L->cfg.device));
-  if (!replica_of) {
-    L->has_replicas = false;
+  if (n_logical == 0) {
+    if (L->has_slot_map) L->router_set = false;
+    L->has_slot_map = false;
+    L->E_router = L->E;
     return CSK_OK;
   }
-  bool any = false;
-  for (int e = 0; e < L->E; ++e) {
-    const int s = replica_of[e];
-    if (s < -1 || s >= L->E || s == e)
-      return fail(L, CSK_ERR_INVALID, "replica_of[%d] = %d is not -1 or another expert slot below %d", e, s, L->E);
-    if (s >= 0 && replica_of[s] >= 0)
-      return fail(L, CSK_ERR_INVALID, "slot %d is a replica of expert %d and cannot have a replica itself", s, e);
-    any = any || s >= 0;
+  if (n_logical < L->k || n_logical > L->E || !primary_slot)
+    return fail(L, CSK_ERR_INVALID, "slot map: need top_k <= n_logical <= num_experts (%d) and a primary_slot array, got %d",
+                L->E, n_logical);
+  std::vector<int> map(2 * (size_t)L->E, -1);
+  std::vector<char> used(L->E, 0);
+  for (int e = 0; e < n_logical; ++e) {
+    for (int c = 0; c < 2; ++c) {
+      const int s = c == 0 ? primary_slot[e] : (replica_slot ? replica_slot[e] : -1);
+      if (c == 1 && s == -1) continue;
+      if (s < 0 || s >= L->E) return fail(L, CSK_ERR_INVALID, "slot map: slot %d of expert %d is outside [0,%d)", s, e, L->E);
+      if (used[s]) return fail(L, CSK_ERR_INVALID, "slot map: slot %d is used twice", s);
+      used[s] = 1;
+      map[(size_t)c * L->E + e] = s;
+    }
   }
-  CSK_CUDA(L, cudaMemcpyAsync(L->d_replica_of, replica_of, sizeof(int) * L->E, cudaMemcpyHostToDevice, L->stream));
+  CSK_CUDA(L, cudaMemcpyAsync(L->d_slot_map, map.data(), sizeof(int) * map.size(), cudaMemcpyHostToDevice, L->stream));
   CSK_CUDA(L, cudaStreamSynchronize(L->stream));
-  L->has_replicas = any;
+  L->has_slot_map = true;
+  L->E_router = n_logical;
+  L->router_set = false;  // the router's weights are per logical expert from here on
   return CSK_OK;
 }
 

@@ -19,10 +19,12 @@
 //   * one lane issues eight tcgen05.mma (kind::f16, A from tensor memory, B = the
 //     token tile via a shared-memory descriptor) per k-step, four per half, into
 //     two fp32 accumulators in tensor memory;
-//   * sixteen epilogue warps (per half: four lane quarters x two column ranges) read the accumulator (lane = weight row, column =
+//   * sixteen epilogue warps read the accumulators (lane = weight row, column =
 //     token), scale by the matrix's power of two, add the bias and either apply
-//     the gated activation (gate and up rows are interleaved on adjacent lanes
-//     and meet by one shuffle) and store fp16 rows, or store fp32 output rows.
+//     the gated activation (the gate and the up accumulator of a feature sit in the
+//     same lane, 192 columns apart; a warp finishes four lane quarters' worth of
+//     48 token columns) and store fp16 rows, or (plain matrix: per half, four lane
+//     quarters x two column ranges) store fp32 output rows.
 //
 // Tensor memory (512 columns): [0,384) the accumulators of the two halves, 192
 // columns each; [384,512) a ring of two dequantised weight tiles, 2 x 32 columns
@@ -67,14 +69,14 @@ constexpr uint32_t kTmemABase = 2 * kTileM;                 // first column of t
 //   bytes    0..4095  codes: [column block 0/1][row 0..127][16 bytes = 32 codes, nibble i of
 //                     word w = column 8w + i]
 //   bytes 4096..4351  E8M0 scales: [column block][row]
-// For the fused gate/up matrix row 2i of half h is gate feature 128*n_tile + 64*h + i
-// and row 2i+1 the up row of the same feature.
+// For the fused gate/up matrix half 0 holds the gate rows and half 1 the up rows of the
+// SAME 128 features (128*n_tile ..), so a feature's two accumulators sit in one
+// tensor-memory lane, 192 columns apart.
 struct TileLayout {
   int N, K, paired, n_tiles, k_tiles;
-  __host__ __device__ int feats_per_half() const { return paired ? kTileW / 2 : kTileW; }
-  __host__ __device__ int feats_per_tile() const { return 2 * feats_per_half(); }
-  // halves of tile nt that hold any real row (the last tile may need only one)
-  __host__ __device__ int halves(int nt) const { return nt * feats_per_tile() + feats_per_half() < N ? 2 : 1; }
+  __host__ __device__ int feats_per_tile() const { return paired ? kTileW : 2 * kTileW; }
+  // halves of tile nt that hold any real row (the last tile of a plain matrix may need only one)
+  __host__ __device__ int halves(int nt) const { return paired || nt * 2 * kTileW + kTileW < N ? 2 : 1; }
   __host__ __device__ size_t bytes() const { return (size_t)n_tiles * k_tiles * kTilePacked; }
   __host__ __device__ int k_pad() const { return k_tiles * kTileK; }
 };
@@ -102,8 +104,8 @@ __global__ void k_repack_tile(const uint8_t* __restrict__ src0, const uint8_t* _
     uint32_t out = 0;
     auto source = [&](int trow, const uint8_t*& src, int& feat) {
       if (L.paired) {
-        src = (trow & 1) ? src1 : src0;
-        feat = nt * kTileW + half * (kTileW / 2) + (trow >> 1);
+        src = half ? src1 : src0;
+        feat = nt * kTileW + trow;
       } else {
         src = src0;
         feat = nt * 2 * kTileW + half * kTileW + trow;
@@ -151,8 +153,8 @@ __global__ void k_unpack_tile(const uint8_t* __restrict__ packed, uint8_t* __res
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_blocks; i += (size_t)gridDim.x * blockDim.x) {
     const int feat = (int)(i / kb), blk_g = (int)(i % kb);
     const int nt = feat / L.feats_per_tile();
-    const int half = (feat % L.feats_per_tile()) / L.feats_per_half();
-    const int trow = L.paired ? (feat % (kTileW / 2)) * 2 + which_half : feat % kTileW;
+    const int half = L.paired ? which_half : (feat % (2 * kTileW)) / kTileW;
+    const int trow = feat % kTileW;
     const int kt = blk_g / 2, blk = blk_g & 1;
     const uint8_t* tile = packed + ((size_t)nt * L.k_tiles + kt) * kTilePacked + (size_t)half * kHalfPacked;
     uint8_t* o = out + i * 17;
@@ -219,6 +221,14 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
         "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
       : "memory");
 }
@@ -489,9 +499,12 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
   } else {
     // ------------------------------ epilogue ------------------------------
     const int quarter = warp & 3;  // tensor-memory lanes 32*quarter .. +31 belong to this warp
-    const int half = ((warp - 2 - kDequantWarps) >> 2) & 1;  // which half of the weight tile this warp finishes
-    const int c_begin = ((warp - 2 - kDequantWarps) >> 3) * (kTileM / 2);  // ... and which 96 token columns
-    const int c_end = c_begin + kTileM / 2;
+    const int ew = warp - 2 - kDequantWarps;
+    // plain matrix: a warp finishes one half x one of two column ranges; gate/up: both halves
+    // (gate and up of its lane's feature) x one of four 48-column ranges
+    const int half = GATED ? 0 : (ew >> 2) & 1;
+    const int c_begin = GATED ? (ew >> 2) * 48 : (ew >> 3) * 96;
+    const int c_end = GATED ? c_begin + 48 : (c_begin ? kTileM : 96);
     const int trow = quarter * 32 + lane;
     long it = 0;
     bool ok = true;
@@ -512,27 +525,26 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
       if (!active) {
         // this half of the last weight tile is padding: nothing to finish
       } else if (GATED) {
-        // even lane = gate row, odd lane = up row of feature `feat`
-        const int feat = nt * kTileW + half * (kTileW / 2) + (trow >> 1);
+        // lane = feature; its gate accumulator is in half 0, its up accumulator in half 1
+        const int feat = nt * kTileW + trow;
         const bool feat_ok = feat < L.N;
-        const bool odd = trow & 1;
-        float my_bias = 0.f;
-        if (A.has_bias && feat_ok) my_bias = odd ? bias[feat] : bias[A.F + feat];
-        for (int c0 = c_begin; c0 < min(rt.rows, c_end); c0 += 32) {
-          uint32_t r[32];
-          tmem_ld32(t_acc + c0, r);
+        float bu = 0.f, bg = 0.f;
+        if (A.has_bias && feat_ok) {
+          bu = bias[feat];
+          bg = bias[A.F + feat];
+        }
+        __half* out = A.a_out + (size_t)rt.row0 * A.lda + feat;
+        for (int c0 = c_begin; c0 < min(rt.rows, c_end); c0 += 16) {
+          uint32_t rg[16], ru[16];
+          tmem_ld16(t_acc + c0, rg);
+          tmem_ld16(t_acc + kTileM + c0, ru);
           tmem_ld_wait();
 #pragma unroll
-          for (int jj = 0; jj < 16; ++jj) {
-            // the pair exchanges both tokens; the even lane finishes token 2jj, the odd lane token 2jj+1
-            const float v0 = __uint_as_float(r[2 * jj]) * oscale + my_bias;
-            const float v1 = __uint_as_float(r[2 * jj + 1]) * oscale + my_bias;
-            const float p0 = __shfl_xor_sync(0xffffffffu, v0, 1);
-            const float p1 = __shfl_xor_sync(0xffffffffu, v1, 1);
-            const float gate = odd ? p1 : v0, up = odd ? v1 : p0;
-            const int tok = c0 + 2 * jj + (odd ? 1 : 0);
-            if (feat_ok && tok < rt.rows)
-              A.a_out[(size_t)(rt.row0 + tok) * A.lda + feat] = __float2half_rn(gated_act_fast(gate, up, A.act));
+          for (int j = 0; j < 16; ++j) {
+            const float gate = fmaf(__uint_as_float(rg[j]), oscale, bg);
+            const float up = fmaf(__uint_as_float(ru[j]), oscale, bu);
+            if (feat_ok && c0 + j < rt.rows)
+              out[(size_t)(c0 + j) * A.lda] = __float2half_rn(gated_act_fast(gate, up, A.act));
           }
         }
       } else {

@@ -58,11 +58,6 @@ class Placement:
     def n_slots(self):
         return len(self.slots)
 
-    def is_primary(self):
-        """mask of the slots the router may select"""
-        rep = set(int(s) for s in self.replica_of if s >= 0)
-        return np.array([e >= 0 and p not in rep for p, e in enumerate(self.slots)])
-
 
 def plan_placement(load, world: int, extra_slots: int = 0) -> Placement:
     """Placement of E experts on `world` ranks from a measured load per expert (rows it
@@ -141,29 +136,30 @@ class GpuBackend:
         self.row_dtype = torch.float16
         self.H, self.k = shape.hidden, shape.top_k
 
-    def physical_router(self, Wg, rb):
-        """Router rows in slot order; replica and empty slots get a zero row and a bias no
-        token's logit can beat."""
+    def slot_map(self):
+        """(primary_slot[e], replica_slot[e]) of every logical expert."""
         pl = self.placement
-        prim = pl.is_primary()
-        W = np.zeros((pl.n_slots, Wg.shape[1]), dtype=np.float32)
-        b = np.full(pl.n_slots, -1e30, dtype=np.float32)
-        W[prim] = Wg[pl.slots[prim]]
-        b[prim] = 0.0 if rb is None else rb[pl.slots[prim]]
-        return W, (b if (rb is not None or not prim.all()) else None)
+        E = self.sh.num_experts
+        primary = -np.ones(E, dtype=np.int32)
+        replica = -np.ones(E, dtype=np.int32)
+        copies = set(int(s) for s in pl.replica_of if s >= 0)
+        for p, e in enumerate(pl.slots):
+            if e >= 0 and p not in copies:
+                primary[e] = p
+                replica[e] = pl.replica_of[p]
+        assert (primary >= 0).all(), "every expert needs a slot"
+        return primary, replica
 
     def load_synthetic(self):
         sh = self.sh
-        W, b = self.physical_router(synth.router_weight(sh), synth.router_bias(sh))
-        self.layer.set_router(W, b)
+        self.layer.ep_set_slot_map(*self.slot_map())
+        self.layer.set_router(synth.router_weight(sh), synth.router_bias(sh))
         for p in range(self.e0, self.e0 + self.eloc):
             e = int(self.placement.slots[p])
             if e < 0:
                 continue
             w = synth.expert_weights(sh, e)
             self.layer.load_expert(p, w["w_up"], w["w_gate"], w["w_down"], w["b_up"], w["b_gate"], w["b_down"])
-        if (self.placement.replica_of >= 0).any():
-            self.layer.ep_set_replicas(self.placement.replica_of)
 
     def stream(self):
         return self.torch.cuda.current_stream(self.dev).cuda_stream
@@ -250,7 +246,10 @@ class EpBench:
         load = torch.from_numpy(calibration_load(sh, h)).to(self.dev)
         import torch.distributed as dist
         dist.all_reduce(load)
-        place = plan_placement(load.cpu().numpy(), world, extra_slots=1 if world > 1 else 0)
+        load = load.cpu().numpy()
+        place = plan_placement(load, world, extra_slots=1)
+        if not (place.replica_of >= 0).any():
+            place = plan_placement(load, world, extra_slots=0)   # no expert worth a second copy: no spare slots
         # a rank may receive more rows than it sends when routing is uneven: leave 3x head-room
         self.backend = GpuBackend(sh, rank, world, local, max_tokens=3 * sh.tokens, placement=place)
         self.backend.load_synthetic()

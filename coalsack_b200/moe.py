@@ -62,6 +62,7 @@ class MoeLayer:
                           int(sigmoid_gating), int(weight_before_ffn), device, expert_begin,
                           expert_count, 0, max_tokens)
         self.E, self.k, self.H, self.F = num_experts, top_k, hidden, ffn
+        self.E_router = num_experts  # experts the router scores (fewer than E under an expert-parallel slot map)
         self.max_tokens = max_tokens
         self._h = C.c_void_p()
         rc = self._lib.csk_moe_create(C.byref(self.cfg), C.byref(self._h))
@@ -93,8 +94,8 @@ class MoeLayer:
     # -- weights ------------------------------------------------------------
     def set_router(self, gate_w, gate_bias=None):
         gate_w, gate_bias = _np_f32(gate_w), _np_f32(gate_bias)
-        if gate_w.shape != (self.E, self.H):
-            raise RuntimeError(f"moe_router: gate_weights shape mismatch, expected [{self.E}, {self.H}], "
+        if gate_w.shape != (self.E_router, self.H):
+            raise RuntimeError(f"moe_router: gate_weights shape mismatch, expected [{self.E_router}, {self.H}], "
                                f"got [{gate_w.shape[0]}, {gate_w.shape[1]}]")
         self._check(self._lib.csk_moe_set_router(self._h, _p(gate_w), _p(gate_bias)))
 
@@ -189,15 +190,19 @@ class MoeLayer:
         self._check(self._lib.csk_moe_ep_combine_dev(self._h, _p(d_back), T, _p(d_out), _p(d_router_out),
                                                      stream))
 
-    def ep_set_replicas(self, replica_of):
-        """replica_of[e] = slot holding a second copy of expert e's weights, or -1 (None: off)."""
-        if replica_of is None:
-            self._check(self._lib.csk_moe_ep_set_replicas(self._h, None))
+    def ep_set_slot_map(self, primary_slot, replica_slot=None):
+        """Router over len(primary_slot) logical experts; dispatch groups expert e under slot
+        primary_slot[e] (odd tokens under replica_slot[e] where that is >= 0).  None removes the map."""
+        if primary_slot is None:
+            self._check(self._lib.csk_moe_ep_set_slot_map(self._h, 0, None, None))
+            self.E_router = self.E
             return
-        a = np.ascontiguousarray(replica_of, dtype=np.int32)
-        if a.shape != (self.E,):
-            raise ValueError(f"replica_of must have shape ({self.E},)")
-        self._check(self._lib.csk_moe_ep_set_replicas(self._h, _p(a)))
+        p = np.ascontiguousarray(primary_slot, dtype=np.int32)
+        r = None if replica_slot is None else np.ascontiguousarray(replica_slot, dtype=np.int32)
+        if r is not None and r.shape != p.shape:
+            raise ValueError("replica_slot must have the shape of primary_slot")
+        self._check(self._lib.csk_moe_ep_set_slot_map(self._h, int(p.shape[0]), _p(p), _p(r)))
+        self.E_router = int(p.shape[0])
 
     # -- knobs / observability ---------------------------------------------------
     def set_path(self, path):

@@ -196,14 +196,20 @@ int csk_moe_ep_experts_dev(csk_moe_layer* layer, const void* d_recv_f16,
                            float* d_ret, void* stream);
 int csk_moe_ep_combine_dev(csk_moe_layer* layer, const float* d_back, int64_t T, float* d_out,
                            float* d_router_out_out, void* stream);
-/* Replicas of heavily loaded experts.  replica_of is [num_experts] int32 (host):
- * replica_of[e] = s >= 0 says that expert slot s holds a second copy of expert e's
- * weights; csk_moe_ep_dispatch_dev then sends the rows of every odd-numbered token
- * that chose e to slot s instead (the router output it reports keeps e).  -1 = no
- * replica; a null pointer switches the feature off.  The router must never select
- * a replica slot itself (give it a zero weight row and a very negative bias).
- * Affects only the csk_moe_ep_* stages.  No counterpart in the reference. */
-int csk_moe_ep_set_replicas(csk_moe_layer* layer, const int32_t* replica_of);
+/* Expert placement for the csk_moe_ep_* stages.  Without a map the layer's
+ * num_experts are both the router's experts and the slots that rows are grouped
+ * by.  With a map the router has n_logical <= num_experts experts (set_router
+ * then takes [n_logical, H] weights, router outputs carry logical ids) and
+ * csk_moe_ep_dispatch_dev groups the rows of logical expert e under slot
+ * primary_slot[e] -- or, for odd-numbered tokens, under replica_slot[e] when
+ * that is >= 0 (a second copy of a heavily loaded expert on another rank).
+ * Both arrays are [n_logical] int32 on the host; replica_slot may be null.
+ * Slots must be distinct and below num_experts.  Call it before
+ * csk_moe_set_router.  While a map is set, csk_moe_forward* (which group by the
+ * router's own ids) are refused.  n_logical = 0 removes the map.
+ * No counterpart in the reference. */
+int csk_moe_ep_set_slot_map(csk_moe_layer* layer, int32_t n_logical, const int32_t* primary_slot,
+                            const int32_t* replica_slot);
 
 /* ---- knobs and observability ------------------------------------------- */
 int csk_moe_set_path(csk_moe_layer* layer, int32_t path /* CSK_PATH_* */);

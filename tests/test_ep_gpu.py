@@ -11,20 +11,20 @@ from tests import cases
 pytestmark = pytest.mark.gpu
 
 
-def run_emulated_ep(torch, sh, N, tokens, Wg, rb, ex, path, replica_of=None):
+def run_emulated_ep(torch, sh, N, tokens, Wg, rb, ex, path, slot_map=None):
     E, k, H = sh.num_experts, sh.top_k, sh.hidden
     eloc = E // N
     dev = torch.device("cuda", 0)
     layers, hs = [], []
     for r in range(N):
         lay = MoeLayer.from_shape(sh, max_tokens=max(sum(tokens), 1), expert_begin=r * eloc, expert_count=eloc)
+        if slot_map is not None:
+            lay.ep_set_slot_map(*slot_map)
         lay.set_router(Wg, rb)
         lay.load_experts({n: (None if ex.get(n) is None else ex[n][r * eloc:(r + 1) * eloc])
                           for n in ("w_up", "w_gate", "w_down", "b_up", "b_gate", "b_down")},
                          ids=range(r * eloc, (r + 1) * eloc))
         lay.set_path(path)
-        if replica_of is not None:
-            lay.ep_set_replicas(replica_of)
         layers.append(lay)
         hs.append(torch.from_numpy(synth.hidden_states(sh, tokens[r], rep=r)).to(dev))
     pitch = layers[0].ep_row_pitch()
@@ -81,7 +81,7 @@ def test_emulated_ep_matches_checker(gpu_lib, port, path, N, tokens):
 @pytest.mark.parametrize("path", [PATH_STREAM, PATH_TILE])
 def test_emulated_ep_with_replicated_experts(gpu_lib, port, path):
     """Two ranks, five slots each for eight experts: the planner gives the heaviest experts a
-    second copy; odd tokens go there.  Output and (logical) routing must match the checker."""
+    second copy; odd tokens go there.  Output and routing (logical ids) must match the checker."""
     import torch
     from coalsack_b200.ep import plan_placement
     sh = synth.tiny(seed=83, E=8, k=3, H=192, F=160, T=1, has_bias=True)
@@ -89,17 +89,18 @@ def test_emulated_ep_with_replicated_experts(gpu_lib, port, path):
     load = np.array([900, 100, 90, 80, 70, 60, 50, 40])
     pl = plan_placement(load, 2, extra_slots=1)
     assert (pl.replica_of >= 0).any() and pl.n_slots == 10
-    prim = pl.is_primary()
-    Wp = np.zeros((pl.n_slots, sh.hidden), dtype=np.float32)
-    bp = np.full(pl.n_slots, -1e30, dtype=np.float32)
-    Wp[prim] = Wg[pl.slots[prim]]
-    bp[prim] = rb[pl.slots[prim]]
+    copies = set(int(s) for s in pl.replica_of if s >= 0)
+    primary = -np.ones(8, dtype=np.int32)
+    replica = -np.ones(8, dtype=np.int32)
+    for p, e in enumerate(pl.slots):
+        if e >= 0 and p not in copies:
+            primary[e], replica[e] = p, pl.replica_of[p]
     src = np.where(pl.slots >= 0, pl.slots, 0)           # empty slots carry some expert's weights, never routed
     exp = {n: (None if ex.get(n) is None else [ex[n][e] for e in src]) for n in ex}
     shp = sh.with_(num_experts=pl.n_slots)
     tokens = (37, 64)
-    for out, ro, h in run_emulated_ep(torch, shp, 2, tokens, Wp, bp, exp, path, replica_of=pl.replica_of):
+    for out, ro, h in run_emulated_ep(torch, shp, 2, tokens, Wg, rb, exp, path, slot_map=(primary, replica)):
         want, want_ro = port.moe_layer(h, Wg, rb, ex, sh.top_k, sh.act, nthreads=4)
-        assert np.array_equal(pl.slots[ro[..., 0].astype(np.int64)], want_ro[..., 0].astype(np.int64))
+        assert np.array_equal(ro[..., 0], want_ro[..., 0])
         mx, mr = cases.err_stats(out, want)
         assert mx <= cases.MAX_ABS_OVER_RMS and mr <= cases.MEAN_REL, (path, mx, mr)
