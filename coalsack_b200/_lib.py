@@ -50,6 +50,14 @@ SYMBOLS = {
     "csk_moe_ep_combine_dev": (C.c_int, [_vp, _vp, _i64, _vp, _vp, _vp]),
     "csk_moe_ep_row_pitch": (C.c_int, [_vp]),
     "csk_moe_ep_set_slot_map": (C.c_int, [_vp, _i32, _vp, _vp]),
+    "csk_moe_ep_p2p_export": (C.c_int, [_vp, _vp]),
+    "csk_moe_ep_p2p_import": (C.c_int, [_vp, _i32, _i32, _vp]),
+    "csk_moe_ep_p2p_local_ptrs": (C.c_int, [_vp, _vp, _vp, _vp]),
+    "csk_moe_ep_p2p_import_ptrs": (C.c_int, [_vp, _i32, _i32, _vp, _vp, _vp]),
+    "csk_moe_ep_p2p_counts_dev": (C.c_int, [_vp, _vp, _i64, _vp, _vp, _vp]),
+    "csk_moe_ep_p2p_scatter_dev": (C.c_int, [_vp, _vp, _i64, _vp, _vp]),
+    "csk_moe_ep_p2p_experts_dev": (C.c_int, [_vp, _vp, _i64, _vp]),
+    "csk_moe_ep_p2p_combine_dev": (C.c_int, [_vp, _i64, _vp, _vp, _vp]),
     "csk_moe_set_path": (C.c_int, [_vp, _i32]),
     "csk_moe_enable_timing": (C.c_int, [_vp, _i32]),
     "csk_moe_get_timings": (C.c_int, [_vp, C.POINTER(Timings)]),

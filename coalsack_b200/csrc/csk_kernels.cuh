@@ -845,4 +845,141 @@ __global__ void k_ep_ungroup(const float* __restrict__ y, float* __restrict__ re
   }
 }
 
+// ---------------------------------------------------------------------------
+// Expert parallelism over peer memory (NVLink): the dispatch writes every row
+// straight into the row buffer of the rank that owns its expert slot, at its
+// final expert-grouped position, and the down projection's epilogue writes
+// every output row straight into the return buffer of the rank that owns the
+// token.  The only collectives left are the (tiny) exchange of row counts and
+// two barriers.  All cross-GPU traffic is plain stores to peer pointers.
+//
+// Layout of a destination's row buffer: slot-major, within a slot the rows of
+// source rank 0, then 1, ...  Every rank derives all positions from the full
+// count table all_counts[source][slot].
+// ---------------------------------------------------------------------------
+struct RowOrigin {
+  int src;   // rank that sent the row
+  int pair;  // index of the (token, k) pair there = row of its return buffer
+};
+
+// One block of 1024 threads, E <= 1024.  base[e] = first row, in the buffer of the
+// rank owning slot e, of the rows THIS rank sends to e; cursor[e] = 0.
+__global__ void __launch_bounds__(1024)
+k_ep_p2p_base(const int* __restrict__ all_counts, int world, int me, int E, int e_per_rank, int max_rows,
+              int* __restrict__ base, int* __restrict__ cursor, int* __restrict__ meta) {
+  __shared__ int s_scan[1024];
+  __shared__ int s_warp[32];
+  const int e = threadIdx.x, lane = e & 31, warp = e >> 5;
+  int tot = 0, before = 0;
+  if (e < E)
+    for (int s = 0; s < world; ++s) {
+      const int c = all_counts[s * E + e];
+      tot += c;
+      if (s < me) before += c;
+    }
+  int r = tot;
+  for (int o = 1; o < 32; o <<= 1) {
+    const int a = __shfl_up_sync(0xffffffffu, r, o);
+    if (lane >= o) r += a;
+  }
+  if (lane == 31) s_warp[warp] = r;
+  __syncthreads();
+  if (warp == 0) {
+    int a = s_warp[lane];
+    for (int o = 1; o < 32; o <<= 1) {
+      const int u = __shfl_up_sync(0xffffffffu, a, o);
+      if (lane >= o) a += u;
+    }
+    s_warp[lane] = a;
+  }
+  __syncthreads();
+  s_scan[e] = (warp ? s_warp[warp - 1] : 0) + r - tot;  // exclusive prefix over all slots
+  __syncthreads();
+  if (e < E) {
+    const int first = (e / e_per_rank) * e_per_rank;  // first slot of the owning rank
+    const int in_rank = s_scan[e] - s_scan[first];    // rows of that rank's earlier slots
+    base[e] = in_rank + before;
+    cursor[e] = 0;
+    if (in_rank + tot > max_rows) atomicOr(&meta[3], kDevErrCapacity);
+  }
+}
+
+// One warp per (token, slot) pair: claim the next row of this rank's share of the slot on
+// the owning rank, write the token's hidden row there as fp16 (peer store) with its origin.
+__global__ void k_ep_p2p_scatter(const float* __restrict__ router_out, const float* __restrict__ hidden,
+                                 int n_pairs, int k, int H, int E, int e_per_rank, int me,
+                                 const int* __restrict__ base, int* __restrict__ cursor,
+                                 __half* const* __restrict__ peer_x16, RowOrigin* const* __restrict__ peer_info,
+                                 int ldx, int max_rows, int weight_before_ffn, int* __restrict__ row_of_pair,
+                                 int* __restrict__ meta) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  for (int i = blockIdx.x * warps_per_block + (threadIdx.x >> 5); i < n_pairs; i += gridDim.x * warps_per_block) {
+    const int e = (int)router_out[2 * (size_t)i];
+    const float w = router_out[2 * (size_t)i + 1];
+    int pos = -1;
+    if (e >= 0 && e < E) {
+      if (lane == 0) pos = base[e] + atomicAdd(&cursor[e], 1);
+      pos = __shfl_sync(0xffffffffu, pos, 0);
+      if (pos >= max_rows) pos = -1;
+    } else if (lane == 0) {
+      atomicOr(&meta[3], kDevErrExpertRange);
+    }
+    if (lane == 0) row_of_pair[i] = pos < 0 ? -1 : i;  // the return buffer is indexed by pair
+    if (pos < 0) continue;
+    const int dst_rank = e / e_per_rank;
+    const float* src = hidden + (size_t)(i / k) * H;
+    __half* dst = peer_x16[dst_rank] + (size_t)pos * ldx;
+    if (lane == 0) peer_info[dst_rank][pos] = RowOrigin{me, i};
+    const float mul = weight_before_ffn ? w : 1.0f;
+    for (int d = lane * 8; d < H; d += 256) {
+      const float4 v0 = *reinterpret_cast<const float4*>(src + d);
+      const float4 v1 = *reinterpret_cast<const float4*>(src + d + 4);
+      __half2 a = __floats2half2_rn(v0.x * mul, v0.y * mul), b = __floats2half2_rn(v0.z * mul, v0.w * mul);
+      __half2 c = __floats2half2_rn(v1.x * mul, v1.y * mul), f = __floats2half2_rn(v1.z * mul, v1.w * mul);
+      uint4 o;
+      o.x = *reinterpret_cast<uint32_t*>(&a);
+      o.y = *reinterpret_cast<uint32_t*>(&b);
+      o.z = *reinterpret_cast<uint32_t*>(&c);
+      o.w = *reinterpret_cast<uint32_t*>(&f);
+      *reinterpret_cast<uint4*>(dst + d) = o;
+    }
+  }
+  __threadfence_system();  // the peer stores before whatever signals their arrival
+}
+
+// counts[e] of the slots this rank owns = rows it received (all sources); zero elsewhere.
+__global__ void k_ep_p2p_local_counts(const int* __restrict__ all_counts, int world, int E, int e_begin, int e_count,
+                                      int* __restrict__ counts) {
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= E) return;
+  int tot = 0;
+  if (e >= e_begin && e < e_begin + e_count)
+    for (int s = 0; s < world; ++s) tot += all_counts[s * E + e];
+  counts[e] = tot;
+}
+
+// Where each received row's output goes: the pair's row of the sender's return buffer.
+__global__ void k_ep_p2p_rowptr(const RowOrigin* __restrict__ info, const int* __restrict__ meta, float* const* __restrict__ peer_back,
+                                int H, float** __restrict__ row_ptr) {
+  const int rows = meta[1];
+  for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < rows; r += gridDim.x * blockDim.x) {
+    const RowOrigin o = info[r];
+    row_ptr[r] = peer_back[o.src] + (size_t)o.pair * H;
+  }
+}
+
+// Output rows computed into a local buffer (streaming path) -> their owners' return buffers.
+__global__ void k_ep_p2p_return(const float* __restrict__ y, int H, float* const* __restrict__ row_ptr,
+                                const int* __restrict__ meta) {
+  const int rows = meta[1];
+  const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+  for (int r = blockIdx.x * wpb + (threadIdx.x >> 5); r < rows; r += gridDim.x * wpb) {
+    const float4* s = reinterpret_cast<const float4*>(y + (size_t)r * H);
+    float4* d = reinterpret_cast<float4*>(row_ptr[r]);
+    for (int i = lane; i < H / 4; i += 32) d[i] = s[i];
+  }
+  __threadfence_system();
+}
+
 }  // namespace csk

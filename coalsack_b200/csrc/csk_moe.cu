@@ -39,6 +39,16 @@ struct csk_moe_layer {
   float* d_logits = nullptr;  // [max_T,E] router scratch
   float* d_rbias = nullptr;
   bool router_set = false, has_rbias = false;
+  // expert parallelism over peer memory
+  int p2p_rank = -1, p2p_world = 0;
+  RowOrigin* d_info = nullptr;        // [max_rows] origin of every received row
+  float* d_back = nullptr;            // [max_T*k, H] output rows returned for this rank's pairs
+  float** d_row_ptr = nullptr;        // [max_rows] where each received row's output goes
+  int* d_p2p_base = nullptr;          // [E]
+  __half** d_peer_x16 = nullptr;      // [world] every rank's row buffer (own entry: d_x16)
+  RowOrigin** d_peer_info = nullptr;  // [world]
+  float** d_peer_back = nullptr;      // [world]
+  std::vector<void*> ipc_opened;      // peer mappings to close
   bool pdl = false;  // launch the layer's kernels with programmatic dependent launch (small batches)
 
   int64_t max_T = 0, max_rows = 0;
@@ -273,17 +283,18 @@ int tile_rows_for(const csk_moe_layer* L, int path, int64_t rows) {
 // grouped gate/up + activation + down over the row tiles listed in d_tiles;
 // x16 holds the grouped rows; output rows go to y (through out_row_map if set)
 int launch_experts(csk_moe_layer* L, int path, int tile_rows, int64_t n_rows_hint, int64_t rows_per_expert_max,
-                   const __half* x16, float* y, int ldy, const int* out_row_map, cudaStream_t s, StageTimer& tm) {
+                   const __half* x16, float* y, int ldy, const int* out_row_map, cudaStream_t s, StageTimer& tm,
+                   float* const* out_row_ptr = nullptr) {
   if (path == CSK_PATH_TILE) {
     if (x16 != L->d_x16) return fail(L, CSK_ERR_INVALID, "the tile path reads the handle's own row buffer");
     int rc = tile_launch(L->tile, L->d_weights, L->expert_stride, L->off_tgu, L->off_td, L->off_bias,
-                         L->off_meta, L->Tgu, L->Td, L->d_a16, L->lda, y, ldy, out_row_map, L->d_tiles,
+                         L->off_meta, L->Tgu, L->Td, L->d_a16, L->lda, y, ldy, out_row_map, out_row_ptr, L->d_tiles,
                          L->d_meta, L->cfg.has_bias, L->cfg.activation, L->F, L->sm_count, s,
                          [&]() { tm.mark(); });
     if (rc) return fail(L, rc, "tensor-core path: %s", L->tile.err.c_str());
     L->last.launches += 2;
   } else {
-    if (out_row_map) return fail(L, CSK_ERR_INVALID, "row map needs the tile path");
+    if (out_row_map || out_row_ptr) return fail(L, CSK_ERR_INVALID, "row maps need the tile path");
     // no tile holds more rows than its expert received
     const int x_rows = (int)std::max<int64_t>(1, std::min<int64_t>(tile_rows, rows_per_expert_max));
     const int kp = std::max(L->Lgu.k_pad(), L->Ld.k_pad());
@@ -505,6 +516,7 @@ int csk_moe_create(const csk_moe_config* cfg, csk_moe_layer** out) {
   CK(cudaMalloc(&L->d_router, sizeof(float) * L->max_T * L->k * 2));
   CK(cudaMalloc(&L->d_router_phys, sizeof(float) * L->max_T * L->k * 2));
   CK(cudaMalloc(&L->d_slot_map, sizeof(int) * 2 * L->E));
+  CK(cudaMalloc(&L->d_p2p_base, sizeof(int) * L->E));
   L->E_router = L->E;
   CK(cudaMalloc(&L->d_out, sizeof(float) * L->max_T * L->H));
   const size_t pad_rows = kTileM;
@@ -548,7 +560,9 @@ int csk_moe_destroy(csk_moe_layer* L) {
   for (auto& g : L->graphs)
     if (g.exec) cudaGraphExecDestroy(g.exec);
   tile_destroy(L->tile);
-  void* dev[] = {L->d_router_phys, L->d_slot_map, L->d_weights, L->d_resident, L->d_stage, L->d_wg, L->d_wg_few, L->d_wg_many, L->d_route_cnt, L->d_logits, L->d_rbias, L->d_hidden,
+  for (void* p : L->ipc_opened) cudaIpcCloseMemHandle(p);
+  void* dev[] = {L->d_info, L->d_back, L->d_row_ptr, L->d_p2p_base, L->d_peer_x16, L->d_peer_info, L->d_peer_back,
+                 L->d_router_phys, L->d_slot_map, L->d_weights, L->d_resident, L->d_stage, L->d_wg, L->d_wg_few, L->d_wg_many, L->d_route_cnt, L->d_logits, L->d_rbias, L->d_hidden,
                  L->d_router, L->d_out, L->d_x16, L->d_a16, L->d_y, L->d_counts, L->d_offsets,
                  L->d_cursor, L->d_row_of_pair, L->d_out_row_map, L->d_seg, L->d_tiles, L->d_meta};
   for (void* p : dev)
@@ -931,6 +945,204 @@ int csk_moe_ep_set_slot_map(csk_moe_layer* L, int32_t n_logical, const int32_t* 
   return CSK_OK;
 }
 
+// ---- expert parallelism over peer memory ----------------------------------------
+namespace {
+// End of an experts stage: enqueue only, unless timing is on (then wait, check the status word, read the events).
+int ep_finish(csk_moe_layer* L, cudaStream_t s, int n_marks) {
+  L->last_stream = s;
+  if (!L->timing) return CSK_OK;  // csk_moe_sync reports what the kernels found
+  int rc = check_device_status(L, s);
+  if (rc) return rc;
+  if (n_marks == 3) {  // the status check above already waited for the stream
+    cudaEventElapsedTime(&L->last.gate_up_ms, L->ev[0], L->ev[1]);
+    cudaEventElapsedTime(&L->last.down_ms, L->ev[1], L->ev[2]);
+    L->last.total_ms = L->last.gate_up_ms + L->last.down_ms;
+  }
+  return CSK_OK;
+}
+int p2p_alloc_local(csk_moe_layer* L) {
+  if (L->d_info) return CSK_OK;
+  CSK_CUDA(L, cudaMalloc(&L->d_info, sizeof(RowOrigin) * (size_t)L->max_rows));
+  CSK_CUDA(L, cudaMalloc(&L->d_back, sizeof(float) * (size_t)L->max_T * L->k * L->H));
+  CSK_CUDA(L, cudaMalloc(&L->d_row_ptr, sizeof(float*) * (size_t)L->max_rows));
+  return CSK_OK;
+}
+int p2p_set_peers(csk_moe_layer* L, int rank, int world, void* const* x16, void* const* info, void* const* back) {
+  if (world < 1 || world > 64 || rank < 0 || rank >= world) return fail(L, CSK_ERR_INVALID, "p2p: bad rank/world %d/%d", rank, world);
+  if (L->E % world || L->Eloc != L->E / world || L->e0 != rank * L->Eloc)
+    return fail(L, CSK_ERR_INVALID, "p2p: rank %d of %d must own expert slots [%d, %d)", rank, world,
+                rank * (L->E / std::max(1, world)), (rank + 1) * (L->E / std::max(1, world)));
+  for (void** p : {(void**)&L->d_peer_x16, (void**)&L->d_peer_info, (void**)&L->d_peer_back}) {
+    if (*p) cudaFree(*p);
+    *p = nullptr;
+  }
+  CSK_CUDA(L, cudaMalloc(&L->d_peer_x16, sizeof(void*) * world));
+  CSK_CUDA(L, cudaMalloc(&L->d_peer_info, sizeof(void*) * world));
+  CSK_CUDA(L, cudaMalloc(&L->d_peer_back, sizeof(void*) * world));
+  CSK_CUDA(L, cudaMemcpy(L->d_peer_x16, x16, sizeof(void*) * world, cudaMemcpyHostToDevice));
+  CSK_CUDA(L, cudaMemcpy(L->d_peer_info, info, sizeof(void*) * world, cudaMemcpyHostToDevice));
+  CSK_CUDA(L, cudaMemcpy(L->d_peer_back, back, sizeof(void*) * world, cudaMemcpyHostToDevice));
+  L->p2p_rank = rank;
+  L->p2p_world = world;
+  return CSK_OK;
+}
+}  // namespace
+
+int csk_moe_ep_p2p_local_ptrs(csk_moe_layer* L, void** x16, void** info, void** back) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  CSK_CUDA(L, cudaSetDevice(L->cfg.device));
+  int rc = p2p_alloc_local(L);
+  if (rc) return rc;
+  if (x16) *x16 = L->d_x16;
+  if (info) *info = L->d_info;
+  if (back) *back = L->d_back;
+  return CSK_OK;
+}
+
+int csk_moe_ep_p2p_export(csk_moe_layer* L, uint8_t* handles) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  if (!handles) return fail(L, CSK_ERR_INVALID, "null argument");
+  CSK_CUDA(L, cudaSetDevice(L->cfg.device));
+  int rc = p2p_alloc_local(L);
+  if (rc) return rc;
+  static_assert(sizeof(cudaIpcMemHandle_t) == CSK_IPC_HANDLE_BYTES, "handle size");
+  void* bufs[3] = {L->d_x16, L->d_info, L->d_back};
+  for (int i = 0; i < 3; ++i) {
+    cudaIpcMemHandle_t h;
+    CSK_CUDA(L, cudaIpcGetMemHandle(&h, bufs[i]));
+    memcpy(handles + (size_t)i * CSK_IPC_HANDLE_BYTES, &h, CSK_IPC_HANDLE_BYTES);
+  }
+  return CSK_OK;
+}
+
+int csk_moe_ep_p2p_import(csk_moe_layer* L, int32_t rank, int32_t world, const uint8_t* all_handles) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  if (!all_handles) return fail(L, CSK_ERR_INVALID, "null argument");
+  CSK_CUDA(L, cudaSetDevice(L->cfg.device));
+  int rc = p2p_alloc_local(L);
+  if (rc) return rc;
+  if (world < 1 || world > 64 || rank < 0 || rank >= world) return fail(L, CSK_ERR_INVALID, "p2p: bad rank/world %d/%d", rank, world);
+  std::vector<void*> ptr(3 * (size_t)world, nullptr);
+  void* own[3] = {L->d_x16, L->d_info, L->d_back};
+  for (int r = 0; r < world; ++r)
+    for (int i = 0; i < 3; ++i) {
+      if (r == rank) {
+        ptr[(size_t)i * world + r] = own[i];
+        continue;
+      }
+      cudaIpcMemHandle_t h;
+      memcpy(&h, all_handles + ((size_t)r * 3 + i) * CSK_IPC_HANDLE_BYTES, CSK_IPC_HANDLE_BYTES);
+      void* p = nullptr;
+      CSK_CUDA(L, cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+      L->ipc_opened.push_back(p);
+      ptr[(size_t)i * world + r] = p;
+    }
+  return p2p_set_peers(L, rank, world, ptr.data(), ptr.data() + world, ptr.data() + 2 * (size_t)world);
+}
+
+int csk_moe_ep_p2p_import_ptrs(csk_moe_layer* L, int32_t rank, int32_t world, void* const* x16, void* const* info,
+                               void* const* back) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  if (!x16 || !info || !back) return fail(L, CSK_ERR_INVALID, "null argument");
+  CSK_CUDA(L, cudaSetDevice(L->cfg.device));
+  int rc = p2p_alloc_local(L);
+  if (rc) return rc;
+  return p2p_set_peers(L, rank, world, x16, info, back);
+}
+
+// Stage 1: route, map to slots, count this rank's rows per slot.
+int csk_moe_ep_p2p_counts_dev(csk_moe_layer* L, const float* d_hidden, int64_t T, const float* d_router_in,
+                              int32_t* d_counts, void* stream) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  if (!d_hidden || !d_counts) return fail(L, CSK_ERR_INVALID, "null argument");
+  if (L->p2p_world <= 0) return fail(L, CSK_ERR_INVALID, "p2p: peers were never imported");
+  if (T <= 0 || T > L->max_T) return fail(L, CSK_ERR_NOMEM, "T=%lld outside (0, max_tokens]", (long long)T);
+  CSK_CUDA(L, cudaSetDevice(L->cfg.device));
+  cudaStream_t s = pick(L, stream);
+  L->last = csk_moe_timings{};
+  L->last_T = T;
+  if (!d_router_in) {
+    int rc = launch_router(L, d_hidden, T, L->d_router, s);
+    if (rc) return rc;
+  } else if (d_router_in != L->d_router) {
+    CSK_CUDA(L, cudaMemcpyAsync(L->d_router, d_router_in, sizeof(float) * T * L->k * 2, cudaMemcpyDeviceToDevice, s));
+  }
+  const int n_pairs = (int)(T * L->k);
+  const float* router = L->d_router;
+  if (L->has_slot_map) {
+    k_ep_slots<<<grid_for((size_t)n_pairs, 256, 4 * L->sm_count), 256, 0, s>>>(
+        L->d_router, L->d_router_phys, n_pairs, L->k, L->E_router, L->d_slot_map, L->d_slot_map + L->E);
+    router = L->d_router_phys;
+  }
+  CSK_CUDA(L, cudaMemsetAsync(L->d_counts, 0, sizeof(int) * L->E, s));
+  CSK_CUDA(L, cudaMemsetAsync(L->d_meta, 0, sizeof(int) * 8, s));
+  k_hist<<<grid_for(n_pairs, 256, 2 * L->sm_count), 256, sizeof(int) * L->E, s>>>(router, n_pairs, L->E, -1, L->d_counts,
+                                                                                 L->d_meta);
+  CSK_CUDA(L, cudaGetLastError());
+  CSK_CUDA(L, cudaMemcpyAsync(d_counts, L->d_counts, sizeof(int) * L->E, cudaMemcpyDeviceToDevice, s));
+  return CSK_OK;
+}
+
+// Stage 2 (after the all-gather of the counts): rows to the ranks that own their slots.
+int csk_moe_ep_p2p_scatter_dev(csk_moe_layer* L, const float* d_hidden, int64_t T, const int32_t* d_all_counts,
+                               void* stream) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  if (!d_hidden || !d_all_counts) return fail(L, CSK_ERR_INVALID, "null argument");
+  if (L->p2p_world <= 0) return fail(L, CSK_ERR_INVALID, "p2p: peers were never imported");
+  if (T != L->last_T) return fail(L, CSK_ERR_INVALID, "p2p: scatter must follow counts of the same batch");
+  CSK_CUDA(L, cudaSetDevice(L->cfg.device));
+  cudaStream_t s = pick(L, stream);
+  const int n_pairs = (int)(T * L->k);
+  const float* router = L->has_slot_map ? L->d_router_phys : L->d_router;
+  k_ep_p2p_base<<<1, 1024, 0, s>>>(d_all_counts, L->p2p_world, L->p2p_rank, L->E, L->Eloc, (int)L->max_rows,
+                                   L->d_p2p_base, L->d_cursor, L->d_meta);
+  k_ep_p2p_scatter<<<grid_for(n_pairs, 8, 8 * L->sm_count), 256, 0, s>>>(
+      router, d_hidden, n_pairs, L->k, L->H, L->E, L->Eloc, L->p2p_rank, L->d_p2p_base, L->d_cursor, L->d_peer_x16,
+      L->d_peer_info, L->ldx, (int)L->max_rows, L->cfg.weight_before_ffn, L->d_row_of_pair, L->d_meta);
+  CSK_CUDA(L, cudaGetLastError());
+  return CSK_OK;
+}
+
+// Stage 3 (after a barrier: every rank's rows have landed): the resident experts over the
+// received rows; output rows go straight to their owners' return buffers.
+int csk_moe_ep_p2p_experts_dev(csk_moe_layer* L, const int32_t* d_all_counts, int64_t rows_hint, void* stream) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  if (!d_all_counts) return fail(L, CSK_ERR_INVALID, "null argument");
+  if (L->p2p_world <= 0) return fail(L, CSK_ERR_INVALID, "p2p: peers were never imported");
+  CSK_CUDA(L, cudaSetDevice(L->cfg.device));
+  cudaStream_t s = pick(L, stream);
+  rows_hint = std::max<int64_t>(1, std::min<int64_t>(rows_hint, L->max_rows));
+  const int path = choose_path(L, rows_hint);
+  const int tile_rows = tile_rows_for(L, path, rows_hint);
+  // the status word of the dispatch stays; the tile list is rebuilt from the received counts
+  k_ep_p2p_local_counts<<<(L->E + 255) / 256, 256, 0, s>>>(d_all_counts, L->p2p_world, L->E, L->e0, L->Eloc, L->d_counts);
+  k_scan<<<1, 1024, 0, s>>>(L->d_counts, L->E, L->e0, L->Eloc, tile_rows, (int)L->max_rows, L->max_tiles,
+                            L->d_resident, L->d_offsets, L->d_cursor, L->d_tiles, L->d_meta, nullptr, 0, -1);
+  k_ep_p2p_rowptr<<<4 * L->sm_count, 256, 0, s>>>(L->d_info, L->d_meta, L->d_peer_back, L->H, L->d_row_ptr);
+  CSK_CUDA(L, cudaGetLastError());
+  StageTimer tm(L, s);
+  tm.mark();
+  int rc;
+  if (path == CSK_PATH_TILE) {
+    rc = launch_experts(L, path, tile_rows, rows_hint, rows_hint, L->d_x16, nullptr, L->H, nullptr, s, tm, L->d_row_ptr);
+  } else {
+    rc = launch_experts(L, path, tile_rows, rows_hint, rows_hint, L->d_x16, L->d_y, L->H, nullptr, s, tm);
+    if (!rc) {
+      k_ep_p2p_return<<<8 * L->sm_count, 256, 0, s>>>(L->d_y, L->H, L->d_row_ptr, L->d_meta);
+      CSK_CUDA(L, cudaGetLastError());
+    }
+  }
+  if (rc) return rc;
+  return ep_finish(L, s, tm.n);
+}
+
+// Stage 4 (after a second barrier: every output row of this rank's pairs has landed).
+int csk_moe_ep_p2p_combine_dev(csk_moe_layer* L, int64_t T, float* d_out, float* d_router_out, void* stream) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  if (L->p2p_world <= 0) return fail(L, CSK_ERR_INVALID, "p2p: peers were never imported");
+  return csk_moe_ep_combine_dev(L, L->d_back, T, d_out, d_router_out, stream);
+}
+
 int csk_moe_ep_experts_dev(csk_moe_layer* L, const void* d_recv_f16, const int32_t* d_recv_counts,
                            int32_t n_src, int64_t total_rows, float* d_ret, void* stream) {
   if (check_layer(L)) return CSK_ERR_INVALID;
@@ -967,16 +1179,7 @@ int csk_moe_ep_experts_dev(csk_moe_layer* L, const void* d_recv_f16, const int32
     }
   }
   if (rc) return rc;
-  L->last_stream = s;
-  if (!L->timing) return CSK_OK;  // enqueue only; csk_moe_sync reports what the kernels found
-  rc = check_device_status(L, s);
-  if (rc) return rc;
-  if (tm.n == 3) {  // the status check above already waited for the stream
-    cudaEventElapsedTime(&L->last.gate_up_ms, L->ev[0], L->ev[1]);
-    cudaEventElapsedTime(&L->last.down_ms, L->ev[1], L->ev[2]);
-    L->last.total_ms = L->last.gate_up_ms + L->last.down_ms;
-  }
-  return CSK_OK;
+  return ep_finish(L, s, tm.n);
 }
 
 int csk_moe_ep_combine_dev(csk_moe_layer* L, const float* d_back, int64_t T, float* d_out,

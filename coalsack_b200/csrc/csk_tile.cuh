@@ -263,6 +263,7 @@ struct TileArgs {
   float* y_out;           // !GATED: output rows [rows, ldy]
   int ldy;
   const int* out_row_map; // optional indirection of output rows (!GATED)
+  float* const* out_row_ptr;  // or: where each output row goes (possibly another GPU's memory); wins over the map
   const RowTile* tiles;
   const int* n_tiles_ptr;
   int* meta;              // meta[3] = device status word
@@ -555,14 +556,18 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
           uint32_t r[32];
           tmem_ld32(t_acc + c0, r);
           tmem_ld_wait();
-          // lane j fetches the output row of token c0 + j once; every lane then reads it by shuffle
-          int my_orow = rt.row0 + c0 + lane;
-          if (A.out_row_map) my_orow = (c0 + lane < rt.rows) ? A.out_row_map[rt.row0 + c0 + lane] : 0;
+          // lane j fetches the address of token c0 + j's output row once; every lane then reads it by shuffle
+          float* my_row = nullptr;
+          if (c0 + lane < rt.rows) {
+            const int gr = rt.row0 + c0 + lane;
+            my_row = A.out_row_ptr ? A.out_row_ptr[gr]
+                                   : A.y_out + (size_t)(A.out_row_map ? A.out_row_map[gr] : gr) * A.ldy;
+          }
+          const unsigned long long my_bits = reinterpret_cast<unsigned long long>(my_row);
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
-            const int orow = __shfl_sync(0xffffffffu, my_orow, j);
-            if (n_ok && c0 + j < rt.rows)
-              A.y_out[(size_t)orow * A.ldy + n] = __uint_as_float(r[j]) * oscale + my_bias;
+            float* row = reinterpret_cast<float*>(__shfl_sync(0xffffffffu, my_bits, j));
+            if (n_ok && c0 + j < rt.rows) row[n] = __uint_as_float(r[j]) * oscale + my_bias;
           }
         }
       }
@@ -570,6 +575,7 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_tmem_empty);
     }
+    if (!GATED && A.out_row_ptr) __threadfence_system();  // rows written to other GPUs before the kernel is seen as done
   }
 
   // ------------------------------ teardown ------------------------------
@@ -637,7 +643,8 @@ inline int tile_set_buffers(TileState& st, const __half* x16, int ldx, const __h
 
 inline int tile_launch(TileState& st, const uint8_t* weights, size_t expert_stride, size_t off_gu, size_t off_d,
                        size_t off_bias, size_t off_meta, const TileLayout& Lgu, const TileLayout& Ld, __half* a16,
-                       int lda, float* y, int ldy, const int* out_row_map, const RowTile* tiles, int* meta,
+                       int lda, float* y, int ldy, const int* out_row_map, float* const* out_row_ptr,
+                       const RowTile* tiles, int* meta,
                        int has_bias, int act, int F, int sm_count, cudaStream_t s, const std::function<void()>& mark) {
   if (!st.available || !st.maps_ready) {
     st.err = "tensor-core path is not initialised";
@@ -669,6 +676,7 @@ inline int tile_launch(TileState& st, const uint8_t* weights, size_t expert_stri
   a.y_out = y;
   a.ldy = ldy;
   a.out_row_map = out_row_map;
+  a.out_row_ptr = out_row_ptr;
   a.meta_slot = 1;
   k_tile<false><<<sm_count, kTileThreads, smem, s>>>(st.tmap_a, a);
   mark();

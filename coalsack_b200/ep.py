@@ -233,6 +233,46 @@ class EpLayer:
         return total
 
 
+class P2pEpLayer:
+    """The same step with the rows moved by the kernels themselves over NVLink peer memory:
+    dispatch stores each row into the owning rank's row buffer at its final position, the down
+    projection's epilogue stores each output row into the token owner's return buffer.  The
+    process group is left with an all-gather of 4*E bytes per rank and two barriers; nothing in
+    the step waits on the host.  GPU backend only (`GpuBackend`)."""
+
+    def __init__(self, backend, world, group=None):
+        import torch
+        import torch.distributed as dist
+        self.torch, self.dist = torch, dist
+        self.b, self.world, self.group = backend, world, group
+        lay = backend.layer
+        rank = dist.get_rank(group)
+        # exchange the CUDA IPC handles of the three buffers every peer writes into
+        mine = torch.frombuffer(bytearray(lay.ep_p2p_export()), dtype=torch.uint8).to(backend.dev)
+        allh = torch.empty(world * mine.numel(), dtype=torch.uint8, device=backend.dev)
+        dist.all_gather_into_tensor(allh, mine, group=group)
+        lay.ep_p2p_import(rank, world, bytes(allh.cpu().numpy().tobytes()))
+        E = lay.E
+        self.counts = torch.zeros(E, dtype=torch.int32, device=backend.dev)
+        self.all_counts = torch.zeros(world * E, dtype=torch.int32, device=backend.dev)
+        self.token = torch.zeros(1, dtype=torch.int32, device=backend.dev)
+
+    def _barrier(self):
+        # stream-ordered: every rank's kernels before it have finished (their peer stores are done)
+        self.dist.all_reduce(self.token, group=self.group)
+
+    def forward(self, hidden, T, out):
+        lay, st = self.b.layer, self.b.stream()
+        lay.ep_p2p_counts_dev(hidden, T, self.counts, stream=st)
+        self.dist.all_gather_into_tensor(self.all_counts, self.counts, group=self.group)
+        lay.ep_p2p_scatter_dev(hidden, T, self.all_counts, stream=st)
+        self._barrier()
+        lay.ep_p2p_experts_dev(self.all_counts, T * self.b.k, stream=st)
+        self._barrier()
+        lay.ep_p2p_combine_dev(T, out, stream=st)
+        return T * self.b.k
+
+
 class EpBench:
     """bench.py's N > 1 runner: weak scaling, T tokens per rank."""
 
@@ -253,7 +293,10 @@ class EpBench:
         # a rank may receive more rows than it sends when routing is uneven: leave 3x head-room
         self.backend = GpuBackend(sh, rank, world, local, max_tokens=3 * sh.tokens, placement=place)
         self.backend.load_synthetic()
-        self.ep = EpLayer(self.backend, world)
+        # rows move over peer memory unless CSK_EP_NCCL=1 asks for the all-to-all version
+        import os
+        self.p2p = os.environ.get("CSK_EP_NCCL", "0") != "1"
+        self.ep = P2pEpLayer(self.backend, world) if self.p2p else EpLayer(self.backend, world)
         self.h_host = torch.from_numpy(h).pin_memory()
         self.out_host = torch.empty_like(self.h_host).pin_memory()
         self.d_hidden = self.h_host.to(self.dev)

@@ -204,6 +204,41 @@ class MoeLayer:
         self._check(self._lib.csk_moe_ep_set_slot_map(self._h, int(p.shape[0]), _p(p), _p(r)))
         self.E_router = int(p.shape[0])
 
+    # -- expert parallelism over peer memory ---------------------------------------
+    IPC_BYTES = 3 * 64
+
+    def ep_p2p_export(self) -> bytes:
+        buf = (C.c_uint8 * self.IPC_BYTES)()
+        self._check(self._lib.csk_moe_ep_p2p_export(self._h, buf))
+        return bytes(buf)
+
+    def ep_p2p_import(self, rank, world, all_handles: bytes):
+        if len(all_handles) != world * self.IPC_BYTES:
+            raise ValueError("all_handles must hold world * 192 bytes")
+        buf = (C.c_uint8 * len(all_handles)).from_buffer_copy(all_handles)
+        self._check(self._lib.csk_moe_ep_p2p_import(self._h, rank, world, buf))
+
+    def ep_p2p_local_ptrs(self):
+        p = [C.c_void_p() for _ in range(3)]
+        self._check(self._lib.csk_moe_ep_p2p_local_ptrs(self._h, C.byref(p[0]), C.byref(p[1]), C.byref(p[2])))
+        return tuple(x.value for x in p)
+
+    def ep_p2p_import_ptrs(self, rank, world, x16, info, back):
+        arr = lambda v: (C.c_void_p * world)(*v)
+        self._check(self._lib.csk_moe_ep_p2p_import_ptrs(self._h, rank, world, arr(x16), arr(info), arr(back)))
+
+    def ep_p2p_counts_dev(self, d_hidden, T, d_counts, d_router_in=None, stream=None):
+        self._check(self._lib.csk_moe_ep_p2p_counts_dev(self._h, _p(d_hidden), T, _p(d_router_in), _p(d_counts), stream))
+
+    def ep_p2p_scatter_dev(self, d_hidden, T, d_all_counts, stream=None):
+        self._check(self._lib.csk_moe_ep_p2p_scatter_dev(self._h, _p(d_hidden), T, _p(d_all_counts), stream))
+
+    def ep_p2p_experts_dev(self, d_all_counts, rows_hint, stream=None):
+        self._check(self._lib.csk_moe_ep_p2p_experts_dev(self._h, _p(d_all_counts), rows_hint, stream))
+
+    def ep_p2p_combine_dev(self, T, d_out, d_router_out=None, stream=None):
+        self._check(self._lib.csk_moe_ep_p2p_combine_dev(self._h, T, _p(d_out), _p(d_router_out), stream))
+
     # -- knobs / observability ---------------------------------------------------
     def set_path(self, path):
         self._check(self._lib.csk_moe_set_path(self._h, path))

@@ -211,6 +211,46 @@ int csk_moe_ep_combine_dev(csk_moe_layer* layer, const float* d_back, int64_t T,
 int csk_moe_ep_set_slot_map(csk_moe_layer* layer, int32_t n_logical, const int32_t* primary_slot,
                             const int32_t* replica_slot);
 
+/* ---- expert parallelism over peer memory (NVLink) --------------------------
+ * The same step without all-to-all collectives for the rows: dispatch writes each
+ * row straight into the row buffer of the rank that owns its expert slot, at its
+ * final expert-grouped position; the down projection's epilogue writes each output
+ * row straight into the return buffer of the rank that owns the token.  What is
+ * left for the caller's communication library is an all-gather of the per-slot
+ * row counts and two barriers:
+ *
+ *   counts_dev   : route, map to slots, count this rank's rows per slot -> d_counts [E]
+ *   <all-gather of d_counts into d_all_counts [world, E]>
+ *   scatter_dev  : fp16 rows -> the owners' buffers (peer stores)
+ *   <barrier>
+ *   experts_dev  : resident experts over the received rows; fp32 output rows ->
+ *                  the token owners' buffers (peer stores)
+ *   <barrier>
+ *   combine_dev  : weighted sum over k of the rows returned to this rank
+ *
+ * Setup, once: every rank exports three buffers as CUDA IPC handles (export),
+ * the 3 * CSK_IPC_HANDLE_BYTES bytes of all ranks are gathered in rank order and
+ * imported (import).  Ranks that live in one process exchange raw pointers
+ * instead (local_ptrs / import_ptrs).  Rank r must own expert slots
+ * [r*E/world, (r+1)*E/world) and all ranks must use the same max_tokens.
+ * rows_hint: expected number of received rows (chooses the kernel; T*top_k when
+ * the load is even).  No counterpart in the reference. */
+#define CSK_IPC_HANDLE_BYTES 64
+int csk_moe_ep_p2p_export(csk_moe_layer* layer, uint8_t* handles /* 3 * CSK_IPC_HANDLE_BYTES */);
+int csk_moe_ep_p2p_import(csk_moe_layer* layer, int32_t rank, int32_t world,
+                          const uint8_t* all_handles /* world * 3 * CSK_IPC_HANDLE_BYTES */);
+int csk_moe_ep_p2p_local_ptrs(csk_moe_layer* layer, void** x16, void** info, void** back);
+int csk_moe_ep_p2p_import_ptrs(csk_moe_layer* layer, int32_t rank, int32_t world, void* const* x16,
+                               void* const* info, void* const* back);
+int csk_moe_ep_p2p_counts_dev(csk_moe_layer* layer, const float* d_hidden, int64_t T,
+                              const float* d_router_out_in, int32_t* d_counts, void* stream);
+int csk_moe_ep_p2p_scatter_dev(csk_moe_layer* layer, const float* d_hidden, int64_t T,
+                               const int32_t* d_all_counts, void* stream);
+int csk_moe_ep_p2p_experts_dev(csk_moe_layer* layer, const int32_t* d_all_counts, int64_t rows_hint,
+                               void* stream);
+int csk_moe_ep_p2p_combine_dev(csk_moe_layer* layer, int64_t T, float* d_out, float* d_router_out_out,
+                               void* stream);
+
 /* ---- knobs and observability ------------------------------------------- */
 int csk_moe_set_path(csk_moe_layer* layer, int32_t path /* CSK_PATH_* */);
 

@@ -104,3 +104,66 @@ def test_emulated_ep_with_replicated_experts(gpu_lib, port, path):
         assert np.array_equal(ro[..., 0], want_ro[..., 0])
         mx, mr = cases.err_stats(out, want)
         assert mx <= cases.MAX_ABS_OVER_RMS and mr <= cases.MEAN_REL, (path, mx, mr)
+
+
+def run_emulated_p2p(torch, sh, N, tokens, Wg, rb, ex, path, slot_map=None):
+    """N ranks as N handles on one GPU; the peers' buffers are exchanged as raw pointers and the
+    stages run in lockstep (all ranks' scatter, then all ranks' experts, ...), so no kernel ever
+    waits for another."""
+    E, k, H = sh.num_experts, sh.top_k, sh.hidden
+    eloc = E // N
+    dev = torch.device("cuda", 0)
+    cap = max(sum(tokens), 1)
+    layers, hs = [], []
+    for r in range(N):
+        lay = MoeLayer.from_shape(sh, max_tokens=cap, expert_begin=r * eloc, expert_count=eloc)
+        if slot_map is not None:
+            lay.ep_set_slot_map(*slot_map)
+        lay.set_router(Wg, rb)
+        lay.load_experts({n: (None if ex.get(n) is None else ex[n][r * eloc:(r + 1) * eloc])
+                          for n in ("w_up", "w_gate", "w_down", "b_up", "b_gate", "b_down")},
+                         ids=range(r * eloc, (r + 1) * eloc))
+        lay.set_path(path)
+        layers.append(lay)
+        hs.append(torch.from_numpy(synth.hidden_states(sh, tokens[r], rep=r)).to(dev))
+    ptrs = [lay.ep_p2p_local_ptrs() for lay in layers]
+    for r, lay in enumerate(layers):
+        lay.ep_p2p_import_ptrs(r, N, [p[0] for p in ptrs], [p[1] for p in ptrs], [p[2] for p in ptrs])
+    counts = [torch.zeros(E, dtype=torch.int32, device=dev) for _ in range(N)]
+    for r in range(N):
+        if tokens[r]:
+            layers[r].ep_p2p_counts_dev(hs[r], tokens[r], counts[r])
+    torch.cuda.synchronize()
+    all_counts = torch.cat(counts).contiguous()
+    for r in range(N):
+        if tokens[r]:
+            layers[r].ep_p2p_scatter_dev(hs[r], tokens[r], all_counts)
+    torch.cuda.synchronize()
+    for r in range(N):
+        layers[r].ep_p2p_experts_dev(all_counts, max(1, sum(tokens) * k // N))
+        layers[r].sync()
+    outs = []
+    for r in range(N):
+        if not tokens[r]:
+            continue
+        out = torch.empty((tokens[r], H), dtype=torch.float32, device=dev)
+        ro = torch.empty((tokens[r], k, 2), dtype=torch.float32, device=dev)
+        layers[r].ep_p2p_combine_dev(tokens[r], out, ro)
+        torch.cuda.synchronize()
+        outs.append((out.cpu().numpy(), ro.cpu().numpy(), hs[r].cpu().numpy()))
+    for lay in layers:
+        lay.close()
+    return outs
+
+
+@pytest.mark.parametrize("path", [PATH_STREAM, PATH_TILE])
+@pytest.mark.parametrize("N,tokens", [(2, (37, 64)), (4, (3, 1, 50, 9))])
+def test_emulated_p2p_matches_checker(gpu_lib, port, path, N, tokens):
+    import torch
+    sh = synth.tiny(seed=85, E=8, k=3, H=192, F=160, T=1, has_bias=True)
+    _, Wg, rb, ex = cases.layer_inputs(sh, router_scale=40.0)
+    for out, ro, h in run_emulated_p2p(torch, sh, N, tokens, Wg, rb, ex, path):
+        want, want_ro = port.moe_layer(h, Wg, rb, ex, sh.top_k, sh.act, nthreads=4)
+        assert np.array_equal(ro[..., 0], want_ro[..., 0])
+        mx, mr = cases.err_stats(out, want)
+        assert mx <= cases.MAX_ABS_OVER_RMS and mr <= cases.MEAN_REL, (path, N, mx, mr)
