@@ -1005,12 +1005,19 @@ int csk_moe_ep_p2p_export(csk_moe_layer* L, uint8_t* handles) {
   CSK_CUDA(L, cudaSetDevice(L->cfg.device));
   int rc = p2p_alloc_local(L);
   if (rc) return rc;
-  static_assert(sizeof(cudaIpcMemHandle_t) == CSK_IPC_HANDLE_BYTES, "handle size");
+  static_assert(sizeof(cudaIpcMemHandle_t) + sizeof(uint64_t) == CSK_IPC_HANDLE_BYTES, "handle size");
   void* bufs[3] = {L->d_x16, L->d_info, L->d_back};
   for (int i = 0; i < 3; ++i) {
+    // a handle names the whole allocation a pointer lies in (small buffers share one): ship the offset too
     cudaIpcMemHandle_t h;
     CSK_CUDA(L, cudaIpcGetMemHandle(&h, bufs[i]));
-    memcpy(handles + (size_t)i * CSK_IPC_HANDLE_BYTES, &h, CSK_IPC_HANDLE_BYTES);
+    CUdeviceptr base = 0;
+    size_t size = 0;
+    if (cuMemGetAddressRange(&base, &size, (CUdeviceptr)bufs[i]) != CUDA_SUCCESS)
+      return fail(L, CSK_ERR_CUDA, "p2p: cuMemGetAddressRange failed");
+    const uint64_t off = (uint64_t)((CUdeviceptr)bufs[i] - base);
+    memcpy(handles + (size_t)i * CSK_IPC_HANDLE_BYTES, &h, sizeof(h));
+    memcpy(handles + (size_t)i * CSK_IPC_HANDLE_BYTES + sizeof(h), &off, sizeof(off));
   }
   return CSK_OK;
 }
@@ -1023,6 +1030,8 @@ int csk_moe_ep_p2p_import(csk_moe_layer* L, int32_t rank, int32_t world, const u
   if (rc) return rc;
   if (world < 1 || world > 64 || rank < 0 || rank >= world) return fail(L, CSK_ERR_INVALID, "p2p: bad rank/world %d/%d", rank, world);
   std::vector<void*> ptr(3 * (size_t)world, nullptr);
+  std::vector<cudaIpcMemHandle_t> opened_handles;
+  std::vector<void*> opened_ptrs;
   void* own[3] = {L->d_x16, L->d_info, L->d_back};
   for (int r = 0; r < world; ++r)
     for (int i = 0; i < 3; ++i) {
@@ -1031,11 +1040,21 @@ int csk_moe_ep_p2p_import(csk_moe_layer* L, int32_t rank, int32_t world, const u
         continue;
       }
       cudaIpcMemHandle_t h;
-      memcpy(&h, all_handles + ((size_t)r * 3 + i) * CSK_IPC_HANDLE_BYTES, CSK_IPC_HANDLE_BYTES);
+      uint64_t off = 0;
+      const uint8_t* rec = all_handles + ((size_t)r * 3 + i) * CSK_IPC_HANDLE_BYTES;
+      memcpy(&h, rec, sizeof(h));
+      memcpy(&off, rec + sizeof(h), sizeof(off));
+      // two of a peer's buffers may lie in one allocation: open each allocation once
       void* p = nullptr;
-      CSK_CUDA(L, cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
-      L->ipc_opened.push_back(p);
-      ptr[(size_t)i * world + r] = p;
+      for (size_t j = 0; j < opened_handles.size(); ++j)
+        if (!memcmp(&opened_handles[j], &h, sizeof(h))) p = opened_ptrs[j];
+      if (!p) {
+        CSK_CUDA(L, cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+        L->ipc_opened.push_back(p);
+        opened_handles.push_back(h);
+        opened_ptrs.push_back(p);
+      }
+      ptr[(size_t)i * world + r] = static_cast<uint8_t*>(p) + off;
     }
   return p2p_set_peers(L, rank, world, ptr.data(), ptr.data() + world, ptr.data() + 2 * (size_t)world);
 }

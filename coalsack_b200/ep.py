@@ -162,7 +162,14 @@ class GpuBackend:
             self.layer.load_expert(p, w["w_up"], w["w_gate"], w["w_down"], w["b_up"], w["b_gate"], w["b_down"])
 
     def stream(self):
-        return self.torch.cuda.current_stream(self.dev).cuda_stream
+        """Handle of torch's current stream, which the process group's collectives order themselves with.
+        It must not be the legacy default stream: the C ABI reads a null stream as "the layer's own
+        stream", and kernels there would race with the collectives."""
+        h = self.torch.cuda.current_stream(self.dev).cuda_stream
+        if not h:
+            raise RuntimeError("run the expert-parallel step inside `with torch.cuda.stream(s)` for a "
+                               "non-default stream s (a null stream handle means the layer's own stream)")
+        return h
 
     def new_rows(self, n):
         return self.torch.empty((n, self.pitch), dtype=self.row_dtype, device=self.dev)
@@ -301,11 +308,12 @@ class EpBench:
         self.out_host = torch.empty_like(self.h_host).pin_memory()
         self.d_hidden = self.h_host.to(self.dev)
         self.d_out = torch.empty_like(self.d_hidden)
-        self.torch_stream = torch.cuda.current_stream(self.dev)
+        self.torch_stream = torch.cuda.Stream(device=self.dev)
         self.T = sh.tokens
 
     def step_dev(self):
-        self.ep.forward(self.d_hidden, self.T, self.d_out)
+        with self.torch.cuda.stream(self.torch_stream):
+            self.ep.forward(self.d_hidden, self.T, self.d_out)
 
     def sync(self):
         self.torch.cuda.synchronize()
@@ -319,8 +327,12 @@ class EpBench:
         n = max(3, min(steps, 10))
         rows = 0
         for _ in range(n):
-            rows = self.ep.forward(self.d_hidden, self.T, self.d_out)
+            with self.torch.cuda.stream(self.torch_stream):
+                rows = self.ep.forward(self.d_hidden, self.T, self.d_out)
             self.torch.cuda.synchronize()
+            if self.p2p:  # rows this rank's experts actually received
+                b = self.backend
+                rows = int(self.ep.all_counts.view(self.world, -1)[:, b.e0:b.e0 + b.eloc].sum().item())
             t = lay.timings()
             acc["gate_up_ms"] += t["gate_up_ms"]
             acc["down_ms"] += t["down_ms"]
@@ -336,14 +348,16 @@ class EpBench:
         import time
         torch = self.torch
         for _ in range(warmup):
-            self.d_hidden.copy_(self.h_host, non_blocking=True)
-            self.step_dev()
-            self.out_host.copy_(self.d_out, non_blocking=True)
+            with torch.cuda.stream(self.torch_stream):
+                self.d_hidden.copy_(self.h_host, non_blocking=True)
+                self.step_dev()
+                self.out_host.copy_(self.d_out, non_blocking=True)
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         for _ in range(steps):
-            self.d_hidden.copy_(self.h_host, non_blocking=True)
-            self.step_dev()
-            self.out_host.copy_(self.d_out, non_blocking=True)
+            with torch.cuda.stream(self.torch_stream):
+                self.d_hidden.copy_(self.h_host, non_blocking=True)
+                self.step_dev()
+                self.out_host.copy_(self.d_out, non_blocking=True)
             torch.cuda.synchronize()
         return (time.perf_counter() - t0) * 1e3 / steps

@@ -205,7 +205,7 @@ class MoeLayer:
         self.E_router = int(p.shape[0])
 
     # -- expert parallelism over peer memory ---------------------------------------
-    IPC_BYTES = 3 * 64
+    IPC_BYTES = 3 * 72
 
     def ep_p2p_export(self) -> bytes:
         buf = (C.c_uint8 * self.IPC_BYTES)()
@@ -214,7 +214,7 @@ class MoeLayer:
 
     def ep_p2p_import(self, rank, world, all_handles: bytes):
         if len(all_handles) != world * self.IPC_BYTES:
-            raise ValueError("all_handles must hold world * 192 bytes")
+            raise ValueError(f"all_handles must hold world * {self.IPC_BYTES} bytes")
         buf = (C.c_uint8 * len(all_handles)).from_buffer_copy(all_handles)
         self._check(self._lib.csk_moe_ep_p2p_import(self._h, rank, world, buf))
 

@@ -235,7 +235,7 @@ int csk_moe_ep_set_slot_map(csk_moe_layer* layer, int32_t n_logical, const int32
  * [r*E/world, (r+1)*E/world) and all ranks must use the same max_tokens.
  * rows_hint: expected number of received rows (chooses the kernel; T*top_k when
  * the load is even).  No counterpart in the reference. */
-#define CSK_IPC_HANDLE_BYTES 64
+#define CSK_IPC_HANDLE_BYTES 72 /* a CUDA IPC memory handle and the buffer's offset in that allocation */
 int csk_moe_ep_p2p_export(csk_moe_layer* layer, uint8_t* handles /* 3 * CSK_IPC_HANDLE_BYTES */);
 int csk_moe_ep_p2p_import(csk_moe_layer* layer, int32_t rank, int32_t world,
                           const uint8_t* all_handles /* world * 3 * CSK_IPC_HANDLE_BYTES */);
