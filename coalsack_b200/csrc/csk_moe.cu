@@ -1006,6 +1006,15 @@ int csk_moe_ep_p2p_export(csk_moe_layer* L, uint8_t* handles) {
   int rc = p2p_alloc_local(L);
   if (rc) return rc;
   static_assert(sizeof(cudaIpcMemHandle_t) + sizeof(uint64_t) == CSK_IPC_HANDLE_BYTES, "handle size");
+  // the driver entry point is looked up at run time: the library has no link-time dependency on libcuda
+  typedef CUresult (*GetRangeFn)(CUdeviceptr*, size_t*, CUdeviceptr);
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn) {
+    cudaGetLastError();
+    return fail(L, CSK_ERR_CUDA, "p2p: cuMemGetAddressRange not found in the driver");
+  }
+  const GetRangeFn get_range = (GetRangeFn)fn;
   void* bufs[3] = {L->d_x16, L->d_info, L->d_back};
   for (int i = 0; i < 3; ++i) {
     // a handle names the whole allocation a pointer lies in (small buffers share one): ship the offset too
@@ -1013,7 +1022,7 @@ int csk_moe_ep_p2p_export(csk_moe_layer* L, uint8_t* handles) {
     CSK_CUDA(L, cudaIpcGetMemHandle(&h, bufs[i]));
     CUdeviceptr base = 0;
     size_t size = 0;
-    if (cuMemGetAddressRange(&base, &size, (CUdeviceptr)bufs[i]) != CUDA_SUCCESS)
+    if (get_range(&base, &size, (CUdeviceptr)bufs[i]) != CUDA_SUCCESS)
       return fail(L, CSK_ERR_CUDA, "p2p: cuMemGetAddressRange failed");
     const uint64_t off = (uint64_t)((CUdeviceptr)bufs[i] - base);
     memcpy(handles + (size_t)i * CSK_IPC_HANDLE_BYTES, &h, sizeof(h));
