@@ -270,13 +270,18 @@ class P2pEpLayer:
 
     def forward(self, hidden, T, out):
         lay, st = self.b.layer, self.b.stream()
-        lay.ep_p2p_counts_dev(hidden, T, self.counts, stream=st)
+        if T:
+            lay.ep_p2p_counts_dev(hidden, T, self.counts, stream=st)
+        else:
+            self.counts.zero_()  # a rank without tokens still serves its experts
         self.dist.all_gather_into_tensor(self.all_counts, self.counts, group=self.group)
-        lay.ep_p2p_scatter_dev(hidden, T, self.all_counts, stream=st)
+        if T:
+            lay.ep_p2p_scatter_dev(hidden, T, self.all_counts, stream=st)
         self._barrier()
-        lay.ep_p2p_experts_dev(self.all_counts, T * self.b.k, stream=st)
+        lay.ep_p2p_experts_dev(self.all_counts, max(T, 1) * self.b.k, stream=st)
         self._barrier()
-        lay.ep_p2p_combine_dev(T, out, stream=st)
+        if T:
+            lay.ep_p2p_combine_dev(T, out, stream=st)
         return T * self.b.k
 
 

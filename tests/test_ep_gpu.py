@@ -157,7 +157,7 @@ def run_emulated_p2p(torch, sh, N, tokens, Wg, rb, ex, path, slot_map=None):
 
 
 @pytest.mark.parametrize("path", [PATH_STREAM, PATH_TILE])
-@pytest.mark.parametrize("N,tokens", [(2, (37, 64)), (4, (3, 1, 50, 9))])
+@pytest.mark.parametrize("N,tokens", [(2, (37, 64)), (4, (3, 1, 50, 9)), (2, (0, 40))])
 def test_emulated_p2p_matches_checker(gpu_lib, port, path, N, tokens):
     import torch
     sh = synth.tiny(seed=85, E=8, k=3, H=192, F=160, T=1, has_bias=True)
