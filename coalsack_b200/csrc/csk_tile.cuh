@@ -12,10 +12,13 @@
 //   * per 64-column k-step the producer warp issues one TMA tensor load of the
 //     192 x 64 fp16 token tile (128-byte swizzle) and one bulk copy of the packed
 //     weight tile (2 x 4352 bytes: codes + E8M0 scales, one contiguous span);
-//   * eight dequantiser warps turn the packed tile into fp16 (cvt.e2m1x2 ->
-//     half2, times 2^(e - e_max + 13)) and write it straight into tensor memory
-//     with tcgen05.st: thread = one weight row, 32 columns of one 32-element
-//     block = 16 registers.  The dequantised weights never touch shared memory;
+//   * eight dequantiser warps in two groups of four turn the packed tile into fp16
+//     (cvt.e2m1x2 -> half2, times 2^(e - e_max + 13)) and write it straight into
+//     tensor memory with tcgen05.st: thread = one weight row x the 64 columns of
+//     the k-step, one half of the tile after the other.  The groups alternate
+//     k-steps and each owns one slot of the two-slot weight ring; a half is
+//     published as soon as it is stored, so the MMAs of the first half run while
+//     the second is converted.  The dequantised weights never touch shared memory;
 //   * one lane issues eight tcgen05.mma (kind::f16, A from tensor memory, B = the
 //     token tile via a shared-memory descriptor) per k-step, four per half, into
 //     two fp32 accumulators in tensor memory;
@@ -287,7 +290,7 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
   const uint32_t bar_base = smem_u32(bars);
   auto bar_full_raw = [&](int s) { return bar_base + 8u * s; };               // TMA landed
   auto bar_empty_raw = [&](int s) { return bar_base + 8u * (8 + s); };        // MMAs of that k-step retired
-  auto bar_full_a = [&](int s) { return bar_base + 8u * (16 + s); };          // weight tile written to tensor memory
+  auto bar_full_a = [&](int s, int hf) { return bar_base + 8u * (16 + 2 * s + hf); };  // half tile written to tensor memory
   auto bar_empty_a = [&](int s) { return bar_base + 8u * (20 + s); };
   const uint32_t bar_tmem_full = bar_base + 8u * 24;    // both accumulators complete
   const uint32_t bar_tmem_empty = bar_base + 8u * 26;   // all epilogue warps done reading them
@@ -302,8 +305,9 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
       mbar_init(bar_full_raw(s), 1);
       mbar_init(bar_empty_raw(s), 1);
     }
-    for (int s = 0; s < 4; ++s) {
-      mbar_init(bar_full_a(s), kDequantWarps);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar_full_a(s, 0), kDequantWarps / 2);
+      mbar_init(bar_full_a(s, 1), kDequantWarps / 2);
       mbar_init(bar_empty_a(s), 1);
     }
     mbar_init(bar_tmem_full, 1);
@@ -388,19 +392,27 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
         }
         tc_fence_after();
         for (int kt = 0; kt < KT; ++kt) {
-          if (!mbar_wait(bar_full_raw(s), ph, abort_flag) || !mbar_wait(bar_full_a(sa), pha, abort_flag)) {
+          if (!mbar_wait(bar_full_raw(s), ph, abort_flag)) {
             ok = false;
             break;
           }
-          tc_fence_after();
           const uint64_t db = umma_desc_sw128(smem_base + (uint32_t)s * kTileRawBytes);
-          for (int h = 0; h < halves; ++h) {
+          for (int h = 0; h < 2; ++h) {
+            // the halves of a k-step arrive one after the other: the MMAs of the first run while
+            // the second is still being converted
+            if (!mbar_wait(bar_full_a(sa, h), pha, abort_flag)) {
+              ok = false;
+              break;
+            }
+            if (h >= halves) continue;
+            tc_fence_after();
             const uint32_t d_tmem = tmem_base + (uint32_t)h * kTileM;
             const uint32_t a_tmem = tmem_base + kTmemABase + (uint32_t)sa * 64 + (uint32_t)h * 32;
 #pragma unroll
             for (int k4 = 0; k4 < kTileK / 16; ++k4)
               umma_f16_ts(d_tmem, a_tmem + (uint32_t)k4 * 8, db + (uint64_t)(k4 * 2), idesc, (kt | k4) ? 1u : 0u);
           }
+          if (!ok) break;
           umma_commit(bar_empty_raw(s));
           umma_commit(bar_empty_a(sa));
           if (++s == NR) {
@@ -422,80 +434,75 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
     }
   } else if (warp < 2 + kDequantWarps) {
     // ------------------------------ dequantisers ------------------------------
-    // thread = weight row (tensor-memory lane) x one 32-column block of the k-step
+    // Two groups of four warps; group g converts the k-steps whose running number is g mod 2
+    // and owns slot g of the tensor-memory weight ring.  thread = weight row (tensor-memory
+    // lane) x the 64 columns of the k-step, one half after the other: the first half is
+    // converted BEFORE the slot is awaited (so only the store is on the slot's critical path),
+    // the second while the MMAs of the first run.
     const int quarter = warp & 3;            // lanes 32*quarter .. +31 are this warp's
-    const int blk = (warp - 2) >> 2;         // which 32-column block
+    const int grp = (warp - 2) >> 2;         // which k-steps / which slot
     const int trow = quarter * 32 + lane;
-    int s = 0, sa = 0, pending = -1;
-    uint32_t ph = 0, pha = 0;
+    long c = 0;                              // running k-step number of this CTA
+    uint32_t uses = 0;                       // how often this group has filled its slot
     bool ok = true;
+    auto convert = [&](const uint8_t* packed, int emax, uint32_t (&h)[2][16]) {
+#pragma unroll
+      for (int blk = 0; blk < 2; ++blk) {
+        const uint4 cw = *reinterpret_cast<const uint4*>(packed + (blk * 128 + trow) * 16);
+        const int e = packed[4096 + blk * 128 + trow];
+        const uint32_t sh2 = h2_pow2(e - emax + 13);
+        uint32_t t[4];
+        dequant_word(cw.x, t);
+        h[blk][0] = t[0]; h[blk][1] = t[1]; h[blk][2] = t[2]; h[blk][3] = t[3];
+        dequant_word(cw.y, t);
+        h[blk][4] = t[0]; h[blk][5] = t[1]; h[blk][6] = t[2]; h[blk][7] = t[3];
+        dequant_word(cw.z, t);
+        h[blk][8] = t[0]; h[blk][9] = t[1]; h[blk][10] = t[2]; h[blk][11] = t[3];
+        dequant_word(cw.w, t);
+        h[blk][12] = t[0]; h[blk][13] = t[1]; h[blk][14] = t[2]; h[blk][15] = t[3];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) h[blk][i] = hmul2_u32(h[blk][i], sh2);
+      }
+    };
     for (long item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
       const RowTile rt = A.tiles[item / L.n_tiles];
       const int halves = L.halves((int)(item % L.n_tiles));
       const int* emeta = reinterpret_cast<const int*>(A.weights + (size_t)rt.expert * A.expert_stride + A.meta_offset);
       const int emax = emeta[A.meta_slot];
-      for (int kt = 0; kt < KT; ++kt) {
+      for (int kt = 0; kt < KT; ++kt, ++c) {
+        if ((int)(c & 1) != grp) continue;
+        const int s = (int)(c % NR);
+        const uint32_t ph = (uint32_t)((c / NR) & 1);
         if (!mbar_wait(bar_full_raw(s), ph, abort_flag)) {
           ok = false;
           break;
         }
-        // convert first (shared memory -> registers), so that the tensor-memory store of
-        // the previous k-step retires while this one is being prepared
+        const uint8_t* packed = smem + (size_t)s * kTileRawBytes + kTileABytes;
+        const uint32_t t_slot = tmem_base + ((uint32_t)(quarter * 32) << 16) + kTmemABase + (uint32_t)grp * 64;
         uint32_t h[2][16];
-#pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-          if (hf < halves) {
-            const uint8_t* packed = smem + (size_t)s * kTileRawBytes + kTileABytes + hf * kHalfPacked;
-            const uint4 c = *reinterpret_cast<const uint4*>(packed + (blk * 128 + trow) * 16);
-            const int e = packed[4096 + blk * 128 + trow];
-            const uint32_t sh2 = h2_pow2(e - emax + 13);
-            uint32_t t[4];
-            dequant_word(c.x, t);
-            h[hf][0] = t[0]; h[hf][1] = t[1]; h[hf][2] = t[2]; h[hf][3] = t[3];
-            dequant_word(c.y, t);
-            h[hf][4] = t[0]; h[hf][5] = t[1]; h[hf][6] = t[2]; h[hf][7] = t[3];
-            dequant_word(c.z, t);
-            h[hf][8] = t[0]; h[hf][9] = t[1]; h[hf][10] = t[2]; h[hf][11] = t[3];
-            dequant_word(c.w, t);
-            h[hf][12] = t[0]; h[hf][13] = t[1]; h[hf][14] = t[2]; h[hf][15] = t[3];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) h[hf][i] = hmul2_u32(h[hf][i], sh2);
-          }
-        }
-        if (pending >= 0) {  // publish the tile stored in the previous iteration
-          tmem_st_wait();
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar_full_a(pending));
-          pending = -1;
-        }
-        if (!mbar_wait(bar_empty_a(sa), pha ^ 1, abort_flag)) {
+        convert(packed, emax, h);
+        if (!mbar_wait(bar_empty_a(grp), (uses & 1) ^ 1, abort_flag)) {
           ok = false;
           break;
         }
+        ++uses;
         tc_fence_after();
-#pragma unroll
-        for (int hf = 0; hf < 2; ++hf)
-          if (hf < halves)
-            tmem_st16(tmem_base + ((uint32_t)(quarter * 32) << 16) + kTmemABase + (uint32_t)sa * 64 + (uint32_t)hf * 32 +
-                          (uint32_t)blk * 16,
-                      h[hf]);
-        pending = sa;
-        if (++s == NR) {
-          s = 0;
-          ph ^= 1;
+        tmem_st16(t_slot, h[0]);
+        tmem_st16(t_slot + 16, h[1]);
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_full_a(grp, 0));
+        if (halves > 1) {
+          convert(packed + kHalfPacked, emax, h);
+          tmem_st16(t_slot + 32, h[0]);
+          tmem_st16(t_slot + 48, h[1]);
+          tmem_st_wait();
+          tc_fence_before();
+          __syncwarp();
         }
-        if (++sa == NA) {
-          sa = 0;
-          pha ^= 1;
-        }
+        if (lane == 0) mbar_arrive(bar_full_a(grp, 1));
       }
-    }
-    if (pending >= 0) {
-      tmem_st_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_full_a(pending));
     }
   } else {
     // ------------------------------ epilogue ------------------------------
