@@ -1,21 +1,30 @@
-"""Expert parallelism for the MoE layer: one process per GPU, experts sharded,
-tokens data-parallel, two all-to-all exchanges per step.
+"""Expert parallelism for the MoE layer: one process per GPU, expert slots sharded,
+tokens data-parallel.
 
 The reference runs every expert of a layer serially on one host thread
-(src/llm/llm_engine.cpp:737-747); sharding experts across GPUs is new here.  Rank
-r holds experts [r*E/N, (r+1)*E/N) and its own batch of tokens.  A step is
+(src/llm/llm_engine.cpp:737-747); sharding experts across GPUs is new here.  Every
+rank holds E/N expert slots (plus a spare when an expert is worth a second copy) and
+its own batch of tokens.  Two host loops drive the same kernels:
 
-    dispatch   route the local tokens, group their (token, expert) rows by
-               destination rank then expert                      (compute backend)
-    gather     all ranks' per-expert row counts                  (all_gather)
-    exchange   rows to the ranks that own their experts          (all_to_all, variable splits)
-    experts    gated MLP of the resident experts over the rows   (compute backend)
-    exchange   output rows back to the ranks that own the tokens (all_to_all)
-    combine    weighted sum over the k slots in router order     (compute backend)
+``P2pEpLayer`` (default on GPUs): rows travel as peer stores issued by the kernels
+themselves over NVLink --
 
-The collective plumbing is backend-agnostic (NCCL on GPUs; the same code runs on
-gloo with a CPU compute backend in the tests).  The compute backend on GPUs is
-``GpuBackend`` over the C ABI's ``csk_moe_ep_*`` entry points.
+    counts     route the local tokens, map experts to slots, count rows per slot
+    gather     all ranks' counts                                  (all_gather, 4*E bytes)
+    scatter    every row straight into the owning rank's row buffer, at its final
+               expert-grouped position
+    barrier
+    experts    gated MLP of the resident experts; the down projection's epilogue
+               stores every output row straight into the token owner's buffer
+    barrier
+    combine    weighted sum over the k slots in router order
+
+``EpLayer``: the same step with two all-to-all exchanges (dispatch -> gather of counts
+-> all_to_all of rows -> experts -> all_to_all of output rows -> combine).  Its
+collective plumbing is backend-agnostic: the same code runs on gloo with a CPU compute
+backend in the tests.
+
+Placement (`plan_placement`) comes from the load of one calibration batch.
 """
 from __future__ import annotations
 
