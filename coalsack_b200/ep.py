@@ -67,6 +67,18 @@ class Placement:
     def n_slots(self):
         return len(self.slots)
 
+    def slot_map(self, E: int):
+        """(primary_slot[e], replica_slot[e]) of every logical expert, as csk_moe_ep_set_slot_map takes them."""
+        primary = -np.ones(E, dtype=np.int32)
+        replica = -np.ones(E, dtype=np.int32)
+        copies = set(int(s) for s in self.replica_of if s >= 0)
+        for p, e in enumerate(self.slots):
+            if e >= 0 and p not in copies:
+                primary[e] = p
+                replica[e] = self.replica_of[p]
+        assert (primary >= 0).all(), "every expert needs a slot"
+        return primary, replica
+
 
 def plan_placement(load, world: int, extra_slots: int = 0) -> Placement:
     """Placement of E experts on `world` ranks from a measured load per expert (rows it
@@ -146,18 +158,7 @@ class GpuBackend:
         self.H, self.k = shape.hidden, shape.top_k
 
     def slot_map(self):
-        """(primary_slot[e], replica_slot[e]) of every logical expert."""
-        pl = self.placement
-        E = self.sh.num_experts
-        primary = -np.ones(E, dtype=np.int32)
-        replica = -np.ones(E, dtype=np.int32)
-        copies = set(int(s) for s in pl.replica_of if s >= 0)
-        for p, e in enumerate(pl.slots):
-            if e >= 0 and p not in copies:
-                primary[e] = p
-                replica[e] = pl.replica_of[p]
-        assert (primary >= 0).all(), "every expert needs a slot"
-        return primary, replica
+        return self.placement.slot_map(self.sh.num_experts)
 
     def load_synthetic(self):
         sh = self.sh

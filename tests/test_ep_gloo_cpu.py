@@ -78,3 +78,27 @@ def test_balanced_placement_spreads_a_skewed_load():
         assert worst <= worst_strided
         # no rank can do better than the mean, nor than the single heaviest expert plus the lightest others
         assert worst >= load.sum() / N - 1e-9
+
+
+def test_plan_placement_with_second_copies():
+    from coalsack_b200.ep import plan_placement
+    load = np.array([900, 100, 90, 80, 70, 60, 50, 40], dtype=np.float64)
+    pl = plan_placement(load, 2, extra_slots=1)
+    assert pl.n_slots == 10 and pl.per_rank == 5
+    primary, replica = pl.slot_map(8)
+    assert sorted(set(primary.tolist())) == sorted(primary.tolist())          # distinct slots
+    assert replica[0] >= 0, "the expert with 60 % of the rows gets a second copy"
+    for e in range(8):
+        assert pl.slots[primary[e]] == e
+        if replica[e] >= 0:
+            assert pl.slots[replica[e]] == e
+            assert primary[e] // pl.per_rank != replica[e] // pl.per_rank    # the copies sit on different ranks
+    # the busiest rank with the split (each copy serves half the rows) beats the best whole-expert packing
+    def rank_load(p):
+        l = np.zeros(2)
+        for slot, e in enumerate(p.slots):
+            if e >= 0:
+                shared = replica[e] >= 0 if p is pl else False
+                l[slot // p.per_rank] += load[e] / (2 if shared else 1)
+        return l.max()
+    assert rank_load(pl) < rank_load(plan_placement(load, 2, extra_slots=0))
