@@ -288,6 +288,9 @@ def run_ours(args):
             "e2e": {"value": T * world / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": T * H * 4 * world, "d2h_bytes_per_step": T * H * 4 * world},
             "gpu_launches": int(stage["launches"]) * args.steps, "path": stage["path"], "roofline": roofline}
+    if world > 1:
+        line["config"]["exchange"] = ("rows stored into peer memory by the dispatch and down-projection kernels (NVLink)"
+                                      if getattr(runner, "p2p", False) else "all-to-all collectives (NCCL)")
     if cb:
         line["cpu_baseline"] = cb
     print(json.dumps(line))

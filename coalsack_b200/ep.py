@@ -318,7 +318,19 @@ class EpBench:
         # rows move over peer memory unless CSK_EP_NCCL=1 asks for the all-to-all version
         import os
         self.p2p = os.environ.get("CSK_EP_NCCL", "0") != "1"
-        self.ep = P2pEpLayer(self.backend, world) if self.p2p else EpLayer(self.backend, world)
+        if self.p2p:
+            try:
+                self.ep = P2pEpLayer(self.backend, world)
+            except Exception as exc:  # no peer access between these GPUs: the all-to-all step still works
+                import sys
+                print(f"[rank {rank}] peer-memory step unavailable ({exc}); using the all-to-all step", file=sys.stderr)
+                self.p2p = False
+            # every rank must take the same step
+            agree = torch.tensor([1 if self.p2p else 0], device=self.dev)
+            dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+            self.p2p = bool(agree.item())
+        if not self.p2p:
+            self.ep = EpLayer(self.backend, world)
         self.h_host = torch.from_numpy(h).pin_memory()
         self.out_host = torch.empty_like(self.h_host).pin_memory()
         self.d_hidden = self.h_host.to(self.dev)
