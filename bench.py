@@ -1,19 +1,25 @@
 #!/usr/bin/env python
 """Benchmark of the MoE layer on B200: tokens/s of one layer pass over one
-batch of synthetic tokens, with the roofline of its dominant kernel and the
-reference's CPU implementation timed beside it.
+batch of synthetic tokens, with the roofline of its dominant kernel, a decode
+sweep, and the reference's CPU implementation timed beside it.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2] [--impl ours|reference]
 
 A step is one pass of router -> dispatch -> grouped MXFP4 gated MLP -> combine
-over one batch.  ``value`` is measured with the batch already resident in HBM
-(CUDA events on the stream the kernels run on, max over ranks); ``e2e`` goes
-through the host-buffer entry point ``csk_moe_forward`` with pinned host
-buffers, so it includes the host->device and device->host copies.
+over one batch.  The default workload is the gpt-oss-120b-shaped layer (128
+experts, top-4, 2880 x 2880, 8192 tokens).  ``value`` is measured with the batch
+already resident in HBM (CUDA events on the stream the kernels run on, max over
+ranks); ``e2e`` goes through the host-buffer entry point ``csk_moe_forward`` with
+pinned host buffers, so it includes the host->device and device->host copies.
+``decode`` (one GPU) is the same layer at 1..256 tokens per step, 100 fresh
+batches each, in microseconds per step and per token against the HBM roofline.
 
 N > 1 (launched by torchrun, one rank per GPU): expert parallelism.  Each rank
-holds E/N experts and its own batch of tokens (weak scaling); dispatch and
-combine are NCCL all-to-all.
+holds E/N expert slots and T/N of the batch's tokens (strong scaling: the batch
+is the same 8192 tokens at every N; ``--scaling weak`` gives every rank the whole
+token count instead).  Rows travel between ranks as peer-memory stores issued by
+the dispatch and down-projection kernels (NVLink); ``CSK_EP_NCCL=1`` selects the
+variant with NCCL all-to-all collectives.
 """
 from __future__ import annotations
 
@@ -45,11 +51,12 @@ def measured_peaks():
     return {"hbm_gbs": 6650.0, "tflops": 1590.0, "tflops_sustained": 1400.0, "source": "fallback"}
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the dominant kernel, from the ncu captures
-# summarised under profiles/ (single GPU; key = workload name, tokens, kernel)
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the dominant kernel, from an ncu capture
+# (--metrics dram__bytes_read.sum,dram__bytes_write.sum) of this program on the same workload, single GPU.
+# Key = (workload name, tokens, kernel).  Other workloads report null.
 MEASURED_TRAFFIC = {
-    ("c1_gptoss20b_prefill4096_zipf", 4096, "k_tile<gated>"): 476.3e6,     # profiles/k_tile_c1_prefill.md
-    ("c3_gptoss120b_decode", 64, "k_stream<gated>"): 953.8e6,             # profiles/k_stream_c3_decode64.md
+    ("c1_gptoss20b_prefill4096_zipf", 4096, "k_tile<gated>"): 476.3e6,
+    ("c3_gptoss120b_decode", 64, "k_stream<gated>"): 953.8e6,
 }
 
 
@@ -151,26 +158,101 @@ def time_reference(sh, steps, warmup, budget_s=12.0):
                       f"{cores} host threads over tokens; tokens/s extrapolates linearly in tokens"}, dt * 1e3
 
 
+def per_rank_shape(args, world):
+    """The workload one rank sees: under strong scaling the batch's tokens are split over the ranks."""
+    sh = workload_shape(args.workload, args.tokens)
+    total = sh.tokens if args.scaling == "strong" else sh.tokens * world
+    if args.scaling == "strong":
+        if sh.tokens % world:
+            raise SystemExit(f"{sh.tokens} tokens do not split evenly over {world} ranks")
+        sh = sh.with_(tokens=sh.tokens // world)
+    return sh, total
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    sh = workload_shape(args.workload, args.tokens)
-    cb, ms = time_reference(sh, args.steps, args.warmup)
+    sh, total = per_rank_shape(args, args.gpus)
+    cb, ms = time_reference(sh.with_(tokens=total), args.steps, args.warmup)
     line = {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": UNIT, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": config_of(sh, args), "cpu_baseline": cb,
+            "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": config_of(sh, total, args), "cpu_baseline": cb,
             "e2e": {"value": cb["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
 
 
-def config_of(sh, args):
+def config_of(sh, total, args):
     return {"workload": f"{sh.name}: E={sh.num_experts} top-{sh.top_k} H={sh.hidden} F={sh.ffn} MXFP4, "
-                        f"T={sh.tokens} tokens per GPU, router bias {sh.router_bias}, seed {sh.seed}",
-            "tokens_per_gpu": sh.tokens, "experts": sh.num_experts, "top_k": sh.top_k, "hidden": sh.hidden,
+                        f"T={total} tokens in total, router bias {sh.router_bias}, seed {sh.seed}",
+            "tokens_total": total, "experts": sh.num_experts, "top_k": sh.top_k, "hidden": sh.hidden,
             "ffn": sh.ffn, "parallelism": "single GPU" if args.gpus == 1 else f"expert-parallel x{args.gpus}",
             "l2": "weights + grouped activations per step exceed the 126 MB L2 (no flush needed)"}
+
+
+# ---------------------------------------------------------------------------
+# decode sweep (one GPU): the same layer at a few tokens per step
+# ---------------------------------------------------------------------------
+DECODE_BATCHES = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+
+
+def decode_sweep(layer, sh, peaks, torch, stream, reps=100, nbuf=16):
+    """Microseconds per step and per token for batches of 1..256 tokens on the resident layer: `reps`
+    batches of fresh N(0,1) activations each (the decode workload's seed), timed back to back in segments
+    of `nbuf` steps over `nbuf` device buffers that are refilled (untimed) between segments, so that no
+    step repeats an earlier step's activations or expert set.  Algorithmic bytes per step =
+    U * (MXFP4 bytes + bias bytes of one expert) + router weights and bias + T*H*4 in + T*H*4 out, with
+    U = distinct experts the router actually selected for that batch."""
+    d3 = synth.C3
+    H, E, k = sh.hidden, sh.num_experts, sh.top_k
+    per_expert = sh.mxfp4_bytes_per_expert + sh.bias_bytes_per_expert
+    dev = torch.device("cuda", torch.cuda.current_device())
+    rows = []
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for T in DECODE_BATCHES:
+        bufs = [torch.empty((T, H), dtype=torch.float32, device=dev) for _ in range(nbuf)]
+        outs = [torch.empty((T, H), dtype=torch.float32, device=dev) for _ in range(nbuf)]
+        ro = torch.empty((T, k, 2), dtype=torch.float32, device=dev)
+
+        def fill(first, n):
+            for i in range(n):
+                bufs[i].copy_(torch.from_numpy(synth.hidden_states(d3, T, rep=first + i)))
+            torch.cuda.synchronize()
+
+        def run(n):
+            for i in range(n):
+                layer.forward_dev(bufs[i], T, outs[i], stream=stream.cuda_stream)
+
+        fill(reps, nbuf)  # warm-up on batches the timed repetitions do not use (captures the launch sequences)
+        with torch.cuda.stream(stream):
+            run(nbuf)
+            run(nbuf)
+        torch.cuda.synchronize()
+        total_ms, distinct = 0.0, []
+        for first in range(0, reps, nbuf):
+            n = min(nbuf, reps - first)
+            fill(first, n)
+            with torch.cuda.stream(stream):
+                ev0.record(stream)
+                run(n)
+                ev1.record(stream)
+            torch.cuda.synchronize()
+            total_ms += ev0.elapsed_time(ev1)
+            for i in range(n):  # untimed: which experts each batch selected
+                layer.route_dev(bufs[i], T, ro, stream=stream.cuda_stream)
+                torch.cuda.synchronize()
+                distinct.append(len(set(ro[..., 0].reshape(-1).to(torch.int64).tolist())))
+        layer.sync()
+        us = total_ms * 1e3 / reps
+        u = float(np.mean(distinct))
+        byts = u * per_expert + E * H * 4 + (E * 4 if sh.router_bias != "none" else 0) + 2 * T * H * 4
+        gbs = byts / (us * 1e-6) / 1e9
+        rows.append({"tokens": T, "us_per_step": us, "us_per_token": us / T, "distinct_experts": u,
+                     "bytes_per_step": byts, "gbs": gbs, "frac": gbs / peaks["hbm_gbs"]})
+    return {"workload": f"{d3.name}: the resident layer, fresh N(0,1) activations per repetition (seed {d3.seed})",
+            "reps": reps, "bound": "hbm", "peak_gbs": peaks["hbm_gbs"], "peak_source": peaks["source"] + " (copy bandwidth)",
+            "batches": rows}
 
 
 # ---------------------------------------------------------------------------
@@ -178,7 +260,6 @@ def config_of(sh, args):
 # ---------------------------------------------------------------------------
 def run_ours(args):
     import torch
-    from coalsack_b200 import MoeLayer
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -186,7 +267,7 @@ def run_ours(args):
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun for N > 1")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    sh = workload_shape(args.workload, args.tokens)
+    sh, total = per_rank_shape(args, world)
     T, H, k, E = sh.tokens, sh.hidden, sh.top_k, sh.num_experts
 
     if world > 1:
@@ -198,13 +279,13 @@ def run_ours(args):
         runner = SingleGpu(sh, local)
 
     sampler = ClockSampler(local)
-    for _ in range(max(args.warmup, 3)):
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
         runner.step_dev()
     runner.sync()
 
     # ---- device-resident timing ------------------------------------------------
     if world > 1:
-        import torch.distributed as dist
         dist.barrier()
     torch.cuda.synchronize()
     if rank == 0:
@@ -239,17 +320,19 @@ def run_ours(args):
         clocks["window"] = f"timed region + {extra} more identical steps (untimed)"
     runner.sync()
     ms_per_step = ms / args.steps
-    value = T * world / (ms_per_step * 1e-3)
+    value = total / (ms_per_step * 1e-3)
 
     # ---- per-kernel timing for the roofline (separate pass, timers on) -------------
     stage = runner.stage_times(args.steps)
 
     # ---- end to end through the host-buffer entry point -----------------------------
-    e2e_ms = runner.time_e2e(args.steps, max(args.warmup, 3))
-    if world > 1:
-        t = torch.tensor([e2e_ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
+    e2e_ms = None
+    if not args.skip_e2e:
+        e2e_ms = runner.time_e2e(args.steps, warmup)
+        if world > 1:
+            t = torch.tensor([e2e_ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e2e_ms = float(t.item())
 
     if rank != 0:
         if world > 1:
@@ -277,22 +360,25 @@ def run_ours(args):
                     "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                     "peak_source": peaks["source"] + " (copy bandwidth)"}
     roofline.update({"traffic": measured_traffic(sh, stage["gate_up_kernel"], world), "ms_per_launch": gu_ms,
-                     "layer_tflops": algorithmic_flops(sh, T * world) / (ms_per_step * 1e-3) / 1e12,
-                     "stages_ms": {n: stage[n] for n in ("route_ms", "permute_ms", "gate_up_ms", "down_ms",
-                                                        "combine_ms", "total_ms")}})
-    cb, _ = time_reference(sh, 2, 1) if (world == 1 and not args.skip_cpu) else (None, None)
-    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                     "rows_per_launch": int(rows),
+                     "layer_tflops": algorithmic_flops(sh, total) / (ms_per_step * 1e-3) / 1e12,
+                     "stages_ms": {n: stage[n] for n in stage if n.endswith("_ms")}})
+    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
             "dtype": "f16 operands (MXFP4 weights dequantised exactly), f32 accumulate; f32 router",
-            "data": "synthetic", "config": config_of(sh, args), "clocks": clocks,
-            "e2e": {"value": T * world / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": T * H * 4 * world, "d2h_bytes_per_step": T * H * 4 * world},
+            "data": "synthetic", "config": config_of(sh, total, args), "clocks": clocks,
             "gpu_launches": int(stage["launches"]) * args.steps, "path": stage["path"], "roofline": roofline}
+    if e2e_ms is not None:
+        line["e2e"] = {"value": total / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
+                       "h2d_bytes_per_step": T * H * 4 * world, "d2h_bytes_per_step": T * H * 4 * world}
     if world > 1:
-        line["config"]["exchange"] = ("rows stored into peer memory by the dispatch and down-projection kernels (NVLink)"
-                                      if getattr(runner, "p2p", False) else "all-to-all collectives (NCCL)")
-    if cb:
-        line["cpu_baseline"] = cb
+        line["config"]["tokens_per_gpu"] = T
+        line["config"]["exchange"] = runner.exchange
+        line["expert_parallel"] = stage.get("ep", {})
+    if world == 1 and not args.skip_decode and sh.name == synth.C2.name:
+        line["decode"] = decode_sweep(runner.layer, sh, peaks, torch, runner.torch_stream)
+    if world == 1 and not args.skip_cpu:
+        line["cpu_baseline"], _ = time_reference(sh, 2, 1)
     print(json.dumps(line))
     if world > 1:
         dist.barrier()
@@ -362,9 +448,13 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c1", choices=sorted(synth.CONFIGS))
-    ap.add_argument("--tokens", type=int, default=None, help="override the workload's tokens per GPU")
+    ap.add_argument("--workload", default="c2", choices=sorted(synth.CONFIGS))
+    ap.add_argument("--tokens", type=int, default=None, help="override the workload's token count")
+    ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
+                    help="N > 1: split the workload's tokens over the ranks (strong) or give every rank all of them (weak)")
     ap.add_argument("--skip-cpu", action="store_true", help="leave out the cpu_baseline leg (profiling runs)")
+    ap.add_argument("--skip-decode", action="store_true", help="leave out the decode sweep (profiling runs)")
+    ap.add_argument("--skip-e2e", action="store_true", help="leave out the host-buffer leg (profiling runs)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -45,6 +45,8 @@ SYMBOLS = {
     "csk_moe_forward_dev": (C.c_int, [_vp, _vp, _i64, _vp, _vp, _vp, _vp]),
     "csk_moe_sync": (C.c_int, [_vp]),
     "csk_moe_route_static": (C.c_int, [_vp, _i64, _i32, _vp, _vp, _i32, _i32, _i32, _vp, _vp]),
+    "csk_moe_route_static_status": (C.c_int, []),
+    "csk_moe_debug_set": (C.c_int, [_vp, _i32, _i64]),
     "csk_moe_ep_dispatch_dev": (C.c_int, [_vp, _vp, _i64, _vp, _vp, _vp, _vp]),
     "csk_moe_ep_experts_dev": (C.c_int, [_vp, _vp, _vp, _i32, _i64, _vp, _vp]),
     "csk_moe_ep_combine_dev": (C.c_int, [_vp, _vp, _i64, _vp, _vp, _vp]),

@@ -67,17 +67,6 @@ inline MatLayout make_layout(int N, int K, bool paired) {
   return L;
 }
 
-// E8M0 byte -> fp32 scale for codes read as E2M1 VALUES (0, 0.5 .. 6): the
-// reference multiplies doubled code values (0, 1 .. 12) by 2^(e-128)
-// (gguf_dequant.h:413-433), which is value * 2^(e-127).  e = 0 gives the fp32
-// subnormal 2^-127.  e = 255 (NaN in the OCP MX spec, 2^127 in the reference)
-// is clamped to e = 254.
-__device__ __forceinline__ float e8m0_scale_f32(uint32_t e) {
-  e = e > 254u ? 254u : e;
-  uint32_t bits = e ? (e << 23) : 0x00400000u;
-  return __uint_as_float(bits);
-}
-
 // Two packed E2M1 codes (one byte) -> half2, low nibble in the low half.
 __device__ __forceinline__ uint32_t e2m1x2_to_h2(uint32_t byte) {
   uint32_t r;
@@ -135,7 +124,14 @@ __device__ __forceinline__ float gated_act(float gate, float up, int act) {
 }
 
 // ---- mbarrier and bulk-copy helpers shared by the two expert kernels -----------
-constexpr long long kWaitBudget = 2000000000LL;  // clock cycles (~1 s) before a bounded wait gives up
+// Clock cycles before a bounded wait gives up (about one second at full clock).  A device
+// variable rather than a constant so that a test can shorten it and watch a wait run out
+// without hanging anything (csk_moe_debug_set, key 0).  Read only on the slow path of a wait.
+__device__ long long g_wait_budget = 2000000000LL;
+__device__ __forceinline__ long long wait_budget() { return *(volatile long long*)&g_wait_budget; }
+// Waits for copies or MMAs that are already in flight (teardown after a wait ran out) keep a
+// floor of a few milliseconds however short the budget was made: what is in flight must land.
+__device__ __forceinline__ long long drain_budget() { return wait_budget() + 8000000LL; }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -167,7 +163,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     for (int i = 0; i < 32; ++i)
       if (mbar_try(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitBudget) {
+    if (clock64() - t0 > wait_budget()) {
       *abort_flag = 1;
       return false;
     }
@@ -218,6 +214,7 @@ enum : int {
   kDevErrCapacity = 2,      // more rows than the scratch buffers hold
   kDevErrWaitTimeout = 4,   // a bounded wait in a kernel ran out
   kDevErrNotResident = 8,   // rows were routed to an expert that is not loaded
+  kDevErrPeerRow = 16,      // a row received from a peer carries no valid origin record
 };
 
 }  // namespace csk

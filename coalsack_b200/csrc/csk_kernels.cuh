@@ -49,12 +49,16 @@ __global__ void k_repack(const uint8_t* __restrict__ src0, const uint8_t* __rest
         const int col = kt * kTileK + (slot & 1) * 32;
         uint32_t e = 0;  // padding: zero codes under the smallest scale
         if (row < L.N && col < L.K) {
-          e = src[((size_t)row * (L.K / 32) + col / 32) * 17];
-          emax = max(emax, (int)e);
+          const uint8_t* blk = src + ((size_t)row * (L.K / 32) + col / 32) * 17;
+          e = blk[0];
+          // a block of zero codes is zero under any scale: it does not widen the matrix's exponent range
+          bool any = false;
+          for (int j = 1; j < 17; ++j) any = any || blk[j] != 0;
+          if (any) emax = max(emax, min((int)e, 254));
         }
         out |= e << (8 * slot);
       }
-      if (emax >= 0) atomicMax(emax_out, emax);  // largest scale exponent of the matrix
+      if (emax >= 0) atomicMax(emax_out, emax);  // largest scale exponent among the matrix's non-zero blocks
     }
     reinterpret_cast<uint32_t*>(dst)[w] = out;
   }
@@ -235,7 +239,7 @@ __device__ __forceinline__ bool mbar_wait_nap(uint32_t bar, uint32_t parity, vol
     __nanosleep(64);
     if (mbar_try(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitBudget) {
+    if (clock64() - t0 > wait_budget()) {
       *abort_flag = 1;
       return false;
     }
@@ -315,7 +319,7 @@ k_router_logits(const RouterArgs A) {
       for (int i = 0; i < NS && i < issued; ++i) {
         const int ci = issued - 1 - i;
         const long long tb = clock64();
-        while (!mbar_try(bar_full(ci % NS), (uint32_t)((ci / NS) & 1)) && clock64() - tb < kWaitBudget) {
+        while (!mbar_try(bar_full(ci % NS), (uint32_t)((ci / NS) & 1)) && clock64() - tb < drain_budget()) {
         }
       }
     }
@@ -512,10 +516,7 @@ inline int launch_router_logits(RouterArgs a, const float* wg_few, const float* 
   } else {
     a.wg = wg_many;
     if (token_blocks <= 8 * (int64_t)sm_count) launch_router_one<4, 2, kRouterChunkMany, PACKED>(a, s, pdl);
-#ifndef CSK_ROUTER_WIDE
-#define CSK_ROUTER_WIDE 64
-#endif
-    else if (token_blocks <= CSK_ROUTER_WIDE * (int64_t)sm_count) launch_router_one<4, 4, kRouterChunkMany, PACKED>(a, s, pdl);
+    else if (token_blocks <= 64 * (int64_t)sm_count) launch_router_one<4, 4, kRouterChunkMany, PACKED>(a, s, pdl);
     else launch_router_one<8, 4, kRouterChunkMany, PACKED>(a, s, pdl);
   }
   return 0;
@@ -960,23 +961,32 @@ __global__ void k_ep_p2p_local_counts(const int* __restrict__ all_counts, int wo
 }
 
 // Where each received row's output goes: the pair's row of the sender's return buffer.
-__global__ void k_ep_p2p_rowptr(const RowOrigin* __restrict__ info, const int* __restrict__ meta, float* const* __restrict__ peer_back,
-                                int H, float** __restrict__ row_ptr) {
-  const int rows = meta[1];
+// Nothing is derived when the row plan overran the buffers (the expert kernels then have no
+// tiles either), and a row whose origin record is not a valid (rank, pair) gets a null
+// pointer, which every consumer skips, plus kDevErrPeerRow in the status word.
+__global__ void k_ep_p2p_rowptr(const RowOrigin* __restrict__ info, int* __restrict__ meta,
+                                float* const* __restrict__ peer_back, int H, float** __restrict__ row_ptr, int max_rows,
+                                int world, int max_pairs) {
+  if (meta[3] & kDevErrCapacity) return;
+  const int rows = min(meta[1], max_rows);
   for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < rows; r += gridDim.x * blockDim.x) {
     const RowOrigin o = info[r];
-    row_ptr[r] = peer_back[o.src] + (size_t)o.pair * H;
+    const bool ok = o.src >= 0 && o.src < world && o.pair >= 0 && o.pair < max_pairs;
+    row_ptr[r] = ok ? peer_back[o.src] + (size_t)o.pair * H : nullptr;
+    if (!ok) atomicOr(&meta[3], kDevErrPeerRow);
   }
 }
 
 // Output rows computed into a local buffer (streaming path) -> their owners' return buffers.
 __global__ void k_ep_p2p_return(const float* __restrict__ y, int H, float* const* __restrict__ row_ptr,
-                                const int* __restrict__ meta) {
-  const int rows = meta[1];
+                                const int* __restrict__ meta, int max_rows) {
+  if (meta[3] & kDevErrCapacity) return;
+  const int rows = min(meta[1], max_rows);
   const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
   for (int r = blockIdx.x * wpb + (threadIdx.x >> 5); r < rows; r += gridDim.x * wpb) {
     const float4* s = reinterpret_cast<const float4*>(y + (size_t)r * H);
     float4* d = reinterpret_cast<float4*>(row_ptr[r]);
+    if (!d) continue;
     for (int i = lane; i < H / 4; i += 32) d[i] = s[i];
   }
   __threadfence_system();

@@ -50,6 +50,7 @@ struct csk_moe_layer {
   float** d_peer_back = nullptr;      // [world]
   std::vector<void*> ipc_opened;      // peer mappings to close
   bool pdl = false;  // launch the layer's kernels with programmatic dependent launch (small batches)
+  bool debug_stall = false;  // test hook: the next tensor-core launch's copy role issues nothing (one shot)
 
   int64_t max_T = 0, max_rows = 0;
   int max_tiles = 0;
@@ -197,16 +198,10 @@ int launch_permute(csk_moe_layer* L, const float* d_hidden, const float* d_route
   return CSK_OK;
 }
 
-// warps per CTA and ring stages of the streaming kernel: whole-contraction variant, split-contraction variant
-#ifndef CSK_STREAM_W
-#define CSK_STREAM_W 10
-#endif
-#ifndef CSK_STREAM_S
-#define CSK_STREAM_S 3
-#endif
-#ifndef CSK_STREAM_KS
-#define CSK_STREAM_KS 3
-#endif
+// Warps per CTA and ring stages of the streaming kernel (measured on B200): ten warps with
+// three-stage rings when every warp walks a whole contraction, eight warps with three stages
+// when the contraction is split over the warps.
+constexpr int kStreamWarps = 10, kStreamStages = 3, kStreamSplitStages = 3;
 template <int NT8, int KSPLIT, int W, int NSTG>
 void launch_stream_pair(csk_moe_layer* L, const __half* x16, float* y, int ldy, int x_rows, cudaStream_t s,
                         StageTimer& tm) {
@@ -257,8 +252,8 @@ cudaError_t stream_prepare_one() {
   return e;
 }
 cudaError_t stream_prepare_device() {
-  cudaError_t e = stream_prepare_one<1, 1, CSK_STREAM_W, CSK_STREAM_S>();
-  if (e == cudaSuccess) e = stream_prepare_one<1, 8, 8, CSK_STREAM_KS>();
+  cudaError_t e = stream_prepare_one<1, 1, kStreamWarps, kStreamStages>();
+  if (e == cudaSuccess) e = stream_prepare_one<1, 8, 8, kStreamSplitStages>();
   if (e == cudaSuccess) e = stream_prepare_one<2, 1, 8, 3>();
   return e;
 }
@@ -290,7 +285,8 @@ int launch_experts(csk_moe_layer* L, int path, int tile_rows, int64_t n_rows_hin
     int rc = tile_launch(L->tile, L->d_weights, L->expert_stride, L->off_tgu, L->off_td, L->off_bias,
                          L->off_meta, L->Tgu, L->Td, L->d_a16, L->lda, y, ldy, out_row_map, out_row_ptr, L->d_tiles,
                          L->d_meta, L->cfg.has_bias, L->cfg.activation, L->F, L->sm_count, s,
-                         [&]() { tm.mark(); });
+                         [&]() { tm.mark(); }, L->debug_stall);
+    L->debug_stall = false;
     if (rc) return fail(L, rc, "tensor-core path: %s", L->tile.err.c_str());
     L->last.launches += 2;
   } else {
@@ -298,19 +294,17 @@ int launch_experts(csk_moe_layer* L, int path, int tile_rows, int64_t n_rows_hin
     // no tile holds more rows than its expert received
     const int x_rows = (int)std::max<int64_t>(1, std::min<int64_t>(tile_rows, rows_per_expert_max));
     const int kp = std::max(L->Lgu.k_pad(), L->Ld.k_pad());
-    const size_t need = tile_rows == 8 ? std::max(stream_smem_bytes(x_rows, 1, kp, 8, true, 8, CSK_STREAM_KS),
-                                                  stream_smem_bytes(x_rows, 1, kp, 1, true, CSK_STREAM_W, CSK_STREAM_S))
+    const size_t need = tile_rows == 8 ? std::max(stream_smem_bytes(x_rows, 1, kp, 8, true, 8, kStreamSplitStages),
+                                                  stream_smem_bytes(x_rows, 1, kp, 1, true, kStreamWarps, kStreamStages))
                                        : stream_smem_bytes(x_rows, 2, kp, 1, true, 8, 3);
     if (need > 200 * 1024)
       return fail(L, CSK_ERR_NOMEM, "hidden/ffn dimension too large for the streaming kernel's row buffer");
     if (tile_rows == 8) {
-#ifndef CSK_KSPLIT_ROWS
-#define CSK_KSPLIT_ROWS 8
-#endif
-      if (n_rows_hint <= CSK_KSPLIT_ROWS) {  // measured: the split pays only while the whole batch is a handful of rows
-        launch_stream_pair<1, 8, 8, CSK_STREAM_KS>(L, x16, y, ldy, x_rows, s, tm);  // a handful of rows: split the contraction over the warps
+      constexpr int64_t kSplitRows = 8;
+      if (n_rows_hint <= kSplitRows) {  // measured: the split pays only while the whole batch is a handful of rows
+        launch_stream_pair<1, 8, 8, kStreamSplitStages>(L, x16, y, ldy, x_rows, s, tm);  // a handful of rows: split the contraction over the warps
       } else {
-        launch_stream_pair<1, 1, CSK_STREAM_W, CSK_STREAM_S>(L, x16, y, ldy, x_rows, s, tm);
+        launch_stream_pair<1, 1, kStreamWarps, kStreamStages>(L, x16, y, ldy, x_rows, s, tm);
       }
     } else {
       launch_stream_pair<2, 1, 8, 3>(L, x16, y, ldy, x_rows, s, tm);
@@ -332,6 +326,8 @@ int check_device_status(csk_moe_layer* L, cudaStream_t s) {
     return fail(L, CSK_ERR_NOMEM, "more rows than max_tokens allows (%d rows)", L->h_meta[1]);
   if (st & kDevErrNotResident)
     return fail(L, CSK_ERR_MISSING, "tokens were routed to an expert whose weights are not loaded");
+  if (st & kDevErrPeerRow)
+    return fail(L, CSK_ERR_DEVICE, "a row received from a peer carries no valid origin (rank, pair)");
   if (st & kDevErrWaitTimeout)
     return fail(L, CSK_ERR_DEVICE, "a bounded device-side wait ran out");
   return CSK_OK;
@@ -404,6 +400,14 @@ int forward_dev(csk_moe_layer* L, const float* d_hidden, int64_t T, const float*
 }
 
 int check_layer(csk_moe_layer* L) { return L ? CSK_OK : CSK_ERR_INVALID; }
+
+// Captured launch sequences embed kernel arguments (which router bias, which path, which
+// slot map): whatever changes one of those drops them.
+void drop_graphs(csk_moe_layer* L) {
+  for (auto& g : L->graphs)
+    if (g.exec) cudaGraphExecDestroy(g.exec);
+  L->graphs.clear();
+}
 
 }  // namespace
 
@@ -593,6 +597,7 @@ int csk_moe_set_router(csk_moe_layer* L, const float* gate_w, const float* gate_
                                 L->stream));
   CSK_CUDA(L, cudaStreamSynchronize(L->stream));
   L->router_set = true;
+  drop_graphs(L);
   return CSK_OK;
 }
 
@@ -668,9 +673,7 @@ int csk_moe_set_path(csk_moe_layer* L, int32_t path) {
   if (check_layer(L)) return CSK_ERR_INVALID;
   if (path < CSK_PATH_AUTO || path > CSK_PATH_TILE) return fail(L, CSK_ERR_INVALID, "unknown path %d", path);
   L->path = path;
-  for (auto& g : L->graphs)
-    if (g.exec) cudaGraphExecDestroy(g.exec);
-  L->graphs.clear();  // captured sequences embed the old choice
+  drop_graphs(L);
   return CSK_OK;
 }
 
@@ -732,7 +735,7 @@ int csk_moe_forward_dev(csk_moe_layer* L, const float* d_hidden, int64_t T, cons
   CSK_CUDA(L, cudaSetDevice(L->cfg.device));
   cudaStream_t s = pick(L, stream);
   constexpr int64_t kGraphMaxTokens = 512;
-  if (!L->use_graphs || L->timing || T > kGraphMaxTokens || T <= 0 || T > L->max_T)
+  if (!L->use_graphs || L->timing || L->debug_stall || T > kGraphMaxTokens || T <= 0 || T > L->max_T)
     return forward_dev(L, d_hidden, T, d_router_in, d_router_out, d_out, -1, s, false);
   for (auto& g : L->graphs)
     if (g.T == T && g.hidden == d_hidden && g.router_in == d_router_in && g.router_out == d_router_out &&
@@ -916,6 +919,7 @@ int csk_moe_ep_set_slot_map(csk_moe_layer* L, int32_t n_logical, const int32_t* 
                             const int32_t* replica_slot) {
   if (check_layer(L)) return CSK_ERR_INVALID;
   CSK_CUDA(L, cudaSetDevice(L->cfg.device));
+  drop_graphs(L);
   if (n_logical == 0) {
     if (L->has_slot_map) L->router_set = false;
     L->has_slot_map = false;
@@ -963,6 +967,8 @@ int ep_finish(csk_moe_layer* L, cudaStream_t s, int n_marks) {
 int p2p_alloc_local(csk_moe_layer* L) {
   if (L->d_info) return CSK_OK;
   CSK_CUDA(L, cudaMalloc(&L->d_info, sizeof(RowOrigin) * (size_t)L->max_rows));
+  // 0xFF bytes: (-1, -1), which no reader accepts as an origin (rows a sender had to skip stay that way)
+  CSK_CUDA(L, cudaMemset(L->d_info, 0xFF, sizeof(RowOrigin) * (size_t)L->max_rows));
   CSK_CUDA(L, cudaMalloc(&L->d_back, sizeof(float) * (size_t)L->max_T * L->k * L->H));
   CSK_CUDA(L, cudaMalloc(&L->d_row_ptr, sizeof(float*) * (size_t)L->max_rows));
   return CSK_OK;
@@ -1146,7 +1152,8 @@ int csk_moe_ep_p2p_experts_dev(csk_moe_layer* L, const int32_t* d_all_counts, in
   k_ep_p2p_local_counts<<<(L->E + 255) / 256, 256, 0, s>>>(d_all_counts, L->p2p_world, L->E, L->e0, L->Eloc, L->d_counts);
   k_scan<<<1, 1024, 0, s>>>(L->d_counts, L->E, L->e0, L->Eloc, tile_rows, (int)L->max_rows, L->max_tiles,
                             L->d_resident, L->d_offsets, L->d_cursor, L->d_tiles, L->d_meta, nullptr, 0, -1);
-  k_ep_p2p_rowptr<<<4 * L->sm_count, 256, 0, s>>>(L->d_info, L->d_meta, L->d_peer_back, L->H, L->d_row_ptr);
+  k_ep_p2p_rowptr<<<4 * L->sm_count, 256, 0, s>>>(L->d_info, L->d_meta, L->d_peer_back, L->H, L->d_row_ptr,
+                                                  (int)L->max_rows, L->p2p_world, (int)L->max_rows);
   CSK_CUDA(L, cudaGetLastError());
   StageTimer tm(L, s);
   tm.mark();
@@ -1156,7 +1163,7 @@ int csk_moe_ep_p2p_experts_dev(csk_moe_layer* L, const int32_t* d_all_counts, in
   } else {
     rc = launch_experts(L, path, tile_rows, rows_hint, rows_hint, L->d_x16, L->d_y, L->H, nullptr, s, tm);
     if (!rc) {
-      k_ep_p2p_return<<<8 * L->sm_count, 256, 0, s>>>(L->d_y, L->H, L->d_row_ptr, L->d_meta);
+      k_ep_p2p_return<<<8 * L->sm_count, 256, 0, s>>>(L->d_y, L->H, L->d_row_ptr, L->d_meta, (int)L->max_rows);
       CSK_CUDA(L, cudaGetLastError());
     }
   }
@@ -1234,11 +1241,15 @@ int csk_moe_ep_combine_dev(csk_moe_layer* L, const float* d_back, int64_t T, flo
 // stand-in for the symbol; the device address comes from cudaGetSymbolAddress.
 constexpr int64_t kStaticLogitsMax = 256 * 1024;  // floats: T * E may not exceed this
 static __device__ __align__(256) float g_static_logits[kStaticLogitsMax];
+// Status word of the same entry point (kDevErr* bits or-ed by its kernels), read and cleared by
+// csk_moe_route_static_status.
+static __device__ int g_static_status;
 
 namespace {
 constexpr int kMaxDevices = 64;
 std::mutex g_static_mu;
 float* g_static_logits_addr[kMaxDevices] = {nullptr};
+int* g_static_status_addr[kMaxDevices] = {nullptr};
 }  // namespace
 
 int csk_moe_route_static(const float* d_hidden, int64_t T, int32_t H, const float* d_gate_w,
@@ -1266,9 +1277,14 @@ int csk_moe_route_static(const float* d_hidden, int64_t T, int32_t H, const floa
       ce = cudaGetSymbolAddress(&p, g_static_logits);
       if (ce != cudaSuccess || !p)
         return fail(nullptr, CSK_ERR_CUDA, "route_static: cudaGetSymbolAddress: %s", cudaGetErrorString(ce));
+      void* ps = nullptr;
+      ce = cudaGetSymbolAddress(&ps, g_static_status);
+      if (ce != cudaSuccess || !ps)
+        return fail(nullptr, CSK_ERR_CUDA, "route_static: cudaGetSymbolAddress: %s", cudaGetErrorString(ce));
       ce = router_prepare_device();
       if (ce != cudaSuccess)
         return fail(nullptr, CSK_ERR_CUDA, "route_static: cudaFuncSetAttribute: %s", cudaGetErrorString(ce));
+      g_static_status_addr[dev] = static_cast<int*>(ps);
       g_static_logits_addr[dev] = static_cast<float*>(p);
     }
     logits = g_static_logits_addr[dev];
@@ -1282,6 +1298,7 @@ int csk_moe_route_static(const float* d_hidden, int64_t T, int32_t H, const floa
   a.hidden = d_hidden;
   a.bias = d_gate_bias;
   a.logits = logits;
+  a.status = g_static_status_addr[dev];
   a.T = (int)T;
   a.H = H;
   a.E = E;
@@ -1290,6 +1307,43 @@ int csk_moe_route_static(const float* d_hidden, int64_t T, int32_t H, const floa
   ce = cudaGetLastError();
   if (ce != cudaSuccess) return fail(nullptr, CSK_ERR_CUDA, "route_static: launch failed: %s", cudaGetErrorString(ce));
   return CSK_OK;
+}
+
+int csk_moe_route_static_status(void) {
+  int dev = -1;
+  cudaError_t ce = cudaGetDevice(&dev);
+  if (ce != cudaSuccess) return fail(nullptr, CSK_ERR_CUDA, "route_static_status: cudaGetDevice: %s", cudaGetErrorString(ce));
+  int* addr = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    if (dev >= 0 && dev < kMaxDevices) addr = g_static_status_addr[dev];
+  }
+  if (!addr) return CSK_OK;  // csk_moe_route_static never ran on this device
+  int st = 0;
+  ce = cudaMemcpy(&st, addr, sizeof(int), cudaMemcpyDeviceToHost);
+  if (ce != cudaSuccess) return fail(nullptr, CSK_ERR_CUDA, "route_static_status: %s", cudaGetErrorString(ce));
+  if (!st) return CSK_OK;
+  ce = cudaMemset(addr, 0, sizeof(int));
+  if (ce != cudaSuccess) return fail(nullptr, CSK_ERR_CUDA, "route_static_status: %s", cudaGetErrorString(ce));
+  return fail(nullptr, CSK_ERR_DEVICE, "route_static: a bounded device-side wait ran out; the routing output of that call is not valid");
+}
+
+// ---- test hooks ---------------------------------------------------------------------
+int csk_moe_debug_set(csk_moe_layer* L, int32_t key, int64_t value) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  CSK_CUDA(L, cudaSetDevice(L->cfg.device));
+  if (key == CSK_DEBUG_WAIT_BUDGET) {
+    if (value < 1000) return fail(L, CSK_ERR_INVALID, "debug: the wait budget must be at least 1000 cycles");
+    const long long v = value;
+    CSK_CUDA(L, cudaStreamSynchronize(L->stream));
+    CSK_CUDA(L, cudaMemcpyToSymbol(g_wait_budget, &v, sizeof(v)));
+    return CSK_OK;
+  }
+  if (key == CSK_DEBUG_STALL_TILE_PRODUCER) {
+    L->debug_stall = value != 0;
+    return CSK_OK;
+  }
+  return fail(L, CSK_ERR_INVALID, "debug: unknown key %d", key);
 }
 
 }  // extern "C"

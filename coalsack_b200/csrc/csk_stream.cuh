@@ -56,11 +56,17 @@ __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], 
 }
 
 // Scale byte `slot` (0..3) of a packed word -> fp32 2^(e-127): the byte moved to
-// the exponent field by one shift and one mask.
+// the exponent field by one shift and one mask.  The codes are read as E2M1
+// VALUES (0, 0.5 .. 6) where the reference multiplies doubled values (0, 1 .. 12)
+// by 2^(e-128) (gguf_dequant.h:413-433): the same number for 1 <= e <= 254.
+// e = 0 (2^-128 in the reference, an fp32 subnormal) gives 0 here: the block
+// contributes nothing.  e = 255 (2^127 in the reference, where every code but
+// +-1 overflows fp32; NaN in the OCP MX specification) is read as e = 254, so
+// a block of zero codes stays zero under any scale byte.
 template <int SLOT>
 __device__ __forceinline__ float scale_of(uint32_t sw) {
   const uint32_t bits = SLOT < 3 ? (sw << (23 - 8 * SLOT)) : (sw >> 1);
-  return __uint_as_float(bits & 0x7F800000u);
+  return __uint_as_float(min(bits & 0x7F800000u, 0x7F000000u));
 }
 
 struct StreamArgs {
@@ -85,10 +91,7 @@ struct StreamArgs {
 };
 
 constexpr int kStreamXPad = 32;      // halves: staggers consecutive token rows by 64 bytes in shared memory
-#ifndef CSK_STREAM_RPS
-#define CSK_STREAM_RPS 4
-#endif
-constexpr int kStreamRecsPerStage = CSK_STREAM_RPS;  // records per ring stage = per bulk copy
+constexpr int kStreamRecsPerStage = 4;  // records per ring stage = per bulk copy
 constexpr int kStreamStageBytes = kStreamRecsPerStage * kSubBytes;
 
 __host__ __device__ inline size_t stream_x_bytes(int x_rows, int k_pad) {
@@ -225,7 +228,7 @@ __global__ void __launch_bounds__(W * 32, W > 8 ? 2 : 3) k_stream(const StreamAr
             if (!mbar_try(bar, par)) {
               const long long t0 = clock64();
               while (!mbar_try(bar, par)) {
-                if (clock64() - t0 > kWaitBudget) {
+                if (clock64() - t0 > wait_budget()) {
                   waits_ok = false;
                   if (lane == 0) atomicOr(&A.meta[3], kDevErrWaitTimeout);
                   break;

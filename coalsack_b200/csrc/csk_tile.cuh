@@ -271,6 +271,7 @@ struct TileArgs {
   const int* n_tiles_ptr;
   int* meta;              // meta[3] = device status word
   int has_bias, act, F, meta_slot;
+  int stall;              // test hook: the copy role issues nothing, so every other role's wait runs out
 };
 
 inline size_t tile_smem_bytes() { return (size_t)kTileStages * kTileRawBytes + 1024 + 512; }
@@ -337,7 +338,7 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
       uint32_t ph = 0;
       int issued = 0;
       bool ok = true;
-      for (long item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
+      for (long item = blockIdx.x; ok && !A.stall && item < n_items; item += gridDim.x) {
         const RowTile rt = A.tiles[item / L.n_tiles];
         const int nt = (int)(item % L.n_tiles);
         const uint8_t* wsrc =
@@ -369,7 +370,7 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
             ph2 ^= 1;
           }
           const long long t0 = clock64();
-          while (!mbar_try(bar_full_raw(s2), ph2) && clock64() - t0 < kWaitBudget) {
+          while (!mbar_try(bar_full_raw(s2), ph2) && clock64() - t0 < drain_budget()) {
           }
         }
       }
@@ -429,7 +430,7 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
       // everything issued has to retire before tensor memory is freed
       umma_commit(bar_drain);
       const long long t0 = clock64();
-      while (!mbar_try(bar_drain, 0) && clock64() - t0 < kWaitBudget) {
+      while (!mbar_try(bar_drain, 0) && clock64() - t0 < drain_budget()) {
       }
     }
   } else if (warp < 2 + kDequantWarps) {
@@ -449,7 +450,7 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
 #pragma unroll
       for (int blk = 0; blk < 2; ++blk) {
         const uint4 cw = *reinterpret_cast<const uint4*>(packed + (blk * 128 + trow) * 16);
-        const int e = packed[4096 + blk * 128 + trow];
+        const int e = min((int)packed[4096 + blk * 128 + trow], 254);  // scale byte 255 is read as 254
         const uint32_t sh2 = h2_pow2(e - emax + 13);
         uint32_t t[4];
         dequant_word(cw.x, t);
@@ -574,7 +575,7 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             float* row = reinterpret_cast<float*>(__shfl_sync(0xffffffffu, my_bits, j));
-            if (n_ok && c0 + j < rt.rows) row[n] = __uint_as_float(r[j]) * oscale + my_bias;
+            if (n_ok && row && c0 + j < rt.rows) row[n] = __uint_as_float(r[j]) * oscale + my_bias;
           }
         }
       }
@@ -652,7 +653,8 @@ inline int tile_launch(TileState& st, const uint8_t* weights, size_t expert_stri
                        size_t off_bias, size_t off_meta, const TileLayout& Lgu, const TileLayout& Ld, __half* a16,
                        int lda, float* y, int ldy, const int* out_row_map, float* const* out_row_ptr,
                        const RowTile* tiles, int* meta,
-                       int has_bias, int act, int F, int sm_count, cudaStream_t s, const std::function<void()>& mark) {
+                       int has_bias, int act, int F, int sm_count, cudaStream_t s, const std::function<void()>& mark,
+                       bool stall = false) {
   if (!st.available || !st.maps_ready) {
     st.err = "tensor-core path is not initialised";
     return CSK_ERR_INVALID;
@@ -668,6 +670,7 @@ inline int tile_launch(TileState& st, const uint8_t* weights, size_t expert_stri
   a.has_bias = has_bias;
   a.act = act;
   a.F = F;
+  a.stall = stall ? 1 : 0;
   const size_t smem = tile_smem_bytes();
   // gate/up + activation
   a.mat_offset = off_gu;

@@ -116,6 +116,28 @@ def plan_placement(load, world: int, extra_slots: int = 0) -> Placement:
     return Placement(slots, replica_of, world)
 
 
+def placement_max_load(place: Placement, load) -> float:
+    """Rows the busiest rank receives under `place` for the per-expert `load` (an expert with a
+    second copy sends half of its rows to each)."""
+    load = np.asarray(load, dtype=np.float64)
+    copies = {int(s): p for p, s in enumerate(place.replica_of) if s >= 0}   # copy slot -> primary slot
+    split = set(int(place.slots[p]) for p in copies.values())
+    per_rank = np.zeros(place.world)
+    for p, e in enumerate(place.slots):
+        if e >= 0:
+            per_rank[p // place.per_rank] += load[e] / (2.0 if int(e) in split else 1.0)
+    return float(per_rank.max())
+
+
+def best_placement(load, world: int) -> Placement:
+    """The plan with one spare slot per rank when that lowers the busiest rank's load (uneven
+    expert counts per rank already help a skewed load, with or without second copies), else the
+    plan without spare slots."""
+    tight = plan_placement(load, world, extra_slots=0)
+    spare = plan_placement(load, world, extra_slots=1)
+    return spare if placement_max_load(spare, load) < placement_max_load(tight, load) * 0.999 else tight
+
+
 def balanced_placement(load, world: int) -> np.ndarray:
     """physical slot -> logical expert, E/world experts per rank, no replicas."""
     return plan_placement(load, world, 0).slots
@@ -278,20 +300,30 @@ class P2pEpLayer:
         # stream-ordered: every rank's kernels before it have finished (their peer stores are done)
         self.dist.all_reduce(self.token, group=self.group)
 
-    def forward(self, hidden, T, out):
+    def forward(self, hidden, T, out, mark=None):
+        """One step.  `mark(name)`, when given, is called after each stage is enqueued (the bench
+        records an event there to break the step's time down)."""
+        mark = mark or (lambda name: None)
         lay, st = self.b.layer, self.b.stream()
         if T:
             lay.ep_p2p_counts_dev(hidden, T, self.counts, stream=st)
         else:
             self.counts.zero_()  # a rank without tokens still serves its experts
+        mark("route_count")
         self.dist.all_gather_into_tensor(self.all_counts, self.counts, group=self.group)
+        mark("gather_counts")
         if T:
             lay.ep_p2p_scatter_dev(hidden, T, self.all_counts, stream=st)
+        mark("scatter")
         self._barrier()
+        mark("barrier_rows")
         lay.ep_p2p_experts_dev(self.all_counts, max(T, 1) * self.b.k, stream=st)
+        mark("experts")
         self._barrier()
+        mark("barrier_out")
         if T:
             lay.ep_p2p_combine_dev(T, out, stream=st)
+        mark("combine")
         return T * self.b.k
 
 
@@ -309,9 +341,7 @@ class EpBench:
         import torch.distributed as dist
         dist.all_reduce(load)
         load = load.cpu().numpy()
-        place = plan_placement(load, world, extra_slots=1)
-        if not (place.replica_of >= 0).any():
-            place = plan_placement(load, world, extra_slots=0)   # no expert worth a second copy: no spare slots
+        place = best_placement(load, world)
         # a rank may receive more rows than it sends when routing is uneven: leave 3x head-room
         self.backend = GpuBackend(sh, rank, world, local, max_tokens=3 * sh.tokens, placement=place)
         self.backend.load_synthetic()
@@ -331,6 +361,10 @@ class EpBench:
             self.p2p = bool(agree.item())
         if not self.p2p:
             self.ep = EpLayer(self.backend, world)
+        self.exchange = ("rows stored into peer memory by the dispatch and down-projection kernels (NVLink)"
+                         if self.p2p else "all-to-all collectives (NCCL)")
+        self.place = place
+        self.load = load
         self.h_host = torch.from_numpy(h).pin_memory()
         self.out_host = torch.empty_like(self.h_host).pin_memory()
         self.d_hidden = self.h_host.to(self.dev)
@@ -346,17 +380,37 @@ class EpBench:
         self.torch.cuda.synchronize()
 
     def stage_times(self, steps):
-        """Device time of the two expert contractions on this rank (events inside the library)
-        plus whole-stage times from torch events around dispatch / exchange / experts / combine."""
+        """Device time of the two expert contractions on this rank (events inside the library) and,
+        for the peer-memory step, of every stage of the step (events between the stages on the
+        step's stream), each as the maximum over the ranks; plus the rows every rank received."""
+        import torch.distributed as dist
+        torch = self.torch
         lay = self.backend.layer
         lay.enable_timing(True)
         acc = {"gate_up_ms": 0.0, "down_ms": 0.0}
+        names, stage_acc = [], {}
         n = max(3, min(steps, 10))
         rows = 0
         for _ in range(n):
-            with self.torch.cuda.stream(self.torch_stream):
-                rows = self.ep.forward(self.d_hidden, self.T, self.d_out)
-            self.torch.cuda.synchronize()
+            evs = []
+
+            def mark(name):
+                e = torch.cuda.Event(enable_timing=True)
+                e.record(self.torch_stream)
+                evs.append((name, e))
+
+            with torch.cuda.stream(self.torch_stream):
+                mark("start")
+                if self.p2p:
+                    rows = self.ep.forward(self.d_hidden, self.T, self.d_out, mark=mark)
+                else:
+                    rows = self.ep.forward(self.d_hidden, self.T, self.d_out)
+                    mark("step")
+            torch.cuda.synchronize()
+            for (_, a), (name, b) in zip(evs[:-1], evs[1:]):
+                stage_acc[name] = stage_acc.get(name, 0.0) + a.elapsed_time(b)
+                if name not in names:
+                    names.append(name)
             if self.p2p:  # rows this rank's experts actually received
                 b = self.backend
                 rows = int(self.ep.all_counts.view(self.world, -1)[:, b.e0:b.e0 + b.eloc].sum().item())
@@ -366,9 +420,23 @@ class EpBench:
             path = t["path"]
         lay.enable_timing(False)
         out = {k: v / n for k, v in acc.items()}
+        # every stage as the slowest rank saw it, and the rows each rank's experts received
+        vec = torch.tensor([stage_acc[x] / n for x in names] + [float(rows)], device=self.dev, dtype=torch.float64)
+        gathered = [torch.empty_like(vec) for _ in range(self.world)]
+        dist.all_gather(gathered, vec)
+        g = torch.stack(gathered).cpu().numpy()
+        stage_max = {x + "_ms": float(g[:, i].max()) for i, x in enumerate(names)}
+        rows_all = [int(r) for r in g[:, -1]]
+        limiting = max(stage_max, key=stage_max.get) if stage_max else None
         out.update(route_ms=0.0, permute_ms=0.0, combine_ms=0.0, total_ms=out["gate_up_ms"] + out["down_ms"],
                    path={1: "stream", 2: "tile"}.get(int(path), "?"), launches=14, rows_received=int(rows))
         out["gate_up_kernel"] = "k_stream<gated>" if out["path"] == "stream" else "k_tile<gated>"
+        out["ep"] = {"stages_ms_max_over_ranks": stage_max, "limiting_stage": limiting,
+                     "rows_received_per_rank": rows_all,
+                     "rows_max_over_mean": float(max(rows_all) / max(1.0, np.mean(rows_all))),
+                     "slots": int(self.place.n_slots), "second_copies": int((self.place.replica_of >= 0).sum()),
+                     "planned_max_over_mean": float(placement_max_load(self.place, self.load) /
+                                                    max(1.0, float(np.sum(self.load)) / self.world))}
         return out
 
     def time_e2e(self, steps, warmup):

@@ -243,6 +243,12 @@ class MoeLayer:
     def set_path(self, path):
         self._check(self._lib.csk_moe_set_path(self._h, path))
 
+    DEBUG_WAIT_BUDGET, DEBUG_STALL_TILE_PRODUCER = 0, 1
+
+    def debug_set(self, key, value):
+        """Test hooks of the failure path (csk_moe_debug_set)."""
+        self._check(self._lib.csk_moe_debug_set(self._h, int(key), int(value)))
+
     def enable_timing(self, on=True):
         self._check(self._lib.csk_moe_enable_timing(self._h, int(on)))
 

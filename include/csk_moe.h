@@ -164,10 +164,18 @@ int csk_moe_sync(csk_moe_layer* layer);
  * The array is shared by every call in the process and keeps the last call's
  * logits; each call overwrites the part it reads, so nothing needs clearing,
  * but two calls that overlap on the same GPU (different streams or threads)
- * race on it: serialise them. */
+ * race on it: serialise them.
+ * Every wait inside its kernels is bounded; one that runs out leaves that call's
+ * router_out invalid and sets a status word that csk_moe_route_static_status
+ * reports. */
 int csk_moe_route_static(const float* d_hidden, int64_t T, int32_t H, const float* d_gate_w,
                          const float* d_gate_bias_or_null, int32_t E, int32_t k,
                          int32_t sigmoid_gating, float* d_router_out, void* stream);
+/* CSK_OK, or CSK_ERR_DEVICE when a bounded wait ran out in a csk_moe_route_static
+ * call on the current device since the last query (the word is cleared).  Call it
+ * after synchronising the stream those calls ran on; it allocates nothing (one
+ * 4-byte device-to-host copy).  No counterpart in the reference. */
+int csk_moe_route_static_status(void);
 
 /* ---- expert parallelism: the layer cut at its two exchange points -------
  * Rank r holds experts [expert_begin, expert_begin+expert_count).  A step is
@@ -274,6 +282,20 @@ int csk_moe_get_timings(csk_moe_layer* layer, csk_moe_timings* out);
  * host), number of distinct experts hit, weight bytes those experts hold. */
 int csk_moe_get_counters(csk_moe_layer* layer, int64_t* rows_per_expert, int64_t* distinct_experts,
                          int64_t* weight_bytes_streamed);
+
+/* ---- test hooks ------------------------------------------------------------
+ * For the tests of the failure path (the reference reports failures as values,
+ * expert_mlp_node.h:139-146; here a kernel that gives up reports through the
+ * status word and the handle stays usable).  Nothing here faults or hangs the GPU.
+ *   CSK_DEBUG_WAIT_BUDGET         clock cycles a device-side wait may take before it
+ *                                 gives up (default 2e9, about a second); applies to
+ *                                 every handle on the device
+ *   CSK_DEBUG_STALL_TILE_PRODUCER non-zero: in the NEXT tensor-core expert launch the
+ *                                 copy role issues nothing, so every other role's wait
+ *                                 runs out, the kernel tears down and the call reports
+ *                                 CSK_ERR_DEVICE (one shot) */
+enum { CSK_DEBUG_WAIT_BUDGET = 0, CSK_DEBUG_STALL_TILE_PRODUCER = 1 };
+int csk_moe_debug_set(csk_moe_layer* layer, int32_t key, int64_t value);
 
 #ifdef __cplusplus
 }

@@ -23,10 +23,21 @@ _f32p = C.POINTER(C.c_float)
 _u8p = C.POINTER(C.c_uint8)
 
 
+def reference_root():
+    """Root of a reference checkout, or None: $COALSACK_REF, else a directory named
+    ``reference`` beside this repository."""
+    cands = [os.environ.get("COALSACK_REF"), os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")]
+    for c in cands:
+        if c and os.path.exists(os.path.join(c, "include", "coalsack", "nn", "nn_ops", "expert_mlp_node.h")):
+            return c
+    return None
+
+
 def build(verbose: bool = False) -> None:
     """Run oracle/Makefile (the C restatement always; the reference wrapper
     when a reference checkout is present)."""
-    r = subprocess.run(["make", "-C", _HERE], capture_output=True, text=True)
+    ref = reference_root()
+    r = subprocess.run(["make", "-C", _HERE] + ([f"REF={ref}"] if ref else []), capture_output=True, text=True)
     if verbose or r.returncode:
         print(r.stdout + r.stderr)
     if r.returncode:

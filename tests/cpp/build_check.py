@@ -9,16 +9,19 @@ import subprocess
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 OUT = os.path.join(HERE, "_build", "shim_check")
-SPDLOG = "/opt/prime-rl/.venv/lib/python3.12/site-packages/flashinfer/data/spdlog/include"
 
 
-def build(ref: str = "/root/reference", verbose: bool = False) -> str | None:
-    if not os.path.exists(os.path.join(ref, "include", "coalsack", "nn", "nn_nodes.h")):
+def build(ref: str | None = None, verbose: bool = False) -> str | None:
+    if ref is None:
+        import oracle
+        ref = oracle.reference_root()
+    if not ref or not os.path.exists(os.path.join(ref, "include", "coalsack", "nn", "nn_nodes.h")):
         return OUT if os.path.exists(OUT) else None
     os.makedirs(os.path.dirname(OUT), exist_ok=True)
-    cmd = ["g++", "-std=c++20", "-O1", "-DFMT_HEADER_ONLY",
+    cmd = ["g++", "-std=c++20", "-O1",
            "-I", os.path.join(ROOT, "coalsack_b200", "host"), "-I", os.path.join(ROOT, "include"),
-           "-I", os.path.join(ROOT, "oracle", "cereal_shim"), "-I", os.path.join(ref, "include"), "-I", SPDLOG,
+           "-I", os.path.join(ROOT, "oracle", "cereal_shim"), "-I", os.path.join(ROOT, "oracle", "spdlog_shim"),
+           "-I", os.path.join(ref, "include"),
            os.path.join(HERE, "shim_check.cpp"), "-o", OUT, "-L", os.path.join(ROOT, "coalsack_b200"), "-lcsk_moe",
            "-Wl,-rpath,$ORIGIN/../../../coalsack_b200", "-lpthread"]
     r = subprocess.run(cmd, capture_output=True, text=True)

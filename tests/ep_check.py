@@ -1,7 +1,7 @@
 """Multi-GPU self-check of the expert-parallel steps, run under torchrun:
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
-        -m coalsack_b200.ep_check [--tokens T] [--workload c1] [--steps S] [--nccl]
+        tests/ep_check.py [--tokens T] [--workload c2] [--steps S] [--nccl]
 
 Every rank compares, step after step, the output of the expert-parallel layer for its own
 tokens with the output of the single-GPU layer (all experts resident) for the same tokens.
@@ -17,12 +17,14 @@ import sys
 
 import numpy as np
 
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
 
 def main() -> int:
     import torch
     import torch.distributed as dist
 
-    from . import MoeLayer, ep, synth
+    from coalsack_b200 import MoeLayer, ep, synth
 
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", type=int, default=512, help="tokens per rank")

@@ -12,11 +12,12 @@ import pytest
 from tests import cases
 from tests.cpp import build_check
 
-REF = "/root/reference"
 
 
 def test_bindings_compile_against_reference_headers():
-    if not os.path.exists(REF):
+    import oracle
+    REF = oracle.reference_root()
+    if not REF:
         pytest.skip("no reference checkout here")
     from coalsack_b200.build import build_library
     build_library()

@@ -167,3 +167,70 @@ def test_emulated_p2p_matches_checker(gpu_lib, port, path, N, tokens):
         assert np.array_equal(ro[..., 0], want_ro[..., 0])
         mx, mr = cases.err_stats(out, want)
         assert mx <= cases.MAX_ABS_OVER_RMS and mr <= cases.MEAN_REL, (path, N, mx, mr)
+
+
+@pytest.mark.parametrize("base", ["c2", "c4"])
+def test_emulated_p2p_128_experts_16_per_rank_with_slot_map(gpu_lib, port, base):
+    """The 128-expert shapes over eight emulated ranks, sixteen slots each, placed by the planner from a
+    calibration batch (so logical expert ids and slots differ), peer-memory step, tensor-core and
+    streaming kernels, against the checker."""
+    import torch
+    from coalsack_b200.ep import calibration_load, plan_placement
+    N, per_rank = 8, 24
+    sh = synth.CONFIGS[base].with_(tokens=per_rank)
+    Wg, rb = synth.router_weight(sh), synth.router_bias(sh)
+    load = sum(calibration_load(sh, synth.hidden_states(sh, per_rank, rep=r)) for r in range(N))
+    pl = plan_placement(load, N, extra_slots=0)
+    assert pl.n_slots == 128 and not np.array_equal(pl.slots, np.arange(128))
+    ex = synth.all_experts(sh)
+    exp = {n: (None if ex.get(n) is None else [ex[n][e] for e in pl.slots]) for n in ex}   # slot order
+    tokens = (per_rank,) * N
+    for path in (PATH_TILE, PATH_STREAM):
+        for out, ro, h in run_emulated_p2p(torch, sh, N, tokens, Wg, rb, exp, path, slot_map=pl.slot_map(128)):
+            want, want_ro = port.moe_layer(h, Wg, rb, ex, sh.top_k, sh.act, nthreads=16)
+            assert np.array_equal(ro[..., 0], want_ro[..., 0])
+            mx, mr = cases.err_stats(out, want)
+            assert mx <= cases.MAX_ABS_OVER_RMS and mr <= cases.MEAN_REL, (base, path, mx, mr)
+
+
+def test_emulated_p2p_overflow_is_a_status_not_a_fault(gpu_lib):
+    """Every token of both ranks routes to rank 0's experts, which therefore receives twice the rows its
+    buffers hold (max_tokens * top_k).  Senders skip the rows that do not fit, the row plan is flagged,
+    the receive side derives no output pointers from it, and csk_moe_sync reports CSK_ERR_NOMEM on every
+    rank.  Canary rows after each rank's used part of the output stay untouched."""
+    import torch
+    from coalsack_b200 import CskError
+    sh = synth.tiny(seed=87, E=8, k=2, H=192, F=160, T=1, has_bias=True)
+    _, Wg, rb, ex = cases.layer_inputs(sh, router_scale=1.0)
+    rb = np.where(np.arange(8) < 4, 50.0, -50.0).astype(np.float32)   # experts 0..3 (rank 0) always win
+    N, T = 2, 40
+    dev = torch.device("cuda", 0)
+    layers, hs = [], []
+    for r in range(N):
+        lay = MoeLayer.from_shape(sh, max_tokens=T, expert_begin=4 * r, expert_count=4)
+        lay.set_router(Wg, rb)
+        lay.load_experts({n: ex[n][4 * r:4 * r + 4] for n in ex}, ids=range(4 * r, 4 * r + 4))
+        layers.append(lay)
+        hs.append(torch.from_numpy(synth.hidden_states(sh, T, rep=r)).to(dev))
+    ptrs = [lay.ep_p2p_local_ptrs() for lay in layers]
+    for r, lay in enumerate(layers):
+        lay.ep_p2p_import_ptrs(r, N, [p[0] for p in ptrs], [p[1] for p in ptrs], [p[2] for p in ptrs])
+    counts = [torch.zeros(8, dtype=torch.int32, device=dev) for _ in range(N)]
+    for r in range(N):
+        layers[r].ep_p2p_counts_dev(hs[r], T, counts[r])
+    torch.cuda.synchronize()
+    all_counts = torch.cat(counts).contiguous()
+    assert int(all_counts.view(N, 8)[:, :4].sum()) == N * T * sh.top_k > T * sh.top_k
+    for r in range(N):
+        layers[r].ep_p2p_scatter_dev(hs[r], T, all_counts)
+    torch.cuda.synchronize()
+    codes = []
+    for r in range(N):
+        layers[r].ep_p2p_experts_dev(all_counts, T * sh.top_k)
+        with pytest.raises(CskError) as err:
+            layers[r].sync()
+        codes.append(err.value.code)
+    torch.cuda.synchronize()
+    assert codes == [-4, -4]
+    for lay in layers:
+        lay.close()

@@ -1,7 +1,7 @@
 """The benchmark configurations at their full sizes.  The CPU checker cannot run
 whole batches of this size in seconds, so parity is shown three ways: router
 indices for EVERY token against the restatement (bit-exact), layer outputs for
-a seeded sample of tokens against the restatement, and size-independent
+a seeded sample of 512 tokens against the restatement, and size-independent
 properties over the whole batch (routing weights sum to one; permuting the
 tokens permutes the outputs bit for bit; the two expert kernels agree)."""
 import numpy as np
@@ -31,7 +31,7 @@ def _experts_dict(sh, cache):
     return ex
 
 
-def _check_config(sh, port, sample=48, also_stream=True):
+def _check_config(sh, port, sample=512, also_stream=True):
     T = sh.tokens
     lay, cache = _load(sh, T)
     h = synth.hidden_states(sh)
@@ -86,7 +86,7 @@ def test_config4_qwen_shape_2048(gpu_lib, port):
 
 
 def test_config2_prefill_8192_128_experts(gpu_lib, port):
-    _check_config(synth.C2, port, sample=32, also_stream=False)
+    _check_config(synth.C2, port, also_stream=False)
 
 
 def test_config3_decode_batches(gpu_lib, port):
@@ -95,12 +95,12 @@ def test_config3_decode_batches(gpu_lib, port):
     lay, cache = _load(sh, 256)
     Wg, rb = synth.router_weight(sh), synth.router_bias(sh)
     ex = _experts_dict(sh, cache)
-    for T, rep in ((1, 0), (2, 1), (4, 2), (16, 3), (64, 4), (256, 5)):
+    for T, rep in ((1, 0), (2, 1), (4, 2), (8, 6), (16, 3), (32, 7), (64, 4), (128, 8), (256, 5)):
         h = synth.hidden_states(sh, T, rep=rep)
         out, ro = lay.forward(h)
         want_ro = port.router(h, Wg, rb, sh.top_k)
         assert np.array_equal(ro[..., 0], want_ro[..., 0]), T
-        n = min(T, 24)
+        n = min(T, 64)
         want, _ = port.moe_layer(h[:n], Wg, rb, ex, sh.top_k, sh.act, nthreads=16, router_out=ro[:n])
         mx, mr = cases.err_stats(out[:n], want)
         assert mx <= cases.MAX_ABS_OVER_RMS and mr <= cases.MEAN_REL, (T, mx, mr)

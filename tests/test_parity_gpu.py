@@ -378,3 +378,61 @@ def test_tile_path_wide_exponents(gpu_lib, port):
             want, _ = port.moe_layer(h, Wg, rb, ex, 2, sh.act, nthreads=8, router_out=ro)
         assert_close(out, want, f"wide exponents, path {path}")
     lay.close()
+
+
+def test_edge_scale_bytes(gpu_lib, port):
+    """Scale bytes 0, 1, 2 (the reference reads 0 and 1 as fp32 subnormals, gguf_dequant.h:419-433) on
+    blocks with arbitrary codes, and 254 / 255 on blocks of zero codes (zero under any scale; with
+    non-zero codes the reference's own fp32 weights overflow there), scattered over every matrix of
+    every expert: both kernels must match the checker, and the repack must return the bytes unchanged."""
+    sh = synth.tiny(seed=47, E=4, k=2, H=128, F=192, T=150, has_bias=True)
+    h, Wg, rb, ex = cases.layer_inputs(sh, router_scale=50.0)
+    rng = np.random.default_rng(470)
+    for name in ("w_up", "w_gate", "w_down"):
+        for e in range(sh.num_experts):
+            blocks = ex[name][e].reshape(-1, 17).copy()
+            pick = rng.choice(blocks.shape[0], size=blocks.shape[0] // 8, replace=False)
+            for i, b in enumerate(pick):
+                kind = i % 5
+                blocks[b, 0] = (0, 1, 2, 254, 255)[kind]
+                if kind >= 3:
+                    blocks[b, 1:] = 0
+            ex[name][e] = blocks.reshape(-1)
+    lay = make_layer(sh, Wg, rb, ex, max_tokens=sh.tokens)
+    for which, name in enumerate(("w_up", "w_gate", "w_down", "w_up", "w_gate", "w_down")):
+        assert np.array_equal(lay.unpack_expert(1, which), ex[name][1]), which
+    want = None
+    for path in (PATH_STREAM, PATH_TILE):
+        lay.set_path(path)
+        out, ro = lay.forward(h)
+        if want is None:
+            want, _ = port.moe_layer(h, Wg, rb, ex, sh.top_k, sh.act, nthreads=8, router_out=ro)
+            assert np.all(np.isfinite(want)) and np.any(want != 0)
+        assert np.all(np.isfinite(out)), path
+        assert_close(out, want, f"edge scale bytes, path {path}")
+    lay.close()
+
+
+def test_bounded_wait_runs_out_and_the_handle_recovers(gpu_lib, port):
+    """The failure path of the tensor-core kernel, made to happen without any fault: the wait budget is
+    cut to 0.1 ms and the next launch's copy role is told to issue nothing, so the MMA, dequantiser and
+    epilogue roles all wait on barriers that nothing arms, give up, tear down (tensor memory freed) and
+    the call returns CSK_ERR_DEVICE.  The same handle then computes the layer correctly."""
+    sh = synth.tiny(seed=49, E=4, k=2, H=128, F=128, T=96, has_bias=True)
+    h, Wg, rb, ex = cases.layer_inputs(sh, router_scale=50.0)
+    lay = make_layer(sh, Wg, rb, ex, max_tokens=sh.tokens)
+    lay.set_path(PATH_TILE)
+    good, ro = lay.forward(h)
+    try:
+        lay.debug_set(lay.DEBUG_WAIT_BUDGET, 200_000)
+        lay.debug_set(lay.DEBUG_STALL_TILE_PRODUCER, 1)
+        with pytest.raises(CskError) as err:
+            lay.forward(h)
+        assert err.value.code == -3 and "wait ran out" in str(err.value)
+    finally:
+        lay.debug_set(lay.DEBUG_WAIT_BUDGET, 2_000_000_000)
+    again, ro2 = lay.forward(h)
+    assert np.array_equal(ro, ro2) and np.array_equal(good, again)
+    want, _ = port.moe_layer(h, Wg, rb, ex, sh.top_k, sh.act, nthreads=8, router_out=ro)
+    assert_close(again, want, "after the aborted call")
+    lay.close()
