@@ -61,6 +61,8 @@ SYMBOLS = {
     "csk_moe_ep_p2p_experts_dev": (C.c_int, [_vp, _vp, _i64, _vp]),
     "csk_moe_ep_p2p_combine_dev": (C.c_int, [_vp, _i64, _vp, _vp, _vp]),
     "csk_moe_set_path": (C.c_int, [_vp, _i32]),
+    "csk_moe_set_router_mode": (C.c_int, [_vp, _i32]),
+    "csk_moe_get_router_stats": (C.c_int, [_vp, _vp, _vp]),
     "csk_moe_enable_timing": (C.c_int, [_vp, _i32]),
     "csk_moe_get_timings": (C.c_int, [_vp, C.POINTER(Timings)]),
     "csk_moe_get_counters": (C.c_int, [_vp, _vp, _vp, _vp]),

@@ -142,19 +142,33 @@ __global__ void k_pack_router(const float* __restrict__ wg, float* __restrict__ 
 // The logits sit in registers (lane l holds experts l, l+32, ...); each of the
 // k rounds is an arg-max by shuffles (ties -> lower expert id; the reference
 // leaves ties unspecified).
-__device__ __forceinline__ void warp_topk(const float* __restrict__ l, int E, int k, int sigmoid,
-                                          float* __restrict__ out /* [k][2] */) {
+//
+// With `bounds` (the logits then come from the fast kernel, see k_router_logits)
+// one more round finds the runner-up, and the selection is CERTIFIED only if every
+// gap between neighbours of the k+1 best logits exceeds the sum of their error
+// bounds: the reference's own logits, which lie within those bounds, then order
+// the same experts the same way.  Returns false (warp-uniform) when a gap is too
+// small; the caller then sends the token through the order-faithful chain.
+// CG: logits and bounds are global memory written by other blocks (read through L2); else
+// they are the block's own shared memory.
+// NV: logits per lane (E <= 32 * NV); the selection loops are unrolled over it.
+template <bool CG, int NV>
+__device__ __forceinline__ bool warp_topk_nv(const float* __restrict__ l, int E, int k, int sigmoid,
+                                             float* __restrict__ out /* [k][2] */,
+                                             const float* __restrict__ bounds) {
   const int lane = threadIdx.x & 31;
-  float v[kMaxExperts / 32];
+  float v[NV];
 #pragma unroll
-  for (int i = 0; i < kMaxExperts / 32; ++i) v[i] = (i * 32 < E && i * 32 + lane < E) ? __ldcg(l + i * 32 + lane) : -INFINITY;
-  float sel_v[kMaxTopK];
-  int sel_i[kMaxTopK];
-  for (int j = 0; j < k; ++j) {
+  for (int i = 0; i < NV; ++i)
+    v[i] = (i * 32 < E && i * 32 + lane < E) ? (CG ? __ldcg(l + i * 32 + lane) : l[i * 32 + lane]) : -INFINITY;
+  float sel_v[kMaxTopK + 1];
+  int sel_i[kMaxTopK + 1];
+  const int rounds = bounds ? min(k + 1, E) : k;
+  for (int j = 0; j < rounds; ++j) {
     float bv = -INFINITY;
     int bi = 0x7fffffff;
 #pragma unroll
-    for (int i = 0; i < kMaxExperts / 32; ++i) {
+    for (int i = 0; i < NV; ++i) {
       if (i * 32 < E) {  // warp-uniform
         const float x = v[i];
         if (x > bv) {  // ascending expert id within the lane: '>' keeps the lowest on ties
@@ -175,9 +189,18 @@ __device__ __forceinline__ void warp_topk(const float* __restrict__ l, int E, in
     sel_i[j] = bi;
     // the winner leaves the pool: NaN never wins a '>' test again
 #pragma unroll
-    for (int i = 0; i < kMaxExperts / 32; ++i)
+    for (int i = 0; i < NV; ++i)
       if (i * 32 < E && bi == i * 32 + lane) v[i] = __int_as_float(0xffc00000);
   }
+  int certified = 1;
+  if (bounds && lane == 0) {
+    float b[kMaxTopK + 1];
+    for (int j = 0; j < rounds; ++j)
+      b[j] = (sel_i[j] >= 0 && sel_i[j] < E) ? (CG ? __ldcg(bounds + sel_i[j]) : bounds[sel_i[j]]) : INFINITY;
+    for (int j = 0; j + 1 < rounds; ++j)
+      if (!(sel_v[j] - sel_v[j + 1] > b[j] + b[j + 1])) certified = 0;  // also false for NaN
+  }
+  certified = __shfl_sync(0xffffffffu, certified, 0);
   if (lane == 0) {
     float w[kMaxTopK];
     if (sigmoid) {
@@ -198,6 +221,18 @@ __device__ __forceinline__ void warp_topk(const float* __restrict__ l, int E, in
       out[j * 2 + 1] = w[j];
     }
   }
+  return certified != 0;
+}
+
+template <bool CG = true>
+__device__ __forceinline__ bool warp_topk(const float* __restrict__ l, int E, int k, int sigmoid,
+                                          float* __restrict__ out /* [k][2] */,
+                                          const float* __restrict__ bounds = nullptr) {
+  if (E <= 32) return warp_topk_nv<CG, 1>(l, E, k, sigmoid, out, bounds);
+  if (E <= 64) return warp_topk_nv<CG, 2>(l, E, k, sigmoid, out, bounds);
+  if (E <= 128) return warp_topk_nv<CG, 4>(l, E, k, sigmoid, out, bounds);
+  if (E <= 256) return warp_topk_nv<CG, 8>(l, E, k, sigmoid, out, bounds);
+  return warp_topk_nv<CG, kMaxExperts / 32>(l, E, k, sigmoid, out, bounds);
 }
 
 struct RouterArgs {
@@ -209,6 +244,11 @@ struct RouterArgs {
   int* counters;         // one per token block, all zero between launches; null = logits only
   int* status;           // device status word or null
   int T, H, E, k, sigmoid;
+  // order-faithful kernel over a token list (the fall-back pass): token_list[0 .. *n_list)
+  const int* token_list;
+  int* n_list;           // read at start; reset to zero, with fb_done, by the last block to finish
+  int* fb_done;          // ticket of that reset
+  unsigned long long* fb_total;  // running number of tokens that took the fall-back pass (statistics)
 };
 
 // A block is one producer warp (four with plain weights) plus TW consumer warps.  A
@@ -266,7 +306,7 @@ k_router_logits(const RouterArgs A) {
 
   const int T = A.T, H = A.H, E = A.E;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int t0 = blockIdx.x * BT, e0 = blockIdx.y * 32;
+  const int e0 = blockIdx.y * 32;
   const int n_chunks = (H + CH - 1) / CH;
 
   if (tid == 0) {
@@ -281,7 +321,17 @@ k_router_logits(const RouterArgs A) {
   __syncthreads();
   griddep_wait();
   griddep_launch();
+  // tokens of this launch: all T, or the entries of a list built by an earlier kernel
+  const int* const list = A.token_list;
+  const int n_tok = list ? min(*reinterpret_cast<volatile int*>(A.n_list), T) : T;
+  auto token_at = [&](int ti) { return ti < n_tok ? (list ? list[ti] : ti) : -1; };
 
+  // A block takes the token blocks blockIdx.x, blockIdx.x + gridDim.x, ...  (one each unless the launch
+  // is list-driven and the list turned out longer than the grid).  The ring's barriers carry on from
+  // one token block to the next: cg0 = chunks this block has moved so far.
+  for (int tb = blockIdx.x, iter = 0; tb * BT < n_tok; tb += gridDim.x, ++iter) {
+  const int t0 = tb * BT;
+  const int cg0 = iter * n_chunks;
   if (warp < NP) {
     // ------------------------------ producers ------------------------------
     const int n_e = min(32, E - e0);
@@ -293,8 +343,8 @@ k_router_logits(const RouterArgs A) {
     bool ok = true;
     if (!PACKED || n_mine) {
       for (int ci = 0; ci < n_chunks; ++ci) {
-        const int st = ci % NS;
-        if (ci >= NS && !mbar_wait_nap(bar_empty(st), (uint32_t)((ci / NS - 1) & 1), abort_flag)) {
+        const int cg = cg0 + ci, st = cg % NS;
+        if (cg >= NS && !mbar_wait_nap(bar_empty(st), (uint32_t)((cg / NS - 1) & 1), abort_flag)) {
           ok = false;
           break;
         }
@@ -317,9 +367,9 @@ k_router_logits(const RouterArgs A) {
     if (!ok) {
       // let the copies still in flight land before the block goes away
       for (int i = 0; i < NS && i < issued; ++i) {
-        const int ci = issued - 1 - i;
-        const long long tb = clock64();
-        while (!mbar_try(bar_full(ci % NS), (uint32_t)((ci / NS) & 1)) && clock64() - tb < drain_budget()) {
+        const int cg = cg0 + issued - 1 - i;
+        const long long tc = clock64();
+        while (!mbar_try(bar_full(cg % NS), (uint32_t)((cg / NS) & 1)) && clock64() - tc < drain_budget()) {
         }
       }
     }
@@ -327,17 +377,21 @@ k_router_logits(const RouterArgs A) {
     // ------------------------------ consumers ------------------------------
     const int w = warp - NP;
     float acc[TT];
+    int tok[TT];
 #pragma unroll
-    for (int i = 0; i < TT; ++i) acc[i] = 0.f;
+    for (int i = 0; i < TT; ++i) {
+      acc[i] = 0.f;
+      tok[i] = token_at(t0 + w * TT + i);
+    }
     // this warp's token rows of chunk ci -> its rows of stage ci % NS
     auto load_tokens = [&](int ci) {
       const int d0 = ci * CH;
       const int dc = min(CH, H - d0);
-      const uint32_t dst = smem_u32(stages + (size_t)(ci % NS) * stage_floats + (32 + w * TT) * LD);
+      const uint32_t dst = smem_u32(stages + (size_t)((cg0 + ci) % NS) * stage_floats + (32 + w * TT) * LD);
 #pragma unroll
       for (int i = 0; i < TT; ++i) {
-        const int t = t0 + w * TT + i;
-        if (t < T)
+        const int t = tok[i];
+        if (t >= 0)
           for (int c = lane * 4; c < dc; c += 128)
             cp_async16(dst + (uint32_t)(i * LD + c) * 4, A.hidden + (size_t)t * H + d0 + c);
       }
@@ -348,12 +402,12 @@ k_router_logits(const RouterArgs A) {
     }
     bool ok = true;
     for (int ci = 0; ci < n_chunks; ++ci) {
-      const int st = ci % NS;
+      const int cg = cg0 + ci, st = cg % NS;
       cp_async_wait<NS - 2>();  // this lane's part of the token rows of chunk ci has landed ...
       __syncwarp();             // ... and the other lanes'; the rows used in the last iteration are free
       if (ci + NS - 1 < n_chunks) load_tokens(ci + NS - 1);
       cp_async_commit();
-      if (!mbar_wait(bar_full(st), (uint32_t)((ci / NS) & 1), abort_flag)) {
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_full(st), (uint32_t)((cg / NS) & 1), abort_flag))) {  // warp-uniform
         ok = false;
         break;
       }
@@ -438,34 +492,52 @@ k_router_logits(const RouterArgs A) {
       const float b = (A.bias && e < E) ? A.bias[e] : 0.f;
 #pragma unroll
       for (int i = 0; i < TT; ++i) {
-        const int t = t0 + w * TT + i;
-        if (t < T && e < E) A.logits[(size_t)t * E + e] = __fadd_rn(acc[i], b);
+        const int t = tok[i];
+        if (t >= 0 && e < E) A.logits[(size_t)t * E + e] = __fadd_rn(acc[i], b);
       }
       __threadfence();  // the logits before the block's ticket below
     }
   }
   __syncthreads();
-  if (tid == 0 && *abort_flag && A.status) atomicOr(A.status, kDevErrWaitTimeout);
-  if (A.counters == nullptr) return;
+  if (*abort_flag) break;  // a wait ran out: the ring's state is unknown, the block stops here
 
   // ---- the last block of this token block selects the top-k ----
-  if (tid == 0) {
-    int last = 1;
-    if (gridDim.y > 1) {
-      __threadfence();  // this block's logits before its ticket
-      last = atomicAdd(&A.counters[blockIdx.x], 1) == (int)gridDim.y - 1;
-      if (last) {
-        A.counters[blockIdx.x] = 0;  // ready for the next launch
-        __threadfence();             // the other blocks' logits after their tickets
+  if (A.counters != nullptr) {
+    if (tid == 0) {
+      int last = 1;
+      if (gridDim.y > 1) {
+        __threadfence();  // this block's logits before its ticket
+        last = atomicAdd(&A.counters[tb], 1) == (int)gridDim.y - 1;
+        if (last) {
+          A.counters[tb] = 0;  // ready for the next launch
+          __threadfence();     // the other blocks' logits after their tickets
+        }
+      }
+      *ticket = last;
+    }
+    __syncthreads();
+    if (*ticket) {
+      for (int i = warp; i < BT; i += TW + NP) {
+        const int t = token_at(t0 + i);
+        if (t < 0) continue;
+        warp_topk(A.logits + (size_t)t * E, E, A.k, A.sigmoid, A.router_out + (size_t)t * A.k * 2);
       }
     }
-    *ticket = last;
+    __syncthreads();  // `ticket` is rewritten by the next token block
   }
-  __syncthreads();
-  if (!*ticket) return;
-  for (int i = warp; i < BT; i += TW + NP) {
-    const int t = t0 + i;
-    if (t < T) warp_topk(A.logits + (size_t)t * E, E, A.k, A.sigmoid, A.router_out + (size_t)t * A.k * 2);
+  }  // token blocks of this block
+
+  if (tid == 0 && *abort_flag && A.status) atomicOr(A.status, kDevErrWaitTimeout);
+  if (list && tid == 0) {
+    // every block of a list-driven launch, busy or idle, has read the list's length by now: the last
+    // one to get here clears it for the next step
+    __threadfence();
+    if (atomicAdd(A.fb_done, 1) == (int)(gridDim.x * gridDim.y) - 1) {
+      if (A.fb_total) atomicAdd(A.fb_total, (unsigned long long)n_tok);
+      *A.n_list = 0;
+      *A.fb_done = 0;
+      __threadfence();
+    }
   }
 }
 
@@ -475,27 +547,23 @@ cudaError_t router_prepare_one() {
                               (int)router_smem_bytes(TW * TT, CH));
 }
 constexpr int kRouterChunkFew = 256, kRouterChunkMany = 128;  // columns per stage: few / many tokens
-// Lets the router kernels use more than the default 48 KB of dynamic shared
-// memory.  Once per device.
-inline cudaError_t router_prepare_device() {
-  cudaError_t e = router_prepare_one<1, 1, kRouterChunkFew, true>();
-  if (e == cudaSuccess) e = router_prepare_one<2, 1, kRouterChunkFew, true>();
-  if (e == cudaSuccess) e = router_prepare_one<4, 1, kRouterChunkFew, true>();
-  if (e == cudaSuccess) e = router_prepare_one<4, 2, kRouterChunkMany, true>();
-  if (e == cudaSuccess) e = router_prepare_one<4, 4, kRouterChunkMany, true>();
-  if (e == cudaSuccess) e = router_prepare_one<8, 4, kRouterChunkMany, true>();
-  if (e == cudaSuccess) e = router_prepare_one<1, 1, kRouterChunkFew, false>();
-  if (e == cudaSuccess) e = router_prepare_one<2, 1, kRouterChunkFew, false>();
-  if (e == cudaSuccess) e = router_prepare_one<4, 1, kRouterChunkFew, false>();
-  if (e == cudaSuccess) e = router_prepare_one<4, 2, kRouterChunkMany, false>();
-  if (e == cudaSuccess) e = router_prepare_one<4, 4, kRouterChunkMany, false>();
-  if (e == cudaSuccess) e = router_prepare_one<8, 4, kRouterChunkMany, false>();
+template <bool PACKED>
+cudaError_t router_prepare_set() {
+  cudaError_t e = router_prepare_one<1, 1, kRouterChunkFew, PACKED>();
+  if (e == cudaSuccess) e = router_prepare_one<2, 1, kRouterChunkFew, PACKED>();
+  if (e == cudaSuccess) e = router_prepare_one<4, 1, kRouterChunkFew, PACKED>();
+  if (e == cudaSuccess) e = router_prepare_one<4, 2, kRouterChunkMany, PACKED>();
+  if (e == cudaSuccess) e = router_prepare_one<4, 4, kRouterChunkMany, PACKED>();
+  if (e == cudaSuccess) e = router_prepare_one<8, 4, kRouterChunkMany, PACKED>();
   return e;
 }
+// Lets the router kernels use more than the default 48 KB of dynamic shared
+// memory.  Once per device.
+inline cudaError_t router_prepare_device();
 
 template <int TW, int TT, int CH, bool PACKED>
-void launch_router_one(const RouterArgs& a, cudaStream_t s, bool pdl) {
-  const dim3 grid((unsigned)((a.T + TW * TT - 1) / (TW * TT)), (unsigned)((a.E + 31) / 32));
+void launch_router_one(const RouterArgs& a, int token_slots, cudaStream_t s, bool pdl) {
+  const dim3 grid((unsigned)((token_slots + TW * TT - 1) / (TW * TT)), (unsigned)((a.E + 31) / 32));
   launch_k(k_router_logits<TW, TT, CH, PACKED>, grid, dim3((TW + router_producer_warps(PACKED)) * 32),
            router_smem_bytes(TW * TT, CH), s, pdl, a);
 }
@@ -503,23 +571,253 @@ void launch_router_one(const RouterArgs& a, cudaStream_t s, bool pdl) {
 // Few tokens per block while that still leaves SMs idle (a block's speed is bounded by its
 // shared-memory reads: one 16-byte word per lane per four columns and chain), more chains per
 // thread once the machine is full.  wg_few / wg_many: the weights packed for the two chunk
-// widths (PACKED) or both the plain [E,H] matrix.  Returns the number of token blocks.
+// widths (PACKED) or both the plain [E,H] matrix.  token_slots: tokens the grid is sized for
+// (a.T, or for a list-driven launch the most entries the list can have).
 template <bool PACKED>
-inline int launch_router_logits(RouterArgs a, const float* wg_few, const float* wg_many, int sm_count,
-                                cudaStream_t s, bool pdl = false) {
-  const int64_t token_blocks = (int64_t)a.T * ((a.E + 31) / 32);  // blocks if every block held one token
+inline void launch_router_logits(RouterArgs a, const float* wg_few, const float* wg_many, int sm_count,
+                                 cudaStream_t s, bool pdl = false, int token_slots = -1) {
+  if (token_slots < 0) token_slots = a.T;
+  const int64_t token_blocks = (int64_t)token_slots * ((a.E + 31) / 32);  // blocks if every block held one token
   if (token_blocks <= 4 * (int64_t)sm_count) {
     a.wg = wg_few;
-    if (token_blocks <= sm_count) launch_router_one<1, 1, kRouterChunkFew, PACKED>(a, s, pdl);
-    else if (token_blocks <= 2 * (int64_t)sm_count) launch_router_one<2, 1, kRouterChunkFew, PACKED>(a, s, pdl);
-    else launch_router_one<4, 1, kRouterChunkFew, PACKED>(a, s, pdl);
+    if (token_blocks <= sm_count) launch_router_one<1, 1, kRouterChunkFew, PACKED>(a, token_slots, s, pdl);
+    else if (token_blocks <= 2 * (int64_t)sm_count) launch_router_one<2, 1, kRouterChunkFew, PACKED>(a, token_slots, s, pdl);
+    else launch_router_one<4, 1, kRouterChunkFew, PACKED>(a, token_slots, s, pdl);
   } else {
     a.wg = wg_many;
-    if (token_blocks <= 8 * (int64_t)sm_count) launch_router_one<4, 2, kRouterChunkMany, PACKED>(a, s, pdl);
-    else if (token_blocks <= 64 * (int64_t)sm_count) launch_router_one<4, 4, kRouterChunkMany, PACKED>(a, s, pdl);
-    else launch_router_one<8, 4, kRouterChunkMany, PACKED>(a, s, pdl);
+    if (token_blocks <= 8 * (int64_t)sm_count) launch_router_one<4, 2, kRouterChunkMany, PACKED>(a, token_slots, s, pdl);
+    else if (token_blocks <= 64 * (int64_t)sm_count) launch_router_one<4, 4, kRouterChunkMany, PACKED>(a, token_slots, s, pdl);
+    else launch_router_one<8, 4, kRouterChunkMany, PACKED>(a, token_slots, s, pdl);
   }
-  return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Fast router with certified selection.
+//
+// The reference's logit is a sequential fp32 chain, which runs at the add latency and, for a
+// handful of tokens, on a handful of SMs.  Here the logits are computed with fused
+// multiply-adds, split over the hidden dimension across many CTAs, and every logit carries a
+// rigorous bound on its distance from the reference's chain value C:
+//   |C - S| <= u (sum_i |S_i| + A),  S_i the exact partial sums in column order, A = sum |h w|
+//   (one rounding per product, one per addition; u = 2^-24), and for column i of 32-column
+//   block j:  |S_i| <= |R_j| + A_j  (R_j the prefix at the block's start), so
+//   sum_i |S_i| <= 32 sum_j |R_j| + 32 A;
+//   the block-wise FMA sum itself is within u (17 A + sum_j |R_j|) of S;
+//   A <= |h|_2 |w_e|_2 (Cauchy-Schwarz; |w_e|_2 precomputed, |h|_2 summed on the way).
+// bound = 1.05 u (33 sum_j |R_j| + 50 |h| |w_e|) + 4 u |logit| covers both, the two roundings
+// of the bias addition and the rounding of the bound's own arithmetic.  The top-k step accepts
+// a selection only when the gaps between neighbours of the k+1 best logits exceed the sum of
+// their bounds; every other token goes through the order-faithful chain (k_router_logits over
+// the list of those tokens).  Expert indices are therefore the reference's in every case.
+//
+// k_router_fast: CTA = (block of 4*TPW tokens, group of 32 experts, part m of the hidden
+// dimension).  A part is a run of 96-column slices; per slice the CTA stages the 32 x 96
+// weight block and its tokens' 96 columns in shared memory, every lane takes ITS expert's 96
+// weights into registers and runs its warp's TPW tokens against them (token values by
+// broadcast loads: one shared-memory wavefront per four FMAs).  Per (token, expert, part) it
+// leaves c = the part's sum and a = sum over the part's blocks of |prefix inside the part|.
+// k_router_finish: one warp per token adds the parts in order (prefix P_m before part m:
+// sum_j |R_j| <= sum_m (blocks_m |P_m| + a_m)), forms logits and bounds, selects and certifies.
+// ---------------------------------------------------------------------------
+constexpr int kFastSliceBlocks = 3;                     // 32-column blocks per slice
+constexpr int kFastSliceCols = 32 * kFastSliceBlocks;   // 96
+constexpr int kFastLdw = kFastSliceCols + 4;            // weight row stride in shared memory (16-byte multiple;
+                                                        // a quarter-warp's 128-bit reads of one column group
+                                                        // of eight neighbouring rows hit distinct banks)
+
+struct FastRouterArgs {
+  const float* hidden;  // [T,H], 16-byte aligned
+  const float* wg;      // [E,H] plain, 16-byte aligned
+  float2* part;         // [T][parts][E]: (c, a)
+  float* hn2;           // [T][parts]: the part's share of the token row's sum of squares
+  int T, H, E;
+};
+
+inline int fast_router_slices(int H) { return (H / 32 + kFastSliceBlocks - 1) / kFastSliceBlocks; }
+inline size_t fast_router_smem(int tpw) { return 2 * (size_t)(32 * kFastLdw + 4 * tpw * kFastSliceCols) * sizeof(float); }
+
+template <int TPW>
+__global__ void __launch_bounds__(128) k_router_fast(const FastRouterArgs A) {
+  constexpr int TB = 4 * TPW;
+  constexpr int kStage = 32 * kFastLdw + TB * kFastSliceCols;  // floats: weight block, then token block
+  extern __shared__ __align__(16) float fast_smem[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int T = A.T, H = A.H, E = A.E;
+  const int t_base = blockIdx.x * TB, e0 = blockIdx.y * 32;
+  const int parts = gridDim.z, m = blockIdx.z;
+  const int n_slices = (H / 32 + kFastSliceBlocks - 1) / kFastSliceBlocks;
+  const int s_begin = n_slices * m / parts, s_end = n_slices * (m + 1) / parts;
+  float R[TPW], aR[TPW], h2[TPW];
+#pragma unroll
+  for (int i = 0; i < TPW; ++i) R[i] = aR[i] = h2[i] = 0.f;
+  griddep_wait();
+  griddep_launch();
+  // all 16-byte pieces of a slice are requested at once (cp.async); what lies outside the matrices is zero
+  auto stage_slice = [&](int sl, int buf) {
+    float* Ws = fast_smem + buf * kStage;
+    float* Hs = Ws + 32 * kFastLdw;
+    const int col0 = sl * kFastSliceCols;
+    for (int idx = tid; idx < 32 * (kFastSliceCols / 4); idx += 128) {
+      const int r = idx / (kFastSliceCols / 4), q = idx % (kFastSliceCols / 4);
+      const int e = e0 + r, col = col0 + q * 4;  // H is a multiple of 32: col < H means the whole piece is inside
+      float* d = Ws + r * kFastLdw + q * 4;
+      if (e < E && col < H) cp_async16(smem_u32(d), A.wg + (size_t)e * H + col);
+      else *reinterpret_cast<float4*>(d) = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    for (int idx = tid; idx < TB * (kFastSliceCols / 4); idx += 128) {
+      const int r = idx / (kFastSliceCols / 4), q = idx % (kFastSliceCols / 4);
+      const int t = t_base + r, col = col0 + q * 4;
+      float* d = Hs + r * kFastSliceCols + q * 4;
+      if (t < T && col < H) cp_async16(smem_u32(d), A.hidden + (size_t)t * H + col);
+      else *reinterpret_cast<float4*>(d) = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    cp_async_commit();
+  };
+  if (s_begin < s_end) stage_slice(s_begin, 0);
+  for (int sl = s_begin; sl < s_end; ++sl) {
+    const int buf = (sl - s_begin) & 1;
+    if (sl + 1 < s_end) {
+      stage_slice(sl + 1, buf ^ 1);  // the other buffer's readers finished before the barrier that ended slice sl - 1
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const float* Ws = fast_smem + buf * kStage;
+    const float* Hs = Ws + 32 * kFastLdw;
+    float w[kFastSliceCols];
+#pragma unroll
+    for (int q = 0; q < kFastSliceCols / 4; ++q) {
+      const float4 v = *reinterpret_cast<const float4*>(Ws + lane * kFastLdw + q * 4);
+      w[q * 4 + 0] = v.x;
+      w[q * 4 + 1] = v.y;
+      w[q * 4 + 2] = v.z;
+      w[q * 4 + 3] = v.w;
+    }
+    // TG tokens at a time: 2 * TG independent FMA chains and TG broadcast loads in flight per lane
+    constexpr int TG = TPW < 4 ? TPW : 4;
+#pragma unroll
+    for (int i0 = 0; i0 < TPW; i0 += TG) {
+      const float* hp = Hs + (warp * TPW + i0) * kFastSliceCols;
+#pragma unroll
+      for (int blk = 0; blk < kFastSliceBlocks; ++blk) {
+        float b0[TG], b1[TG];
+#pragma unroll
+        for (int j = 0; j < TG; ++j) b0[j] = b1[j] = 0.f;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          float4 hv[TG];
+#pragma unroll
+          for (int j = 0; j < TG; ++j)
+            hv[j] = *reinterpret_cast<const float4*>(hp + j * kFastSliceCols + blk * 32 + q * 4);
+#pragma unroll
+          for (int j = 0; j < TG; ++j) {
+            b0[j] = fmaf(hv[j].x, w[blk * 32 + q * 4 + 0], b0[j]);
+            b1[j] = fmaf(hv[j].y, w[blk * 32 + q * 4 + 1], b1[j]);
+          }
+#pragma unroll
+          for (int j = 0; j < TG; ++j) {
+            b0[j] = fmaf(hv[j].z, w[blk * 32 + q * 4 + 2], b0[j]);
+            b1[j] = fmaf(hv[j].w, w[blk * 32 + q * 4 + 3], b1[j]);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < TG; ++j) {
+          const float hx = hp[j * kFastSliceCols + blk * 32 + lane];  // the warp's lanes share the row's squares
+          h2[i0 + j] = fmaf(hx, hx, h2[i0 + j]);
+          R[i0 + j] += b0[j] + b1[j];
+          aR[i0 + j] += fabsf(R[i0 + j]);
+        }
+      }
+    }
+    __syncthreads();  // this buffer is refilled during the next slice
+  }
+  const int e = e0 + lane;
+#pragma unroll
+  for (int i = 0; i < TPW; ++i) {
+    const int t = t_base + warp * TPW + i;
+    float q = h2[i];
+    if (blockIdx.y == 0) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o);
+    }
+    if (t < T) {
+      if (e < E) A.part[((size_t)t * parts + m) * E + e] = make_float2(R[i], aR[i]);
+      if (blockIdx.y == 0 && lane == 0) A.hn2[(size_t)t * parts + m] = q;
+    }
+  }
+}
+
+struct FinishRouterArgs {
+  const float2* part;   // [T][parts][E]
+  const float* hn2;     // [T][parts]
+  const float* bias;    // [E] or null
+  const float* wnorm;   // [E] upper bounds of the gate rows' 2-norms
+  float* router_out;    // [T,k,2]
+  int* fb_list;         // tokens whose selection is not certified ...
+  int* fb_count;        // ... and how many (zero between steps)
+  int T, H, E, k, sigmoid, parts;
+};
+
+constexpr int kFastMaxParts = 32;
+
+// One block per token, one thread per expert (at most 256 threads; more experts take turns): a
+// thread's loads of its expert's parts are all in flight at once; logits and bounds meet in
+// shared memory, where warp 0 selects.
+__global__ void __launch_bounds__(256) k_router_finish(const FinishRouterArgs A) {
+  __shared__ float s_logit[kMaxExperts], s_bound[kMaxExperts];
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x;
+  const int parts = A.parts, E = A.E;
+  const int n_slices = (A.H / 32 + kFastSliceBlocks - 1) / kFastSliceBlocks;
+  griddep_wait();
+  griddep_launch();
+  float h2 = lane < parts ? __ldcg(A.hn2 + (size_t)t * parts + lane) : 0.f;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) h2 += __shfl_xor_sync(0xffffffffu, h2, o);  // every warp, all lanes
+  const float hn = sqrtf(h2) * 1.001f;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    float2 v[kFastMaxParts];
+#pragma unroll
+    for (int m = 0; m < kFastMaxParts; ++m)
+      v[m] = m < parts ? __ldcg(A.part + ((size_t)t * parts + m) * E + e) : make_float2(0.f, 0.f);
+    const float bias = A.bias ? A.bias[e] : 0.f;
+    const float wn = A.wnorm[e];
+    float P = 0.f, sr = 0.f;
+#pragma unroll
+    for (int m = 0; m < kFastMaxParts; ++m) {
+      if (m < parts) {
+        const int blocks = kFastSliceBlocks * (n_slices * (m + 1) / parts - n_slices * m / parts);
+        sr += (float)blocks * fabsf(P) + v[m].y;
+        P += v[m].x;
+      }
+    }
+    const float logit = __fadd_rn(P, bias);
+    s_logit[e] = logit;
+    s_bound[e] = 6.3e-8f * (33.f * sr + 50.f * hn * wn) + 2.4e-7f * fabsf(logit) + 1e-30f;
+  }
+  __syncthreads();
+  if (threadIdx.x >= 32) return;
+  const bool sure = warp_topk<false>(s_logit, E, A.k, A.sigmoid, A.router_out + (size_t)t * A.k * 2, s_bound);
+  if (!sure && lane == 0) A.fb_list[atomicAdd(A.fb_count, 1)] = t;  // at most one entry per token
+}
+
+inline cudaError_t router_prepare_device() {
+  cudaError_t e = router_prepare_set<true>();
+  if (e == cudaSuccess) e = router_prepare_set<false>();
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(k_router_fast<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fast_router_smem(8));
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(k_router_fast<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fast_router_smem(16));
+  return e;
+}
+
+// 2-norm of every expert's gate row, rounded up (the fast router's Cauchy-Schwarz term).
+__global__ void k_router_wnorm(const float* __restrict__ wg, float* __restrict__ wnorm, int E, int H) {
+  const int e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (e >= E) return;
+  float acc = 0.f;
+  for (int d = lane; d < H; d += 32) acc = fmaf(wg[(size_t)e * H + d], wg[(size_t)e * H + d], acc);
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) wnorm[e] = sqrtf(acc) * 1.001f;
 }
 
 __global__ void __launch_bounds__(128)
@@ -567,11 +865,17 @@ __global__ void k_hist(const float* __restrict__ router_out, int n_pairs, int E,
 // With router_out given (small batches) the block first builds the histogram
 // itself -- counts and the status word then need no clearing beforehand and the
 // whole plan is one launch.
+//
+// With row_of_pair / pair_of_row given as well (the streaming kernel then gathers its token
+// rows itself) the block also places every pair: row_of_pair[i] = its row in the grouped
+// order (-1: not placed), pair_of_row[row] = i.  Which row of its expert's segment a pair
+// gets depends on the order of the block's atomics; a row's value does not depend on it.
 __global__ void __launch_bounds__(1024)
 k_scan(int* __restrict__ counts, int E, int e_begin, int e_count, int tile_rows, int max_rows,
        int max_tiles, const uint8_t* __restrict__ resident, int* __restrict__ offsets,
        int* __restrict__ cursor, RowTile* __restrict__ tiles, int* __restrict__ meta,
-       const float* __restrict__ router_out, int n_pairs, int only_expert) {
+       const float* __restrict__ router_out, int n_pairs, int only_expert,
+       int* __restrict__ row_of_pair = nullptr, int* __restrict__ pair_of_row = nullptr) {
   __shared__ int s_row_off[1025];
   __shared__ int s_tile_off[1025];
   __shared__ int s_warp[2][32];
@@ -650,6 +954,23 @@ k_scan(int* __restrict__ counts, int E, int e_begin, int e_count, int tile_rows,
   }
   __syncthreads();
   if (e == 0) meta[2] = s_distinct;
+  if (router_out && row_of_pair) {
+    // s_warp is free now: reuse nothing of it; the cursors live in s_cur
+    __shared__ int s_cur[1024];
+    s_cur[e] = 0;
+    __syncthreads();
+    const bool over = total_rows > max_rows || total_tiles > max_tiles;
+    for (int i = e; i < n_pairs; i += 1024) {
+      const int x = (int)router_out[2 * (size_t)i];
+      int pos = -1;
+      if (!over && x >= 0 && x < E && (only_expert < 0 || x == only_expert)) {
+        pos = s_row_off[x] + atomicAdd(&s_cur[x], 1);
+        if (pos >= max_rows) pos = -1;
+      }
+      row_of_pair[i] = pos;
+      if (pos >= 0) pair_of_row[pos] = i;
+    }
+  }
   if (total_rows > max_rows || total_tiles > max_tiles) return;
   for (int i = threadIdx.x; i < total_tiles; i += blockDim.x) {
     // largest expert x with s_tile_off[x] <= i (experts without tiles repeat an offset)

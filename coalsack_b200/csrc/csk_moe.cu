@@ -36,6 +36,14 @@ struct csk_moe_layer {
   float* d_wg_few = nullptr;   // the same repacked for the router kernel's two chunk widths
   float* d_wg_many = nullptr;
   int* d_route_cnt = nullptr;  // [max_T] tickets of the router's token blocks (zero between launches)
+  float2* d_part = nullptr;    // [part_rows,E] partial sums of the fast router, one row per (token, part of H)
+  float* d_hn2 = nullptr;      // [part_rows] the parts' shares of the token rows' sums of squares
+  int64_t part_rows = 0;
+  float* d_wnorm = nullptr;    // [E] 2-norms of the gate rows
+  int* d_fb_list = nullptr;    // [max_T] tokens the fast router could not certify
+  int* d_fb = nullptr;         // [0] entries of d_fb_list, [1] ticket of its reset, [2..3] 64-bit running total
+  int router_mode = CSK_ROUTER_CERTIFIED;
+  int64_t routed_tokens = 0;   // tokens routed in certified mode since creation
   float* d_logits = nullptr;  // [max_T,E] router scratch
   float* d_rbias = nullptr;
   bool router_set = false, has_rbias = false;
@@ -69,6 +77,9 @@ struct csk_moe_layer {
   int* d_offsets = nullptr;      // [E+1]
   int* d_cursor = nullptr;       // [E]
   int* d_row_of_pair = nullptr;  // [max_rows]
+  int* d_pair_of_row = nullptr;  // [max_rows] inverse map (small batches on the streaming kernel)
+  const float* gather_hidden = nullptr;  // transient: the streaming kernel's gate/up launch gathers rows from here
+  const float* gather_router = nullptr;
   int* d_out_row_map = nullptr;  // [max_rows] (expert-parallel receive side)
   int* d_seg = nullptr;          // [2*1024+2] segment plan (expert-parallel receive side)
   RowTile* d_tiles = nullptr;
@@ -164,22 +175,98 @@ int launch_router(csk_moe_layer* L, const float* d_hidden, int64_t T, float* d_r
   a.E = L->E_router;
   a.k = L->k;
   a.sigmoid = L->cfg.sigmoid_gating;
-  launch_router_logits<true>(a, L->d_wg_few, L->d_wg_many, L->sm_count, s, L->pdl);
+  // The certified pass pays off while the chain kernel cannot fill the machine (a chain runs at the
+  // add latency on one SM per 32 experts and token block, however few tokens there are); from a few
+  // hundred tokens on the chain kernel is bound by its shared-memory traffic, like the fast one.
+  constexpr int64_t kCertifiedMaxTokens = 128;
+  if (L->router_mode == CSK_ROUTER_CHAIN || T > kCertifiedMaxTokens) {
+    launch_router_logits<true>(a, L->d_wg_few, L->d_wg_many, L->sm_count, s, L->pdl);
+    CSK_CUDA(L, cudaGetLastError());
+    L->last.launches += 1;
+    return CSK_OK;
+  }
+  // fast logits with error bounds; tokens whose selection the bounds do not certify are listed ...
+  const int groups = (L->E_router + 31) / 32;
+  {
+    FastRouterArgs f{};
+    f.hidden = d_hidden;
+    f.wg = L->d_wg;
+    f.part = L->d_part;
+    f.hn2 = L->d_hn2;
+    f.T = (int)T;
+    f.H = L->H;
+    f.E = L->E_router;
+    const int tpw = T <= 4 ? 1 : T <= 8 ? 2 : T <= 16 ? 4 : T <= 32 ? 8 : 16;
+    const int token_blocks = (int)((T + 4 * tpw - 1) / (4 * tpw));
+    // enough parts of the hidden dimension to put a CTA on every SM (few tokens); one part once
+    // the token blocks alone fill the machine
+    int parts = std::min(std::min(fast_router_slices(L->H), kFastMaxParts),
+                         std::max(1, (L->sm_count + token_blocks * groups - 1) / (token_blocks * groups)));
+    while (parts > 1 && T * parts > L->part_rows) --parts;
+    const dim3 grid((unsigned)token_blocks, (unsigned)groups, (unsigned)parts);
+    const size_t smem = fast_router_smem(tpw);
+    switch (tpw) {
+      case 1: launch_k(k_router_fast<1>, grid, dim3(128), smem, s, L->pdl, f); break;
+      case 2: launch_k(k_router_fast<2>, grid, dim3(128), smem, s, L->pdl, f); break;
+      case 4: launch_k(k_router_fast<4>, grid, dim3(128), smem, s, L->pdl, f); break;
+      case 8: launch_k(k_router_fast<8>, grid, dim3(128), smem, s, L->pdl, f); break;
+      default: launch_k(k_router_fast<16>, grid, dim3(128), smem, s, L->pdl, f); break;
+    }
+    FinishRouterArgs g{};
+    g.part = L->d_part;
+    g.hn2 = L->d_hn2;
+    g.bias = a.bias;
+    g.wnorm = L->d_wnorm;
+    g.router_out = d_router;
+    g.fb_list = L->d_fb_list;
+    g.fb_count = L->d_fb;
+    g.T = (int)T;
+    g.H = L->H;
+    g.E = L->E_router;
+    g.k = L->k;
+    g.sigmoid = L->cfg.sigmoid_gating;
+    g.parts = parts;
+    launch_k(k_router_finish, dim3((unsigned)T), dim3((unsigned)std::min(32 * groups, 256)), 0, s, L->pdl, g);
+  }
+  // ... and go through the order-faithful chain (a grid for a few percent of the tokens; its blocks
+  // walk the list however long it turned out, and leave at once when it is empty)
+  RouterArgs b = a;
+  b.token_list = L->d_fb_list;
+  b.n_list = L->d_fb;
+  b.fb_done = L->d_fb + 1;
+  b.fb_total = reinterpret_cast<unsigned long long*>(L->d_fb + 2);
+  const int slots = (int)std::min<int64_t>(T, std::max(1, 4 * L->sm_count / groups));
+  launch_router_logits<true>(b, L->d_wg_few, L->d_wg_many, L->sm_count, s, L->pdl, slots);
   CSK_CUDA(L, cudaGetLastError());
-  L->last.launches += 1;
+  L->last.launches += 3;
+  L->routed_tokens += T;
   return CSK_OK;
 }
 
 // histogram -> scan (+ row tiles of `tile_rows`) -> scatter rows as fp16 into x16
+constexpr int kOneBlockPairs = 8192;  // up to here histogram, scan and tile list are one single-block launch
+
+// place_only: no fp16 row buffer is written; the block that scans also places every pair
+// (row_of_pair, pair_of_row) and the streaming kernel gathers its token rows itself.
 int launch_permute(csk_moe_layer* L, const float* d_hidden, const float* d_router, int64_t T,
                    int only_expert, int tile_rows, int e_begin, int e_count, __half* x16, int ldx,
-                   int64_t max_rows, cudaStream_t s) {
+                   int64_t max_rows, cudaStream_t s, bool place_only = false) {
   const int n_pairs = (int)(T * L->k);
   const uint8_t* res = e_count ? L->d_resident : nullptr;
-  if (n_pairs <= 8192) {
+  if (place_only) {
+    if (n_pairs > kOneBlockPairs) return fail(L, CSK_ERR_INVALID, "internal: too many pairs for the one-block plan");
+    launch_k(k_scan, dim3(1), dim3(1024), 0, s, L->pdl, L->d_counts, L->E, e_begin, e_count, tile_rows, (int)max_rows,
+             L->max_tiles, res, L->d_offsets, L->d_cursor, L->d_tiles, L->d_meta, d_router, n_pairs, only_expert,
+             L->d_row_of_pair, L->d_pair_of_row);
+    CSK_CUDA(L, cudaGetLastError());
+    L->last.launches += 1;
+    return CSK_OK;
+  }
+  if (n_pairs <= kOneBlockPairs) {
     // small batch: histogram, scan and tile list in one single-block launch
     launch_k(k_scan, dim3(1), dim3(1024), 0, s, L->pdl, L->d_counts, L->E, e_begin, e_count, tile_rows, (int)max_rows,
-             L->max_tiles, res, L->d_offsets, L->d_cursor, L->d_tiles, L->d_meta, d_router, n_pairs, only_expert);
+             L->max_tiles, res, L->d_offsets, L->d_cursor, L->d_tiles, L->d_meta, d_router, n_pairs, only_expert,
+             (int*)nullptr, (int*)nullptr);
     L->last.launches += 1;
   } else {
     CSK_CUDA(L, cudaMemsetAsync(L->d_counts, 0, sizeof(int) * L->E, s));
@@ -187,7 +274,7 @@ int launch_permute(csk_moe_layer* L, const float* d_hidden, const float* d_route
     k_hist<<<grid_for(n_pairs, 256, 2 * L->sm_count), 256, sizeof(int) * L->E, s>>>(
         d_router, n_pairs, L->E, only_expert, L->d_counts, L->d_meta);
     k_scan<<<1, 1024, 0, s>>>(L->d_counts, L->E, e_begin, e_count, tile_rows, (int)max_rows, L->max_tiles, res,
-                              L->d_offsets, L->d_cursor, L->d_tiles, L->d_meta, nullptr, 0, -1);
+                              L->d_offsets, L->d_cursor, L->d_tiles, L->d_meta, nullptr, 0, -1, nullptr, nullptr);
     L->last.launches += 2;
   }
   launch_k(k_scatter, dim3(grid_for(n_pairs, 8, 8 * L->sm_count)), dim3(256), 0, s, L->pdl, d_router, d_hidden,
@@ -216,6 +303,12 @@ void launch_stream_pair(csk_moe_layer* L, const __half* x16, float* y, int ldy, 
   a.F = L->F;
   a.meta = L->d_meta;
   a.x_rows = x_rows;
+  a.gather_hidden = L->gather_hidden;  // set by the caller for this launch only (null: rows come from x16)
+  a.pair_of_row = L->d_pair_of_row;
+  a.router = L->gather_router;
+  a.top_k = L->k;
+  a.H = L->H;
+  a.weight_before_ffn = L->cfg.weight_before_ffn;
   // every CTA takes one contiguous range of work units; as many CTAs as fit at once
   const size_t per_sm_limit = W > 8 ? 2 : 3;
   auto grid_for_smem = [&](size_t smem) {
@@ -232,6 +325,7 @@ void launch_stream_pair(csk_moe_layer* L, const __half* x16, float* y, int ldy, 
   launch_k(k_stream<NT8, true, KSPLIT, W, NSTG>, dim3(grid_for_smem(smem)), dim3(W * 32), smem, s, L->pdl, a);
   tm.mark();
   // down
+  a.gather_hidden = nullptr;
   a.mat_offset = L->off_d;
   a.L = L->Ld;
   a.x = L->d_a16;
@@ -378,11 +472,17 @@ int forward_dev(csk_moe_layer* L, const float* d_hidden, int64_t T, const float*
   const int64_t rows = only_expert >= 0 ? T : T * L->k;
   const int path = choose_path(L, only_expert >= 0 ? rows * std::max(1, L->Eloc) : rows);
   const int tile_rows = tile_rows_for(L, path, only_expert >= 0 ? rows * std::max(1, L->Eloc) : rows);
+  if (reinterpret_cast<uintptr_t>(d_hidden) % 16) return fail(L, CSK_ERR_INVALID, "hidden states must be 16-byte aligned");
+  // small batches on the streaming kernel: no fp16 row buffer in between, the kernel gathers its rows
+  const bool gather = path == CSK_PATH_STREAM && T * L->k <= kOneBlockPairs;
   int rc = launch_permute(L, d_hidden, router, T, only_expert, tile_rows, L->e0, L->Eloc, L->d_x16,
-                          L->ldx, L->max_rows, s);
+                          L->ldx, L->max_rows, s, gather);
   if (rc) return rc;
   tm.mark();
+  L->gather_hidden = gather ? d_hidden : nullptr;
+  L->gather_router = router;
   rc = launch_experts(L, path, tile_rows, rows, T, L->d_x16, L->d_y, L->H, nullptr, s, tm);
+  L->gather_hidden = nullptr;
   if (rc) return rc;
   launch_k(k_combine, dim3((unsigned)T), dim3(256), 0, s, L->pdl, router, L->d_row_of_pair, (const float*)L->d_y, L->H,
            d_out, (int)T, L->k, L->H, (int)L->cfg.weight_before_ffn, (int)(only_expert >= 0));
@@ -515,6 +615,13 @@ int csk_moe_create(const csk_moe_config* cfg, csk_moe_layer** out) {
   CK(cudaMalloc(&L->d_route_cnt, sizeof(int) * L->max_T));
   CK(cudaMemset(L->d_route_cnt, 0, sizeof(int) * L->max_T));
   CK(cudaMalloc(&L->d_logits, sizeof(float) * L->max_T * L->E));
+  CK(cudaMalloc(&L->d_wnorm, sizeof(float) * L->E));
+  L->part_rows = L->max_T + 64 * (int64_t)(L->sm_count + fast_router_slices(L->H));
+  CK(cudaMalloc(&L->d_part, sizeof(float2) * L->part_rows * L->E));
+  CK(cudaMalloc(&L->d_hn2, sizeof(float) * L->part_rows));
+  CK(cudaMalloc(&L->d_fb_list, sizeof(int) * L->max_T));
+  CK(cudaMalloc(&L->d_fb, sizeof(int) * 4));
+  CK(cudaMemset(L->d_fb, 0, sizeof(int) * 4));
   CK(cudaMalloc(&L->d_rbias, sizeof(float) * L->E));
   CK(cudaMalloc(&L->d_hidden, sizeof(float) * L->max_T * L->H));
   CK(cudaMalloc(&L->d_router, sizeof(float) * L->max_T * L->k * 2));
@@ -533,6 +640,8 @@ int csk_moe_create(const csk_moe_config* cfg, csk_moe_layer** out) {
   CK(cudaMalloc(&L->d_offsets, sizeof(int) * (L->E + 1)));
   CK(cudaMalloc(&L->d_cursor, sizeof(int) * L->E));
   CK(cudaMalloc(&L->d_row_of_pair, sizeof(int) * L->max_rows));
+  CK(cudaMalloc(&L->d_pair_of_row, sizeof(int) * L->max_rows));
+  CK(cudaMemset(L->d_pair_of_row, 0, sizeof(int) * L->max_rows));
   CK(cudaMalloc(&L->d_out_row_map, sizeof(int) * L->max_rows));
   CK(cudaMalloc(&L->d_seg, sizeof(int) * (3 * 1024 + 8)));
   CK(cudaMalloc(&L->d_tiles, sizeof(RowTile) * L->max_tiles));
@@ -565,10 +674,10 @@ int csk_moe_destroy(csk_moe_layer* L) {
     if (g.exec) cudaGraphExecDestroy(g.exec);
   tile_destroy(L->tile);
   for (void* p : L->ipc_opened) cudaIpcCloseMemHandle(p);
-  void* dev[] = {L->d_info, L->d_back, L->d_row_ptr, L->d_p2p_base, L->d_peer_x16, L->d_peer_info, L->d_peer_back,
+  void* dev[] = {L->d_part, L->d_hn2, L->d_wnorm, L->d_fb_list, L->d_fb, L->d_info, L->d_back, L->d_row_ptr, L->d_p2p_base, L->d_peer_x16, L->d_peer_info, L->d_peer_back,
                  L->d_router_phys, L->d_slot_map, L->d_weights, L->d_resident, L->d_stage, L->d_wg, L->d_wg_few, L->d_wg_many, L->d_route_cnt, L->d_logits, L->d_rbias, L->d_hidden,
                  L->d_router, L->d_out, L->d_x16, L->d_a16, L->d_y, L->d_counts, L->d_offsets,
-                 L->d_cursor, L->d_row_of_pair, L->d_out_row_map, L->d_seg, L->d_tiles, L->d_meta};
+                 L->d_cursor, L->d_row_of_pair, L->d_pair_of_row, L->d_out_row_map, L->d_seg, L->d_tiles, L->d_meta};
   for (void* p : dev)
     if (p) cudaFree(p);
   if (L->h_meta) cudaFreeHost(L->h_meta);
@@ -590,6 +699,7 @@ int csk_moe_set_router(csk_moe_layer* L, const float* gate_w, const float* gate_
       L->d_wg, L->d_wg_few, L->E_router, L->H, kRouterChunkFew);
   k_pack_router<<<grid_for(router_packed_floats(L->E_router, L->H, kRouterChunkMany), 256, 1024), 256, 0, L->stream>>>(
       L->d_wg, L->d_wg_many, L->E_router, L->H, kRouterChunkMany);
+  k_router_wnorm<<<(L->E_router + 7) / 8, 256, 0, L->stream>>>(L->d_wg, L->d_wnorm, L->E_router, L->H);
   CSK_CUDA(L, cudaGetLastError());
   L->has_rbias = gate_bias != nullptr;
   if (gate_bias)
@@ -674,6 +784,24 @@ int csk_moe_set_path(csk_moe_layer* L, int32_t path) {
   if (path < CSK_PATH_AUTO || path > CSK_PATH_TILE) return fail(L, CSK_ERR_INVALID, "unknown path %d", path);
   L->path = path;
   drop_graphs(L);
+  return CSK_OK;
+}
+
+int csk_moe_set_router_mode(csk_moe_layer* L, int32_t mode) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  if (mode != CSK_ROUTER_CERTIFIED && mode != CSK_ROUTER_CHAIN) return fail(L, CSK_ERR_INVALID, "unknown router mode %d", mode);
+  L->router_mode = mode;
+  drop_graphs(L);
+  return CSK_OK;
+}
+
+int csk_moe_get_router_stats(csk_moe_layer* L, int64_t* routed_tokens, int64_t* chain_tokens) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  CSK_CUDA(L, cudaSetDevice(L->cfg.device));
+  unsigned long long fb = 0;
+  CSK_CUDA(L, cudaMemcpy(&fb, L->d_fb + 2, sizeof(fb), cudaMemcpyDeviceToHost));
+  if (routed_tokens) *routed_tokens = L->routed_tokens;
+  if (chain_tokens) *chain_tokens = (int64_t)fb;
   return CSK_OK;
 }
 
@@ -1151,7 +1279,7 @@ int csk_moe_ep_p2p_experts_dev(csk_moe_layer* L, const int32_t* d_all_counts, in
   // the status word of the dispatch stays; the tile list is rebuilt from the received counts
   k_ep_p2p_local_counts<<<(L->E + 255) / 256, 256, 0, s>>>(d_all_counts, L->p2p_world, L->E, L->e0, L->Eloc, L->d_counts);
   k_scan<<<1, 1024, 0, s>>>(L->d_counts, L->E, L->e0, L->Eloc, tile_rows, (int)L->max_rows, L->max_tiles,
-                            L->d_resident, L->d_offsets, L->d_cursor, L->d_tiles, L->d_meta, nullptr, 0, -1);
+                            L->d_resident, L->d_offsets, L->d_cursor, L->d_tiles, L->d_meta, nullptr, 0, -1, nullptr, nullptr);
   k_ep_p2p_rowptr<<<4 * L->sm_count, 256, 0, s>>>(L->d_info, L->d_meta, L->d_peer_back, L->H, L->d_row_ptr,
                                                   (int)L->max_rows, L->p2p_world, (int)L->max_rows);
   CSK_CUDA(L, cudaGetLastError());
@@ -1196,7 +1324,7 @@ int csk_moe_ep_experts_dev(csk_moe_layer* L, const void* d_recv_f16, const int32
   CSK_CUDA(L, cudaMemsetAsync(L->d_counts, 0, sizeof(int) * L->E, s));
   k_ep_plan<<<1, 1024, 0, s>>>(d_recv_counts, n_src, L->Eloc, L->e0, L->d_counts, L->d_seg);
   k_scan<<<1, 1024, 0, s>>>(L->d_counts, L->E, L->e0, L->Eloc, tile_rows, (int)L->max_rows, L->max_tiles,
-                            L->d_resident, L->d_offsets, L->d_cursor, L->d_tiles, L->d_meta, nullptr, 0, -1);
+                            L->d_resident, L->d_offsets, L->d_cursor, L->d_tiles, L->d_meta, nullptr, 0, -1, nullptr, nullptr);
   k_ep_regroup<<<dim3((unsigned)(n_src * L->Eloc), (unsigned)std::max(1, 16 * L->sm_count / (n_src * L->Eloc))), 128, 0, s>>>((const __half*)d_recv_f16, L->d_x16, L->ldx, L->d_seg,
                                                L->d_offsets, n_src, L->Eloc, L->e0, L->d_out_row_map);
   CSK_CUDA(L, cudaGetLastError());

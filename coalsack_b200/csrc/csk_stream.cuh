@@ -88,6 +88,13 @@ struct StreamArgs {
   int act;
   int F;                      // ffn dim (bias block: b_up[F], b_gate[F], b_down[H])
   int x_rows;                 // token rows staged per tile: >= the rows of every tile, <= 8*NT8
+  // GATED, optional: gather the tile's token rows straight from the layer's input instead of from x
+  // (row r of the grouped order is pair pair_of_row[r] = token * top_k + slot; fp32 -> fp16 on the way,
+  // times the pair's routing weight when that is applied before the expert)
+  const float* gather_hidden; // [T,H] fp32 or null
+  const int* pair_of_row;     // [rows]
+  const float* router;        // [T,k,2]
+  int top_k, H, weight_before_ffn;
 };
 
 constexpr int kStreamXPad = 32;      // halves: staggers consecutive token rows by 64 bytes in shared memory
@@ -176,26 +183,54 @@ __global__ void __launch_bounds__(W * 32, W > 8 ? 2 : 3) k_stream(const StreamAr
   for (long u = u_begin; u < u_end; ++u) {
     const int tile_i = (int)(u / units_per_tile);
     const int uq = (int)(u % units_per_tile);
-    if (tile_i != cur_tile) {
-      // bring the tile's token rows into shared memory
-      __syncthreads();
-      rt = A.tiles[tile_i];
-      cur_tile = tile_i;
-      const int w16 = L.k_pad() / 8;
-      const int n_rows = min(rt.rows, x_rows);
-      for (int i = threadIdx.x; i < n_rows * w16; i += W * 32) {
-        const int r = i / w16, c = (i % w16) * 8;
-        const __half* src = A.x + (size_t)(rt.row0 + r) * A.ldx + c;
-        const uint32_t dst = xs_u32 + (uint32_t)(r * ldxs + c) * 2;
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-      }
-      asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
-      __syncthreads();
-    }
+    const bool new_tile = tile_i != cur_tile;
+    if (new_tile) rt = A.tiles[tile_i];
     const int grp = KSPLIT == 1 ? uq * W + warp : uq;
     const bool active = grp < groups;
     const uint8_t* wsrc =
         A.weights + (size_t)rt.expert * A.expert_stride + A.mat_offset + (size_t)grp * group_bytes;
+    // lane 0 is this warp's producer: ring stage st <- stage i of the group's stream.  The first
+    // stages are requested before the tile's token rows are staged, so both are in flight together.
+    auto fill = [&](int st, int i) {
+      const uint32_t bar = bar_u32 + 8u * st;
+      const size_t off = (size_t)i * SB;
+      const uint32_t bytes = (uint32_t)min((size_t)SB, group_bytes - off);
+      mbar_expect_tx(bar, bytes);
+      bulk_load(ring_u32 + (uint32_t)st * SB, wsrc + off, bytes, bar);
+    };
+    if (active && sb < se && lane == 0)
+      for (int i = 0; i < NSTG && sb + i < se; ++i) fill(i, sb + i);
+    if (new_tile) {
+      // bring the tile's token rows into shared memory
+      __syncthreads();
+      cur_tile = tile_i;
+      const int n_rows = min(rt.rows, x_rows);
+      if (GATED && A.gather_hidden) {
+        const int w4 = L.k_pad() / 4;
+        for (int i = threadIdx.x; i < n_rows * w4; i += W * 32) {
+          const int r = i / w4, c = (i % w4) * 4;
+          const int pair = A.pair_of_row[rt.row0 + r];
+          float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (c < A.H) v = __ldg(reinterpret_cast<const float4*>(A.gather_hidden + (size_t)(pair / A.top_k) * A.H + c));
+          const float mul = A.weight_before_ffn ? A.router[2 * (size_t)pair + 1] : 1.0f;
+          const __half2 lo = __floats2half2_rn(v.x * mul, v.y * mul), hi = __floats2half2_rn(v.z * mul, v.w * mul);
+          uint2 o;
+          o.x = *reinterpret_cast<const uint32_t*>(&lo);
+          o.y = *reinterpret_cast<const uint32_t*>(&hi);
+          *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(xs) + (size_t)(r * ldxs + c) * 2) = o;
+        }
+      } else {
+        const int w16 = L.k_pad() / 8;
+        for (int i = threadIdx.x; i < n_rows * w16; i += W * 32) {
+          const int r = i / w16, c = (i % w16) * 8;
+          const __half* src = A.x + (size_t)(rt.row0 + r) * A.ldx + c;
+          const uint32_t dst = xs_u32 + (uint32_t)(r * ldxs + c) * 2;
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+        }
+        asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+      }
+      __syncthreads();
+    }
 
     float acc[NACC][NT8][4];
 #pragma unroll
@@ -206,16 +241,6 @@ __global__ void __launch_bounds__(W * 32, W > 8 ? 2 : 3) k_stream(const StreamAr
         for (int c = 0; c < 4; ++c) acc[m][j][c] = 0.f;
 
     if (active && sb < se) {
-      // lane 0 is this warp's producer: ring stage st <- stage i of the group's stream
-      auto fill = [&](int st, int i) {
-        const uint32_t bar = bar_u32 + 8u * st;
-        const size_t off = (size_t)i * SB;
-        const uint32_t bytes = (uint32_t)min((size_t)SB, group_bytes - off);
-        mbar_expect_tx(bar, bytes);
-        bulk_load(ring_u32 + (uint32_t)st * SB, wsrc + off, bytes, bar);
-      };
-      if (lane == 0)
-        for (int i = 0; i < NSTG && sb + i < se; ++i) fill(i, sb + i);
       __syncwarp();
 
       for (int i0 = sb; i0 < se; i0 += NSTG) {

@@ -243,6 +243,17 @@ class MoeLayer:
     def set_path(self, path):
         self._check(self._lib.csk_moe_set_path(self._h, path))
 
+    ROUTER_CERTIFIED, ROUTER_CHAIN = 0, 1
+
+    def set_router_mode(self, mode):
+        self._check(self._lib.csk_moe_set_router_mode(self._h, int(mode)))
+
+    def router_stats(self):
+        """(tokens routed in certified mode, tokens of those recomputed by the chain)."""
+        a, b = C.c_int64(0), C.c_int64(0)
+        self._check(self._lib.csk_moe_get_router_stats(self._h, C.byref(a), C.byref(b)))
+        return a.value, b.value
+
     DEBUG_WAIT_BUDGET, DEBUG_STALL_TILE_PRODUCER = 0, 1
 
     def debug_set(self, key, value):

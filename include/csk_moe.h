@@ -262,6 +262,21 @@ int csk_moe_ep_p2p_combine_dev(csk_moe_layer* layer, int64_t T, float* d_out, fl
 /* ---- knobs and observability ------------------------------------------- */
 int csk_moe_set_path(csk_moe_layer* layer, int32_t path /* CSK_PATH_* */);
 
+/* How the router reaches the reference's selection (moe_router_node.h:161-177: each
+ * logit a sequential fp32 multiply-then-add chain over the hidden dimension, top-k by
+ * logit).  Both modes return the same expert indices as the reference, bit for bit.
+ *   CSK_ROUTER_CERTIFIED (default): logits by fused multiply-adds in 32-column blocks
+ *     with a rigorous bound on their distance from the chain's value; a token whose k+1
+ *     best logits are further apart than the bounds keeps that selection, any other
+ *     token is recomputed by the chain.  Routing WEIGHTS of certified tokens come from
+ *     the fast logits and differ from the reference's by a few ulp (below 1e-6).
+ *   CSK_ROUTER_CHAIN: every logit by the reference's own chain. */
+enum { CSK_ROUTER_CERTIFIED = 0, CSK_ROUTER_CHAIN = 1 };
+int csk_moe_set_router_mode(csk_moe_layer* layer, int32_t mode);
+/* Tokens routed in certified mode since the handle was created, and how many of them
+ * had to be recomputed by the chain (waits for the device). */
+int csk_moe_get_router_stats(csk_moe_layer* layer, int64_t* routed_tokens, int64_t* chain_tokens);
+
 /* Device time of the stages of the last forward call on this handle, in
  * milliseconds (CUDA events on the stream the kernels ran on).  Collection is
  * off by default; csk_moe_enable_timing(layer, 1) turns it on. */

@@ -37,9 +37,12 @@ int main(int argc, char** argv) {
   dynamic_tensor rb(dtype::float32, {E}, take(sizeof(float) * E));
   const size_t wbytes = (size_t)H * F / 32 * 17;
 
+  const bool verbose = argc > 3;
   moe_router_node router;
   router.set_config(E, k);
+  if (verbose) std::fprintf(stderr, "router ...\n");
   dynamic_tensor ro = router.compute_test(hidden, Wg, rb);
+  if (verbose) std::fprintf(stderr, "router done\n");
 
   std::vector<dynamic_tensor> merge_in = {ro};
   for (int e = 0; e < E; ++e) {
@@ -68,6 +71,7 @@ int main(int argc, char** argv) {
     f["router"] = std::make_shared<dynamic_tensor_message>(ro);
     auto msg = result_message::ok(f);
     msg->set_frame_number(3);
+    if (verbose) std::fprintf(stderr, "expert %d ...\n", e);
     node->process("default", msg);
     auto res = std::dynamic_pointer_cast<result_message>(sink->last);
     if (!res || !res->is_ok()) {
@@ -76,6 +80,7 @@ int main(int argc, char** argv) {
     }
     merge_in.push_back(std::dynamic_pointer_cast<dynamic_tensor_message>(res->get_field("y"))->get_tensor());
   }
+  if (verbose) std::fprintf(stderr, "merge ...\n");
   expert_merge_node merge;
   merge.set_config(E, k);
   dynamic_tensor out = merge.compute_test(merge_in);
