@@ -370,7 +370,8 @@ def run_ours(args):
             "gpu_launches": int(stage["launches"]) * args.steps, "path": stage["path"], "roofline": roofline}
     if e2e_ms is not None:
         line["e2e"] = {"value": total / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
-                       "h2d_bytes_per_step": T * H * 4 * world, "d2h_bytes_per_step": T * H * 4 * world}
+                       "h2d_bytes_per_step": T * H * 4 * world,
+                       "d2h_bytes_per_step": (T * H * 4 + (T * k * 2 * 4 if world == 1 else 0)) * world}
     if world > 1:
         line["config"]["tokens_per_gpu"] = T
         line["config"]["exchange"] = runner.exchange
@@ -403,6 +404,7 @@ class SingleGpu:
         h = synth.hidden_states(sh)
         self.h_host = torch.from_numpy(h).pin_memory()
         self.out_host = torch.empty_like(self.h_host).pin_memory()
+        self.ro_host = torch.empty((sh.tokens, sh.top_k, 2), dtype=torch.float32).pin_memory()
         self.d_hidden = self.h_host.to(dev)
         self.d_out = torch.empty_like(self.d_hidden)
         self.torch_stream = torch.cuda.Stream(device=dev)
@@ -435,10 +437,10 @@ class SingleGpu:
 
     def time_e2e(self, steps, warmup):
         for _ in range(warmup):
-            self.layer.forward(self.h_host, out=self.out_host)
+            self.layer.forward(self.h_host, out=self.out_host, router_out_buf=self.ro_host)
         t0 = time.perf_counter()
         for _ in range(steps):
-            self.layer.forward(self.h_host, out=self.out_host)
+            self.layer.forward(self.h_host, out=self.out_host, router_out_buf=self.ro_host)
         return (time.perf_counter() - t0) * 1e3 / steps
 
 

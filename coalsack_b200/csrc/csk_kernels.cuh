@@ -1038,12 +1038,22 @@ __global__ void k_scatter(const float* __restrict__ router_out, const float* __r
 // dense single-expert output of expert_mlp_node (expert_mlp_node.h:503-529):
 // the token's row unweighted, or zeros.
 // ---------------------------------------------------------------------------
+//
+// carry (optional; the host entry point that runs a batch in several passes): block 0 folds this
+// pass's status word into a sticky one and adds its per-expert row counts to running totals --
+// layout: carry[0] = sticky status, carry[1 .. E] = rows per expert.
 __global__ void k_combine(const float* __restrict__ router_out, const int* __restrict__ row_of_pair,
                           const float* __restrict__ y, int ldy, float* __restrict__ out, int T,
-                          int k, int H, int unweighted, int dense_single) {
+                          int k, int H, int unweighted, int dense_single,
+                          const int* __restrict__ meta = nullptr, const int* __restrict__ counts = nullptr,
+                          int* __restrict__ carry = nullptr, int E = 0) {
   const int t = blockIdx.x;
   griddep_wait();
   griddep_launch();
+  if (carry && t == 0) {
+    if (threadIdx.x == 0 && meta[3]) atomicOr(&carry[0], meta[3]);
+    for (int e = threadIdx.x; e < E; e += blockDim.x) carry[1 + e] += counts[e];
+  }
   if (t >= T) return;
   for (int d = threadIdx.x * 4; d < H; d += blockDim.x * 4) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);

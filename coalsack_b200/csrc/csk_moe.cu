@@ -88,6 +88,13 @@ struct csk_moe_layer {
   int64_t* h_counts64 = nullptr;
 
   cudaStream_t stream = nullptr;
+  // the host entry point's pipeline: copy-in and copy-out streams beside `stream`, one event pair per pass
+  cudaStream_t stream_in = nullptr, stream_out = nullptr;
+  static constexpr int kMaxPasses = 8;
+  cudaEvent_t ev_in[kMaxPasses]{}, ev_done[kMaxPasses]{}, ev_free = nullptr;
+  int* d_carry = nullptr;      // [1 + E]: sticky status and per-expert row totals over the passes of one call
+  bool carry_active = false;   // the combine kernel folds each pass into d_carry
+  bool counts_in_carry = false;  // the last call's counters are the totals in d_carry
   cudaEvent_t ev[8]{};
   bool timing = false;
   csk_moe_timings last{};
@@ -409,10 +416,16 @@ int launch_experts(csk_moe_layer* L, int path, int tile_rows, int64_t n_rows_hin
   return CSK_OK;
 }
 
+int report_status(csk_moe_layer* L, int st, cudaStream_t s);
+
 int check_device_status(csk_moe_layer* L, cudaStream_t s) {
   CSK_CUDA(L, cudaMemcpyAsync(L->h_meta, L->d_meta, sizeof(int) * 16, cudaMemcpyDeviceToHost, s));
   CSK_CUDA(L, cudaStreamSynchronize(s));
-  const int st = L->h_meta[3] | L->h_meta[8];
+  return report_status(L, L->h_meta[3] | L->h_meta[8], s);
+}
+
+// The host's view of a status word (h_meta holds the copy it came from).
+int report_status(csk_moe_layer* L, int st, cudaStream_t s) {
   if (L->h_meta[8]) cudaMemsetAsync(L->d_meta + 8, 0, sizeof(int), s);
   if (st & kDevErrExpertRange)
     return fail(L, CSK_ERR_INVALID, "expert_idx out of range in router output");
@@ -450,6 +463,7 @@ int forward_dev(csk_moe_layer* L, const float* d_hidden, int64_t T, const float*
     return fail(L, CSK_ERR_INVALID, "the layer has an expert-parallel slot map: use the csk_moe_ep_* stages");
   L->last = csk_moe_timings{};
   L->last_T = T;
+  if (!L->carry_active) L->counts_in_carry = false;
   // small batches are launch-bound: let each kernel become resident while its predecessor drains
   struct PdlScope {
     csk_moe_layer* l;
@@ -461,14 +475,16 @@ int forward_dev(csk_moe_layer* L, const float* d_hidden, int64_t T, const float*
   const float* router = d_router_in;
   const bool routed = d_router_in == nullptr;
   if (routed) {
-    int rc = launch_router(L, d_hidden, T, L->d_router, s);
+    // the routing is written where the caller wants it (else into the handle's buffer) and read from there
+    float* route_to = d_router_out ? d_router_out : L->d_router;
+    int rc = launch_router(L, d_hidden, T, route_to, s);
     if (rc) return rc;
-    router = L->d_router;
+    router = route_to;
     tm.mark();
-  }
-  if (d_router_out && d_router_out != router)
+  } else if (d_router_out && d_router_out != router) {
     CSK_CUDA(L, cudaMemcpyAsync(d_router_out, router, sizeof(float) * T * L->k * 2,
                                 cudaMemcpyDeviceToDevice, s));
+  }
   const int64_t rows = only_expert >= 0 ? T : T * L->k;
   const int path = choose_path(L, only_expert >= 0 ? rows * std::max(1, L->Eloc) : rows);
   const int tile_rows = tile_rows_for(L, path, only_expert >= 0 ? rows * std::max(1, L->Eloc) : rows);
@@ -485,7 +501,8 @@ int forward_dev(csk_moe_layer* L, const float* d_hidden, int64_t T, const float*
   L->gather_hidden = nullptr;
   if (rc) return rc;
   launch_k(k_combine, dim3((unsigned)T), dim3(256), 0, s, L->pdl, router, L->d_row_of_pair, (const float*)L->d_y, L->H,
-           d_out, (int)T, L->k, L->H, (int)L->cfg.weight_before_ffn, (int)(only_expert >= 0));
+           d_out, (int)T, L->k, L->H, (int)L->cfg.weight_before_ffn, (int)(only_expert >= 0), (const int*)L->d_meta,
+           (const int*)L->d_counts, L->carry_active ? L->d_carry : (int*)nullptr, L->E);
   CSK_CUDA(L, cudaGetLastError());
   L->last.launches++;
   tm.mark();
@@ -602,7 +619,14 @@ int csk_moe_create(const csk_moe_config* cfg, csk_moe_layer** out) {
   CK(cudaGetDeviceProperties(&prop, cfg->device));
   L->sm_count = prop.multiProcessorCount;
   CK(cudaStreamCreateWithFlags(&L->stream, cudaStreamNonBlocking));
+  CK(cudaStreamCreateWithFlags(&L->stream_in, cudaStreamNonBlocking));
+  CK(cudaStreamCreateWithFlags(&L->stream_out, cudaStreamNonBlocking));
   for (auto& e : L->ev) CK(cudaEventCreate(&e));
+  for (auto& e : L->ev_in) CK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+  for (auto& e : L->ev_done) CK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+  CK(cudaEventCreateWithFlags(&L->ev_free, cudaEventDisableTiming));
+  CK(cudaMalloc(&L->d_carry, sizeof(int) * (1 + L->E)));
+  CK(cudaMemset(L->d_carry, 0, sizeof(int) * (1 + L->E)));
   CK(cudaMalloc(&L->d_weights, L->expert_stride * eloc));
   CK(cudaMemset(L->d_weights, 0, L->expert_stride * eloc));
   CK(cudaMalloc(&L->d_resident, eloc));
@@ -684,6 +708,14 @@ int csk_moe_destroy(csk_moe_layer* L) {
   if (L->h_counts64) cudaFreeHost(L->h_counts64);
   for (auto& e : L->ev)
     if (e) cudaEventDestroy(e);
+  for (auto& e : L->ev_in)
+    if (e) cudaEventDestroy(e);
+  for (auto& e : L->ev_done)
+    if (e) cudaEventDestroy(e);
+  if (L->ev_free) cudaEventDestroy(L->ev_free);
+  if (L->d_carry) cudaFree(L->d_carry);
+  if (L->stream_in) cudaStreamDestroy(L->stream_in);
+  if (L->stream_out) cudaStreamDestroy(L->stream_out);
   if (L->stream) cudaStreamDestroy(L->stream);
   delete L;
   return CSK_OK;
@@ -831,7 +863,8 @@ int csk_moe_get_counters(csk_moe_layer* L, int64_t* rows_per_expert, int64_t* di
   if (check_layer(L)) return CSK_ERR_INVALID;
   CSK_CUDA(L, cudaSetDevice(L->cfg.device));
   std::vector<int> c(L->E);
-  CSK_CUDA(L, cudaMemcpy(c.data(), L->d_counts, sizeof(int) * L->E, cudaMemcpyDeviceToHost));
+  CSK_CUDA(L, cudaMemcpy(c.data(), L->counts_in_carry ? L->d_carry + 1 : L->d_counts, sizeof(int) * L->E,
+                         cudaMemcpyDeviceToHost));
   int64_t d = 0;
   for (int e = 0; e < L->E; ++e) {
     if (rows_per_expert) rows_per_expert[e] = c[e];
@@ -927,6 +960,18 @@ int csk_moe_route(csk_moe_layer* L, const float* hidden, int64_t T, float* route
   return CSK_OK;
 }
 
+namespace {
+// How many passes the host entry point cuts a batch into so that the copies of one pass overlap
+// the kernels of another: as many as leave every expert about 128 rows per pass (the tensor-core
+// kernel's cost per row tile is nearly flat below that), at most two (measured: four passes cost more
+// in kernel time than they hide in copies); small batches take one.
+int host_passes(const csk_moe_layer* L, int64_t T) {
+  if (L->timing || L->path == CSK_PATH_STREAM) return 1;
+  const int64_t rows_per_expert = T * L->k / std::max(1, L->Eloc);
+  return (int)std::max<int64_t>(1, std::min<int64_t>(2, rows_per_expert / 128));
+}
+}  // namespace
+
 int csk_moe_forward(csk_moe_layer* L, const float* hidden, int64_t T, const float* router_in,
                     float* router_out, float* out) {
   if (check_layer(L)) return CSK_ERR_INVALID;
@@ -934,19 +979,68 @@ int csk_moe_forward(csk_moe_layer* L, const float* hidden, int64_t T, const floa
   if (T <= 0 || T > L->max_T) return fail(L, CSK_ERR_NOMEM, "T=%lld outside (0, max_tokens]", (long long)T);
   CSK_CUDA(L, cudaSetDevice(L->cfg.device));
   cudaStream_t s = L->stream;
-  CSK_CUDA(L, cudaMemcpyAsync(L->d_hidden, hidden, sizeof(float) * T * L->H, cudaMemcpyHostToDevice, s));
-  if (router_in)
-    CSK_CUDA(L, cudaMemcpyAsync(L->d_router, router_in, sizeof(float) * T * L->k * 2, cudaMemcpyHostToDevice, s));
-  int rc = csk_moe_forward_dev(L, L->d_hidden, T, router_in ? L->d_router : nullptr, nullptr, L->d_out, s);
+  const int passes = host_passes(L, T);
+  if (passes == 1) {
+    CSK_CUDA(L, cudaMemcpyAsync(L->d_hidden, hidden, sizeof(float) * T * L->H, cudaMemcpyHostToDevice, s));
+    if (router_in)
+      CSK_CUDA(L, cudaMemcpyAsync(L->d_router, router_in, sizeof(float) * T * L->k * 2, cudaMemcpyHostToDevice, s));
+    int rc = csk_moe_forward_dev(L, L->d_hidden, T, router_in ? L->d_router : nullptr, nullptr, L->d_out, s);
+    if (rc) return rc;
+    rc = check_device_status(L, s);
+    if (rc) return rc;
+    if (L->timing && L->n_marks > 1) finish_timings(L, L->n_marks, L->last_routed);
+    CSK_CUDA(L, cudaMemcpyAsync(out, L->d_out, sizeof(float) * T * L->H, cudaMemcpyDeviceToHost, s));
+    if (router_out)
+      CSK_CUDA(L, cudaMemcpyAsync(router_out, L->d_router, sizeof(float) * T * L->k * 2, cudaMemcpyDeviceToHost, s));
+    CSK_CUDA(L, cudaStreamSynchronize(s));
+    return CSK_OK;
+  }
+  // Several passes over token ranges, three streams: the rows of pass i+1 arrive and the results of
+  // pass i-1 leave while the kernels of pass i run (tokens are independent, so the passes give the
+  // same rows as one pass would).  One cudaMemcpyAsync per range and direction.  The status word of
+  // every pass is folded into a sticky one that is read once, at the end.
+  CSK_CUDA(L, cudaMemsetAsync(L->d_carry, 0, sizeof(int) * (1 + L->E), s));
+  CSK_CUDA(L, cudaEventRecord(L->ev_free, s));  // earlier work on this handle is done before the copies overwrite d_hidden
+  CSK_CUDA(L, cudaStreamWaitEvent(L->stream_in, L->ev_free, 0));
+  struct CarryScope {
+    csk_moe_layer* l;
+    ~CarryScope() { l->carry_active = false; }
+  } carry_scope{L};
+  L->carry_active = true;
+  const int k2 = L->k * 2;
+  int rc = CSK_OK;
+  for (int p = 0; p < passes && !rc; ++p) {
+    const int64_t t0 = T * p / passes, t1 = T * (p + 1) / passes, n = t1 - t0;
+
+    CSK_CUDA(L, cudaMemcpyAsync(L->d_hidden + t0 * L->H, hidden + t0 * L->H, sizeof(float) * n * L->H,
+                                cudaMemcpyHostToDevice, L->stream_in));
+    if (router_in)
+      CSK_CUDA(L, cudaMemcpyAsync(L->d_router + t0 * k2, router_in + t0 * k2, sizeof(float) * n * k2,
+                                  cudaMemcpyHostToDevice, L->stream_in));
+    CSK_CUDA(L, cudaEventRecord(L->ev_in[p], L->stream_in));
+    CSK_CUDA(L, cudaStreamWaitEvent(s, L->ev_in[p], 0));
+    // the router writes the pass's routing to its place in d_router (kept for router_out and for the counters)
+    rc = forward_dev(L, L->d_hidden + t0 * L->H, n, router_in ? L->d_router + t0 * k2 : nullptr,
+                     router_in ? nullptr : L->d_router + t0 * k2, L->d_out + t0 * L->H, -1, s, false);
+    if (rc) break;
+    CSK_CUDA(L, cudaEventRecord(L->ev_done[p], s));
+    CSK_CUDA(L, cudaStreamWaitEvent(L->stream_out, L->ev_done[p], 0));
+    CSK_CUDA(L, cudaMemcpyAsync(out + t0 * L->H, L->d_out + t0 * L->H, sizeof(float) * n * L->H,
+                                cudaMemcpyDeviceToHost, L->stream_out));
+    if (router_out)
+      CSK_CUDA(L, cudaMemcpyAsync(router_out + t0 * k2, L->d_router + t0 * k2, sizeof(float) * n * k2,
+                                  cudaMemcpyDeviceToHost, L->stream_out));
+  }
+  L->counts_in_carry = true;
+  L->last_T = T;
+  // the sticky status word travels with the last results
+  cudaMemcpyAsync(L->h_meta, L->d_meta, sizeof(int) * 16, cudaMemcpyDeviceToHost, L->stream_out);
+  cudaMemcpyAsync(L->h_meta + 3, L->d_carry, sizeof(int), cudaMemcpyDeviceToHost, L->stream_out);
+  cudaError_t e1 = cudaStreamSynchronize(L->stream_in), e2 = cudaStreamSynchronize(s), e3 = cudaStreamSynchronize(L->stream_out);
   if (rc) return rc;
-  rc = check_device_status(L, s);
-  if (rc) return rc;
-  if (L->timing && L->n_marks > 1) finish_timings(L, L->n_marks, L->last_routed);
-  CSK_CUDA(L, cudaMemcpyAsync(out, L->d_out, sizeof(float) * T * L->H, cudaMemcpyDeviceToHost, s));
-  if (router_out)
-    CSK_CUDA(L, cudaMemcpyAsync(router_out, L->d_router, sizeof(float) * T * L->k * 2, cudaMemcpyDeviceToHost, s));
-  CSK_CUDA(L, cudaStreamSynchronize(s));
-  return CSK_OK;
+  if (e1 != cudaSuccess || e2 != cudaSuccess || e3 != cudaSuccess)
+    return fail(L, CSK_ERR_CUDA, "pipelined forward: %s", cudaGetErrorString(e1 != cudaSuccess ? e1 : e2 != cudaSuccess ? e2 : e3));
+  return report_status(L, L->h_meta[3] | L->h_meta[8], s);
 }
 
 int csk_moe_expert_forward(csk_moe_layer* L, int32_t expert_id, const float* hidden, int64_t T,
@@ -1002,7 +1096,7 @@ int csk_moe_merge(csk_moe_layer* L, const float* router_out, int64_t T, const fl
   CSK_CUDA(L, cudaMemcpyAsync(L->d_row_of_pair, rows.data(), sizeof(int) * rows.size(), cudaMemcpyHostToDevice, s));
   CSK_CUDA(L, cudaMemcpyAsync(L->d_router, router_out, sizeof(float) * T * L->k * 2, cudaMemcpyHostToDevice, s));
   k_combine<<<(unsigned)T, 256, 0, s>>>(L->d_router, L->d_row_of_pair, L->d_y, L->H, L->d_out, (int)T,
-                                        L->k, L->H, L->cfg.weight_before_ffn, 0);
+                                        L->k, L->H, L->cfg.weight_before_ffn, 0, nullptr, nullptr, nullptr, 0);
   CSK_CUDA(L, cudaGetLastError());
   CSK_CUDA(L, cudaMemcpyAsync(out, L->d_out, sizeof(float) * T * L->H, cudaMemcpyDeviceToHost, s));
   CSK_CUDA(L, cudaStreamSynchronize(s));
@@ -1354,7 +1448,7 @@ int csk_moe_ep_combine_dev(csk_moe_layer* L, const float* d_back, int64_t T, flo
   CSK_CUDA(L, cudaSetDevice(L->cfg.device));
   cudaStream_t s = pick(L, stream);
   k_combine<<<(unsigned)T, 256, 0, s>>>(L->d_router, L->d_row_of_pair, d_back, L->H, d_out, (int)T, L->k,
-                                        L->H, L->cfg.weight_before_ffn, 0);
+                                        L->H, L->cfg.weight_before_ffn, 0, nullptr, nullptr, nullptr, 0);
   CSK_CUDA(L, cudaGetLastError());
   if (d_router_out)
     CSK_CUDA(L, cudaMemcpyAsync(d_router_out, L->d_router, sizeof(float) * T * L->k * 2,

@@ -112,7 +112,11 @@ int csk_moe_route(csk_moe_layer* layer, const float* hidden, int64_t T, float* r
  * -> grouped MXFP4 gated MLP -> weighted combine in router order.  Equals
  * moe_router_node + moe_weight_fetch_node + E x expert_mlp_node +
  * expert_merge_node (src/llm/llm_engine.cpp:721-753).  router_out_out
- * (optional) receives the routing actually used.  out is [T,H]. */
+ * (optional) receives the routing actually used.  out is [T,H].
+ * Large batches run as two passes over token ranges on three streams, so that
+ * one range's copies overlap the other's kernels (same results: tokens are
+ * independent); that only helps when the host buffers are page-locked --
+ * copies from or to pageable memory block the calling thread. */
 int csk_moe_forward(csk_moe_layer* layer, const float* hidden, int64_t T,
                     const float* router_out_in, float* router_out_out, float* out);
 
