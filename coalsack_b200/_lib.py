@@ -35,6 +35,9 @@ SYMBOLS = {
     "csk_moe_device_ok": (C.c_int, [C.c_int]),
     "csk_moe_set_router": (C.c_int, [_vp, _vp, _vp]),
     "csk_moe_load_expert_mxfp4": (C.c_int, [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "csk_moe_load_experts_mxfp4": (C.c_int, [_vp, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "csk_moe_save_image": (C.c_int, [_vp, C.c_char_p]),
+    "csk_moe_load_image": (C.c_int, [_vp, C.c_char_p]),
     "csk_moe_unpack_expert_mxfp4": (C.c_int, [_vp, _i32, _i32, _vp]),
     "csk_moe_expert_resident": (C.c_int, [_vp, _i32]),
     "csk_moe_route": (C.c_int, [_vp, _vp, _i64, _vp]),
@@ -44,6 +47,9 @@ SYMBOLS = {
     "csk_moe_route_dev": (C.c_int, [_vp, _vp, _i64, _vp, _vp]),
     "csk_moe_forward_dev": (C.c_int, [_vp, _vp, _i64, _vp, _vp, _vp, _vp]),
     "csk_moe_sync": (C.c_int, [_vp]),
+    "csk_moe_set_ffn_norm": (C.c_int, [_vp, _vp, C.c_float]),
+    "csk_moe_block_forward": (C.c_int, [_vp, _vp, _i64, _vp, _vp]),
+    "csk_moe_block_forward_dev": (C.c_int, [_vp, _vp, _i64, _vp, _vp, _vp]),
     "csk_moe_route_static": (C.c_int, [_vp, _i64, _i32, _vp, _vp, _i32, _i32, _i32, _vp, _vp]),
     "csk_moe_route_static_status": (C.c_int, []),
     "csk_moe_debug_set": (C.c_int, [_vp, _i32, _i64]),
@@ -56,11 +62,13 @@ SYMBOLS = {
     "csk_moe_ep_p2p_import": (C.c_int, [_vp, _i32, _i32, _vp]),
     "csk_moe_ep_p2p_local_ptrs": (C.c_int, [_vp, _vp, _vp, _vp]),
     "csk_moe_ep_p2p_import_ptrs": (C.c_int, [_vp, _i32, _i32, _vp, _vp, _vp]),
+    "csk_moe_ep_p2p_sync_dev": (C.c_int, [_vp, _i32, _vp, _vp, _vp]),
     "csk_moe_ep_p2p_counts_dev": (C.c_int, [_vp, _vp, _i64, _vp, _vp, _vp]),
     "csk_moe_ep_p2p_scatter_dev": (C.c_int, [_vp, _vp, _i64, _vp, _vp]),
     "csk_moe_ep_p2p_experts_dev": (C.c_int, [_vp, _vp, _i64, _vp]),
     "csk_moe_ep_p2p_combine_dev": (C.c_int, [_vp, _i64, _vp, _vp, _vp]),
     "csk_moe_set_path": (C.c_int, [_vp, _i32]),
+    "csk_moe_set_activation": (C.c_int, [_vp, _i32, _i32]),
     "csk_moe_set_router_mode": (C.c_int, [_vp, _i32]),
     "csk_moe_get_router_stats": (C.c_int, [_vp, _vp, _vp]),
     "csk_moe_enable_timing": (C.c_int, [_vp, _i32]),

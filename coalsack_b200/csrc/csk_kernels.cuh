@@ -1046,7 +1046,7 @@ __global__ void k_combine(const float* __restrict__ router_out, const int* __res
                           const float* __restrict__ y, int ldy, float* __restrict__ out, int T,
                           int k, int H, int unweighted, int dense_single,
                           const int* __restrict__ meta = nullptr, const int* __restrict__ counts = nullptr,
-                          int* __restrict__ carry = nullptr, int E = 0) {
+                          int* __restrict__ carry = nullptr, int E = 0, const float* __restrict__ residual = nullptr) {
   const int t = blockIdx.x;
   griddep_wait();
   griddep_launch();
@@ -1078,7 +1078,56 @@ __global__ void k_combine(const float* __restrict__ router_out, const int* __res
         acc.w = __fadd_rn(acc.w, __fmul_rn(w, v.w));
       }
     }
+    if (residual) {
+      // the residual connection around the layer: add(residual, merge output), llm_engine.cpp:773-777
+      const float4 r = *reinterpret_cast<const float4*>(residual + (size_t)t * H + d);
+      acc.x = __fadd_rn(r.x, acc.x);
+      acc.y = __fadd_rn(r.y, acc.y);
+      acc.z = __fadd_rn(r.z, acc.z);
+      acc.w = __fadd_rn(r.w, acc.w);
+    }
     *reinterpret_cast<float4*>(out + (size_t)t * H + d) = acc;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// RMSNorm in front of the router (rmsnorm_node::compute_impl, rmsnorm_node.h:60-82):
+// out = (x / sqrt(sum(x^2) / H + eps)) * w.  The router's expert indices must equal the
+// reference's bit for bit, so its INPUT must too: the sum of squares is the reference's
+// sequential fp32 chain of separate multiplies and adds (one lane walks the row, staged in
+// shared memory by the whole warp), division, square root and products are the IEEE
+// round-to-nearest operations the reference's scalar code performs.  One warp per token.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) k_rmsnorm(const float* __restrict__ x, const float* __restrict__ w, float eps,
+                                                 float* __restrict__ out, int T, int H) {
+  extern __shared__ __align__(16) float rms_rows[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
+  float* row = rms_rows + (size_t)warp * H;
+  griddep_wait();
+  griddep_launch();
+  for (int t = blockIdx.x * wpb + warp; t < T; t += gridDim.x * wpb) {
+    const float* src = x + (size_t)t * H;
+    for (int d = lane * 4; d < H; d += 128) *reinterpret_cast<float4*>(row + d) = __ldg(reinterpret_cast<const float4*>(src + d));
+    __syncwarp();
+    float rms = 0.f;
+    if (lane == 0) {
+      float s = 0.f;
+#pragma unroll 8
+      for (int d = 0; d < H; ++d) s = __fadd_rn(s, __fmul_rn(row[d], row[d]));
+      rms = __fsqrt_rn(__fadd_rn(__fdiv_rn(s, (float)H), eps));
+    }
+    rms = __shfl_sync(0xffffffffu, rms, 0);
+    for (int d = lane * 4; d < H; d += 128) {
+      const float4 v = *reinterpret_cast<const float4*>(row + d);
+      const float4 g = __ldg(reinterpret_cast<const float4*>(w + d));
+      float4 o;
+      o.x = __fmul_rn(__fdiv_rn(v.x, rms), g.x);
+      o.y = __fmul_rn(__fdiv_rn(v.y, rms), g.y);
+      o.z = __fmul_rn(__fdiv_rn(v.z, rms), g.z);
+      o.w = __fmul_rn(__fdiv_rn(v.w, rms), g.w);
+      *reinterpret_cast<float4*>(out + (size_t)t * H + d) = o;
+    }
+    __syncwarp();  // the row buffer is rewritten for the warp's next token
   }
 }
 
@@ -1321,6 +1370,60 @@ __global__ void k_ep_p2p_return(const float* __restrict__ y, int H, float* const
     for (int i = lane; i < H / 4; i += 32) d[i] = s[i];
   }
   __threadfence_system();
+}
+
+// ---------------------------------------------------------------------------
+// Barrier (and, with a payload, the exchange of the per-slot row counts) between the ranks of
+// the peer-memory step, without a collective library: every rank owns a small sync area at
+// the tail of its return buffer, which all peers can write --
+//   flags[3][64]         flags[b][r] = last epoch of barrier b that rank r has reached
+//   all_counts[64][E]    all_counts[r][.] = rank r's row counts of this step
+// A rank stores its payload into every peer's area, fences (system scope), stores the epoch
+// into its flag on every peer, then waits until all of its own flags show the epoch.  Flags only
+// grow, nothing is reset.  The wait is bounded (clock budget); when it runs out the kernel sets
+// kDevErrWaitTimeout and returns.  One block; ranks run on different GPUs, so no rank's wait
+// depends on a kernel queued behind it on the same device.
+// ---------------------------------------------------------------------------
+constexpr int kEpMaxWorld = 64;
+__host__ __device__ inline size_t ep_sync_ints(int E) { return (size_t)3 * kEpMaxWorld + (size_t)kEpMaxWorld * E; }
+
+__global__ void __launch_bounds__(1024)
+k_ep_p2p_sync(float* const* __restrict__ peer_back, size_t tail_floats, int me, int world, int which, int epoch,
+              const int* __restrict__ my_counts, int E, int* __restrict__ all_counts_out, int* __restrict__ meta) {
+  __shared__ int s_timeout;
+  const int tid = threadIdx.x;
+  if (tid == 0) s_timeout = 0;
+  if (my_counts) {
+    for (int idx = tid; idx < world * E; idx += blockDim.x) {
+      const int r = idx / E, e = idx % E;
+      int* tail = reinterpret_cast<int*>(peer_back[r] + tail_floats);
+      tail[3 * kEpMaxWorld + (size_t)me * E + e] = my_counts[e];
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (tid < world) {
+    volatile int* theirs = reinterpret_cast<volatile int*>(peer_back[tid] + tail_floats);
+    theirs[which * kEpMaxWorld + me] = epoch;
+    volatile int* mine = reinterpret_cast<volatile int*>(peer_back[me] + tail_floats);
+    const long long t0 = clock64();
+    while (mine[which * kEpMaxWorld + tid] < epoch) {
+      if (clock64() - t0 > 4 * wait_budget()) {
+        s_timeout = 1;
+        break;
+      }
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (s_timeout) {
+    if (tid == 0) atomicOr(&meta[8], kDevErrWaitTimeout);  // the sticky word: later stages do not clear it
+    return;
+  }
+  if (all_counts_out) {
+    const volatile int* mine = reinterpret_cast<const volatile int*>(peer_back[me] + tail_floats);
+    for (int idx = tid; idx < world * E; idx += blockDim.x) all_counts_out[idx] = mine[3 * kEpMaxWorld + idx];
+  }
 }
 
 }  // namespace csk

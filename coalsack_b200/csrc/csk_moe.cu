@@ -30,6 +30,7 @@ struct csk_moe_layer {
   uint8_t* d_resident = nullptr;  // [Eloc] flags on the device
   std::vector<uint8_t> resident;
   uint8_t* d_stage = nullptr;     // raw 17-byte blocks during load / unpack
+  uint8_t* d_stage2 = nullptr;    // second staging area (bulk load)
   size_t stage_bytes = 0;
 
   float* d_wg = nullptr;   // [E,H]
@@ -49,6 +50,8 @@ struct csk_moe_layer {
   bool router_set = false, has_rbias = false;
   // expert parallelism over peer memory
   int p2p_rank = -1, p2p_world = 0;
+  size_t back_tail = 0;               // floats of d_back in front of its sync area
+  int p2p_epoch[3] = {0, 0, 0};       // epochs of the three flag barriers of a step
   RowOrigin* d_info = nullptr;        // [max_rows] origin of every received row
   float* d_back = nullptr;            // [max_T*k, H] output rows returned for this rank's pairs
   float** d_row_ptr = nullptr;        // [max_rows] where each received row's output goes
@@ -60,6 +63,9 @@ struct csk_moe_layer {
   bool pdl = false;  // launch the layer's kernels with programmatic dependent launch (small batches)
   bool debug_stall = false;  // test hook: the next tensor-core launch's copy role issues nothing (one shot)
 
+  float* d_norm_w = nullptr;   // [H] weight of the RMSNorm in front of the router (csk_moe_set_ffn_norm)
+  float* d_normed = nullptr;   // [max_T,H] its output
+  float norm_eps = 1e-5f;
   int64_t max_T = 0, max_rows = 0;
   int max_tiles = 0;
   float* d_hidden = nullptr;  // [max_T,H] staging for the host entry points
@@ -456,7 +462,8 @@ void finish_timings(csk_moe_layer* L, int n_marks, bool routed) {
 // The whole layer on device buffers.  only_expert >= 0 gives the dense output
 // of that single expert node.
 int forward_dev(csk_moe_layer* L, const float* d_hidden, int64_t T, const float* d_router_in,
-                float* d_router_out, float* d_out, int only_expert, cudaStream_t s, bool sync_check) {
+                float* d_router_out, float* d_out, int only_expert, cudaStream_t s, bool sync_check,
+                const float* d_residual = nullptr) {
   if (T <= 0 || T > L->max_T) return fail(L, CSK_ERR_NOMEM, "T=%lld outside (0, max_tokens=%lld]",
                                           (long long)T, (long long)L->max_T);
   if (L->has_slot_map)
@@ -502,7 +509,7 @@ int forward_dev(csk_moe_layer* L, const float* d_hidden, int64_t T, const float*
   if (rc) return rc;
   launch_k(k_combine, dim3((unsigned)T), dim3(256), 0, s, L->pdl, router, L->d_row_of_pair, (const float*)L->d_y, L->H,
            d_out, (int)T, L->k, L->H, (int)L->cfg.weight_before_ffn, (int)(only_expert >= 0), (const int*)L->d_meta,
-           (const int*)L->d_counts, L->carry_active ? L->d_carry : (int*)nullptr, L->E);
+           (const int*)L->d_counts, L->carry_active ? L->d_carry : (int*)nullptr, L->E, d_residual);
   CSK_CUDA(L, cudaGetLastError());
   L->last.launches++;
   tm.mark();
@@ -698,7 +705,7 @@ int csk_moe_destroy(csk_moe_layer* L) {
     if (g.exec) cudaGraphExecDestroy(g.exec);
   tile_destroy(L->tile);
   for (void* p : L->ipc_opened) cudaIpcCloseMemHandle(p);
-  void* dev[] = {L->d_part, L->d_hn2, L->d_wnorm, L->d_fb_list, L->d_fb, L->d_info, L->d_back, L->d_row_ptr, L->d_p2p_base, L->d_peer_x16, L->d_peer_info, L->d_peer_back,
+  void* dev[] = {L->d_stage2, L->d_norm_w, L->d_normed, L->d_part, L->d_hn2, L->d_wnorm, L->d_fb_list, L->d_fb, L->d_info, L->d_back, L->d_row_ptr, L->d_p2p_base, L->d_peer_x16, L->d_peer_info, L->d_peer_back,
                  L->d_router_phys, L->d_slot_map, L->d_weights, L->d_resident, L->d_stage, L->d_wg, L->d_wg_few, L->d_wg_many, L->d_route_cnt, L->d_logits, L->d_rbias, L->d_hidden,
                  L->d_router, L->d_out, L->d_x16, L->d_a16, L->d_y, L->d_counts, L->d_offsets,
                  L->d_cursor, L->d_row_of_pair, L->d_pair_of_row, L->d_out_row_map, L->d_seg, L->d_tiles, L->d_meta};
@@ -743,21 +750,13 @@ int csk_moe_set_router(csk_moe_layer* L, const float* gate_w, const float* gate_
   return CSK_OK;
 }
 
-int csk_moe_load_expert_mxfp4(csk_moe_layer* L, int32_t expert_id, const uint8_t* w_up,
-                              const uint8_t* w_gate, const uint8_t* w_down, const float* b_up,
-                              const float* b_gate, const float* b_down) {
-  if (check_layer(L)) return CSK_ERR_INVALID;
-  if (expert_id < L->e0 || expert_id >= L->e0 + L->Eloc)
-    return fail(L, CSK_ERR_INVALID, "expert %d is not resident on this device (range [%d,%d))",
-                expert_id, L->e0, L->e0 + L->Eloc);
-  if (!w_up || !w_gate || !w_down) return fail(L, CSK_ERR_INVALID, "null weight pointer");
-  if (L->cfg.has_bias && (!b_up || !b_gate || !b_down))
-    return fail(L, CSK_ERR_INVALID, "layer has biases but a bias pointer is null");
-  CSK_CUDA(L, cudaSetDevice(L->cfg.device));
-  const int le = expert_id - L->e0;
+namespace {
+// One expert: raw blocks to a staging area, the four repacks, biases.  Enqueue only; `stage` is one
+// of the handle's two staging areas (3 * stage_bytes each).
+int load_expert_enqueue(csk_moe_layer* L, int le, const uint8_t* w_up, const uint8_t* w_gate, const uint8_t* w_down,
+                        const float* b_up, const float* b_gate, const float* b_down, uint8_t* stage, cudaStream_t s) {
   uint8_t* base = L->d_weights + (size_t)le * L->expert_stride;
-  cudaStream_t s = L->stream;
-  uint8_t *s_up = L->d_stage, *s_gate = L->d_stage + L->stage_bytes, *s_down = L->d_stage + 2 * L->stage_bytes;
+  uint8_t *s_up = stage, *s_gate = stage + L->stage_bytes, *s_down = stage + 2 * L->stage_bytes;
   CSK_CUDA(L, cudaMemcpyAsync(s_up, w_up, L->stage_bytes, cudaMemcpyHostToDevice, s));
   CSK_CUDA(L, cudaMemcpyAsync(s_gate, w_gate, L->stage_bytes, cudaMemcpyHostToDevice, s));
   CSK_CUDA(L, cudaMemcpyAsync(s_down, w_down, L->stage_bytes, cudaMemcpyHostToDevice, s));
@@ -774,10 +773,121 @@ int csk_moe_load_expert_mxfp4(csk_moe_layer* L, int32_t expert_id, const uint8_t
     CSK_CUDA(L, cudaMemcpyAsync(b + L->F, b_gate, sizeof(float) * L->F, cudaMemcpyHostToDevice, s));
     CSK_CUDA(L, cudaMemcpyAsync(b + 2 * L->F, b_down, sizeof(float) * L->H, cudaMemcpyHostToDevice, s));
   }
-  const uint8_t one = 1;
-  CSK_CUDA(L, cudaMemcpyAsync(L->d_resident + le, &one, 1, cudaMemcpyHostToDevice, s));
-  CSK_CUDA(L, cudaStreamSynchronize(s));
+  CSK_CUDA(L, cudaMemsetAsync(L->d_resident + le, 1, 1, s));
+  return CSK_OK;
+}
+}  // namespace
+
+int csk_moe_load_expert_mxfp4(csk_moe_layer* L, int32_t expert_id, const uint8_t* w_up,
+                              const uint8_t* w_gate, const uint8_t* w_down, const float* b_up,
+                              const float* b_gate, const float* b_down) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  if (expert_id < L->e0 || expert_id >= L->e0 + L->Eloc)
+    return fail(L, CSK_ERR_INVALID, "expert %d is not resident on this device (range [%d,%d))",
+                expert_id, L->e0, L->e0 + L->Eloc);
+  if (!w_up || !w_gate || !w_down) return fail(L, CSK_ERR_INVALID, "null weight pointer");
+  if (L->cfg.has_bias && (!b_up || !b_gate || !b_down))
+    return fail(L, CSK_ERR_INVALID, "layer has biases but a bias pointer is null");
+  CSK_CUDA(L, cudaSetDevice(L->cfg.device));
+  const int le = expert_id - L->e0;
+  int rc = load_expert_enqueue(L, le, w_up, w_gate, w_down, b_up, b_gate, b_down, L->d_stage, L->stream);
+  if (rc) return rc;
+  CSK_CUDA(L, cudaStreamSynchronize(L->stream));
   L->resident[le] = 1;
+  return CSK_OK;
+}
+
+int csk_moe_load_experts_mxfp4(csk_moe_layer* L, int32_t first_expert, int32_t count, const uint8_t* w_up,
+                               const uint8_t* w_gate, const uint8_t* w_down, const float* b_up, const float* b_gate,
+                               const float* b_down) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  if (count <= 0 || first_expert < L->e0 || first_expert + count > L->e0 + L->Eloc)
+    return fail(L, CSK_ERR_INVALID, "experts [%d,%d) are not all resident on this device (range [%d,%d))", first_expert,
+                first_expert + count, L->e0, L->e0 + L->Eloc);
+  if (!w_up || !w_gate || !w_down) return fail(L, CSK_ERR_INVALID, "null weight pointer");
+  if (L->cfg.has_bias && (!b_up || !b_gate || !b_down))
+    return fail(L, CSK_ERR_INVALID, "layer has biases but a bias pointer is null");
+  CSK_CUDA(L, cudaSetDevice(L->cfg.device));
+  if (!L->d_stage2) {
+    cudaError_t e = cudaMalloc(&L->d_stage2, 3 * L->stage_bytes);
+    if (e != cudaSuccess) return fail(L, CSK_ERR_NOMEM, "cudaMalloc failed: %s", cudaGetErrorString(e));
+  }
+  // two staging areas: the copies of expert i+1 run while expert i is repacked
+  cudaStream_t s = L->stream, s2 = L->stream_in;
+  for (int i = 0; i < count; ++i) {
+    const int le = first_expert - L->e0 + i;
+    cudaStream_t st = (i & 1) ? s2 : s;
+    uint8_t* stage = (i & 1) ? L->d_stage2 : L->d_stage;
+    const size_t wb = L->stage_bytes;
+    int rc = load_expert_enqueue(L, le, w_up + (size_t)i * wb, w_gate + (size_t)i * wb, w_down + (size_t)i * wb,
+                                 b_up ? b_up + (size_t)i * L->F : nullptr, b_gate ? b_gate + (size_t)i * L->F : nullptr,
+                                 b_down ? b_down + (size_t)i * L->H : nullptr, stage, st);
+    if (rc) return rc;
+  }
+  CSK_CUDA(L, cudaStreamSynchronize(s));
+  CSK_CUDA(L, cudaStreamSynchronize(s2));
+  for (int i = 0; i < count; ++i) L->resident[first_expert - L->e0 + i] = 1;
+  return CSK_OK;
+}
+
+namespace {
+struct ImageHeader {
+  char magic[8];
+  int32_t E, k, H, F, has_bias, e0, eloc, reserved;
+  uint64_t expert_stride, off_gu, off_d, off_tgu, off_td, off_bias, off_meta;
+};
+ImageHeader image_header_of(const csk_moe_layer* L) {
+  ImageHeader h{};
+  memcpy(h.magic, "CSKMOE01", 8);
+  h.E = L->E; h.k = L->k; h.H = L->H; h.F = L->F; h.has_bias = L->cfg.has_bias; h.e0 = L->e0; h.eloc = L->Eloc;
+  h.expert_stride = L->expert_stride; h.off_gu = L->off_gu; h.off_d = L->off_d; h.off_tgu = L->off_tgu;
+  h.off_td = L->off_td; h.off_bias = L->off_bias; h.off_meta = L->off_meta;
+  return h;
+}
+}  // namespace
+
+int csk_moe_save_image(csk_moe_layer* L, const char* path) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  if (!path) return fail(L, CSK_ERR_INVALID, "null path");
+  CSK_CUDA(L, cudaSetDevice(L->cfg.device));
+  FILE* f = fopen(path, "wb");
+  if (!f) return fail(L, CSK_ERR_INVALID, "cannot open %s for writing", path);
+  const ImageHeader h = image_header_of(L);
+  bool ok = fwrite(&h, sizeof h, 1, f) == 1 && fwrite(L->resident.data(), 1, L->Eloc, f) == (size_t)L->Eloc;
+  std::vector<uint8_t> buf(L->expert_stride);
+  for (int e = 0; ok && e < L->Eloc; ++e) {
+    if (cudaMemcpy(buf.data(), L->d_weights + (size_t)e * L->expert_stride, L->expert_stride, cudaMemcpyDeviceToHost) != cudaSuccess) ok = false;
+    ok = ok && fwrite(buf.data(), 1, buf.size(), f) == buf.size();
+  }
+  ok = fclose(f) == 0 && ok;
+  if (!ok) return fail(L, CSK_ERR_CUDA, "writing the weight image to %s failed", path);
+  return CSK_OK;
+}
+
+int csk_moe_load_image(csk_moe_layer* L, const char* path) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  if (!path) return fail(L, CSK_ERR_INVALID, "null path");
+  CSK_CUDA(L, cudaSetDevice(L->cfg.device));
+  FILE* f = fopen(path, "rb");
+  if (!f) return fail(L, CSK_ERR_INVALID, "cannot open %s", path);
+  ImageHeader h{};
+  const ImageHeader want = image_header_of(L);
+  std::vector<uint8_t> res(L->Eloc);
+  bool ok = fread(&h, sizeof h, 1, f) == 1;
+  if (ok && memcmp(&h, &want, sizeof h) != 0) {
+    fclose(f);
+    return fail(L, CSK_ERR_INVALID, "%s was written for another layer shape, expert range or library layout", path);
+  }
+  ok = ok && fread(res.data(), 1, L->Eloc, f) == (size_t)L->Eloc;
+  std::vector<uint8_t> buf(L->expert_stride);
+  for (int e = 0; ok && e < L->Eloc; ++e) {
+    ok = fread(buf.data(), 1, buf.size(), f) == buf.size();
+    if (ok && cudaMemcpy(L->d_weights + (size_t)e * L->expert_stride, buf.data(), L->expert_stride, cudaMemcpyHostToDevice) != cudaSuccess) ok = false;
+  }
+  fclose(f);
+  if (!ok) return fail(L, CSK_ERR_CUDA, "reading the weight image from %s failed", path);
+  CSK_CUDA(L, cudaMemcpy(L->d_resident, res.data(), L->Eloc, cudaMemcpyHostToDevice));
+  L->resident = res;
   return CSK_OK;
 }
 
@@ -815,6 +925,17 @@ int csk_moe_set_path(csk_moe_layer* L, int32_t path) {
   if (check_layer(L)) return CSK_ERR_INVALID;
   if (path < CSK_PATH_AUTO || path > CSK_PATH_TILE) return fail(L, CSK_ERR_INVALID, "unknown path %d", path);
   L->path = path;
+  drop_graphs(L);
+  return CSK_OK;
+}
+
+int csk_moe_set_activation(csk_moe_layer* L, int32_t activation, int32_t weight_before_ffn) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  if (activation != CSK_ACT_MODIFIED_SWIGLU && activation != CSK_ACT_STANDARD_SWIGLU)
+    return fail(L, CSK_ERR_INVALID, "unknown activation %d", activation);
+  if (L->cfg.activation == activation && (L->cfg.weight_before_ffn != 0) == (weight_before_ffn != 0)) return CSK_OK;
+  L->cfg.activation = activation;
+  L->cfg.weight_before_ffn = weight_before_ffn != 0;
   drop_graphs(L);
   return CSK_OK;
 }
@@ -941,6 +1062,58 @@ int csk_moe_forward_dev(csk_moe_layer* L, const float* d_hidden, int64_t T, cons
   }
   L->graphs.push_back({T, d_hidden, d_router_in, d_router_out, d_out, s, exec});
   CSK_CUDA(L, cudaGraphLaunch(exec, s));
+  return CSK_OK;
+}
+
+// ---- the layer with the steps either side of it ------------------------------
+int csk_moe_set_ffn_norm(csk_moe_layer* L, const float* weight, float eps) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  if (!weight) return fail(L, CSK_ERR_INVALID, "norm weight is null");
+  CSK_CUDA(L, cudaSetDevice(L->cfg.device));
+  if (!L->d_norm_w) {
+    cudaError_t e = cudaMalloc(&L->d_norm_w, sizeof(float) * L->H);
+    if (e == cudaSuccess) e = cudaMalloc(&L->d_normed, sizeof(float) * L->max_T * L->H);
+    if (e != cudaSuccess) return fail(L, CSK_ERR_NOMEM, "cudaMalloc failed: %s", cudaGetErrorString(e));
+    CSK_CUDA(L, cudaFuncSetAttribute(k_rmsnorm, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * (int)sizeof(float) * L->H));
+  }
+  CSK_CUDA(L, cudaMemcpyAsync(L->d_norm_w, weight, sizeof(float) * L->H, cudaMemcpyHostToDevice, L->stream));
+  CSK_CUDA(L, cudaStreamSynchronize(L->stream));
+  L->norm_eps = eps;
+  return CSK_OK;
+}
+
+int csk_moe_block_forward_dev(csk_moe_layer* L, const float* d_x, int64_t T, float* d_router_out, float* d_out,
+                              void* stream) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  if (!d_x || !d_out) return fail(L, CSK_ERR_INVALID, "null argument");
+  if (!L->d_norm_w) return fail(L, CSK_ERR_INVALID, "the norm weight was never set (csk_moe_set_ffn_norm)");
+  if (T <= 0 || T > L->max_T) return fail(L, CSK_ERR_NOMEM, "T=%lld outside (0, max_tokens]", (long long)T);
+  if (reinterpret_cast<uintptr_t>(d_x) % 16 || reinterpret_cast<uintptr_t>(d_out) % 16)
+    return fail(L, CSK_ERR_INVALID, "activations must be 16-byte aligned");
+  if ((size_t)L->H * sizeof(float) * 4 > 200 * 1024) return fail(L, CSK_ERR_NOMEM, "hidden dimension too large for the norm kernel's row buffer");
+  CSK_CUDA(L, cudaSetDevice(L->cfg.device));
+  cudaStream_t s = pick(L, stream);
+  const int blocks = (int)std::min<int64_t>((T + 3) / 4, 4 * (int64_t)L->sm_count);
+  k_rmsnorm<<<blocks, 128, 4 * sizeof(float) * L->H, s>>>(d_x, L->d_norm_w, L->norm_eps, L->d_normed, (int)T, L->H);
+  CSK_CUDA(L, cudaGetLastError());
+  return forward_dev(L, L->d_normed, T, nullptr, d_router_out, d_out, -1, s, false, d_x);
+}
+
+int csk_moe_block_forward(csk_moe_layer* L, const float* x, int64_t T, float* router_out, float* out) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  if (!x || !out) return fail(L, CSK_ERR_INVALID, "null argument");
+  if (T <= 0 || T > L->max_T) return fail(L, CSK_ERR_NOMEM, "T=%lld outside (0, max_tokens]", (long long)T);
+  CSK_CUDA(L, cudaSetDevice(L->cfg.device));
+  cudaStream_t s = L->stream;
+  CSK_CUDA(L, cudaMemcpyAsync(L->d_hidden, x, sizeof(float) * T * L->H, cudaMemcpyHostToDevice, s));
+  int rc = csk_moe_block_forward_dev(L, L->d_hidden, T, L->d_router, L->d_out, s);
+  if (rc) return rc;
+  rc = check_device_status(L, s);
+  if (rc) return rc;
+  CSK_CUDA(L, cudaMemcpyAsync(out, L->d_out, sizeof(float) * T * L->H, cudaMemcpyDeviceToHost, s));
+  if (router_out)
+    CSK_CUDA(L, cudaMemcpyAsync(router_out, L->d_router, sizeof(float) * T * L->k * 2, cudaMemcpyDeviceToHost, s));
+  CSK_CUDA(L, cudaStreamSynchronize(s));
   return CSK_OK;
 }
 
@@ -1191,7 +1364,11 @@ int p2p_alloc_local(csk_moe_layer* L) {
   CSK_CUDA(L, cudaMalloc(&L->d_info, sizeof(RowOrigin) * (size_t)L->max_rows));
   // 0xFF bytes: (-1, -1), which no reader accepts as an origin (rows a sender had to skip stay that way)
   CSK_CUDA(L, cudaMemset(L->d_info, 0xFF, sizeof(RowOrigin) * (size_t)L->max_rows));
-  CSK_CUDA(L, cudaMalloc(&L->d_back, sizeof(float) * (size_t)L->max_T * L->k * L->H));
+  // the return buffer carries the sync area of the flag barriers at its tail (peers can write both)
+  L->back_tail = (size_t)L->max_T * L->k * L->H;
+  const size_t back_bytes = sizeof(float) * L->back_tail + sizeof(int) * ep_sync_ints(L->E);
+  CSK_CUDA(L, cudaMalloc(&L->d_back, back_bytes));
+  CSK_CUDA(L, cudaMemset(reinterpret_cast<uint8_t*>(L->d_back) + sizeof(float) * L->back_tail, 0, sizeof(int) * ep_sync_ints(L->E)));
   CSK_CUDA(L, cudaMalloc(&L->d_row_ptr, sizeof(float*) * (size_t)L->max_rows));
   return CSK_OK;
 }
@@ -1336,6 +1513,23 @@ int csk_moe_ep_p2p_counts_dev(csk_moe_layer* L, const float* d_hidden, int64_t T
                                                                                  L->d_meta);
   CSK_CUDA(L, cudaGetLastError());
   CSK_CUDA(L, cudaMemcpyAsync(d_counts, L->d_counts, sizeof(int) * L->E, cudaMemcpyDeviceToDevice, s));
+  return CSK_OK;
+}
+
+// Barrier `which` (0: counts, 1: rows landed, 2: outputs landed) between the ranks, by flags in peer
+// memory; with d_counts / d_all_counts it also exchanges the per-slot row counts (the all-gather).
+int csk_moe_ep_p2p_sync_dev(csk_moe_layer* L, int32_t which, const int32_t* d_counts, int32_t* d_all_counts, void* stream) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  if (L->p2p_world <= 0) return fail(L, CSK_ERR_INVALID, "p2p: peers were never imported");
+  if (which < 0 || which > 2 || (d_counts == nullptr) != (d_all_counts == nullptr))
+    return fail(L, CSK_ERR_INVALID, "p2p sync: which must be 0..2, counts and all_counts go together");
+  CSK_CUDA(L, cudaSetDevice(L->cfg.device));
+  cudaStream_t s = pick(L, stream);
+  const int epoch = ++L->p2p_epoch[which];
+  k_ep_p2p_sync<<<1, 1024, 0, s>>>(L->d_peer_back, L->back_tail, L->p2p_rank, L->p2p_world, which, epoch, d_counts, L->E,
+                                   d_all_counts, L->d_meta);
+  CSK_CUDA(L, cudaGetLastError());
+  L->last_stream = s;
   return CSK_OK;
 }
 

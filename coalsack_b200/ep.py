@@ -295,10 +295,18 @@ class P2pEpLayer:
         self.counts = torch.zeros(E, dtype=torch.int32, device=backend.dev)
         self.all_counts = torch.zeros(world * E, dtype=torch.int32, device=backend.dev)
         self.token = torch.zeros(1, dtype=torch.int32, device=backend.dev)
+        # the gather of the counts and the two barriers: flags in peer memory written by a kernel of
+        # the library (default), or the process group's collectives (CSK_EP_FLAGS=0)
+        import os
+        self.flags = os.environ.get("CSK_EP_FLAGS", "1") != "0"
+        dist.barrier(group=group)  # every rank has imported before anyone signals
 
-    def _barrier(self):
+    def _barrier(self, which):
         # stream-ordered: every rank's kernels before it have finished (their peer stores are done)
-        self.dist.all_reduce(self.token, group=self.group)
+        if self.flags:
+            self.b.layer.ep_p2p_sync_dev(which, stream=self.b.stream())
+        else:
+            self.dist.all_reduce(self.token, group=self.group)
 
     def forward(self, hidden, T, out, mark=None):
         """One step.  `mark(name)`, when given, is called after each stage is enqueued (the bench
@@ -310,16 +318,19 @@ class P2pEpLayer:
         else:
             self.counts.zero_()  # a rank without tokens still serves its experts
         mark("route_count")
-        self.dist.all_gather_into_tensor(self.all_counts, self.counts, group=self.group)
+        if self.flags:
+            lay.ep_p2p_sync_dev(0, self.counts, self.all_counts, stream=st)
+        else:
+            self.dist.all_gather_into_tensor(self.all_counts, self.counts, group=self.group)
         mark("gather_counts")
         if T:
             lay.ep_p2p_scatter_dev(hidden, T, self.all_counts, stream=st)
         mark("scatter")
-        self._barrier()
+        self._barrier(1)
         mark("barrier_rows")
         lay.ep_p2p_experts_dev(self.all_counts, max(T, 1) * self.b.k, stream=st)
         mark("experts")
-        self._barrier()
+        self._barrier(2)
         mark("barrier_out")
         if T:
             lay.ep_p2p_combine_dev(T, out, stream=st)
@@ -361,7 +372,8 @@ class EpBench:
             self.p2p = bool(agree.item())
         if not self.p2p:
             self.ep = EpLayer(self.backend, world)
-        self.exchange = ("rows stored into peer memory by the dispatch and down-projection kernels (NVLink)"
+        self.exchange = ("rows stored into peer memory by the dispatch and down-projection kernels (NVLink); counts and "
+                         + ("barriers by flags in peer memory" if getattr(self.ep, "flags", False) else "barriers by NCCL")
                          if self.p2p else "all-to-all collectives (NCCL)")
         self.place = place
         self.load = load

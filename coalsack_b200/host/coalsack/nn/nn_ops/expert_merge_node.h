@@ -35,6 +35,10 @@ class expert_merge_node : public variadic_op_node {
                                std::to_string(top_k_) + ", 2]");
     if (router.get_dtype() != dtype::float32) throw std::runtime_error("expert_merge: only float32 supported");
     const int64_t B = router.dim(0), S = router.dim(1);
+    {
+      dynamic_tensor fused;
+      if (run_fused(router, fused)) return fused;
+    }
     int64_t H = 0;
     std::vector<const float*> rows(num_experts_, nullptr);
     for (int64_t e = 0; e < num_experts_; ++e) {
@@ -62,6 +66,30 @@ class expert_merge_node : public variadic_op_node {
   }
 
  private:
+  // Fused mode: the layer's context holds the frame's hidden states and every selected expert's weights
+  // on the GPU: the whole layer (dispatch, grouped MXFP4 MLP, weighted combine in router order) is one
+  // csk_moe_forward with the routing this node was given.
+  bool run_fused(const dynamic_tensor& router, dynamic_tensor& out) {
+    if (!csk_host::fused_moe() || input_names_.size() < 2) return false;
+    const std::string prefix = csk_host::layer_prefix_of(input_names_[1]);
+    if (prefix.empty()) return false;
+    auto ctx = csk_host::layer_registry::get(prefix);
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    if (!ctx->usable || !ctx->have_hidden) return false;
+    const dynamic_tensor& hidden = ctx->hidden;
+    const int64_t B = router.dim(0), S = router.dim(1);
+    if (hidden.ndim() != 3 || hidden.dim(0) != B || hidden.dim(1) != S || hidden.dim(2) != ctx->cfg.hidden)
+      throw std::runtime_error("expert_merge: hidden states and router output disagree in shape");
+    csk_moe_layer* h = ctx->handle.get(ctx->cfg);
+    csk_host::check(csk_moe_set_activation(h, ctx->activation, ctx->weight_before_ffn), h);
+    out = dynamic_tensor(dtype::float32, {B, S, hidden.dim(2)});
+    const int rc = csk_moe_forward(h, hidden.data_ptr<float>(), B * S, router.data_ptr<float>(), nullptr, out.data_ptr<float>());
+    ctx->have_hidden = false;
+    ctx->hidden = dynamic_tensor();
+    csk_host::check(rc, h);
+    return true;
+  }
+
   int64_t num_experts_ = 0, top_k_ = 0;
   bool weight_before_ffn_ = false;
   csk_host::layer_handle handle_;

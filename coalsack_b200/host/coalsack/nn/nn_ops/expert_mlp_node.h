@@ -7,6 +7,8 @@
 // token selected it.  Weights are repacked and uploaded once per weight buffer
 // (csk_moe_load_expert_mxfp4); the forward is csk_moe_expert_forward.
 // fp16 expert weights are not handled by this binding.
+// In fused mode (csk_moe_handle.h) the node only passes the hidden states along and
+// answers with the {0}-shaped placeholder; the merge node runs the whole layer.
 #pragma once
 
 #include <memory>
@@ -67,8 +69,26 @@ class expert_mlp_node : public graph_node {
           if (!f) throw std::runtime_error("expert_mlp: missing field " + name);
           fields.push_back(f);
         }
-        if (!std::dynamic_pointer_cast<dynamic_mx_tensor_message>(fields[1]))
-          throw std::runtime_error("expert_mlp: this GPU binding handles MXFP4 expert weights only");
+        if (pass_along(fields)) {
+          // fused mode: the layer runs once, in the merge node; this node answers with the placeholder
+          out = result_message::ok({{output_name_, std::make_shared<dynamic_tensor_message>(dynamic_tensor(dtype::float32, {0}))}});
+          out->set_frame_number(frame);
+          out->set_timestamp(stamp);
+          output_->send(out);
+          return;
+        }
+        if (!std::dynamic_pointer_cast<dynamic_mx_tensor_message>(fields[1])) {
+          // plain tensors: what the fetch node sends to an expert no token selected ({0}-shaped); the
+          // reference then answers with the {0}-shaped tensor before it looks at any weight
+          // (expert_mlp_node.h:296-302).  Real fp16/fp32 expert weights are not handled here.
+          if (selected_by(as<dynamic_tensor_message>(fields.back(), "router")->get_tensor()))
+            throw std::runtime_error("expert_mlp: this GPU binding handles MXFP4 expert weights only");
+          out = result_message::ok({{output_name_, std::make_shared<dynamic_tensor_message>(dynamic_tensor(dtype::float32, {0}))}});
+          out->set_frame_number(frame);
+          out->set_timestamp(stamp);
+          output_->send(out);
+          return;
+        }
         auto tensor = std::make_shared<dynamic_tensor_message>(run_mxfp4(fields));
         out = result_message::ok({{output_name_, tensor}});
       } catch (const std::exception& e) {
@@ -87,6 +107,34 @@ class expert_mlp_node : public graph_node {
     auto p = std::dynamic_pointer_cast<T>(m);
     if (!p) throw std::runtime_error(std::string("expert_mlp: invalid ") + what + " message type for MXFP4");
     return p;
+  }
+
+  bool selected_by(const dynamic_tensor& router) const {
+    if (router.ndim() != 4 || router.dim(3) != 2)
+      throw std::runtime_error("expert_mlp: router_output must be 4D [batch, seq_len, top_k, 2]");
+    const float* r = router.data_ptr<float>();
+    const int64_t n = router.dim(0) * router.dim(1) * router.dim(2);
+    for (int64_t i = 0; i < n; ++i)
+      if (static_cast<int>(r[2 * i]) == expert_id_) return true;
+    return false;
+  }
+
+  // Fused mode: true when this layer's context took over the frame (the fetch node made the selected
+  // experts resident).  The first expert node of a frame leaves the hidden states there for the merge node.
+  bool pass_along(const std::vector<graph_message_ptr>& f) {
+    if (!csk_host::fused_moe() || input_names_.size() < 2) return false;
+    const std::string prefix = csk_host::layer_prefix_of(input_names_[1]);
+    if (prefix.empty()) return false;
+    auto ctx = csk_host::layer_registry::get(prefix);
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    if (!ctx->usable) return false;
+    ctx->activation = activation_type_ == activation_type::MODIFIED_SWIGLU ? CSK_ACT_MODIFIED_SWIGLU : CSK_ACT_STANDARD_SWIGLU;
+    ctx->weight_before_ffn = weight_before_ffn_;
+    if (!ctx->have_hidden) {
+      ctx->hidden = as<dynamic_tensor_message>(f[0], "input")->get_tensor();
+      ctx->have_hidden = true;
+    }
+    return true;
   }
 
   dynamic_tensor run_mxfp4(const std::vector<graph_message_ptr>& f) {
@@ -159,7 +207,13 @@ class expert_mlp_node : public graph_node {
     return h;
   }
 
-  // Expert weights are constants of the model: repack and upload when the buffer changes.
+  // Expert weights are constants of the model: repack and upload when the buffer changes.  A buffer that
+  // is REWRITTEN in place keeps its address: call invalidate_weights() after such a reload (hashing
+  // 13 MB per expert and frame to notice it would cost more than the expert itself).
+ public:
+  void invalidate_weights() { last_up_ = last_gate_ = last_down_ = nullptr; }
+
+ private:
   void upload(csk_moe_layer* h, const uint8_t* up, const uint8_t* gate, const uint8_t* down, const float* b_up,
               const float* b_gate, const float* b_down) {
     if (up == last_up_ && gate == last_gate_ && down == last_down_) return;

@@ -69,13 +69,18 @@ class moe_router_node : public variadic_op_node {
     c.sigmoid_gating = use_sigmoid_gating_;
     c.max_tokens = B * S;
     csk_moe_layer* h = handle_.get(c);
-    // router weights are constants of the model: upload when the buffer changes
+    // router weights are constants of the model: upload when the buffer OR its contents change (a
+    // checkpoint reloaded into the same allocation keeps the address; the reference reads the tensors
+    // on every call, so a stale copy on the GPU would be a silent difference)
     const float* w = gate.data_ptr<float>();
     const float* b = biased ? in[2].data_ptr<float>() : nullptr;
-    if (handle_.just_created() || w != last_w_ || b != last_b_) {
+    const uint64_t sum = csk_host::content_hash(w, sizeof(float) * num_experts_ * H) ^
+                         (biased ? csk_host::content_hash(b, sizeof(float) * num_experts_) * 0x9E3779B97F4A7C15ull : 0);
+    if (handle_.just_created() || w != last_w_ || b != last_b_ || sum != last_sum_) {
       csk_host::check(csk_moe_set_router(h, w, b), h);
       last_w_ = w;
       last_b_ = b;
+      last_sum_ = sum;
     }
     dynamic_tensor out(dtype::float32, {B, S, top_k_, 2});
     csk_host::check(csk_moe_route(h, hidden.data_ptr<float>(), B * S, out.data_ptr<float>()), h);
@@ -86,8 +91,14 @@ class moe_router_node : public variadic_op_node {
   int64_t num_experts_ = 0, top_k_ = 0;
   bool use_sigmoid_gating_ = false;
   csk_host::layer_handle handle_;
+ public:
+  // Forget the uploaded router weights (after an in-place edit the sampled content check could miss).
+  void invalidate_weights() { last_w_ = nullptr; }
+
+ private:
   const float* last_w_ = nullptr;
   const float* last_b_ = nullptr;
+  uint64_t last_sum_ = 0;
 };
 
 }  // namespace coalsack

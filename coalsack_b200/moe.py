@@ -115,6 +115,23 @@ class MoeLayer:
             b = [experts[n][i] if experts.get(n) is not None else None for n in ("b_up", "b_gate", "b_down")]
             self.load_expert(e, experts["w_up"][i], experts["w_gate"][i], experts["w_down"][i], *b)
 
+    def load_experts_bulk(self, first_expert, w_up, w_gate, w_down, b_up=None, b_gate=None, b_down=None):
+        """Slabs [count, rows*cols/32*17] of MXFP4 blocks (and [count, n] fp32 biases) for experts
+        first_expert .. first_expert + count - 1."""
+        nbytes = self.H * self.F // 32 * 17
+        slabs = [_np_u8(a).reshape(-1, nbytes) for a in (w_up, w_gate, w_down)]
+        count = slabs[0].shape[0]
+        if any(a.shape[0] != count for a in slabs):
+            raise RuntimeError("expert_mlp: weight dimension mismatch")
+        b = [None if a is None else _np_f32(a).reshape(count, -1) for a in (b_up, b_gate, b_down)]
+        self._check(self._lib.csk_moe_load_experts_mxfp4(self._h, first_expert, count, *map(_p, slabs), *map(_p, b)))
+
+    def save_image(self, path):
+        self._check(self._lib.csk_moe_save_image(self._h, str(path).encode()))
+
+    def load_image(self, path):
+        self._check(self._lib.csk_moe_load_image(self._h, str(path).encode()))
+
     def unpack_expert(self, expert_id, which):
         out = np.empty(self.H * self.F // 32 * 17, np.uint8)
         self._check(self._lib.csk_moe_unpack_expert_mxfp4(self._h, expert_id, which, _p(out)))
@@ -142,6 +159,22 @@ class MoeLayer:
         r_out = router_out_buf if router_out_buf is not None else np.empty((T, self.k, 2), np.float32)
         self._check(self._lib.csk_moe_forward(self._h, _p(hidden), T, _p(r_in), _p(r_out), _p(out)))
         return out, r_out
+
+    def set_ffn_norm(self, weight, eps=1e-5):
+        """Weight [H] and epsilon of the RMSNorm in front of the router (rmsnorm_node)."""
+        w = _np_f32(weight).reshape(-1)
+        if w.shape[0] != self.H:
+            raise RuntimeError("rmsnorm: weight shape must be [hidden_dim]")
+        self._check(self._lib.csk_moe_set_ffn_norm(self._h, _p(w), float(eps)))
+
+    def block_forward(self, x):
+        """(x + moe(rmsnorm(x) * weight), router_out): the layer with its norm and residual."""
+        x = _np_f32(x).reshape(-1, self.H)
+        T = x.shape[0]
+        out = np.empty((T, self.H), np.float32)
+        ro = np.empty((T, self.k, 2), np.float32)
+        self._check(self._lib.csk_moe_block_forward(self._h, _p(x), T, _p(ro), _p(out)))
+        return out, ro
 
     def expert_forward(self, expert_id, hidden, router_out):
         """Dense [T,H] output of one expert node, or None for the {0}-shaped empty tensor."""
@@ -226,6 +259,9 @@ class MoeLayer:
     def ep_p2p_import_ptrs(self, rank, world, x16, info, back):
         arr = lambda v: (C.c_void_p * world)(*v)
         self._check(self._lib.csk_moe_ep_p2p_import_ptrs(self._h, rank, world, arr(x16), arr(info), arr(back)))
+
+    def ep_p2p_sync_dev(self, which, d_counts=None, d_all_counts=None, stream=None):
+        self._check(self._lib.csk_moe_ep_p2p_sync_dev(self._h, which, _p(d_counts), _p(d_all_counts), stream))
 
     def ep_p2p_counts_dev(self, d_hidden, T, d_counts, d_router_in=None, stream=None):
         self._check(self._lib.csk_moe_ep_p2p_counts_dev(self._h, _p(d_hidden), T, _p(d_router_in), _p(d_counts), stream))

@@ -94,6 +94,22 @@ int csk_moe_set_router(csk_moe_layer* layer, const float* gate_w, const float* g
 int csk_moe_load_expert_mxfp4(csk_moe_layer* layer, int32_t expert_id, const uint8_t* w_up,
                               const uint8_t* w_gate, const uint8_t* w_down, const float* b_up,
                               const float* b_gate, const float* b_down);
+/* A run of experts from the model's expert tensors: w_up / w_gate / w_down point at expert
+ * `first_expert`'s slice of an [E, rows, cols] MXFP4 tensor (slices of rows*cols/32*17 bytes
+ * one after the other, as the GGUF file holds ffn_{up,gate,down}_exps.weight and as
+ * moe_weight_provider::get cuts them, src/llm/moe_weight_provider.cpp:160-188); the biases
+ * at its row of the [E, n] bias tensors (:110, 194-199).  Copies of one expert overlap the
+ * repack of the previous one.  This is the load-time path that makes a layer device-resident
+ * instead of streaming experts per step through the host cache (src/llm/llm_engine.cpp:283-288). */
+int csk_moe_load_experts_mxfp4(csk_moe_layer* layer, int32_t first_expert, int32_t count, const uint8_t* w_up,
+                               const uint8_t* w_gate, const uint8_t* w_down, const float* b_up,
+                               const float* b_gate, const float* b_down);
+/* The repacked weights of the resident experts as a file, and back: a later start of the same
+ * layer (same shape, expert range and library build) skips the repack.  No counterpart in the
+ * reference. */
+int csk_moe_save_image(csk_moe_layer* layer, const char* path);
+int csk_moe_load_image(csk_moe_layer* layer, const char* path);
+
 /* Inverse of the repack: writes matrix `which` (0 up, 1 gate, 2 down from the
  * streaming kernel's layout; 3 up, 4 gate, 5 down from the tensor-core
  * kernel's layout) of a resident expert back as 17-byte blocks (host).  The
@@ -143,6 +159,19 @@ int csk_moe_forward_dev(csk_moe_layer* layer, const float* d_hidden, int64_t T,
  * one on this handle and reports what its kernels found (an expert id out of
  * range, rows routed to an expert that is not loaded, capacity exceeded). */
 int csk_moe_sync(csk_moe_layer* layer);
+
+/* ---- the layer with the steps either side of it ----------------------------
+ * The reference runs an RMSNorm in front of the router and adds the layer's input
+ * back after the merge (rmsnorm_node.h:20-83, eps 1e-5; src/llm/llm_engine.cpp:714-719
+ * and 773-777); both are passes over [T,H] that cost a round trip each when they
+ * are separate operators.  Here:  n = rmsnorm(x) * weight;  out = x + moe(n).
+ * The norm reproduces the reference's sequential sum of squares, so the router sees
+ * the reference's own input and its expert indices stay bit-exact; the residual is
+ * one fp32 addition in the combine kernel.  set_ffn_norm takes a host weight [H]. */
+int csk_moe_set_ffn_norm(csk_moe_layer* layer, const float* norm_weight, float eps);
+int csk_moe_block_forward(csk_moe_layer* layer, const float* x, int64_t T, float* router_out_or_null, float* out);
+int csk_moe_block_forward_dev(csk_moe_layer* layer, const float* d_x, int64_t T, float* d_router_out_or_null,
+                              float* d_out, void* stream);
 
 /* Routing for callers that must not allocate.  No counterpart in the reference
  * (its router keeps its logits in a std::vector on the host).
@@ -254,6 +283,15 @@ int csk_moe_ep_p2p_import(csk_moe_layer* layer, int32_t rank, int32_t world,
 int csk_moe_ep_p2p_local_ptrs(csk_moe_layer* layer, void** x16, void** info, void** back);
 int csk_moe_ep_p2p_import_ptrs(csk_moe_layer* layer, int32_t rank, int32_t world, void* const* x16,
                                void* const* info, void* const* back);
+/* The gather of the counts and the two barriers without a collective library: flags in a sync
+ * area every peer can write (it rides at the tail of the return buffer, so the handles above
+ * cover it).  which = 0 with d_counts [E] -> d_all_counts [world, E] replaces the all-gather;
+ * which = 1 / 2 with null pointers are the two barriers.  Every rank must call the same sequence.
+ * The wait inside is bounded (a few seconds); when it runs out csk_moe_sync reports
+ * CSK_ERR_DEVICE.  Only for ranks on DIFFERENT GPUs: ranks emulated on one GPU must not wait on
+ * one another's kernels (run their stages in lockstep instead). */
+int csk_moe_ep_p2p_sync_dev(csk_moe_layer* layer, int32_t which, const int32_t* d_counts, int32_t* d_all_counts,
+                            void* stream);
 int csk_moe_ep_p2p_counts_dev(csk_moe_layer* layer, const float* d_hidden, int64_t T,
                               const float* d_router_out_in, int32_t* d_counts, void* stream);
 int csk_moe_ep_p2p_scatter_dev(csk_moe_layer* layer, const float* d_hidden, int64_t T,
@@ -265,6 +303,11 @@ int csk_moe_ep_p2p_combine_dev(csk_moe_layer* layer, int64_t T, float* d_out, fl
 
 /* ---- knobs and observability ------------------------------------------- */
 int csk_moe_set_path(csk_moe_layer* layer, int32_t path /* CSK_PATH_* */);
+
+/* The gated activation and where the routing weight is applied -- the per-node settings
+ * expert_mlp_node::set_activation_type / set_weight_before_ffn (expert_mlp_node.h:44-52) --
+ * changed on an existing handle (the weights stay resident). */
+int csk_moe_set_activation(csk_moe_layer* layer, int32_t activation /* CSK_ACT_* */, int32_t weight_before_ffn);
 
 /* How the router reaches the reference's selection (moe_router_node.h:161-177: each
  * logit a sequential fp32 multiply-then-add chain over the hidden dimension, top-k by

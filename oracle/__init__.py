@@ -99,6 +99,9 @@ class _Lib:
         self._merge.restype = C.c_int
         self._merge.argtypes = [_f32p, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_void_p,
                                 C.c_int, _f32p]
+        self._rms = getattr(L, prefix + "rmsnorm")
+        self._rms.restype = C.c_int
+        self._rms.argtypes = [_f32p, _f32p, C.c_float, _f32p, C.c_int64, C.c_int64]
         self._layer = getattr(L, prefix + "moe_layer")
         self._layer.restype = C.c_int
         if self.is_ref:
@@ -154,6 +157,15 @@ class _Lib:
         if rc:
             self._err(rc, "router")
         return out, lg
+
+    def rmsnorm(self, x, w, eps=1e-5):
+        """RMSNorm over the last dimension of x [T,H] with weight [H]."""
+        x, w = _f32(x), _f32(w)
+        out = np.empty_like(x)
+        rc = self._rms(_fp(x), _fp(w), float(eps), _fp(out), x.shape[0], x.shape[1])
+        if rc:
+            self._err(rc, "rmsnorm")
+        return out
 
     # --- expert ----------------------------------------------------------
     def expert_token(self, x, w_up, w_gate, w_down, b_up, b_gate, b_down, H, F, act):

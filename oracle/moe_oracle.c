@@ -276,3 +276,19 @@ int orc_moe_layer(const float* hidden, int64_t t0, int64_t t1, int64_t H, int64_
   free(scaled);
   return 0;
 }
+
+/* include/coalsack/nn/nn_ops/rmsnorm_node.h:60-82 -- RMSNorm over the last dimension (the FFN norm in
+ * front of the router, src/llm/llm_engine.cpp:714-719): the sum of squares is a sequential fp32 chain of
+ * separate multiplies and adds, rms = sqrt(sum / H + eps), out = (x / rms) * w. */
+int orc_rmsnorm(const float* x, const float* w, float eps, float* out, int64_t T, int64_t H) {
+  for (int64_t i = 0; i < T; ++i) {
+    float sum_sq = 0;
+    for (int64_t j = 0; j < H; ++j) {
+      float val = x[i * H + j];
+      sum_sq += val * val;
+    }
+    float rms = sqrtf(sum_sq / (float)H + eps);
+    for (int64_t j = 0; j < H; ++j) out[i * H + j] = (x[i * H + j] / rms) * w[j];
+  }
+  return 0;
+}

@@ -26,6 +26,7 @@
 #include "coalsack/gguf/gguf_dequant.h"
 #include "coalsack/nn/nn_ops/expert_merge_node.h"
 #include "coalsack/nn/nn_ops/expert_mlp_node.h"
+#include "coalsack/nn/nn_ops/rmsnorm_node.h"
 #include "coalsack/nn/nn_ops/moe_router_node.h"
 #include "coalsack/tensor/dynamic_mx_tensor_message.h"
 #include "coalsack/tensor/dynamic_tensor_message.h"
@@ -266,6 +267,20 @@ int ref_moe_layer(const float* hidden, int64_t T, int64_t H, int64_t F, int64_t 
       g_last_error = err;
       return -1;
     }
+    return 0;
+  } catch (const std::exception& e) {
+    g_last_error = e.what();
+    return -1;
+  }
+}
+
+// FFN RMSNorm (rmsnorm_node::compute_test) over [T, H] with weight [H].
+int ref_rmsnorm(const float* x, const float* w, float eps, float* out, int64_t T, int64_t H) {
+  try {
+    rmsnorm_node node;
+    node.set_epsilon(eps);
+    dynamic_tensor r = node.compute_test(make_f32({1, T, H}, x), make_f32({H}, w));
+    std::memcpy(out, r.data_ptr<float>(), sizeof(float) * T * H);
     return 0;
   } catch (const std::exception& e) {
     g_last_error = e.what();

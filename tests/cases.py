@@ -103,3 +103,11 @@ def err_stats(got, ref):
 
 MAX_ABS_OVER_RMS = 2e-2   # parity tolerance: max-abs error <= 2e-2 x output RMS
 MEAN_REL = 5e-3           # parity tolerance: mean|err| / mean|ref| <= 5e-3
+
+
+def rmsnorm_case():
+    """Input [6, 320] (scaled so that rows differ in magnitude) and weight [320] of the RMSNorm fixture."""
+    g = np.random.default_rng(2024)
+    x = (g.standard_normal((6, 320)) * np.array([0.1, 1.0, 3.0, 10.0, 0.01, 1.0])[:, None]).astype(np.float32)
+    w = (1.0 + 0.1 * g.standard_normal(320)).astype(np.float32)
+    return x, w

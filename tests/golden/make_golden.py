@@ -75,6 +75,11 @@ def main():
     out, ro = r.moe_layer(h, Wg, rb, ex, sh.top_k, sh.act, nthreads=4)
     g["c4x8_router"], g["c4x8_out"] = ro, out
 
+    # the RMSNorm in front of the router (rmsnorm_node::compute_test, eps as graph_builder sets it)
+    x, w = cases.rmsnorm_case()
+    g["rmsnorm_out"] = r.rmsnorm(x, w, 1e-5)
+    g["rmsnorm_crc"] = cases.crc(x, w)
+
     np.savez_compressed(OUT, **g)
     print(f"wrote {OUT}: {os.path.getsize(OUT) / 1024:.1f} KiB, {len(g)} arrays")
 

@@ -1,8 +1,11 @@
 """The C++ operator bindings (coalsack_b200/host) inside coalsack's own headers:
 they compile against the reference tree in place of its CPU operators (CPU
-check), and a program that drives moe_router_node -> E x expert_mlp_node (through
+check); a program that drives moe_router_node -> E x expert_mlp_node (through
 process() with result_messages) -> expert_merge_node on the GPU reproduces the
-CPU checker (GPU check, run from the prebuilt binary)."""
+CPU checker; and the MoE sub-graph built by coalsack's own graph_builder
+(router, weight fetch, E expert nodes, merge, with their sync nodes) does so in
+the strict one-call-per-expert mode and in the fused one-call-per-layer mode
+(GPU checks, run from the prebuilt binaries)."""
 import os
 import subprocess
 
@@ -26,6 +29,10 @@ def test_bindings_compile_against_reference_headers():
     syms = subprocess.run(["nm", "-D", exe], capture_output=True, text=True).stdout
     for s in ("csk_moe_route", "csk_moe_expert_forward", "csk_moe_merge", "csk_moe_load_expert_mxfp4"):
         assert s in syms, f"{s}: the reference's CPU operator was compiled instead of the GPU binding"
+    assert os.path.exists(build_check.GRAPH_OUT)
+    syms = subprocess.run(["nm", "-D", build_check.GRAPH_OUT], capture_output=True, text=True).stdout
+    for s in ("csk_moe_route", "csk_moe_forward", "csk_moe_expert_forward", "csk_moe_load_expert_mxfp4", "csk_moe_set_activation"):
+        assert s in syms, f"{s}: graph_check does not reach the GPU bindings"
 
 
 @pytest.mark.gpu
@@ -61,3 +68,84 @@ def test_graph_nodes_on_gpu_match_checker(gpu_lib, golden, tag, tmp_path):
     assert np.array_equal(ro[..., 0], golden[f"{tag}_router"][..., 0])
     mx, mr = cases.err_stats(out, golden[f"{tag}_out"])
     assert mx <= cases.MAX_ABS_OVER_RMS and mr <= cases.MEAN_REL, (mx, mr)
+
+
+def _write_layer(path, sh, h, Wg, rb, ex):
+    with open(path, "wb") as f:
+        f.write(np.array([sh.num_experts, sh.top_k, sh.hidden, sh.ffn, h.shape[0], sh.act, int(sh.has_bias)],
+                         np.int32).tobytes())
+        f.write(np.ascontiguousarray(h, np.float32).tobytes())
+        f.write(Wg.tobytes())
+        f.write((rb if rb is not None else np.zeros(sh.num_experts, np.float32)).tobytes())
+        for e in range(sh.num_experts):
+            for n in ("w_up", "w_gate", "w_down"):
+                f.write(ex[n][e].tobytes())
+            if sh.has_bias:
+                for n in ("b_up", "b_gate", "b_down"):
+                    f.write(ex[n][e].tobytes())
+
+
+def _run_graph(inp, outp, mode, frames, T, k, H):
+    exe = build_check.GRAPH_OUT
+    r = subprocess.run([exe, str(inp), str(outp), mode, str(frames)], capture_output=True, text=True, timeout=180)
+    assert r.returncode == 0, r.stdout + r.stderr
+    raw = np.fromfile(outp, np.float32)
+    info = dict(kv.split("=") for kv in r.stdout.split("graph_check ok:")[1].split())
+    return raw[:T * k * 2].reshape(T, k, 2), raw[T * k * 2:].reshape(T, H), info
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("tag", ["tiny_a", "tiny_b", "tiny_d"])
+def test_graph_builder_subgraph_strict_and_fused(gpu_lib, golden, tag, tmp_path):
+    """coalsack's graph_builder wires router -> fetch -> experts -> merge; both modes reproduce the reference's
+    output for the layer, and in fused mode the second frame pulls no weights from the provider any more."""
+    if not os.path.exists(build_check.GRAPH_OUT):
+        pytest.skip("tests/cpp/_build/graph_check was not built (needs the reference checkout at build time)")
+    sh, h, Wg, rb, ex, wbf = cases.tiny_case(tag)
+    assert not wbf
+    inp = tmp_path / "in.bin"
+    _write_layer(inp, sh, h, Wg, rb, ex)
+    T, k, H = sh.tokens, sh.top_k, sh.hidden
+    for mode in ("strict", "fused"):
+        ro, out, info = _run_graph(inp, tmp_path / f"out_{mode}.bin", mode, 2, T, k, H)
+        assert np.array_equal(ro[..., 0], golden[f"{tag}_router"][..., 0]), mode
+        mx, mr = cases.err_stats(out, golden[f"{tag}_out"])
+        assert mx <= cases.MAX_ABS_OVER_RMS and mr <= cases.MEAN_REL, (tag, mode, mx, mr)
+        if mode == "fused":
+            # one probe of the first selected expert's shape; no expert is fetched again
+            assert int(info["provider_gets_last_frame"]) <= 1, info
+
+
+@pytest.mark.gpu
+def test_graph_fused_mode_at_the_20b_shape(gpu_lib, port, tmp_path):
+    """The 32-expert 2880 x 2880 layer with 32 tokens through the graph in fused mode: parity with the checker,
+    and the time of a frame next to one csk_moe_forward call on the same batch."""
+    import time
+    from coalsack_b200 import MoeLayer, synth
+    if not os.path.exists(build_check.GRAPH_OUT):
+        pytest.skip("tests/cpp/_build/graph_check was not built (needs the reference checkout at build time)")
+    sh = synth.C0
+    h, Wg, rb, ex = cases.layer_inputs(sh)
+    inp = tmp_path / "c0.bin"
+    _write_layer(inp, sh, h, Wg, rb, ex)
+    T, k, H = sh.tokens, sh.top_k, sh.hidden
+    ro, out, info = _run_graph(inp, tmp_path / "c0_out.bin", "fused", 4, T, k, H)
+    want_ro = port.router(h, Wg, rb, k)
+    assert np.array_equal(ro[..., 0], want_ro[..., 0])
+    want, _ = port.moe_layer(h, Wg, rb, ex, k, sh.act, nthreads=16, router_out=ro)
+    mx, mr = cases.err_stats(out, want)
+    assert mx <= cases.MAX_ABS_OVER_RMS and mr <= cases.MEAN_REL, (mx, mr)
+    lay = MoeLayer.from_shape(sh, max_tokens=64)
+    lay.set_router(Wg, rb)
+    lay.load_experts(ex)
+    for _ in range(3):
+        lay.forward(h)
+    t0 = time.perf_counter()
+    for _ in range(10):
+        lay.forward(h)
+    direct_ms = (time.perf_counter() - t0) * 100.0
+    lay.close()
+    graph_ms = float(info["last_frame_ms"])
+    print(f"fused graph frame {graph_ms:.3f} ms vs csk_moe_forward {direct_ms:.3f} ms ({graph_ms / direct_ms:.2f}x)")
+    # the graph adds the router node's own call, E + 3 message hops and the fetch node's residency check
+    assert graph_ms < 4.0 * direct_ms + 0.5

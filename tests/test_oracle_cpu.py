@@ -111,3 +111,17 @@ def test_port_equals_reference_on_fresh_inputs(port, ref):
     assert np.array_equal(ra, rb_) and np.array_equal(a, b)
     for x in (0, 1, 2, 254, 255):
         assert port.e8m0(x) == ref.e8m0(x)
+
+
+def test_rmsnorm_golden_and_reference(port, golden):
+    """The restated RMSNorm equals the reference's node output bit for bit (fixture), and the reference
+    itself on fresh inputs where its compiled wrapper is present."""
+    x, w = cases.rmsnorm_case()
+    assert cases.crc(x, w) == golden["rmsnorm_crc"]
+    assert np.array_equal(port.rmsnorm(x, w, 1e-5), golden["rmsnorm_out"])
+    import oracle
+    if oracle.have_ref():
+        g = np.random.default_rng(7)
+        x2 = g.standard_normal((9, 2880)).astype(np.float32)
+        w2 = g.standard_normal(2880).astype(np.float32)
+        assert np.array_equal(port.rmsnorm(x2, w2, 1e-6), oracle.ref().rmsnorm(x2, w2, 1e-6))
