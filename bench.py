@@ -276,7 +276,7 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
         runner = ep.EpBench(sh, rank, world, local)
     else:
-        runner = SingleGpu(sh, local)
+        runner = SingleGpu(sh, local, args.path)
 
     sampler = ClockSampler(local)
     warmup = max(args.warmup, 3)
@@ -390,9 +390,9 @@ class SingleGpu:
     """The layer on one GPU: weights resident, one batch in HBM (``step_dev``)
     or in pinned host memory (``time_e2e``)."""
 
-    def __init__(self, sh, local):
+    def __init__(self, sh, local, path="auto"):
         import torch
-        from coalsack_b200 import MoeLayer
+        from coalsack_b200 import MoeLayer, moe
         self.torch = torch
         self.sh = sh
         dev = torch.device("cuda", local)
@@ -401,6 +401,8 @@ class SingleGpu:
         for e in range(sh.num_experts):
             w = synth.expert_weights(sh, e)
             self.layer.load_expert(e, w["w_up"], w["w_gate"], w["w_down"], w["b_up"], w["b_gate"], w["b_down"])
+        self.layer.set_path({"auto": moe.PATH_AUTO, "stream": moe.PATH_STREAM, "tile": moe.PATH_TILE,
+                             "tile_pair": moe.PATH_TILE_PAIR}[path])
         h = synth.hidden_states(sh)
         self.h_host = torch.from_numpy(h).pin_memory()
         self.out_host = torch.empty_like(self.h_host).pin_memory()
@@ -454,6 +456,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=None, help="override the workload's token count")
     ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
                     help="N > 1: split the workload's tokens over the ranks (strong) or give every rank all of them (weak)")
+    ap.add_argument("--path", default="auto", choices=["auto", "stream", "tile", "tile_pair"],
+                    help="force one expert kernel (N=1 profiling runs); auto picks by rows per expert")
     ap.add_argument("--skip-cpu", action="store_true", help="leave out the cpu_baseline leg (profiling runs)")
     ap.add_argument("--skip-decode", action="store_true", help="leave out the decode sweep (profiling runs)")
     ap.add_argument("--skip-e2e", action="store_true", help="leave out the host-buffer leg (profiling runs)")

@@ -12,6 +12,7 @@
 #include "csk_kernels.cuh"
 #include "csk_stream.cuh"
 #include "csk_tile.cuh"
+#include "csk_tile2.cuh"
 
 using namespace csk;
 
@@ -107,6 +108,7 @@ struct csk_moe_layer {
   int path = CSK_PATH_AUTO;
   int sm_count = 148;
   TileState tile;  // tensor maps and launch state of the tensor-core path
+  PairState pair;  // the CTA-pair kernel, where clusters of two can be launched
 
   // Small batches are launch-bound: their kernel sequence is captured once per
   // (T, buffers, stream) into a CUDA graph and replayed.
@@ -372,11 +374,14 @@ int stream_tile_rows(const csk_moe_layer* L, int64_t rows) {
 
 int choose_path(const csk_moe_layer* L, int64_t rows) {
   if (L->path == CSK_PATH_STREAM) return CSK_PATH_STREAM;
-  if (L->path == CSK_PATH_TILE) return CSK_PATH_TILE;
+  if (L->path == CSK_PATH_TILE || L->path == CSK_PATH_TILE_PAIR) return CSK_PATH_TILE;
   // the tensor-core tiles are 128 rows tall: worth it once the average expert
   // fills a good part of one
   return (L->tile.available && rows >= 48 * (int64_t)std::max(1, L->Eloc)) ? CSK_PATH_TILE : CSK_PATH_STREAM;
 }
+
+// the CTA-pair kernel runs only when asked for by name (and clusters of two can be launched)
+bool use_pairs(const csk_moe_layer* L) { return L->pair.available && L->path == CSK_PATH_TILE_PAIR; }
 
 int tile_rows_for(const csk_moe_layer* L, int path, int64_t rows) {
   return path == CSK_PATH_TILE ? kTileM : stream_tile_rows(L, rows);
@@ -389,10 +394,17 @@ int launch_experts(csk_moe_layer* L, int path, int tile_rows, int64_t n_rows_hin
                    float* const* out_row_ptr = nullptr) {
   if (path == CSK_PATH_TILE) {
     if (x16 != L->d_x16) return fail(L, CSK_ERR_INVALID, "the tile path reads the handle's own row buffer");
-    int rc = tile_launch(L->tile, L->d_weights, L->expert_stride, L->off_tgu, L->off_td, L->off_bias,
-                         L->off_meta, L->Tgu, L->Td, L->d_a16, L->lda, y, ldy, out_row_map, out_row_ptr, L->d_tiles,
-                         L->d_meta, L->cfg.has_bias, L->cfg.activation, L->F, L->sm_count, s,
-                         [&]() { tm.mark(); }, L->debug_stall);
+    int rc;
+    if (use_pairs(L))
+      rc = pair_launch(L->pair, L->tile, L->tile.tmap_xh, L->tile.tmap_ah, L->d_weights, L->expert_stride, L->off_tgu,
+                       L->off_td, L->off_bias, L->off_meta, L->Tgu, L->Td, L->d_a16, L->lda, y, ldy, out_row_map,
+                       out_row_ptr, L->d_tiles, L->d_meta, L->cfg.has_bias, L->cfg.activation, L->F, s,
+                       [&]() { tm.mark(); }, L->debug_stall);
+    else
+      rc = tile_launch(L->tile, L->d_weights, L->expert_stride, L->off_tgu, L->off_td, L->off_bias,
+                       L->off_meta, L->Tgu, L->Td, L->d_a16, L->lda, y, ldy, out_row_map, out_row_ptr, L->d_tiles,
+                       L->d_meta, L->cfg.has_bias, L->cfg.activation, L->F, L->sm_count, s,
+                       [&]() { tm.mark(); }, L->debug_stall);
     L->debug_stall = false;
     if (rc) return fail(L, rc, "tensor-core path: %s", L->tile.err.c_str());
     L->last.launches += 2;
@@ -661,7 +673,7 @@ int csk_moe_create(const csk_moe_config* cfg, csk_moe_layer** out) {
   CK(cudaMalloc(&L->d_p2p_base, sizeof(int) * L->E));
   L->E_router = L->E;
   CK(cudaMalloc(&L->d_out, sizeof(float) * L->max_T * L->H));
-  const size_t pad_rows = kTileM;
+  const size_t pad_rows = kTileM;  // a row tile's loads may reach this far past the last row
   CK(cudaMalloc(&L->d_x16, sizeof(__half) * (L->max_rows + pad_rows) * L->ldx));
   CK(cudaMemset(L->d_x16, 0, sizeof(__half) * (L->max_rows + pad_rows) * L->ldx));
   CK(cudaMalloc(&L->d_a16, sizeof(__half) * (L->max_rows + pad_rows) * L->lda));
@@ -685,6 +697,7 @@ int csk_moe_create(const csk_moe_config* cfg, csk_moe_layer** out) {
   {
     int rc = tile_init(L->tile, cfg->device);
     if (!rc) rc = tile_set_buffers(L->tile, L->d_x16, L->ldx, L->d_a16, L->lda, (size_t)L->max_rows + pad_rows);
+    if (!rc) rc = pair_init(L->pair, L->tile, L->sm_count);
     if (rc) {
       rc = fail(nullptr, rc, "tensor-core path setup: %s", L->tile.err.c_str());
       csk_moe_destroy(L);
@@ -923,7 +936,9 @@ int csk_moe_expert_resident(const csk_moe_layer* L, int32_t expert_id) {
 
 int csk_moe_set_path(csk_moe_layer* L, int32_t path) {
   if (check_layer(L)) return CSK_ERR_INVALID;
-  if (path < CSK_PATH_AUTO || path > CSK_PATH_TILE) return fail(L, CSK_ERR_INVALID, "unknown path %d", path);
+  if (path < CSK_PATH_AUTO || path > CSK_PATH_TILE_PAIR) return fail(L, CSK_ERR_INVALID, "unknown path %d", path);
+  if (path == CSK_PATH_TILE_PAIR && !L->pair.available)
+    return fail(L, CSK_ERR_INVALID, "the CTA-pair kernel is not available on this device: %s", L->pair.err.c_str());
   L->path = path;
   drop_graphs(L);
   return CSK_OK;

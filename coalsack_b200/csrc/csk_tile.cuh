@@ -173,8 +173,10 @@ __global__ void k_unpack_tile(const uint8_t* __restrict__ packed, uint8_t* __res
 struct TileState {
   bool available = false;
   std::string err;
-  CUtensorMap tmap_x{};   // grouped input rows  [rows, ldx] fp16
-  CUtensorMap tmap_a{};   // activated rows      [rows, lda] fp16
+  CUtensorMap tmap_x{};   // grouped input rows  [rows, ldx] fp16, boxes of kTileM rows
+  CUtensorMap tmap_a{};   // activated rows      [rows, lda] fp16, boxes of kTileM rows
+  CUtensorMap tmap_xh{};  // the same with boxes of half a row tile (the CTA-pair kernel's half tiles)
+  CUtensorMap tmap_ah{};
   bool maps_ready = false;
   void* encode_fn = nullptr;
 };
@@ -188,6 +190,12 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
       "l"(map), "r"(x), "r"(y), "r"(bar)
       : "memory");
+}
+// True in exactly one lane of a converged warp.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .b32 rx;\n\t.reg .pred px;\n\telect.sync rx|px, 0xffffffff;\n\tselp.b32 %0, 1, 0, px;\n\t}" : "=r"(pred));
+  return pred != 0;
 }
 // K-major operand tile with 128-byte swizzle: rows of 128 bytes, groups of 8
 // rows 1024 bytes apart.
@@ -377,45 +385,52 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
-    if (lane == 0) {
+    // The WHOLE warp runs this loop and one elected lane issues.  tcgen05.mma and tcgen05.commit take
+    // their operands from the warp-uniform register file: in a loop that only one lane runs (a divergent
+    // branch) every descriptor and address has to be moved across for every instruction, and a K=16 MMA
+    // then issues once per ~185 clocks whatever its shape (measured; the pipe needs 96 for 128 x 192 x 16).
+    // Run warp-wide, the same loop keeps the tensor pipe full.
+    {
       int s = 0, sa = 0;
       uint32_t ph = 0, pha = 0;
       long it = 0;
       bool ok = true;
+      const uint32_t tb = __shfl_sync(0xffffffffu, tmem_base, 0);
       for (long item = blockIdx.x; ok && item < n_items; item += gridDim.x, ++it) {
         const RowTile rt = A.tiles[item / L.n_tiles];
         const int halves = L.halves((int)(item % L.n_tiles));
         const int n_mma = max(16, (rt.rows + 15) & ~15);
         const uint32_t idesc = umma_idesc_f16(n_mma);
-        if (!mbar_wait(bar_tmem_empty, (uint32_t)(it & 1) ^ 1, abort_flag)) {
-          ok = false;
-          break;
-        }
+        ok = __all_sync(0xffffffffu, mbar_wait(bar_tmem_empty, (uint32_t)(it & 1) ^ 1, abort_flag));
+        if (!ok) break;
         tc_fence_after();
         for (int kt = 0; kt < KT; ++kt) {
-          if (!mbar_wait(bar_full_raw(s), ph, abort_flag)) {
-            ok = false;
-            break;
-          }
+          ok = __all_sync(0xffffffffu, mbar_wait(bar_full_raw(s), ph, abort_flag));
+          if (!ok) break;
           const uint64_t db = umma_desc_sw128(smem_base + (uint32_t)s * kTileRawBytes);
           for (int h = 0; h < 2; ++h) {
             // the halves of a k-step arrive one after the other: the MMAs of the first run while
             // the second is still being converted
-            if (!mbar_wait(bar_full_a(sa, h), pha, abort_flag)) {
-              ok = false;
-              break;
-            }
+            ok = __all_sync(0xffffffffu, mbar_wait(bar_full_a(sa, h), pha, abort_flag));
+            if (!ok) break;
             if (h >= halves) continue;
             tc_fence_after();
-            const uint32_t d_tmem = tmem_base + (uint32_t)h * kTileM;
-            const uint32_t a_tmem = tmem_base + kTmemABase + (uint32_t)sa * 64 + (uint32_t)h * 32;
+            const uint32_t d_tmem = tb + (uint32_t)h * kTileM;
+            const uint32_t a_tmem = tb + kTmemABase + (uint32_t)sa * 64 + (uint32_t)h * 32;
+            if (elect_one()) {
 #pragma unroll
-            for (int k4 = 0; k4 < kTileK / 16; ++k4)
-              umma_f16_ts(d_tmem, a_tmem + (uint32_t)k4 * 8, db + (uint64_t)(k4 * 2), idesc, (kt | k4) ? 1u : 0u);
+              for (int k4 = 0; k4 < kTileK / 16; ++k4)
+                umma_f16_ts(d_tmem, a_tmem + (uint32_t)k4 * 8, db + (uint64_t)(k4 * 2), idesc, (kt | k4) ? 1u : 0u);
+            }
+            __syncwarp();
           }
           if (!ok) break;
-          umma_commit(bar_empty_raw(s));
-          umma_commit(bar_empty_a(sa));
+          if (elect_one()) {
+            umma_commit(bar_empty_raw(s));
+            umma_commit(bar_empty_a(sa));
+            if (kt == KT - 1) umma_commit(bar_tmem_full);
+          }
+          __syncwarp();
           if (++s == NR) {
             s = 0;
             ph ^= 1;
@@ -425,13 +440,15 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
             pha ^= 1;
           }
         }
-        if (ok) umma_commit(bar_tmem_full);
       }
       // everything issued has to retire before tensor memory is freed
-      umma_commit(bar_drain);
-      const long long t0 = clock64();
-      while (!mbar_try(bar_drain, 0) && clock64() - t0 < drain_budget()) {
+      if (lane == 0) {
+        umma_commit(bar_drain);
+        const long long t0 = clock64();
+        while (!mbar_try(bar_drain, 0) && clock64() - t0 < drain_budget()) {
+        }
       }
+      __syncwarp();
     }
   } else if (warp < 2 + kDequantWarps) {
     // ------------------------------ dequantisers ------------------------------
@@ -623,11 +640,11 @@ inline int tile_init(TileState& st, int device) {
 }
 inline void tile_destroy(TileState&) {}
 
-// [rows, ld] fp16 row-major, boxes of kTileM rows x 64 columns, 128-byte swizzle.
-inline int tile_make_map(TileState& st, CUtensorMap* map, const __half* base, size_t rows, int ld) {
+// [rows, ld] fp16 row-major, boxes of box_rows rows x 64 columns, 128-byte swizzle.
+inline int tile_make_map(TileState& st, CUtensorMap* map, const __half* base, size_t rows, int ld, int box_rows = kTileM) {
   const cuuint64_t dims[2] = {(cuuint64_t)ld, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(__half)};
-  const cuuint32_t box[2] = {(cuuint32_t)kTileK, (cuuint32_t)kTileM};
+  const cuuint32_t box[2] = {(cuuint32_t)kTileK, (cuuint32_t)box_rows};
   const cuuint32_t estr[2] = {1, 1};
   CUresult r = ((EncodeTiledFn)st.encode_fn)(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)base, dims, strides, box,
                                              estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -644,6 +661,8 @@ inline int tile_set_buffers(TileState& st, const __half* x16, int ldx, const __h
   int rc = tile_make_map(st, &st.tmap_x, x16, rows_alloc, ldx);
   if (rc) return rc;
   rc = tile_make_map(st, &st.tmap_a, a16, rows_alloc, lda);
+  if (!rc) rc = tile_make_map(st, &st.tmap_xh, x16, rows_alloc, ldx, kTileM / 2);
+  if (!rc) rc = tile_make_map(st, &st.tmap_ah, a16, rows_alloc, lda, kTileM / 2);
   if (rc) return rc;
   st.maps_ready = true;
   return CSK_OK;

@@ -21,7 +21,7 @@ import numpy as np
 from . import _lib
 from ._lib import Config, Timings
 
-PATH_AUTO, PATH_STREAM, PATH_TILE = 0, 1, 2
+PATH_AUTO, PATH_STREAM, PATH_TILE, PATH_TILE_PAIR = 0, 1, 2, 3
 
 
 class CskError(RuntimeError):

@@ -46,7 +46,12 @@ enum { CSK_ACT_MODIFIED_SWIGLU = 0, CSK_ACT_STANDARD_SWIGLU = 1 };
 
 /* Which expert kernel serves a forward call. AUTO picks by the number of
  * (token, expert) rows; the other two force one kernel (tests, benchmarks). */
-enum { CSK_PATH_AUTO = 0, CSK_PATH_STREAM = 1, CSK_PATH_TILE = 2 };
+enum {
+  CSK_PATH_AUTO = 0,
+  CSK_PATH_STREAM = 1,      /* weight-streaming kernel (few rows per expert)                    */
+  CSK_PATH_TILE = 2,        /* tensor-core kernel, one CTA per work item                        */
+  CSK_PATH_TILE_PAIR = 3    /* tensor-core kernel on CTA pairs (cta_group::2); needs cluster launch */
+};
 
 /* Layer description: graph_builder::config num_experts / expert_top_k /
  * use_sigmoid_gating / weight_before_ffn (include/coalsack/llm/graph_builder.h:29-44)

@@ -7,7 +7,7 @@ tokens permutes the outputs bit for bit; the two expert kernels agree)."""
 import numpy as np
 import pytest
 
-from coalsack_b200 import MoeLayer, PATH_STREAM, PATH_TILE, synth
+from coalsack_b200 import MoeLayer, PATH_STREAM, PATH_TILE, PATH_TILE_PAIR, synth
 from tests import cases
 
 pytestmark = pytest.mark.gpu
@@ -73,6 +73,13 @@ def _check_config(sh, port, sample=512, also_stream=True):
         assert mx <= 1e-2 and mr <= 2e-3, ("stream vs tile", mx, mr)
         mx, mr = cases.err_stats(out_s[pick], want)
         assert mx <= cases.MAX_ABS_OVER_RMS and mr <= cases.MEAN_REL
+    # the CTA-pair tensor kernel (opt-in) on the same rows
+    lay.set_path(PATH_TILE_PAIR)
+    out_2, _ = lay.forward(h, router_out=ro)
+    mx2, mr2 = cases.err_stats(out_2[pick], want)
+    assert mx2 <= cases.MAX_ABS_OVER_RMS and mr2 <= cases.MEAN_REL, ("cta pair", sh.name, mx2, mr2)
+    mx2, mr2 = cases.err_stats(out_2, out)
+    assert mx2 <= 1e-2 and mr2 <= 2e-3, ("cta pair vs one cta", mx2, mr2)
     lay.close()
     return mx, mr
 

@@ -4,7 +4,7 @@ inputs, and the reference itself where its compiled wrapper travelled along."""
 import numpy as np
 import pytest
 
-from coalsack_b200 import (CskError, MoeLayer, PATH_STREAM, PATH_TILE, expert_merge_node, expert_mlp_node,
+from coalsack_b200 import (CskError, MoeLayer, PATH_STREAM, PATH_TILE, PATH_TILE_PAIR, expert_merge_node, expert_mlp_node,
                            moe_router_node, synth)
 from tests import cases
 
@@ -254,7 +254,7 @@ def test_many_rows_one_expert_and_ragged(gpu_lib, port):
     assert rows[0] > 250 and rows[5:].sum() == 0 and rows.sum() == 600
     want, _ = port.moe_layer(h, Wg, rb, ex, 2, sh.act, nthreads=8, router_out=ro)
     assert_close(out, want, "skewed")
-    for path in (PATH_STREAM, PATH_TILE):
+    for path in (PATH_STREAM, PATH_TILE, PATH_TILE_PAIR):
         lay.set_path(path)
         out2, _ = lay.forward(h, router_out=ro)
         assert_close(out2, want, f"skewed path {path}")
@@ -326,11 +326,15 @@ def test_expert_node_empty_and_dense(gpu_lib, golden):
 
 
 # ---- the tensor-core (tcgen05) kernel, forced --------------------------------------
+TILE_KERNELS = [pytest.param(PATH_TILE, id="one_cta"), pytest.param(PATH_TILE_PAIR, id="cta_pair")]
+
+
+@pytest.mark.parametrize("tile", TILE_KERNELS)
 @pytest.mark.parametrize("tag", list(cases.TINY_CASES))
-def test_tile_path_tiny_layers(gpu_lib, golden, tag):
+def test_tile_path_tiny_layers(gpu_lib, golden, tag, tile):
     sh, h, Wg, rb, ex, wbf = cases.tiny_case(tag)
     lay = make_layer(sh, Wg, rb, ex, wbf)
-    lay.set_path(PATH_TILE)
+    lay.set_path(tile)
     out, ro = lay.forward(h)
     assert lay.timings()["path"] == PATH_TILE
     assert same_experts(ro, golden[f"{tag}_router"])
@@ -346,11 +350,12 @@ def test_tile_path_tiny_layers(gpu_lib, golden, tag):
     lay.close()
 
 
-def test_tile_path_c0(gpu_lib, golden, port):
+@pytest.mark.parametrize("tile", TILE_KERNELS)
+def test_tile_path_c0(gpu_lib, golden, port, tile):
     sh = synth.C0
     h, Wg, rb, ex = cases.layer_inputs(sh, 32)
     lay = make_layer(sh, Wg, rb, ex, max_tokens=32)
-    lay.set_path(PATH_TILE)
+    lay.set_path(tile)
     out1, ro1 = lay.forward(h[:1])
     assert_close(out1, golden["c0_t1_out"], "c0 T=1 tile")
     out32, ro32 = lay.forward(h)
@@ -371,7 +376,7 @@ def test_tile_path_wide_exponents(gpu_lib, port):
         ex["w_down"][e] = synth.mxfp4_matrix(sh.seed, synth._T_WDOWN, e, 128, 128, 100, 136)
     lay = make_layer(sh, Wg, rb, ex, max_tokens=200)
     want = None
-    for path in (PATH_TILE, PATH_STREAM):
+    for path in (PATH_TILE, PATH_TILE_PAIR, PATH_STREAM):
         lay.set_path(path)
         out, ro = lay.forward(h)
         if want is None:
@@ -402,7 +407,7 @@ def test_edge_scale_bytes(gpu_lib, port):
     for which, name in enumerate(("w_up", "w_gate", "w_down", "w_up", "w_gate", "w_down")):
         assert np.array_equal(lay.unpack_expert(1, which), ex[name][1]), which
     want = None
-    for path in (PATH_STREAM, PATH_TILE):
+    for path in (PATH_STREAM, PATH_TILE, PATH_TILE_PAIR):
         lay.set_path(path)
         out, ro = lay.forward(h)
         if want is None:
@@ -413,7 +418,8 @@ def test_edge_scale_bytes(gpu_lib, port):
     lay.close()
 
 
-def test_bounded_wait_runs_out_and_the_handle_recovers(gpu_lib, port):
+@pytest.mark.parametrize("tile", TILE_KERNELS)
+def test_bounded_wait_runs_out_and_the_handle_recovers(gpu_lib, port, tile):
     """The failure path of the tensor-core kernel, made to happen without any fault: the wait budget is
     cut to 0.1 ms and the next launch's copy role is told to issue nothing, so the MMA, dequantiser and
     epilogue roles all wait on barriers that nothing arms, give up, tear down (tensor memory freed) and
@@ -421,7 +427,7 @@ def test_bounded_wait_runs_out_and_the_handle_recovers(gpu_lib, port):
     sh = synth.tiny(seed=49, E=4, k=2, H=128, F=128, T=96, has_bias=True)
     h, Wg, rb, ex = cases.layer_inputs(sh, router_scale=50.0)
     lay = make_layer(sh, Wg, rb, ex, max_tokens=sh.tokens)
-    lay.set_path(PATH_TILE)
+    lay.set_path(tile)
     good, ro = lay.forward(h)
     try:
         lay.debug_set(lay.DEBUG_WAIT_BUDGET, 200_000)
