@@ -297,10 +297,11 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
   uint8_t* ctrl = smem + (size_t)NR * kTileRawBytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(ctrl);
   const uint32_t bar_base = smem_u32(bars);
+  // k-step c uses shared-memory stage c % NR and tensor-memory slot c % NA; one barrier per stage tells both the
+  // copy role (stage free) and the dequantisers (slot of k-step c - NA free) that its MMAs have retired
   auto bar_full_raw = [&](int s) { return bar_base + 8u * s; };               // TMA landed
-  auto bar_empty_raw = [&](int s) { return bar_base + 8u * (8 + s); };        // MMAs of that k-step retired
-  auto bar_full_a = [&](int s, int hf) { return bar_base + 8u * (16 + 2 * s + hf); };  // half tile written to tensor memory
-  auto bar_empty_a = [&](int s) { return bar_base + 8u * (20 + s); };
+  auto bar_retired = [&](int s) { return bar_base + 8u * (8 + s); };          // MMAs of the k-step in that stage retired
+  auto bar_full_a = [&](int s) { return bar_base + 8u * (16 + s); };          // both halves of the slot are in tensor memory
   const uint32_t bar_tmem_full = bar_base + 8u * 24;    // both accumulators complete
   const uint32_t bar_tmem_empty = bar_base + 8u * 26;   // all epilogue warps done reading them
   const uint32_t bar_drain = bar_base + 8u * 28;
@@ -312,13 +313,9 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
   if (threadIdx.x == 0) {
     for (int s = 0; s < 8; ++s) {
       mbar_init(bar_full_raw(s), 1);
-      mbar_init(bar_empty_raw(s), 1);
+      mbar_init(bar_retired(s), 1);
     }
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(bar_full_a(s, 0), kDequantWarps / 2);
-      mbar_init(bar_full_a(s, 1), kDequantWarps / 2);
-      mbar_init(bar_empty_a(s), 1);
-    }
+    for (int s = 0; s < 2; ++s) mbar_init(bar_full_a(s), kDequantWarps / 2);
     mbar_init(bar_tmem_full, 1);
     mbar_init(bar_tmem_empty, kEpilogueWarps);
     mbar_init(bar_drain, 1);
@@ -353,7 +350,7 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
             A.weights + (size_t)rt.expert * A.expert_stride + A.mat_offset + (size_t)nt * KT * kTilePacked;
         const uint32_t w_bytes = (uint32_t)L.halves(nt) * kHalfPacked;
         for (int kt = 0; kt < KT; ++kt) {
-          if (!mbar_wait(bar_empty_raw(s), ph ^ 1, abort_flag)) {
+          if (!mbar_wait(bar_retired(s), ph ^ 1, abort_flag)) {
             ok = false;
             break;
           }
@@ -389,56 +386,41 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
     // their operands from the warp-uniform register file: in a loop that only one lane runs (a divergent
     // branch) every descriptor and address has to be moved across for every instruction, and a K=16 MMA
     // then issues once per ~185 clocks whatever its shape (measured; the pipe needs 96 for 128 x 192 x 16).
-    // Run warp-wide, the same loop keeps the tensor pipe full.
+    // The loop is also kept to ONE barrier test per k-step (a satisfied test still costs ~110 clocks): the
+    // token tile of a stage needs no test of its own, because the dequantisers waited for the same stage's
+    // copies before they wrote the slot this warp waits for.  Both halves' MMAs are always issued; a half
+    // that is padding (the last weight tile of a plain matrix) accumulates into columns nobody reads.
     {
-      int s = 0, sa = 0;
-      uint32_t ph = 0, pha = 0;
-      long it = 0;
+      uint32_t c = 0, it = 0;
       bool ok = true;
       const uint32_t tb = __shfl_sync(0xffffffffu, tmem_base, 0);
+      const uint64_t db0 = umma_desc_sw128(smem_base);
+      const uint32_t a_tmem0 = tb + kTmemABase;
       for (long item = blockIdx.x; ok && item < n_items; item += gridDim.x, ++it) {
         const RowTile rt = A.tiles[item / L.n_tiles];
-        const int halves = L.halves((int)(item % L.n_tiles));
         const int n_mma = max(16, (rt.rows + 15) & ~15);
         const uint32_t idesc = umma_idesc_f16(n_mma);
-        ok = __all_sync(0xffffffffu, mbar_wait(bar_tmem_empty, (uint32_t)(it & 1) ^ 1, abort_flag));
+        ok = __all_sync(0xffffffffu, mbar_wait(bar_tmem_empty, (it & 1u) ^ 1u, abort_flag));
         if (!ok) break;
         tc_fence_after();
-        for (int kt = 0; kt < KT; ++kt) {
-          ok = __all_sync(0xffffffffu, mbar_wait(bar_full_raw(s), ph, abort_flag));
+        for (int kt = 0; kt < KT; ++kt, ++c) {
+          const uint32_t s = c % NR, sa = c % NA;
+          ok = __all_sync(0xffffffffu, mbar_wait(bar_full_a(sa), (c / NA) & 1u, abort_flag));
           if (!ok) break;
-          const uint64_t db = umma_desc_sw128(smem_base + (uint32_t)s * kTileRawBytes);
-          for (int h = 0; h < 2; ++h) {
-            // the halves of a k-step arrive one after the other: the MMAs of the first run while
-            // the second is still being converted
-            ok = __all_sync(0xffffffffu, mbar_wait(bar_full_a(sa, h), pha, abort_flag));
-            if (!ok) break;
-            if (h >= halves) continue;
-            tc_fence_after();
-            const uint32_t d_tmem = tb + (uint32_t)h * kTileM;
-            const uint32_t a_tmem = tb + kTmemABase + (uint32_t)sa * 64 + (uint32_t)h * 32;
-            if (elect_one()) {
-#pragma unroll
-              for (int k4 = 0; k4 < kTileK / 16; ++k4)
-                umma_f16_ts(d_tmem, a_tmem + (uint32_t)k4 * 8, db + (uint64_t)(k4 * 2), idesc, (kt | k4) ? 1u : 0u);
-            }
-            __syncwarp();
-          }
-          if (!ok) break;
+          tc_fence_after();
+          const uint64_t db = db0 + (uint64_t)((s * (uint32_t)kTileRawBytes) >> 4);  // start-address field, 16-byte units
+          const uint32_t a_tmem = a_tmem0 + sa * 64;
           if (elect_one()) {
-            umma_commit(bar_empty_raw(s));
-            umma_commit(bar_empty_a(sa));
+#pragma unroll
+            for (int k4 = 0; k4 < kTileK / 16; ++k4)
+              umma_f16_ts(tb, a_tmem + (uint32_t)k4 * 8, db + (uint64_t)(k4 * 2), idesc, (kt | k4) ? 1u : 0u);
+#pragma unroll
+            for (int k4 = 0; k4 < kTileK / 16; ++k4)
+              umma_f16_ts(tb + kTileM, a_tmem + 32 + (uint32_t)k4 * 8, db + (uint64_t)(k4 * 2), idesc, (kt | k4) ? 1u : 0u);
+            umma_commit(bar_retired(s));
             if (kt == KT - 1) umma_commit(bar_tmem_full);
           }
           __syncwarp();
-          if (++s == NR) {
-            s = 0;
-            ph ^= 1;
-          }
-          if (++sa == NA) {
-            sa = 0;
-            pha ^= 1;
-          }
         }
       }
       // everything issued has to retire before tensor memory is freed
@@ -461,7 +443,6 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
     const int grp = (warp - 2) >> 2;         // which k-steps / which slot
     const int trow = quarter * 32 + lane;
     long c = 0;                              // running k-step number of this CTA
-    uint32_t uses = 0;                       // how often this group has filled its slot
     bool ok = true;
     auto convert = [&](const uint8_t* packed, int emax, uint32_t (&h)[2][16]) {
 #pragma unroll
@@ -499,27 +480,23 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
         const uint32_t t_slot = tmem_base + ((uint32_t)(quarter * 32) << 16) + kTmemABase + (uint32_t)grp * 64;
         uint32_t h[2][16];
         convert(packed, emax, h);
-        if (!mbar_wait(bar_empty_a(grp), (uses & 1) ^ 1, abort_flag)) {
+        // the slot was last read by k-step c - 2
+        if (c >= NA && !mbar_wait(bar_retired((int)((c - NA) % NR)), (uint32_t)(((c - NA) / NR) & 1), abort_flag)) {
           ok = false;
           break;
         }
-        ++uses;
         tc_fence_after();
         tmem_st16(t_slot, h[0]);
         tmem_st16(t_slot + 16, h[1]);
+        if (halves > 1) {
+          convert(packed + kHalfPacked, emax, h);  // reuses h: the compiler orders it after the stores above
+          tmem_st16(t_slot + 32, h[0]);
+          tmem_st16(t_slot + 48, h[1]);
+        }
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_full_a(grp, 0));
-        if (halves > 1) {
-          convert(packed + kHalfPacked, emax, h);
-          tmem_st16(t_slot + 32, h[0]);
-          tmem_st16(t_slot + 48, h[1]);
-          tmem_st_wait();
-          tc_fence_before();
-          __syncwarp();
-        }
-        if (lane == 0) mbar_arrive(bar_full_a(grp, 1));
+        if (lane == 0) mbar_arrive(bar_full_a(grp));
       }
     }
   } else {
