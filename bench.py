@@ -55,8 +55,8 @@ def measured_peaks():
 # (--metrics dram__bytes_read.sum,dram__bytes_write.sum) of this program on the same workload, single GPU.
 # Key = (workload name, tokens, kernel).  Other workloads report null.
 MEASURED_TRAFFIC = {
-    ("c1_gptoss20b_prefill4096_zipf", 4096, "k_tile<gated>"): 476.3e6,
-    ("c3_gptoss120b_decode", 64, "k_stream<gated>"): 953.8e6,
+    ("c2_gptoss120b_prefill8192", 8192, "k_tile<gated>"): 1599.2e6,   # 1417.8 MB read + 181.4 MB written
+    ("c3_gptoss120b_decode", 64, "k_stream<gated>"): 954.3e6,        # 949.0 MB read + 5.3 MB written
 }
 
 

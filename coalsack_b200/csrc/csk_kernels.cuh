@@ -50,11 +50,11 @@ __global__ void k_repack(const uint8_t* __restrict__ src0, const uint8_t* __rest
         uint32_t e = 0;  // padding: zero codes under the smallest scale
         if (row < L.N && col < L.K) {
           const uint8_t* blk = src + ((size_t)row * (L.K / 32) + col / 32) * 17;
-          e = blk[0];
+          e = min((uint32_t)blk[0], 254u);  // scale byte 255 is read as 254: stored that way, so the kernel need not clamp
           // a block of zero codes is zero under any scale: it does not widen the matrix's exponent range
           bool any = false;
           for (int j = 1; j < 17; ++j) any = any || blk[j] != 0;
-          if (any) emax = max(emax, min((int)e, 254));
+          if (any) emax = max(emax, (int)e);
         }
         out |= e << (8 * slot);
       }

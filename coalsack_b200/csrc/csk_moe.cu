@@ -44,7 +44,7 @@ struct csk_moe_layer {
   float* d_wnorm = nullptr;    // [E] 2-norms of the gate rows
   int* d_fb_list = nullptr;    // [max_T] tokens the fast router could not certify
   int* d_fb = nullptr;         // [0] entries of d_fb_list, [1] ticket of its reset, [2..3] 64-bit running total
-  int router_mode = CSK_ROUTER_CERTIFIED;
+  int router_mode = CSK_ROUTER_AUTO;
   int64_t routed_tokens = 0;   // tokens routed in certified mode since creation
   float* d_logits = nullptr;  // [max_T,E] router scratch
   float* d_rbias = nullptr;
@@ -190,11 +190,12 @@ int launch_router(csk_moe_layer* L, const float* d_hidden, int64_t T, float* d_r
   a.E = L->E_router;
   a.k = L->k;
   a.sigmoid = L->cfg.sigmoid_gating;
-  // The certified pass pays off while the chain kernel cannot fill the machine (a chain runs at the
-  // add latency on one SM per 32 experts and token block, however few tokens there are); from a few
-  // hundred tokens on the chain kernel is bound by its shared-memory traffic, like the fast one.
-  constexpr int64_t kCertifiedMaxTokens = 128;
-  if (L->router_mode == CSK_ROUTER_CHAIN || T > kCertifiedMaxTokens) {
+  // The certified pass (three launches: sliced FMA logits, certification, chain over the few tokens it
+  // could not separate) beats the one-launch chain only for a handful of tokens, where the chain is a
+  // single 2880-step dependency on a few SMs: measured in graph replay on the 128-expert layer it is
+  // 51 vs 53 us per step at T=1, level at T=4, and behind from T=16 on (361 vs 342 us at T=64).
+  constexpr int64_t kCertifiedMaxTokens = 4;
+  if (L->router_mode == CSK_ROUTER_CHAIN || (L->router_mode == CSK_ROUTER_AUTO && T > kCertifiedMaxTokens)) {
     launch_router_logits<true>(a, L->d_wg_few, L->d_wg_many, L->sm_count, s, L->pdl);
     CSK_CUDA(L, cudaGetLastError());
     L->last.launches += 1;
@@ -851,7 +852,7 @@ struct ImageHeader {
 };
 ImageHeader image_header_of(const csk_moe_layer* L) {
   ImageHeader h{};
-  memcpy(h.magic, "CSKMOE01", 8);
+  memcpy(h.magic, "CSKMOE02", 8);  // 02: the streaming layout stores scale byte 255 as 254
   h.E = L->E; h.k = L->k; h.H = L->H; h.F = L->F; h.has_bias = L->cfg.has_bias; h.e0 = L->e0; h.eloc = L->Eloc;
   h.expert_stride = L->expert_stride; h.off_gu = L->off_gu; h.off_d = L->off_d; h.off_tgu = L->off_tgu;
   h.off_td = L->off_td; h.off_bias = L->off_bias; h.off_meta = L->off_meta;
@@ -957,7 +958,7 @@ int csk_moe_set_activation(csk_moe_layer* L, int32_t activation, int32_t weight_
 
 int csk_moe_set_router_mode(csk_moe_layer* L, int32_t mode) {
   if (check_layer(L)) return CSK_ERR_INVALID;
-  if (mode != CSK_ROUTER_CERTIFIED && mode != CSK_ROUTER_CHAIN) return fail(L, CSK_ERR_INVALID, "unknown router mode %d", mode);
+  if (mode < CSK_ROUTER_AUTO || mode > CSK_ROUTER_CERTIFIED) return fail(L, CSK_ERR_INVALID, "unknown router mode %d", mode);
   L->router_mode = mode;
   drop_graphs(L);
   return CSK_OK;

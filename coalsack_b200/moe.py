@@ -279,7 +279,7 @@ class MoeLayer:
     def set_path(self, path):
         self._check(self._lib.csk_moe_set_path(self._h, path))
 
-    ROUTER_CERTIFIED, ROUTER_CHAIN = 0, 1
+    ROUTER_AUTO, ROUTER_CHAIN, ROUTER_CERTIFIED = 0, 1, 2
 
     def set_router_mode(self, mode):
         self._check(self._lib.csk_moe_set_router_mode(self._h, int(mode)))

@@ -118,7 +118,9 @@ int csk_moe_load_image(csk_moe_layer* layer, const char* path);
 /* Inverse of the repack: writes matrix `which` (0 up, 1 gate, 2 down from the
  * streaming kernel's layout; 3 up, 4 gate, 5 down from the tensor-core
  * kernel's layout) of a resident expert back as 17-byte blocks (host).  The
- * repack is lossless iff this returns the loaded bytes. */
+ * repack is lossless iff this returns the loaded bytes; the one rewrite is that
+ * the streaming layout (which 0..2) stores scale byte 255 as 254, the value the
+ * kernels read it as. */
 int csk_moe_unpack_expert_mxfp4(csk_moe_layer* layer, int32_t expert_id, int32_t which,
                                 uint8_t* out_blocks);
 /* 1 if the expert's weights are resident on the device, 0 if not. */
@@ -316,14 +318,17 @@ int csk_moe_set_activation(csk_moe_layer* layer, int32_t activation /* CSK_ACT_*
 
 /* How the router reaches the reference's selection (moe_router_node.h:161-177: each
  * logit a sequential fp32 multiply-then-add chain over the hidden dimension, top-k by
- * logit).  Both modes return the same expert indices as the reference, bit for bit.
- *   CSK_ROUTER_CERTIFIED (default): logits by fused multiply-adds in 32-column blocks
- *     with a rigorous bound on their distance from the chain's value; a token whose k+1
- *     best logits are further apart than the bounds keeps that selection, any other
- *     token is recomputed by the chain.  Routing WEIGHTS of certified tokens come from
- *     the fast logits and differ from the reference's by a few ulp (below 1e-6).
- *   CSK_ROUTER_CHAIN: every logit by the reference's own chain. */
-enum { CSK_ROUTER_CERTIFIED = 0, CSK_ROUTER_CHAIN = 1 };
+ * logit).  Every mode returns the same expert indices as the reference, bit for bit.
+ *   CSK_ROUTER_CHAIN: every logit by the reference's own chain (one launch).
+ *   CSK_ROUTER_CERTIFIED: logits by fused multiply-adds in 32-column blocks with a
+ *     rigorous bound on their distance from the chain's value; a token whose k+1 best
+ *     logits are further apart than the bounds keeps that selection, any other token is
+ *     recomputed by the chain.  Routing WEIGHTS of certified tokens come from the fast
+ *     logits and differ from the reference's by a few ulp (below 1e-6).
+ *   CSK_ROUTER_AUTO (default): certified for batches of up to 4 tokens, where the chain
+ *     is one long dependency on a few SMs; the chain kernel for anything larger, where it
+ *     is the faster of the two (measured). */
+enum { CSK_ROUTER_AUTO = 0, CSK_ROUTER_CHAIN = 1, CSK_ROUTER_CERTIFIED = 2 };
 int csk_moe_set_router_mode(csk_moe_layer* layer, int32_t mode);
 /* Tokens routed in certified mode since the handle was created, and how many of them
  * had to be recomputed by the chain (waits for the device). */

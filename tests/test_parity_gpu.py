@@ -405,7 +405,10 @@ def test_edge_scale_bytes(gpu_lib, port):
             ex[name][e] = blocks.reshape(-1)
     lay = make_layer(sh, Wg, rb, ex, max_tokens=sh.tokens)
     for which, name in enumerate(("w_up", "w_gate", "w_down", "w_up", "w_gate", "w_down")):
-        assert np.array_equal(lay.unpack_expert(1, which), ex[name][1]), which
+        want_blocks = ex[name][1].reshape(-1, 17).copy()
+        if which < 3:
+            want_blocks[want_blocks[:, 0] == 255, 0] = 254   # the streaming layout stores 255 as what it is read as
+        assert np.array_equal(lay.unpack_expert(1, which), want_blocks.reshape(-1)), which
     want = None
     for path in (PATH_STREAM, PATH_TILE, PATH_TILE_PAIR):
         lay.set_path(path)

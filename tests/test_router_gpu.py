@@ -12,8 +12,11 @@ pytestmark = pytest.mark.gpu
 
 
 def _router_layer(E, k, H, Wg, rb, max_tokens, sigmoid=False):
+    """A router-only layer with the certified pass switched on for every batch size (the default mode
+    keeps it for batches of up to four tokens)."""
     lay = MoeLayer(E, k, H, 32, has_bias=False, sigmoid_gating=sigmoid, max_tokens=max_tokens)
     lay.set_router(Wg, rb)
+    lay.set_router_mode(lay.ROUTER_CERTIFIED)
     return lay
 
 
@@ -25,9 +28,9 @@ def _cpu_router(port, h, Wg, rb, k, threads=16):
 
 
 def test_certified_router_49152_tokens_of_the_120b_shape(gpu_lib, port):
-    """49 152 tokens on the 128-expert router, routed in decode-sized batches of 1 to 128 tokens (the sizes
-    the certified pass serves): indices bit-exact, routing weights within 2e-6, and only a few percent of
-    the tokens needed the chain.  Then one 8192-token batch (served by the chain kernel alone)."""
+    """49 152 tokens on the 128-expert router, routed in decode-sized batches of 1 to 128 tokens through
+    the certified pass: indices bit-exact, routing weights within 2e-6, and only a few percent of
+    the tokens needed the chain.  Then one 8192-token batch in each of the three modes."""
     import torch
     sh = synth.C2
     E, k, H = sh.num_experts, sh.top_k, sh.hidden
@@ -54,7 +57,7 @@ def test_certified_router_49152_tokens_of_the_120b_shape(gpu_lib, port):
     assert routed == 6 * 8192
     assert 0 < chained < 0.08 * routed, (routed, chained)
     print(f"certified router: {chained} of {routed} tokens recomputed by the chain ({100.0 * chained / routed:.2f} %)")
-    for mode in (lay.ROUTER_CERTIFIED, lay.ROUTER_CHAIN):   # a prefill-sized batch, and the chain-only mode
+    for mode in (lay.ROUTER_CERTIFIED, lay.ROUTER_CHAIN, lay.ROUTER_AUTO):   # a prefill-sized batch in every mode
         lay.set_router_mode(mode)
         h = synth.hidden_states(sh, 8192, rep=7)
         got = lay.route(h)
