@@ -339,7 +339,8 @@ class P2pEpLayer:
 
 
 class EpBench:
-    """bench.py's N > 1 runner: weak scaling, T tokens per rank."""
+    """bench.py's N > 1 runner: T tokens per rank (the bench divides a fixed total by the ranks for
+    strong scaling, or keeps the per-rank count for weak scaling)."""
 
     def __init__(self, sh, rank, world, local):
         import torch
@@ -437,13 +438,20 @@ class EpBench:
         gathered = [torch.empty_like(vec) for _ in range(self.world)]
         dist.all_gather(gathered, vec)
         g = torch.stack(gathered).cpu().numpy()
-        stage_max = {x + "_ms": float(g[:, i].max()) for i, x in enumerate(names)}
+        # A stage that computes counts as the slowest rank saw it (max).  A stage that only waits for the
+        # other ranks (the gather of the counts, the two barriers) absorbs whatever skew the ranks arrived
+        # with, so its own cost is what the LAST rank to arrive saw (min).
+        waits = ("gather_counts", "barrier_rows", "barrier_out")
+        stage_max = {x + "_ms": float(g[:, i].min() if x in waits else g[:, i].max()) for i, x in enumerate(names)}
         rows_all = [int(r) for r in g[:, -1]]
         limiting = max(stage_max, key=stage_max.get) if stage_max else None
         out.update(route_ms=0.0, permute_ms=0.0, combine_ms=0.0, total_ms=out["gate_up_ms"] + out["down_ms"],
                    path={1: "stream", 2: "tile"}.get(int(path), "?"), launches=14, rows_received=int(rows))
         out["gate_up_kernel"] = "k_stream<gated>" if out["path"] == "stream" else "k_tile<gated>"
-        out["ep"] = {"stages_ms_max_over_ranks": stage_max, "limiting_stage": limiting,
+        out["ep"] = {"stages_ms_max_over_ranks": stage_max,
+                     "stages_note": "max over ranks; the gather of the counts and the two barriers as the last "
+                                    "rank to arrive saw them (min over ranks)",
+                     "limiting_stage": limiting,
                      "rows_received_per_rank": rows_all,
                      "rows_max_over_mean": float(max(rows_all) / max(1.0, np.mean(rows_all))),
                      "slots": int(self.place.n_slots), "second_copies": int((self.place.replica_of >= 0).sum()),
