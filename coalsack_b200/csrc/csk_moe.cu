@@ -369,16 +369,20 @@ cudaError_t stream_prepare_device() {
 }
 
 int stream_tile_rows(const csk_moe_layer* L, int64_t rows) {
-  // 8-row tiles while the average expert sees at most eight rows, 16-row tiles after
-  return rows <= 8 * (int64_t)std::max(1, L->Eloc) ? 8 : 16;
+  // 8-row tiles up to an average of twelve rows per expert: the 16-row variant of the streaming kernel is
+  // 1.8x slower per weight byte (558 vs 314 us per step at 64 tokens on the 128-expert layer), so it pays
+  // only when nearly every expert would otherwise stream its weights twice.  (Under CSK_PATH_AUTO the
+  // tensor-core kernel has taken over before that point.)
+  return rows <= 12 * (int64_t)std::max(1, L->Eloc) ? 8 : 16;
 }
 
 int choose_path(const csk_moe_layer* L, int64_t rows) {
   if (L->path == CSK_PATH_STREAM) return CSK_PATH_STREAM;
   if (L->path == CSK_PATH_TILE || L->path == CSK_PATH_TILE_PAIR) return CSK_PATH_TILE;
-  // the tensor-core tiles are 128 rows tall: worth it once the average expert
-  // fills a good part of one
-  return (L->tile.available && rows >= 48 * (int64_t)std::max(1, L->Eloc)) ? CSK_PATH_TILE : CSK_PATH_STREAM;
+  // The tensor-core kernel's time is nearly flat in the rows per expert (600 us per step at 256 tokens,
+  // 700 at 1024 on the 128-expert layer), the streaming kernel's grows with the number of 8-row tiles
+  // (494 us at 256 tokens, 816 at 512): they cross at about ten rows per expert.
+  return (L->tile.available && rows >= 10 * (int64_t)std::max(1, L->Eloc)) ? CSK_PATH_TILE : CSK_PATH_STREAM;
 }
 
 // the CTA-pair kernel runs only when asked for by name (and clusters of two can be launched)

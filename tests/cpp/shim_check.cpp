@@ -4,6 +4,7 @@
 // and writes the merged output back.  Built against the reference checkout; the
 // binary runs wherever libcsk_moe.so and a B200 are.
 #include <cstdio>
+#include <cstring>
 #include <fstream>
 #include <iostream>
 #include <vector>
@@ -43,6 +44,27 @@ int main(int argc, char** argv) {
   if (verbose) std::fprintf(stderr, "router ...\n");
   dynamic_tensor ro = router.compute_test(hidden, Wg, rb);
   if (verbose) std::fprintf(stderr, "router done\n");
+
+  // gate weights refilled IN PLACE (same address, same size) must reach the GPU: the node keys its upload on content
+  {
+    float* w = Wg.data_ptr<float>();
+    const size_t n = (size_t)E * H;
+    for (size_t i = 0; i < n; ++i) w[i] = -w[i];
+    dynamic_tensor cached = router.compute_test(hidden, Wg, rb);
+    moe_router_node fresh;
+    fresh.set_config(E, k);
+    dynamic_tensor want = fresh.compute_test(hidden, Wg, rb);
+    for (size_t i = 0; i < n; ++i) w[i] = -w[i];
+    if (std::memcmp(cached.data_ptr<float>(), want.data_ptr<float>(), sizeof(float) * T * k * 2) != 0) {
+      std::cerr << "router kept stale weights after an in-place refill\n";
+      return 1;
+    }
+    dynamic_tensor back = router.compute_test(hidden, Wg, rb);
+    if (std::memcmp(back.data_ptr<float>(), ro.data_ptr<float>(), sizeof(float) * T * k * 2) != 0) {
+      std::cerr << "router did not return to the first weights\n";
+      return 1;
+    }
+  }
 
   std::vector<dynamic_tensor> merge_in = {ro};
   for (int e = 0; e < E; ++e) {
