@@ -18,7 +18,7 @@ class Config(C.Structure):
     """csk_moe_config"""
     _fields_ = [(n, _i32) for n in (
         "num_experts", "top_k", "hidden", "ffn", "activation", "has_bias", "sigmoid_gating",
-        "weight_before_ffn", "device", "expert_begin", "expert_count", "reserved0")] + [("max_tokens", _i64)]
+        "weight_before_ffn", "device", "expert_begin", "expert_count", "weight_format")] + [("max_tokens", _i64)]
 
 
 class Timings(C.Structure):
@@ -35,6 +35,9 @@ SYMBOLS = {
     "csk_moe_device_ok": (C.c_int, [C.c_int]),
     "csk_moe_set_router": (C.c_int, [_vp, _vp, _vp]),
     "csk_moe_load_expert_mxfp4": (C.c_int, [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "csk_moe_load_expert_f16": (C.c_int, [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "csk_moe_dense_forward": (C.c_int, [_vp, _vp, _i64, _vp]),
+    "csk_moe_dense_forward_dev": (C.c_int, [_vp, _vp, _i64, _vp, _vp]),
     "csk_moe_load_experts_mxfp4": (C.c_int, [_vp, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp]),
     "csk_moe_save_image": (C.c_int, [_vp, C.c_char_p]),
     "csk_moe_load_image": (C.c_int, [_vp, C.c_char_p]),

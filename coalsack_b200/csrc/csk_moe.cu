@@ -33,6 +33,8 @@ struct csk_moe_layer {
   uint8_t* d_stage = nullptr;     // raw 17-byte blocks during load / unpack
   uint8_t* d_stage2 = nullptr;    // second staging area (bulk load)
   size_t stage_bytes = 0;
+  bool w16 = false;            // fp16 weights: tensor-core kernel only, no streaming layout
+  float* d_unit_router = nullptr;  // dense FFN (E = k = 1): (expert 0, weight 1) for every token
 
   float* d_wg = nullptr;   // [E,H]
   float* d_wg_few = nullptr;   // the same repacked for the router kernel's two chunk widths
@@ -377,6 +379,7 @@ int stream_tile_rows(const csk_moe_layer* L, int64_t rows) {
 }
 
 int choose_path(const csk_moe_layer* L, int64_t rows) {
+  if (L->w16) return CSK_PATH_TILE;  // fp16 weights exist in the tensor-core layout only
   if (L->path == CSK_PATH_STREAM) return CSK_PATH_STREAM;
   if (L->path == CSK_PATH_TILE || L->path == CSK_PATH_TILE_PAIR) return CSK_PATH_TILE;
   // The tensor-core kernel's time is nearly flat in the rows per expert (600 us per step at 256 tokens,
@@ -389,7 +392,7 @@ int choose_path(const csk_moe_layer* L, int64_t rows) {
 bool use_pairs(const csk_moe_layer* L) { return L->pair.available && L->path == CSK_PATH_TILE_PAIR; }
 
 int tile_rows_for(const csk_moe_layer* L, int path, int64_t rows) {
-  return path == CSK_PATH_TILE ? kTileM : stream_tile_rows(L, rows);
+  return path == CSK_PATH_TILE ? (use_pairs(L) ? kPairN : kTileM) : stream_tile_rows(L, rows);
 }
 
 // grouped gate/up + activation + down over the row tiles listed in d_tiles;
@@ -586,6 +589,8 @@ int csk_moe_create(const csk_moe_config* cfg, csk_moe_layer** out) {
   if (cfg->ffn <= 0 || cfg->ffn % 32)
     return fail(nullptr, CSK_ERR_INVALID,
                 "expert_mlp: expert_ffn_dim must be a multiple of 32 for MXFP4, got %d", cfg->ffn);
+  if (cfg->weight_format != CSK_WEIGHTS_MXFP4 && cfg->weight_format != CSK_WEIGHTS_F16)
+    return fail(nullptr, CSK_ERR_INVALID, "unknown weight format %d", cfg->weight_format);
   if (cfg->activation != CSK_ACT_MODIFIED_SWIGLU && cfg->activation != CSK_ACT_STANDARD_SWIGLU)
     return fail(nullptr, CSK_ERR_INVALID, "unknown activation %d", cfg->activation);
   if (cfg->max_tokens <= 0 || cfg->max_tokens * cfg->top_k > (1 << 28))
@@ -608,14 +613,15 @@ int csk_moe_create(const csk_moe_config* cfg, csk_moe_layer** out) {
   L->F = cfg->ffn;
   L->e0 = e0;
   L->Eloc = eloc;
+  L->w16 = cfg->weight_format == CSK_WEIGHTS_F16;
   L->Lgu = make_layout(L->F, L->H, true);
   L->Ld = make_layout(L->H, L->F, false);
-  L->Tgu = make_tile_layout(L->F, L->H, true);
-  L->Td = make_tile_layout(L->H, L->F, false);
+  L->Tgu = make_tile_layout(L->F, L->H, true, L->w16);
+  L->Td = make_tile_layout(L->H, L->F, false, L->w16);
   auto up256 = [](size_t v) { return (v + 255) / 256 * 256; };
   L->off_gu = 0;
-  L->off_d = up256(L->Lgu.bytes());
-  L->off_tgu = L->off_d + up256(L->Ld.bytes());
+  L->off_d = L->w16 ? 0 : up256(L->Lgu.bytes());                  // fp16 weights have no streaming layout
+  L->off_tgu = L->w16 ? 0 : L->off_d + up256(L->Ld.bytes());
   L->off_td = L->off_tgu + up256(L->Tgu.bytes());
   L->off_bias = L->off_td + up256(L->Td.bytes());
   L->off_meta = L->off_bias + sizeof(float) * (2 * (size_t)L->F + L->H);  // int[4]: e_max of gate/up, of down
@@ -655,7 +661,7 @@ int csk_moe_create(const csk_moe_config* cfg, csk_moe_layer** out) {
   CK(cudaMemset(L->d_weights, 0, L->expert_stride * eloc));
   CK(cudaMalloc(&L->d_resident, eloc));
   CK(cudaMemset(L->d_resident, 0, eloc));
-  L->stage_bytes = (size_t)L->H * L->F / 32 * 17;
+  L->stage_bytes = L->w16 ? (size_t)L->H * L->F * 2 : (size_t)L->H * L->F / 32 * 17;
   CK(cudaMalloc(&L->d_stage, 3 * L->stage_bytes));
   CK(cudaMalloc(&L->d_wg, sizeof(float) * L->E * L->H));
   CK(cudaMalloc(&L->d_wg_few, sizeof(float) * router_packed_floats(L->E, L->H, kRouterChunkFew)));
@@ -674,11 +680,20 @@ int csk_moe_create(const csk_moe_config* cfg, csk_moe_layer** out) {
   CK(cudaMalloc(&L->d_hidden, sizeof(float) * L->max_T * L->H));
   CK(cudaMalloc(&L->d_router, sizeof(float) * L->max_T * L->k * 2));
   CK(cudaMalloc(&L->d_router_phys, sizeof(float) * L->max_T * L->k * 2));
+  if (L->E == 1 && L->k == 1) {  // a dense FFN: every token goes to expert 0 with weight 1
+    std::vector<float> unit(2 * (size_t)L->max_T);
+    for (int64_t t = 0; t < L->max_T; ++t) {
+      unit[2 * t] = 0.0f;
+      unit[2 * t + 1] = 1.0f;
+    }
+    CK(cudaMalloc(&L->d_unit_router, sizeof(float) * unit.size()));
+    CK(cudaMemcpy(L->d_unit_router, unit.data(), sizeof(float) * unit.size(), cudaMemcpyHostToDevice));
+  }
   CK(cudaMalloc(&L->d_slot_map, sizeof(int) * 2 * L->E));
   CK(cudaMalloc(&L->d_p2p_base, sizeof(int) * L->E));
   L->E_router = L->E;
   CK(cudaMalloc(&L->d_out, sizeof(float) * L->max_T * L->H));
-  const size_t pad_rows = kTileM;  // a row tile's loads may reach this far past the last row
+  const size_t pad_rows = std::max(kTileM, kPairN);  // a row tile's loads may reach this far past the last row
   CK(cudaMalloc(&L->d_x16, sizeof(__half) * (L->max_rows + pad_rows) * L->ldx));
   CK(cudaMemset(L->d_x16, 0, sizeof(__half) * (L->max_rows + pad_rows) * L->ldx));
   CK(cudaMalloc(&L->d_a16, sizeof(__half) * (L->max_rows + pad_rows) * L->lda));
@@ -723,7 +738,7 @@ int csk_moe_destroy(csk_moe_layer* L) {
     if (g.exec) cudaGraphExecDestroy(g.exec);
   tile_destroy(L->tile);
   for (void* p : L->ipc_opened) cudaIpcCloseMemHandle(p);
-  void* dev[] = {L->d_stage2, L->d_norm_w, L->d_normed, L->d_part, L->d_hn2, L->d_wnorm, L->d_fb_list, L->d_fb, L->d_info, L->d_back, L->d_row_ptr, L->d_p2p_base, L->d_peer_x16, L->d_peer_info, L->d_peer_back,
+  void* dev[] = {L->d_unit_router, L->d_stage2, L->d_norm_w, L->d_normed, L->d_part, L->d_hn2, L->d_wnorm, L->d_fb_list, L->d_fb, L->d_info, L->d_back, L->d_row_ptr, L->d_p2p_base, L->d_peer_x16, L->d_peer_info, L->d_peer_back,
                  L->d_router_phys, L->d_slot_map, L->d_weights, L->d_resident, L->d_stage, L->d_wg, L->d_wg_few, L->d_wg_many, L->d_route_cnt, L->d_logits, L->d_rbias, L->d_hidden,
                  L->d_router, L->d_out, L->d_x16, L->d_a16, L->d_y, L->d_counts, L->d_offsets,
                  L->d_cursor, L->d_row_of_pair, L->d_pair_of_row, L->d_out_row_map, L->d_seg, L->d_tiles, L->d_meta};
@@ -780,10 +795,17 @@ int load_expert_enqueue(csk_moe_layer* L, int le, const uint8_t* w_up, const uin
   CSK_CUDA(L, cudaMemcpyAsync(s_down, w_down, L->stage_bytes, cudaMemcpyHostToDevice, s));
   int* emeta = reinterpret_cast<int*>(base + L->off_meta);
   CSK_CUDA(L, cudaMemsetAsync(emeta, 0, 16, s));
+  if (L->w16) {
+    const __half *h_up = reinterpret_cast<const __half*>(s_up), *h_gate = reinterpret_cast<const __half*>(s_gate),
+                 *h_down = reinterpret_cast<const __half*>(s_down);
+    k_repack_tile_f16<<<grid_for(L->Tgu.bytes() / 16, 256, 4096), 256, 0, s>>>(h_gate, h_up, base + L->off_tgu, L->Tgu);
+    k_repack_tile_f16<<<grid_for(L->Td.bytes() / 16, 256, 4096), 256, 0, s>>>(h_down, nullptr, base + L->off_td, L->Td);
+  } else {
   k_repack<<<grid_for(L->Lgu.bytes() / 4, 256, 4096), 256, 0, s>>>(s_gate, s_up, base + L->off_gu, L->Lgu, emeta);
   k_repack<<<grid_for(L->Ld.bytes() / 4, 256, 4096), 256, 0, s>>>(s_down, nullptr, base + L->off_d, L->Ld, emeta + 1);
   k_repack_tile<<<grid_for(L->Tgu.bytes() / 4, 256, 4096), 256, 0, s>>>(s_gate, s_up, base + L->off_tgu, L->Tgu);
   k_repack_tile<<<grid_for(L->Td.bytes() / 4, 256, 4096), 256, 0, s>>>(s_down, nullptr, base + L->off_td, L->Td);
+  }
   CSK_CUDA(L, cudaGetLastError());
   if (L->cfg.has_bias) {
     float* b = reinterpret_cast<float*>(base + L->off_bias);
@@ -806,9 +828,30 @@ int csk_moe_load_expert_mxfp4(csk_moe_layer* L, int32_t expert_id, const uint8_t
   if (!w_up || !w_gate || !w_down) return fail(L, CSK_ERR_INVALID, "null weight pointer");
   if (L->cfg.has_bias && (!b_up || !b_gate || !b_down))
     return fail(L, CSK_ERR_INVALID, "layer has biases but a bias pointer is null");
+  if (L->w16) return fail(L, CSK_ERR_INVALID, "this layer holds fp16 weights: use csk_moe_load_expert_f16");
   CSK_CUDA(L, cudaSetDevice(L->cfg.device));
   const int le = expert_id - L->e0;
   int rc = load_expert_enqueue(L, le, w_up, w_gate, w_down, b_up, b_gate, b_down, L->d_stage, L->stream);
+  if (rc) return rc;
+  CSK_CUDA(L, cudaStreamSynchronize(L->stream));
+  L->resident[le] = 1;
+  return CSK_OK;
+}
+
+int csk_moe_load_expert_f16(csk_moe_layer* L, int32_t expert_id, const uint16_t* w_up, const uint16_t* w_gate,
+                            const uint16_t* w_down, const float* b_up, const float* b_gate, const float* b_down) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  if (!L->w16) return fail(L, CSK_ERR_INVALID, "this layer holds MXFP4 weights: use csk_moe_load_expert_mxfp4");
+  if (expert_id < L->e0 || expert_id >= L->e0 + L->Eloc)
+    return fail(L, CSK_ERR_INVALID, "expert %d is not resident on this device (range [%d,%d))",
+                expert_id, L->e0, L->e0 + L->Eloc);
+  if (!w_up || !w_gate || !w_down) return fail(L, CSK_ERR_INVALID, "null weight pointer");
+  if (L->cfg.has_bias && (!b_up || !b_gate || !b_down))
+    return fail(L, CSK_ERR_INVALID, "layer has biases but a bias pointer is null");
+  CSK_CUDA(L, cudaSetDevice(L->cfg.device));
+  const int le = expert_id - L->e0;
+  int rc = load_expert_enqueue(L, le, reinterpret_cast<const uint8_t*>(w_up), reinterpret_cast<const uint8_t*>(w_gate),
+                               reinterpret_cast<const uint8_t*>(w_down), b_up, b_gate, b_down, L->d_stage, L->stream);
   if (rc) return rc;
   CSK_CUDA(L, cudaStreamSynchronize(L->stream));
   L->resident[le] = 1;
@@ -819,6 +862,7 @@ int csk_moe_load_experts_mxfp4(csk_moe_layer* L, int32_t first_expert, int32_t c
                                const uint8_t* w_gate, const uint8_t* w_down, const float* b_up, const float* b_gate,
                                const float* b_down) {
   if (check_layer(L)) return CSK_ERR_INVALID;
+  if (L->w16) return fail(L, CSK_ERR_INVALID, "this layer holds fp16 weights: use csk_moe_load_expert_f16");
   if (count <= 0 || first_expert < L->e0 || first_expert + count > L->e0 + L->Eloc)
     return fail(L, CSK_ERR_INVALID, "experts [%d,%d) are not all resident on this device (range [%d,%d))", first_expert,
                 first_expert + count, L->e0, L->e0 + L->Eloc);
@@ -914,6 +958,7 @@ int csk_moe_unpack_expert_mxfp4(csk_moe_layer* L, int32_t expert_id, int32_t whi
   if (expert_id < L->e0 || expert_id >= L->e0 + L->Eloc || !L->resident[expert_id - L->e0])
     return fail(L, CSK_ERR_MISSING, "expert %d is not loaded", expert_id);
   if (which < 0 || which > 5 || !out) return fail(L, CSK_ERR_INVALID, "bad argument");
+  if (L->w16) return fail(L, CSK_ERR_INVALID, "this layer holds fp16 weights, not MXFP4 blocks");
   CSK_CUDA(L, cudaSetDevice(L->cfg.device));
   const uint8_t* base = L->d_weights + (size_t)(expert_id - L->e0) * L->expert_stride;
   if (which < 3) {
@@ -942,6 +987,8 @@ int csk_moe_expert_resident(const csk_moe_layer* L, int32_t expert_id) {
 int csk_moe_set_path(csk_moe_layer* L, int32_t path) {
   if (check_layer(L)) return CSK_ERR_INVALID;
   if (path < CSK_PATH_AUTO || path > CSK_PATH_TILE_PAIR) return fail(L, CSK_ERR_INVALID, "unknown path %d", path);
+  if (L->w16 && (path == CSK_PATH_STREAM || path == CSK_PATH_TILE_PAIR))
+    return fail(L, CSK_ERR_INVALID, "fp16 weights run on the one-CTA tensor-core kernel only");
   if (path == CSK_PATH_TILE_PAIR && !L->pair.available)
     return fail(L, CSK_ERR_INVALID, "the CTA-pair kernel is not available on this device: %s", L->pair.err.c_str());
   L->path = path;
@@ -1234,6 +1281,27 @@ int csk_moe_forward(csk_moe_layer* L, const float* hidden, int64_t T, const floa
   if (e1 != cudaSuccess || e2 != cudaSuccess || e3 != cudaSuccess)
     return fail(L, CSK_ERR_CUDA, "pipelined forward: %s", cudaGetErrorString(e1 != cudaSuccess ? e1 : e2 != cudaSuccess ? e2 : e3));
   return report_status(L, L->h_meta[3] | L->h_meta[8], s);
+}
+
+int csk_moe_dense_forward_dev(csk_moe_layer* L, const float* d_hidden, int64_t T, float* d_out, void* stream) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  if (!L->d_unit_router) return fail(L, CSK_ERR_INVALID, "dense forward needs a layer with num_experts = top_k = 1");
+  return csk_moe_forward_dev(L, d_hidden, T, L->d_unit_router, nullptr, d_out, stream);
+}
+
+int csk_moe_dense_forward(csk_moe_layer* L, const float* hidden, int64_t T, float* out) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  if (!L->d_unit_router) return fail(L, CSK_ERR_INVALID, "dense forward needs a layer with num_experts = top_k = 1");
+  if (!hidden || !out) return fail(L, CSK_ERR_INVALID, "null argument");
+  if (T <= 0 || T > L->max_T) return fail(L, CSK_ERR_NOMEM, "T=%lld outside (0, max_tokens]", (long long)T);
+  CSK_CUDA(L, cudaSetDevice(L->cfg.device));
+  cudaStream_t s = L->stream;
+  CSK_CUDA(L, cudaMemcpyAsync(L->d_hidden, hidden, sizeof(float) * T * L->H, cudaMemcpyHostToDevice, s));
+  int rc = forward_dev(L, L->d_hidden, T, L->d_unit_router, nullptr, L->d_out, -1, s, true);
+  if (rc) return rc;
+  CSK_CUDA(L, cudaMemcpyAsync(out, L->d_out, sizeof(float) * T * L->H, cudaMemcpyDeviceToHost, s));
+  CSK_CUDA(L, cudaStreamSynchronize(s));
+  return CSK_OK;
 }
 
 int csk_moe_expert_forward(csk_moe_layer* L, int32_t expert_id, const float* hidden, int64_t T,

@@ -63,7 +63,15 @@ constexpr int kHalfPacked = 4352;                           // packed half tile:
 constexpr int kTilePacked = 2 * kHalfPacked;                // packed weight tile (two halves)
 constexpr int kTileRawBytes = kTileABytes + 9216;           // one shared-memory stage (1024-byte multiple)
 constexpr int kTileStages = 6;
+// fp16 weights (dense FFN, fp16 expert slices): a half tile is 128 rows x 64 fp16 = 16 KB, rows of 128 bytes
+// whose eight 16-byte pieces are stored at piece ^ (row & 7) (a quarter-warp reading one piece of eight
+// neighbouring rows then hits eight different bank groups)
+constexpr int kHalf16 = 128 * 128;
+constexpr int kTile16 = 2 * kHalf16;
+constexpr int kTileRawBytes16 = kTileABytes + kTile16;      // 57344, a 1024-byte multiple
+constexpr int kTileStages16 = 3;
 constexpr int kTileAStages = 2;                             // weight tiles resident in tensor memory
+constexpr int kPairBoxRows = 96;                            // TMA box height of the CTA-pair kernel's half tiles
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kTmemABase = 2 * kTileM;                 // first column of the weight ring
 
@@ -76,15 +84,18 @@ constexpr uint32_t kTmemABase = 2 * kTileM;                 // first column of t
 // SAME 128 features (128*n_tile ..), so a feature's two accumulators sit in one
 // tensor-memory lane, 192 columns apart.
 struct TileLayout {
-  int N, K, paired, n_tiles, k_tiles;
+  int N, K, paired, n_tiles, k_tiles, w16;
+  __host__ __device__ int half_bytes() const { return w16 ? kHalf16 : kHalfPacked; }
+  __host__ __device__ int tile_bytes() const { return 2 * half_bytes(); }
   __host__ __device__ int feats_per_tile() const { return paired ? kTileW : 2 * kTileW; }
   // halves of tile nt that hold any real row (the last tile of a plain matrix may need only one)
   __host__ __device__ int halves(int nt) const { return paired || nt * 2 * kTileW + kTileW < N ? 2 : 1; }
-  __host__ __device__ size_t bytes() const { return (size_t)n_tiles * k_tiles * kTilePacked; }
+  __host__ __device__ size_t bytes() const { return (size_t)n_tiles * k_tiles * tile_bytes(); }
   __host__ __device__ int k_pad() const { return k_tiles * kTileK; }
 };
-inline TileLayout make_tile_layout(int N, int K, bool paired) {
+inline TileLayout make_tile_layout(int N, int K, bool paired, bool w16 = false) {
   TileLayout L{};
+  L.w16 = w16 ? 1 : 0;
   L.N = N;
   L.K = K;
   L.paired = paired ? 1 : 0;
@@ -144,6 +155,34 @@ __global__ void k_repack_tile(const uint8_t* __restrict__ src0, const uint8_t* _
       }
     }
     reinterpret_cast<uint32_t*>(dst)[w] = out;
+  }
+}
+
+// fp16 weights, row-major [N,K] (src1 = up matrix when paired), into the fp16 tile layout.  One thread
+// per 16-byte piece (eight columns of one row).
+__global__ void k_repack_tile_f16(const __half* __restrict__ src0, const __half* __restrict__ src1,
+                                  uint8_t* __restrict__ dst, TileLayout L) {
+  const size_t n_pieces = L.bytes() / 16;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_pieces; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t half_idx = i >> 10;  // 1024 pieces per half tile
+    const int pi = (int)(i & 1023);
+    const int trow = pi >> 3, piece = (pi & 7) ^ (trow & 7);  // the piece stored here
+    const int half = (int)(half_idx & 1);
+    const size_t tile = half_idx >> 1;
+    const int kt = (int)(tile % L.k_tiles), nt = (int)(tile / L.k_tiles);
+    const __half* src = L.paired ? (half ? src1 : src0) : src0;
+    const int feat = L.paired ? nt * kTileW + trow : nt * 2 * kTileW + half * kTileW + trow;
+    const int col = kt * kTileK + piece * 8;
+    uint4 out = make_uint4(0u, 0u, 0u, 0u);
+    if (feat < L.N && col < L.K) {  // K is a multiple of 32: a piece is inside or outside as a whole
+      const __half* p = src + (size_t)feat * L.K + col;
+      uint32_t w[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        w[e] = (uint32_t)__half_as_ushort(p[2 * e]) | ((uint32_t)__half_as_ushort(p[2 * e + 1]) << 16);
+      out = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    reinterpret_cast<uint4*>(dst)[i] = out;
   }
 }
 
@@ -282,19 +321,23 @@ struct TileArgs {
   int stall;              // test hook: the copy role issues nothing, so every other role's wait runs out
 };
 
-inline size_t tile_smem_bytes() { return (size_t)kTileStages * kTileRawBytes + 1024 + 512; }
+inline size_t tile_smem_bytes(bool w16 = false) {
+  return (w16 ? (size_t)kTileStages16 * kTileRawBytes16 : (size_t)kTileStages * kTileRawBytes) + 1024 + 512;
+}
 
-template <bool GATED>
+template <bool GATED, bool W16>
 __global__ void __launch_bounds__(kTileThreads, 1)
 k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
   extern __shared__ __align__(1024) uint8_t tile_smem[];
   const TileLayout& L = A.L;
   const int KT = L.k_tiles;
-  constexpr int NR = kTileStages, NA = kTileAStages;
+  constexpr int NR = W16 ? kTileStages16 : kTileStages, NA = kTileAStages;
+  constexpr int RAW = W16 ? kTileRawBytes16 : kTileRawBytes;  // bytes of a shared-memory stage
+  constexpr int HALF_B = W16 ? kHalf16 : kHalfPacked, TILE_B = 2 * HALF_B;
 
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)tile_smem + 1023) & ~(uintptr_t)1023);
   const uint32_t smem_base = smem_u32(smem);  // ring of [token tile | packed weight tile]
-  uint8_t* ctrl = smem + (size_t)NR * kTileRawBytes;
+  uint8_t* ctrl = smem + (size_t)NR * RAW;
   uint64_t* bars = reinterpret_cast<uint64_t*>(ctrl);
   const uint32_t bar_base = smem_u32(bars);
   // k-step c uses shared-memory stage c % NR and tensor-memory slot c % NA; one barrier per stage tells both the
@@ -315,7 +358,7 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
       mbar_init(bar_full_raw(s), 1);
       mbar_init(bar_retired(s), 1);
     }
-    for (int s = 0; s < 2; ++s) mbar_init(bar_full_a(s), kDequantWarps / 2);
+    for (int s = 0; s < NA; ++s) mbar_init(bar_full_a(s), kDequantWarps / 2);
     mbar_init(bar_tmem_full, 1);
     mbar_init(bar_tmem_empty, kEpilogueWarps);
     mbar_init(bar_drain, 1);
@@ -347,17 +390,17 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
         const RowTile rt = A.tiles[item / L.n_tiles];
         const int nt = (int)(item % L.n_tiles);
         const uint8_t* wsrc =
-            A.weights + (size_t)rt.expert * A.expert_stride + A.mat_offset + (size_t)nt * KT * kTilePacked;
-        const uint32_t w_bytes = (uint32_t)L.halves(nt) * kHalfPacked;
+            A.weights + (size_t)rt.expert * A.expert_stride + A.mat_offset + (size_t)nt * KT * TILE_B;
+        const uint32_t w_bytes = (uint32_t)L.halves(nt) * HALF_B;
         for (int kt = 0; kt < KT; ++kt) {
           if (!mbar_wait(bar_retired(s), ph ^ 1, abort_flag)) {
             ok = false;
             break;
           }
-          const uint32_t st = smem_base + (uint32_t)s * kTileRawBytes;
+          const uint32_t st = smem_base + (uint32_t)s * RAW;
           mbar_expect_tx(bar_full_raw(s), kTileABytes + w_bytes);
           tma_load_2d(st, &tmap, kt * kTileK, rt.row0, bar_full_raw(s));
-          bulk_load(st + kTileABytes, wsrc + (size_t)kt * kTilePacked, w_bytes, bar_full_raw(s));
+          bulk_load(st + kTileABytes, wsrc + (size_t)kt * TILE_B, w_bytes, bar_full_raw(s));
           ++issued;
           if (++s == NR) {
             s = 0;
@@ -408,7 +451,7 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
           ok = __all_sync(0xffffffffu, mbar_wait(bar_full_a(sa), (c / NA) & 1u, abort_flag));
           if (!ok) break;
           tc_fence_after();
-          const uint64_t db = db0 + (uint64_t)((s * (uint32_t)kTileRawBytes) >> 4);  // start-address field, 16-byte units
+          const uint64_t db = db0 + (uint64_t)((s * (uint32_t)RAW) >> 4);  // start-address field, 16-byte units
           const uint32_t a_tmem = a_tmem0 + sa * 64;
           if (elect_one()) {
 #pragma unroll
@@ -445,6 +488,18 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
     long c = 0;                              // running k-step number of this CTA
     bool ok = true;
     auto convert = [&](const uint8_t* packed, int emax, uint32_t (&h)[2][16]) {
+      if (W16) {  // the row's 64 fp16 values as they are: eight 16-byte pieces, stored at piece ^ (row & 7)
+        const uint8_t* row = packed + trow * 128;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint4 v = *reinterpret_cast<const uint4*>(row + ((j ^ (trow & 7)) << 4));
+          h[j >> 2][(j & 3) * 4 + 0] = v.x;
+          h[j >> 2][(j & 3) * 4 + 1] = v.y;
+          h[j >> 2][(j & 3) * 4 + 2] = v.z;
+          h[j >> 2][(j & 3) * 4 + 3] = v.w;
+        }
+        return;
+      }
 #pragma unroll
       for (int blk = 0; blk < 2; ++blk) {
         const uint4 cw = *reinterpret_cast<const uint4*>(packed + (blk * 128 + trow) * 16);
@@ -472,15 +527,26 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
         if ((int)(c & 1) != grp) continue;
         const int s = (int)(c % NR);
         const uint32_t ph = (uint32_t)((c / NR) & 1);
+        if (NR % 2 != 0 && c >= NR) {
+          // An odd ring hands a stage to the two groups in turn, so this group never saw the stage's previous
+          // fill complete: were that fill still in flight (copies may complete out of order), the parity test
+          // below would take the fill before it for the one awaited, and the conversion would read the
+          // wrong k-step.  The stage's previous MMAs having retired implies its previous fill has landed.
+          if (!mbar_wait(bar_retired(s), (uint32_t)(((c - NR) / NR) & 1), abort_flag)) {
+            ok = false;
+            break;
+          }
+        }
         if (!mbar_wait(bar_full_raw(s), ph, abort_flag)) {
           ok = false;
           break;
         }
-        const uint8_t* packed = smem + (size_t)s * kTileRawBytes + kTileABytes;
-        const uint32_t t_slot = tmem_base + ((uint32_t)(quarter * 32) << 16) + kTmemABase + (uint32_t)grp * 64;
+        const uint8_t* packed = smem + (size_t)s * RAW + kTileABytes;
+        const int sa = (int)(c % NA);
+        const uint32_t t_slot = tmem_base + ((uint32_t)(quarter * 32) << 16) + kTmemABase + (uint32_t)sa * 64;
         uint32_t h[2][16];
         convert(packed, emax, h);
-        // the slot was last read by k-step c - 2
+        // the slot was last read by k-step c - NA
         if (c >= NA && !mbar_wait(bar_retired((int)((c - NA) % NR)), (uint32_t)(((c - NA) / NR) & 1), abort_flag)) {
           ok = false;
           break;
@@ -489,14 +555,18 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
         tmem_st16(t_slot, h[0]);
         tmem_st16(t_slot + 16, h[1]);
         if (halves > 1) {
-          convert(packed + kHalfPacked, emax, h);  // reuses h: the compiler orders it after the stores above
+          // h is reused: the stores above read their registers asynchronously, so they have to be waited for
+          // before the registers change (with fp16 weights the second conversion is only eight loads, and
+          // without this wait rows of the first half were occasionally stored with the second half's values)
+          tmem_st_wait();
+          convert(packed + HALF_B, emax, h);
           tmem_st16(t_slot + 32, h[0]);
           tmem_st16(t_slot + 48, h[1]);
         }
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_full_a(grp));
+        if (lane == 0) mbar_arrive(bar_full_a(sa));
       }
     }
   } else {
@@ -506,8 +576,8 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
     // plain matrix: a warp finishes one half x one of two column ranges; gate/up: both halves
     // (gate and up of its lane's feature) x one of four 48-column ranges
     const int half = GATED ? 0 : (ew >> 2) & 1;
-    const int c_begin = GATED ? (ew >> 2) * 48 : (ew >> 3) * 96;
-    const int c_end = GATED ? c_begin + 48 : (c_begin ? kTileM : 96);
+    const int c_begin = GATED ? (ew >> 2) * (kTileM / 4) : (ew >> 3) * (kTileM / 2);
+    const int c_end = c_begin + (GATED ? kTileM / 4 : kTileM / 2);
     const int trow = quarter * 32 + lane;
     long it = 0;
     bool ok = true;
@@ -518,7 +588,7 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
       const uint8_t* ebase = A.weights + (size_t)rt.expert * A.expert_stride;
       const float* bias = reinterpret_cast<const float*>(ebase + A.bias_offset);
       const int emax = reinterpret_cast<const int*>(ebase + A.meta_offset)[A.meta_slot];
-      const float oscale = ldexpf(1.0f, emax - 140);
+      const float oscale = W16 ? 1.0f : ldexpf(1.0f, emax - 140);
       if (!mbar_wait(bar_tmem_full, (uint32_t)(it & 1), abort_flag)) {
         ok = false;
         break;
@@ -606,10 +676,14 @@ inline int tile_init(TileState& st, int device) {
     return CSK_ERR_CUDA;
   }
   st.encode_fn = fn;
-  for (auto* f : {(const void*)k_tile<true>, (const void*)k_tile<false>}) {
-    if (cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tile_smem_bytes()) != cudaSuccess) {
-      st.err = std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(cudaGetLastError());
-      return CSK_ERR_CUDA;
+  for (int w16 = 0; w16 < 2; ++w16) {
+    const void* fs[2] = {w16 ? (const void*)k_tile<true, true> : (const void*)k_tile<true, false>,
+                         w16 ? (const void*)k_tile<false, true> : (const void*)k_tile<false, false>};
+    for (const void* f : fs) {
+      if (cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tile_smem_bytes(w16 != 0)) != cudaSuccess) {
+        st.err = std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(cudaGetLastError());
+        return CSK_ERR_CUDA;
+      }
     }
   }
   st.available = true;
@@ -638,8 +712,8 @@ inline int tile_set_buffers(TileState& st, const __half* x16, int ldx, const __h
   int rc = tile_make_map(st, &st.tmap_x, x16, rows_alloc, ldx);
   if (rc) return rc;
   rc = tile_make_map(st, &st.tmap_a, a16, rows_alloc, lda);
-  if (!rc) rc = tile_make_map(st, &st.tmap_xh, x16, rows_alloc, ldx, kTileM / 2);
-  if (!rc) rc = tile_make_map(st, &st.tmap_ah, a16, rows_alloc, lda, kTileM / 2);
+  if (!rc) rc = tile_make_map(st, &st.tmap_xh, x16, rows_alloc, ldx, kPairBoxRows);
+  if (!rc) rc = tile_make_map(st, &st.tmap_ah, a16, rows_alloc, lda, kPairBoxRows);
   if (rc) return rc;
   st.maps_ready = true;
   return CSK_OK;
@@ -667,14 +741,16 @@ inline int tile_launch(TileState& st, const uint8_t* weights, size_t expert_stri
   a.act = act;
   a.F = F;
   a.stall = stall ? 1 : 0;
-  const size_t smem = tile_smem_bytes();
+  const bool w16 = Lgu.w16 != 0;
+  const size_t smem = tile_smem_bytes(w16);
   // gate/up + activation
   a.mat_offset = off_gu;
   a.L = Lgu;
   a.a_out = a16;
   a.lda = lda;
   a.meta_slot = 0;
-  k_tile<true><<<sm_count, kTileThreads, smem, s>>>(st.tmap_x, a);
+  if (w16) k_tile<true, true><<<sm_count, kTileThreads, smem, s>>>(st.tmap_x, a);
+  else k_tile<true, false><<<sm_count, kTileThreads, smem, s>>>(st.tmap_x, a);
   mark();
   // down
   a.mat_offset = off_d;
@@ -684,7 +760,8 @@ inline int tile_launch(TileState& st, const uint8_t* weights, size_t expert_stri
   a.out_row_map = out_row_map;
   a.out_row_ptr = out_row_ptr;
   a.meta_slot = 1;
-  k_tile<false><<<sm_count, kTileThreads, smem, s>>>(st.tmap_a, a);
+  if (w16) k_tile<false, true><<<sm_count, kTileThreads, smem, s>>>(st.tmap_a, a);
+  else k_tile<false, false><<<sm_count, kTileThreads, smem, s>>>(st.tmap_a, a);
   mark();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {

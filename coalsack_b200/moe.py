@@ -56,11 +56,12 @@ class MoeLayer:
 
     def __init__(self, num_experts, top_k, hidden, ffn, activation=0, has_bias=True,
                  sigmoid_gating=False, weight_before_ffn=False, device=0, expert_begin=0,
-                 expert_count=0, max_tokens=1024):
+                 expert_count=0, max_tokens=1024, weights_f16=False):
         self._lib = _lib.load()
         self.cfg = Config(num_experts, top_k, hidden, ffn, int(activation), int(has_bias),
                           int(sigmoid_gating), int(weight_before_ffn), device, expert_begin,
-                          expert_count, 0, max_tokens)
+                          expert_count, 1 if weights_f16 else 0, max_tokens)
+        self.weights_f16 = bool(weights_f16)
         self.E, self.k, self.H, self.F = num_experts, top_k, hidden, ffn
         self.E_router = num_experts  # experts the router scores (fewer than E under an expert-parallel slot map)
         self.max_tokens = max_tokens
@@ -107,6 +108,29 @@ class MoeLayer:
                 raise RuntimeError("expert_mlp: weight dimension mismatch")
         b = [_np_f32(b_up), _np_f32(b_gate), _np_f32(b_down)]
         self._check(self._lib.csk_moe_load_expert_mxfp4(self._h, expert_id, *map(_p, arrs), *map(_p, b)))
+
+    def load_expert_f16(self, expert_id, w_up, w_gate, w_down, b_up=None, b_gate=None, b_down=None):
+        """fp16 weights: w_up, w_gate [F,H], w_down [H,F] (numpy float16 or the uint16 bit patterns)."""
+        arrs = []
+        for a, shape in ((w_up, (self.F, self.H)), (w_gate, (self.F, self.H)), (w_down, (self.H, self.F))):
+            a = np.asarray(a)
+            a = np.ascontiguousarray(a.view(np.uint16) if a.dtype == np.float16 else a.astype(np.uint16, copy=False))
+            if a.size != shape[0] * shape[1]:
+                raise RuntimeError("dense_ffn: weight dimension mismatch")
+            arrs.append(a.reshape(-1))
+        b = [_np_f32(b_up), _np_f32(b_gate), _np_f32(b_down)]
+        self._check(self._lib.csk_moe_load_expert_f16(self._h, expert_id, *map(_p, arrs), *map(_p, b)))
+
+    def dense_forward(self, hidden):
+        """The dense FFN (a layer with one expert and top-1): every row through the weight set."""
+        hidden = _np_f32(hidden)
+        T = hidden.size // self.H
+        out = np.empty((T, self.H), dtype=np.float32)
+        self._check(self._lib.csk_moe_dense_forward(self._h, _p(hidden), T, _p(out)))
+        return out.reshape(hidden.shape)
+
+    def dense_forward_dev(self, d_hidden, T, d_out, stream=None):
+        self._check(self._lib.csk_moe_dense_forward_dev(self._h, _p(d_hidden), T, _p(d_out), stream))
 
     def load_experts(self, experts: dict, ids=None):
         """``experts``: lists as made by ``synth.all_experts`` (index i <-> ids[i])."""
@@ -445,6 +469,59 @@ class expert_mlp_node:
         out = lay.expert_forward(self.expert_id_, hidden_states.reshape(B * S, H),
                                  router_output.reshape(B * S, k, 2))
         return out.reshape(B, S, H)
+
+
+class dense_ffn_node:
+    """dense_ffn_node (dense_ffn_node.h:28-219): the shared expert's dense gated FFN with standard
+    SwiGLU; fp16 weights, fp32 hidden states and biases.  ``compute(inputs)`` takes the reference's
+    4 or 7 inputs: hidden [B,S,H], gate_w [F,H], up_w [F,H], down_w [H,F] (float16)
+    [, gate_b [F], up_b [F], down_b [H]]."""
+
+    def __init__(self, device=0):
+        self.device = device
+        self._layer = None
+        self._key = None
+
+    def compute(self, inputs):
+        if len(inputs) not in (4, 7):
+            raise RuntimeError("dense_ffn: expected 4 or 7 inputs (hidden, gate_w, up_w, down_w[, gate_b, up_b, "
+                               f"down_b]), got {len(inputs)}")
+        hidden, gate_w, up_w, down_w = inputs[:4]
+        hidden = np.asarray(hidden)
+        if hidden.ndim != 3:
+            raise RuntimeError(f"dense_ffn: hidden_states must be 3D [B, S, D], got {hidden.ndim}D")
+        if any(np.asarray(w).ndim != 2 for w in (gate_w, up_w, down_w)):
+            raise RuntimeError("dense_ffn: weight tensors must be 2D")
+        if any(np.asarray(w).dtype != np.float16 for w in (gate_w, up_w, down_w)):
+            raise RuntimeError("dense_ffn: this build takes FLOAT16 weights (FLOAT32 weights are not supported)")
+        if hidden.dtype != np.float32:
+            raise RuntimeError("dense_ffn: hidden_states must be FLOAT32")
+        B, S, H = hidden.shape
+        F = gate_w.shape[0]
+        if gate_w.shape[1] != H or up_w.shape != (F, H):
+            raise RuntimeError("dense_ffn: gate_w/up_w shape mismatch")
+        if down_w.shape != (H, F):
+            raise RuntimeError(f"dense_ffn: down_w shape mismatch, expected [{H}, {F}], got "
+                               f"[{down_w.shape[0]}, {down_w.shape[1]}]")
+        has_bias = len(inputs) == 7
+        key = (H, F, has_bias, id(gate_w), id(up_w), id(down_w))
+        T = B * S
+        if self._layer is None or self._key != key or self._layer.max_tokens < T:
+            if self._layer is not None:
+                self._layer.close()
+            self._layer = MoeLayer(1, 1, H, F, activation=1, has_bias=has_bias, device=self.device,
+                                   max_tokens=max(T, 64), weights_f16=True)
+            b = inputs[4:7] if has_bias else (None, None, None)
+            # the reference's input order is gate, up, down; biases gate, up, down
+            self._layer.load_expert_f16(0, up_w, gate_w, down_w, b[1] if has_bias else None,
+                                        b[0] if has_bias else None, b[2] if has_bias else None)
+            self._key = key
+        return self._layer.dense_forward(hidden.reshape(T, H)).reshape(B, S, H)
+
+    def close(self):
+        if self._layer is not None:
+            self._layer.close()
+            self._layer = None
 
 
 class expert_merge_node:

@@ -57,6 +57,13 @@ enum {
  * use_sigmoid_gating / weight_before_ffn (include/coalsack/llm/graph_builder.h:29-44)
  * plus the per-node settings (moe_router_node.h:27-34, expert_mlp_node.h:44-52,
  * expert_merge_node.h:17-24). */
+/* How the experts' weight matrices arrive:
+ *   CSK_WEIGHTS_MXFP4  17-byte MXFP4 blocks (csk_moe_load_expert_mxfp4); both expert kernels.
+ *   CSK_WEIGHTS_F16    fp16 row-major matrices (csk_moe_load_expert_f16): the reference's fp16 expert
+ *                      slices (expert_mlp_node.h:533-647) and, with num_experts = top_k = 1, its dense
+ *                      shared-expert FFN (dense_ffn_node.h:28-219).  Tensor-core kernel only. */
+enum { CSK_WEIGHTS_MXFP4 = 0, CSK_WEIGHTS_F16 = 1 };
+
 typedef struct csk_moe_config {
   int32_t num_experts;        /* E, experts of the whole layer                    */
   int32_t top_k;              /* k                                                */
@@ -69,7 +76,7 @@ typedef struct csk_moe_config {
   int32_t device;             /* CUDA device ordinal                              */
   int32_t expert_begin;       /* first expert resident on this device ...         */
   int32_t expert_count;       /* ... and how many (0 = all E); expert parallelism */
-  int32_t reserved0;
+  int32_t weight_format;      /* CSK_WEIGHTS_MXFP4 (0, default) or CSK_WEIGHTS_F16         */
   int64_t max_tokens;         /* largest T (and, under expert parallelism, the
                                  largest number of received rows / k) of a call   */
 } csk_moe_config;
@@ -109,6 +116,18 @@ int csk_moe_load_expert_mxfp4(csk_moe_layer* layer, int32_t expert_id, const uin
 int csk_moe_load_experts_mxfp4(csk_moe_layer* layer, int32_t first_expert, int32_t count, const uint8_t* w_up,
                                const uint8_t* w_gate, const uint8_t* w_down, const float* b_up,
                                const float* b_gate, const float* b_down);
+/* Expert weights as fp16 row-major matrices (layers created with CSK_WEIGHTS_F16): w_up and w_gate
+ * [F,H], w_down [H,F], as dynamic_tensor holds FLOAT16 weights (dense_ffn_node.h:24, uint16 bit
+ * patterns); biases fp32 or NULL as in csk_moe_load_expert_mxfp4. */
+int csk_moe_load_expert_f16(csk_moe_layer* layer, int32_t expert_id, const uint16_t* w_up, const uint16_t* w_gate,
+                            const uint16_t* w_down, const float* b_up, const float* b_gate, const float* b_down);
+
+/* The dense gated FFN of dense_ffn_node (dense_ffn_node.h:28-219: every token through the one weight
+ * set, standard SwiGLU, biases optional) on a layer created with num_experts = top_k = 1,
+ * CSK_WEIGHTS_F16 and CSK_ACT_STANDARD_SWIGLU: no router is involved.  hidden and out [T,H] fp32. */
+int csk_moe_dense_forward(csk_moe_layer* layer, const float* hidden, int64_t T, float* out);
+int csk_moe_dense_forward_dev(csk_moe_layer* layer, const float* d_hidden, int64_t T, float* d_out, void* stream);
+
 /* The repacked weights of the resident experts as a file, and back: a later start of the same
  * layer (same shape, expert range and library build) skips the repack.  No counterpart in the
  * reference. */

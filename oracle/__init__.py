@@ -102,6 +102,10 @@ class _Lib:
         self._rms = getattr(L, prefix + "rmsnorm")
         self._rms.restype = C.c_int
         self._rms.argtypes = [_f32p, _f32p, C.c_float, _f32p, C.c_int64, C.c_int64]
+        self._dense = getattr(L, prefix + "dense_ffn_f16")
+        self._dense.restype = C.c_int
+        self._dense.argtypes = [_f32p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p,
+                                C.c_void_p, C.c_void_p, C.c_void_p, _f32p]
         self._layer = getattr(L, prefix + "moe_layer")
         self._layer.restype = C.c_int
         if self.is_ref:
@@ -165,6 +169,21 @@ class _Lib:
         rc = self._rms(_fp(x), _fp(w), float(eps), _fp(out), x.shape[0], x.shape[1])
         if rc:
             self._err(rc, "rmsnorm")
+        return out
+
+    def dense_ffn(self, hidden, gate_w, up_w, down_w, gate_b=None, up_b=None, down_b=None):
+        """dense_ffn_node: hidden [T,H] fp32; gate_w, up_w [F,H], down_w [H,F] float16; biases fp32 or None."""
+        hidden = _f32(hidden)
+        T, H = hidden.shape
+        w = [np.ascontiguousarray(np.asarray(a).view(np.uint16) if np.asarray(a).dtype == np.float16 else a,
+                                  dtype=np.uint16) for a in (gate_w, up_w, down_w)]
+        F = w[0].shape[0]
+        b = [None if a is None else _f32(a) for a in (gate_b, up_b, down_b)]
+        out = np.empty((T, H), dtype=np.float32)
+        rc = self._dense(_fp(hidden), T, H, F, *[a.ctypes.data for a in w],
+                         *[None if a is None else a.ctypes.data for a in b], _fp(out))
+        if rc:
+            self._err(rc, "dense_ffn")
         return out
 
     # --- expert ----------------------------------------------------------

@@ -292,3 +292,76 @@ int orc_rmsnorm(const float* x, const float* w, float eps, float* out, int64_t T
   }
   return 0;
 }
+
+/* fp16 bit pattern -> fp32 (what _mm256_cvtph_ps / _cvtsh_ss compute: exact). */
+static float half_to_float(uint16_t h) {
+  const uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+  const uint32_t exp = (h >> 10) & 0x1Fu, man = h & 0x3FFu;
+  uint32_t bits;
+  if (exp == 0) {
+    if (man == 0) {
+      bits = sign;
+    } else {  /* subnormal: normalise */
+      int e = -1;
+      uint32_t m = man;
+      do {
+        ++e;
+        m <<= 1;
+      } while ((m & 0x400u) == 0);
+      bits = sign | ((uint32_t)(127 - 15 - e) << 23) | ((m & 0x3FFu) << 13);
+    }
+  } else if (exp == 31) {
+    bits = sign | 0x7F800000u | (man << 13);
+  } else {
+    bits = sign | ((exp + 112u) << 23) | (man << 13);
+  }
+  float f;
+  memcpy(&f, &bits, 4);
+  return f;
+}
+
+/* include/coalsack/nn/nn_ops/dense_ffn_node.h:164-216 -- one row of fp16 weights against an fp32
+ * vector: eight running lanes, one fused multiply-add per lane and group of eight columns, the lanes
+ * folded by horizontal_sum_avx2 (:151-161: lo + hi halves, then (s0 + s1) + (s2 + s3) with s_i =
+ * lane_i + lane_{i+4}).  n must be a multiple of eight: the reference's scalar loop for the columns past
+ * the last full group is left to its compiler (partly vectorised, partly fused at -O2), and no layer this
+ * library accepts has such columns (hidden and ffn sizes are multiples of 32). */
+static float row_dot_f16(const float* x, const uint16_t* w, int64_t n) {
+  float lane[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  int64_t i = 0;
+  for (; i + 7 < n; i += 8)
+    for (int l = 0; l < 8; ++l) lane[l] = fmaf(x[i + l], half_to_float(w[i + l]), lane[l]);
+  /* sum128 = lo + hi; sums = sum128 + movehdup(sum128): element 0 = s0 + s1, element 2 = s2 + s3;
+   * movehl brings element 2 down; add_ss: (s0 + s1) + (s2 + s3) */
+  const float s0 = lane[0] + lane[4], s1 = lane[1] + lane[5], s2 = lane[2] + lane[6], s3 = lane[3] + lane[7];
+  float sum = (s0 + s1) + (s2 + s3);
+  return sum;
+}
+
+/* include/coalsack/nn/nn_ops/dense_ffn_node.h:28-118, 164-216 -- the dense gated FFN of the shared
+ * expert, fp16 weights: gate = x.Wg + bg, up = x.Wu + bu, act = gate / (1 + exp(-gate)) * up,
+ * out = act.Wd + bd; weights [F,H], [F,H], [H,F] as fp16 bit patterns, biases fp32 or NULL. */
+int orc_dense_ffn_f16(const float* hidden, int64_t T, int64_t H, int64_t F, const uint16_t* gate_w,
+                      const uint16_t* up_w, const uint16_t* down_w, const float* gate_b, const float* up_b,
+                      const float* down_b, float* out) {
+  if (H % 8 || F % 8) return -3;  /* see row_dot_f16 */
+  float* act = (float*)malloc(sizeof(float) * (size_t)F);
+  if (!act) return -2;
+  for (int64_t t = 0; t < T; ++t) {
+    const float* x = hidden + t * H;
+    for (int64_t o = 0; o < F; ++o) {
+      float g = row_dot_f16(x, gate_w + o * H, H), u = row_dot_f16(x, up_w + o * H, H);
+      if (gate_b) g += gate_b[o];
+      if (up_b) u += up_b[o];
+      const float silu = g / (1.0f + expf(-g));
+      act[o] = silu * u;
+    }
+    for (int64_t o = 0; o < H; ++o) {
+      float s = row_dot_f16(act, down_w + o * F, F);
+      if (down_b) s += down_b[o];
+      out[t * H + o] = s;
+    }
+  }
+  free(act);
+  return 0;
+}

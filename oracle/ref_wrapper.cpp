@@ -24,6 +24,7 @@
 #include <vector>
 
 #include "coalsack/gguf/gguf_dequant.h"
+#include "coalsack/nn/nn_ops/dense_ffn_node.h"
 #include "coalsack/nn/nn_ops/expert_merge_node.h"
 #include "coalsack/nn/nn_ops/expert_mlp_node.h"
 #include "coalsack/nn/nn_ops/rmsnorm_node.h"
@@ -280,6 +281,34 @@ int ref_rmsnorm(const float* x, const float* w, float eps, float* out, int64_t T
     rmsnorm_node node;
     node.set_epsilon(eps);
     dynamic_tensor r = node.compute_test(make_f32({1, T, H}, x), make_f32({H}, w));
+    std::memcpy(out, r.data_ptr<float>(), sizeof(float) * T * H);
+    return 0;
+  } catch (const std::exception& e) {
+    g_last_error = e.what();
+    return -1;
+  }
+}
+
+// The shared expert's dense FFN (dense_ffn_node::compute, protected: reached through a subclass).
+struct dense_ffn_probe : public dense_ffn_node {
+  using dense_ffn_node::compute;
+};
+int ref_dense_ffn_f16(const float* hidden, int64_t T, int64_t H, int64_t F, const uint16_t* gate_w,
+                      const uint16_t* up_w, const uint16_t* down_w, const float* gate_b, const float* up_b,
+                      const float* down_b, float* out) {
+  try {
+    dense_ffn_probe node;
+    std::vector<dynamic_tensor> in;
+    in.push_back(make_f32({1, T, H}, hidden));
+    in.push_back(dynamic_tensor(dtype::float16, {F, H}, gate_w));
+    in.push_back(dynamic_tensor(dtype::float16, {F, H}, up_w));
+    in.push_back(dynamic_tensor(dtype::float16, {H, F}, down_w));
+    if (gate_b) {
+      in.push_back(make_f32({F}, gate_b));
+      in.push_back(make_f32({F}, up_b));
+      in.push_back(make_f32({H}, down_b));
+    }
+    dynamic_tensor r = node.compute(in);
     std::memcpy(out, r.data_ptr<float>(), sizeof(float) * T * H);
     return 0;
   } catch (const std::exception& e) {

@@ -111,3 +111,16 @@ def rmsnorm_case():
     x = (g.standard_normal((6, 320)) * np.array([0.1, 1.0, 3.0, 10.0, 0.01, 1.0])[:, None]).astype(np.float32)
     w = (1.0 + 0.1 * g.standard_normal(320)).astype(np.float32)
     return x, w
+
+
+def dense_ffn_case(H=256, F=192, T=9, bias=True, seed=77):
+    """Inputs of the shared expert's dense FFN fixture: hidden [T,H] fp32, gate/up [F,H] and down [H,F]
+    float16 (N(0, 0.05), with a few subnormal and large entries), fp32 biases or None."""
+    g = np.random.default_rng(seed)
+    hidden = g.standard_normal((T, H)).astype(np.float32)
+    gate_w = (g.standard_normal((F, H)) * 0.05).astype(np.float16)
+    up_w = (g.standard_normal((F, H)) * 0.05).astype(np.float16)
+    down_w = (g.standard_normal((H, F)) * 0.05).astype(np.float16)
+    gate_w[0, :4] = np.array([6e-8, -3e-6, 1.5, -2.0], dtype=np.float16)   # subnormals and large values
+    b = [(g.standard_normal(n) * 0.01).astype(np.float32) for n in (F, F, H)] if bias else [None, None, None]
+    return hidden, gate_w, up_w, down_w, b[0], b[1], b[2]

@@ -80,6 +80,12 @@ def main():
     g["rmsnorm_out"] = r.rmsnorm(x, w, 1e-5)
     g["rmsnorm_crc"] = cases.crc(x, w)
 
+    # the shared expert's dense FFN (dense_ffn_node::compute), fp16 weights, with and without biases
+    for tag, bias in (("dense_b", True), ("dense_nb", False)):
+        hidden, gw, uw, dw, bg, bu, bd = cases.dense_ffn_case(bias=bias)
+        g[tag + "_out"] = r.dense_ffn(hidden, gw, uw, dw, bg, bu, bd)
+        g[tag + "_crc"] = cases.crc(hidden, gw.view(np.uint16), uw.view(np.uint16), dw.view(np.uint16))
+
     np.savez_compressed(OUT, **g)
     print(f"wrote {OUT}: {os.path.getsize(OUT) / 1024:.1f} KiB, {len(g)} arrays")
 

@@ -125,3 +125,16 @@ def test_rmsnorm_golden_and_reference(port, golden):
         x2 = g.standard_normal((9, 2880)).astype(np.float32)
         w2 = g.standard_normal(2880).astype(np.float32)
         assert np.array_equal(port.rmsnorm(x2, w2, 1e-6), oracle.ref().rmsnorm(x2, w2, 1e-6))
+
+
+@pytest.mark.parametrize("tag,bias", [("dense_b", True), ("dense_nb", False)])
+def test_dense_ffn_golden_and_reference(port, golden, tag, bias):
+    """The restated dense FFN (dense_ffn_node, fp16 weights) equals the reference's node output bit for bit
+    on the fixture, and the compiled reference itself on fresh inputs where its wrapper is present."""
+    hidden, gw, uw, dw, bg, bu, bd = cases.dense_ffn_case(bias=bias)
+    assert cases.crc(hidden, gw.view(np.uint16), uw.view(np.uint16), dw.view(np.uint16)) == golden[tag + "_crc"]
+    assert np.array_equal(port.dense_ffn(hidden, gw, uw, dw, bg, bu, bd), golden[tag + "_out"])
+    import oracle
+    if oracle.have_ref():
+        args = cases.dense_ffn_case(H=2880, F=96, T=3, bias=bias, seed=78)
+        assert np.array_equal(port.dense_ffn(*args), oracle.ref().dense_ffn(*args))
