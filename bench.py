@@ -13,6 +13,8 @@ ranks); ``e2e`` goes through the host-buffer entry point ``csk_moe_forward`` wit
 pinned host buffers, so it includes the host->device and device->host copies.
 ``decode`` (one GPU) is the same layer at 1..256 tokens per step, 100 fresh
 batches each, in microseconds per step and per token against the HBM roofline.
+``dense_ffn`` (one GPU) is the shared expert's dense FFN (fp16 weights of the layer's
+size) on the same token count, in TFLOP/s against the measured bf16 peak.
 
 N > 1 (launched by torchrun, one rank per GPU): expert parallelism.  Each rank
 holds E/N expert slots and T/N of the batch's tokens (strong scaling: the batch
@@ -197,6 +199,35 @@ def config_of(sh, total, args):
 DECODE_BATCHES = (1, 2, 4, 8, 16, 32, 64, 128, 256)
 
 
+def dense_ffn_point(sh, peaks, torch, stream, steps=10):
+    """The shared expert's dense FFN (fp16 weights, the layer's H and F) on the workload's token count:
+    device time per call, flops = 6*T*H*F, against the measured bf16 peak."""
+    from coalsack_b200 import MoeLayer
+    T, H, F = sh.tokens, sh.hidden, sh.ffn
+    g = np.random.Generator(np.random.Philox(key=[sh.seed, 77]))
+    w = [(g.standard_normal(s, dtype=np.float32) * 0.03).astype(np.float16) for s in ((F, H), (F, H), (H, F))]
+    lay = MoeLayer(1, 1, H, F, activation=synth.STANDARD_SWIGLU, has_bias=False, max_tokens=T, weights_f16=True)
+    lay.load_expert_f16(0, w[0], w[1], w[2])
+    d_h = torch.from_numpy(synth.hidden_states(sh)).cuda()
+    d_o = torch.empty_like(d_h)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            lay.dense_forward_dev(d_h, T, d_o, stream=stream.cuda_stream)
+        ev0.record(stream)
+        for _ in range(steps):
+            lay.dense_forward_dev(d_h, T, d_o, stream=stream.cuda_stream)
+        ev1.record(stream)
+    torch.cuda.synchronize()
+    lay.sync()
+    ms = ev0.elapsed_time(ev1) / steps
+    lay.close()
+    tf = 6.0 * T * H * F / (ms * 1e-3) / 1e12
+    return {"workload": f"dense_ffn_node: fp16 weights {H}x{F}, {T} tokens, standard SwiGLU, no biases",
+            "ms_per_call": ms, "tokens_per_s": T / (ms * 1e-3), "tflops": tf, "frac": tf / peaks["tflops"],
+            "peak": peaks["tflops"], "peak_source": peaks["source"] + " (burst bf16 cuBLAS)"}
+
+
 def decode_sweep(layer, sh, peaks, torch, stream, reps=100, nbuf=16):
     """Microseconds per step and per token for batches of 1..256 tokens on the resident layer: `reps`
     batches of fresh N(0,1) activations each (the decode workload's seed), timed back to back in segments
@@ -378,6 +409,7 @@ def run_ours(args):
         line["expert_parallel"] = stage.get("ep", {})
     if world == 1 and not args.skip_decode and sh.name == synth.C2.name:
         line["decode"] = decode_sweep(runner.layer, sh, peaks, torch, runner.torch_stream)
+        line["dense_ffn"] = dense_ffn_point(sh, peaks, torch, runner.torch_stream)
     if world == 1 and not args.skip_cpu:
         line["cpu_baseline"], _ = time_reference(sh, 2, 1)
     print(json.dumps(line))

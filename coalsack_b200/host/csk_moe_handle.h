@@ -58,7 +58,8 @@ class layer_handle {
                       want.hidden == cfg_.hidden && want.ffn == cfg_.ffn && want.activation == cfg_.activation &&
                       want.has_bias == cfg_.has_bias && want.sigmoid_gating == cfg_.sigmoid_gating &&
                       want.weight_before_ffn == cfg_.weight_before_ffn && want.expert_begin == cfg_.expert_begin &&
-                      want.expert_count == cfg_.expert_count && want.max_tokens <= cfg_.max_tokens;
+                      want.expert_count == cfg_.expert_count && want.weight_format == cfg_.weight_format &&
+                      want.max_tokens <= cfg_.max_tokens;
     if (!same) {
       reset();
       cfg_ = want;

@@ -12,6 +12,7 @@ OUT = os.path.join(HERE, "_build", "shim_check")
 
 
 GRAPH_OUT = os.path.join(HERE, "_build", "graph_check")
+DENSE_OUT = os.path.join(HERE, "_build", "dense_check")
 
 
 def _compile(src, out, ref, extra_inc=(), verbose=False):
@@ -42,6 +43,7 @@ def build(ref: str | None = None, verbose: bool = False) -> str | None:
     os.makedirs(os.path.dirname(OUT), exist_ok=True)
     _compile(os.path.join(HERE, "shim_check.cpp"), OUT, ref, verbose=verbose)
     _compile(os.path.join(HERE, "graph_check.cpp"), GRAPH_OUT, ref, extra_inc=[os.path.join(HERE, "stub")], verbose=verbose)
+    _compile(os.path.join(HERE, "dense_check.cpp"), DENSE_OUT, ref, verbose=verbose)
     return OUT
 
 

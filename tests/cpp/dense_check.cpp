@@ -1,0 +1,59 @@
+// Drives coalsack's dense FFN node -- through graph_builder::make_dense_ffn's own node type, with the GPU
+// operator binding in place of the reference's CPU operator -- on a seeded case read from a file written
+// by the test, twice (the second call reuses the uploaded weights), then once more after the gate matrix
+// was refilled in place, and writes the outputs back.
+#include <cstdio>
+#include <cstring>
+#include <fstream>
+#include <iostream>
+#include <vector>
+
+#include "coalsack/nn/nn_nodes.h"
+#include "coalsack/nn/nn_ops/dense_ffn_node.h"
+
+using namespace coalsack;
+
+int main(int argc, char** argv) {
+  if (argc < 3) return 2;
+  // file: int32 H, F, T, has_bias ; hidden[T,H] f32 ; gate[F,H] f16 ; up[F,H] f16 ; down[H,F] f16 ; (bg[F], bu[F], bd[H] f32)
+  std::ifstream f(argv[1], std::ios::binary);
+  std::vector<char> buf((std::istreambuf_iterator<char>(f)), std::istreambuf_iterator<char>());
+  const char* p = buf.data();
+  auto take = [&](size_t n) { const char* q = p; p += n; return q; };
+  const int32_t* hd = reinterpret_cast<const int32_t*>(take(4 * 4));
+  const int H = hd[0], F = hd[1], T = hd[2], has_bias = hd[3];
+  dynamic_tensor hidden(dtype::float32, {1, T, H}, take(sizeof(float) * T * H));
+  dynamic_tensor gate(dtype::float16, {F, H}, take(2u * F * H));
+  dynamic_tensor up(dtype::float16, {F, H}, take(2u * F * H));
+  dynamic_tensor down(dtype::float16, {H, F}, take(2u * F * H));
+  std::vector<dynamic_tensor> in = {hidden, gate, up, down};
+  if (has_bias) {
+    in.push_back(dynamic_tensor(dtype::float32, {F}, take(sizeof(float) * F)));
+    in.push_back(dynamic_tensor(dtype::float32, {F}, take(sizeof(float) * F)));
+    in.push_back(dynamic_tensor(dtype::float32, {H}, take(sizeof(float) * H)));
+  }
+  dense_ffn_node node;
+  dynamic_tensor a = node.compute_test(in);
+  dynamic_tensor b = node.compute_test(in);
+  if (std::memcmp(a.data_ptr<float>(), b.data_ptr<float>(), sizeof(float) * T * H) != 0) {
+    std::cerr << "second call differs from the first\n";
+    return 1;
+  }
+  // the gate matrix refilled in place (negated): the upload is keyed on content, so the output must change
+  uint16_t* g = in[1].data_ptr<uint16_t>();
+  for (size_t i = 0; i < (size_t)F * H; ++i) g[i] ^= 0x8000u;
+  dynamic_tensor c = node.compute_test(in);
+  std::ofstream o(argv[2], std::ios::binary);
+  o.write(reinterpret_cast<const char*>(a.data_ptr<float>()), sizeof(float) * T * H);
+  o.write(reinterpret_cast<const char*>(c.data_ptr<float>()), sizeof(float) * T * H);
+  // error envelope: the reference's text for a wrong input count
+  try {
+    node.compute_test({hidden, gate});
+    std::cerr << "no exception for two inputs\n";
+    return 1;
+  } catch (const std::exception& e) {
+    if (std::string(e.what()).find("expected 4 or 7 inputs") == std::string::npos) return 1;
+  }
+  std::printf("dense_check ok: H=%d F=%d T=%d bias=%d\n", H, F, T, has_bias);
+  return 0;
+}

@@ -33,6 +33,10 @@ def test_bindings_compile_against_reference_headers():
     syms = subprocess.run(["nm", "-D", build_check.GRAPH_OUT], capture_output=True, text=True).stdout
     for s in ("csk_moe_route", "csk_moe_forward", "csk_moe_expert_forward", "csk_moe_load_expert_mxfp4", "csk_moe_set_activation"):
         assert s in syms, f"{s}: graph_check does not reach the GPU bindings"
+    assert os.path.exists(build_check.DENSE_OUT)
+    syms = subprocess.run(["nm", "-D", build_check.DENSE_OUT], capture_output=True, text=True).stdout
+    for s in ("csk_moe_load_expert_f16", "csk_moe_dense_forward"):
+        assert s in syms, f"{s}: dense_check does not reach the GPU binding"
 
 
 @pytest.mark.gpu
@@ -149,3 +153,26 @@ def test_graph_fused_mode_at_the_20b_shape(gpu_lib, port, tmp_path):
     print(f"fused graph frame {graph_ms:.3f} ms vs csk_moe_forward {direct_ms:.3f} ms ({graph_ms / direct_ms:.2f}x)")
     # the graph adds the router node's own call, E + 3 message hops and the fetch node's residency check
     assert graph_ms < 4.0 * direct_ms + 0.5
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("bias", [True, False])
+def test_dense_ffn_node_binding(gpu_lib, port, bias, tmp_path):
+    """coalsack's dense_ffn_node type with the GPU binding behind it: output against the restatement, the
+    weights uploaded once and again after an in-place refill, the reference's error text."""
+    exe = build_check.DENSE_OUT
+    if not os.path.exists(exe):
+        pytest.skip("tests/cpp/_build/dense_check was not built (needs the reference checkout at build time)")
+    hidden, gw, uw, dw, bg, bu, bd = cases.dense_ffn_case(H=256, F=192, T=37, bias=bias, seed=83)
+    inp, outp = tmp_path / "in.bin", tmp_path / "out.bin"
+    with open(inp, "wb") as f:
+        f.write(np.array([256, 192, 37, int(bias)], np.int32).tobytes())
+        for a in (hidden, gw, uw, dw) + ((bg, bu, bd) if bias else ()):
+            f.write(np.ascontiguousarray(a).tobytes())
+    r = subprocess.run([exe, str(inp), str(outp)], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stdout + r.stderr
+    raw = np.fromfile(outp, np.float32).reshape(2, 37, 256)
+    for got, gate in ((raw[0], gw), (raw[1], -gw)):
+        want = port.dense_ffn(hidden, gate, uw, dw, bg, bu, bd)
+        mx, mr = cases.err_stats(got, want)
+        assert mx <= cases.MAX_ABS_OVER_RMS and mr <= cases.MEAN_REL, (mx, mr)
