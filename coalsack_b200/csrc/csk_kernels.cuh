@@ -1388,11 +1388,20 @@ constexpr int kEpMaxWorld = 64;
 __host__ __device__ inline size_t ep_sync_ints(int E) { return (size_t)3 * kEpMaxWorld + (size_t)kEpMaxWorld * E; }
 
 __global__ void __launch_bounds__(1024)
-k_ep_p2p_sync(float* const* __restrict__ peer_back, size_t tail_floats, int me, int world, int which, int epoch,
-              const int* __restrict__ my_counts, int E, int* __restrict__ all_counts_out, int* __restrict__ meta) {
-  __shared__ int s_timeout;
+k_ep_p2p_sync(float* const* __restrict__ peer_back, size_t tail_floats, int me, int world, int which,
+              int* __restrict__ epochs, const int* __restrict__ my_counts, int E, int* __restrict__ all_counts_out,
+              int* __restrict__ meta) {
+  __shared__ int s_timeout, s_epoch;
   const int tid = threadIdx.x;
-  if (tid == 0) s_timeout = 0;
+  // The barrier's generation lives on the device and every launch advances its own rank's copy: all
+  // ranks launch the same sequence, so their copies agree, and a captured launch sequence can be
+  // replayed (a generation passed from the host would be frozen into the graph).
+  if (tid == 0) {
+    s_timeout = 0;
+    s_epoch = ++epochs[which];
+  }
+  __syncthreads();
+  const int epoch = s_epoch;
   if (my_counts) {
     for (int idx = tid; idx < world * E; idx += blockDim.x) {
       const int r = idx / E, e = idx % E;

@@ -54,7 +54,7 @@ struct csk_moe_layer {
   // expert parallelism over peer memory
   int p2p_rank = -1, p2p_world = 0;
   size_t back_tail = 0;               // floats of d_back in front of its sync area
-  int p2p_epoch[3] = {0, 0, 0};       // epochs of the three flag barriers of a step
+  int* d_p2p_epoch = nullptr;         // device: generations of the three flag barriers of a step
   RowOrigin* d_info = nullptr;        // [max_rows] origin of every received row
   float* d_back = nullptr;            // [max_T*k, H] output rows returned for this rank's pairs
   float** d_row_ptr = nullptr;        // [max_rows] where each received row's output goes
@@ -680,6 +680,8 @@ int csk_moe_create(const csk_moe_config* cfg, csk_moe_layer** out) {
   CK(cudaMalloc(&L->d_hidden, sizeof(float) * L->max_T * L->H));
   CK(cudaMalloc(&L->d_router, sizeof(float) * L->max_T * L->k * 2));
   CK(cudaMalloc(&L->d_router_phys, sizeof(float) * L->max_T * L->k * 2));
+  CK(cudaMalloc(&L->d_p2p_epoch, sizeof(int) * 4));
+  CK(cudaMemset(L->d_p2p_epoch, 0, sizeof(int) * 4));
   if (L->E == 1 && L->k == 1) {  // a dense FFN: every token goes to expert 0 with weight 1
     std::vector<float> unit(2 * (size_t)L->max_T);
     for (int64_t t = 0; t < L->max_T; ++t) {
@@ -738,7 +740,7 @@ int csk_moe_destroy(csk_moe_layer* L) {
     if (g.exec) cudaGraphExecDestroy(g.exec);
   tile_destroy(L->tile);
   for (void* p : L->ipc_opened) cudaIpcCloseMemHandle(p);
-  void* dev[] = {L->d_unit_router, L->d_stage2, L->d_norm_w, L->d_normed, L->d_part, L->d_hn2, L->d_wnorm, L->d_fb_list, L->d_fb, L->d_info, L->d_back, L->d_row_ptr, L->d_p2p_base, L->d_peer_x16, L->d_peer_info, L->d_peer_back,
+  void* dev[] = {L->d_p2p_epoch, L->d_unit_router, L->d_stage2, L->d_norm_w, L->d_normed, L->d_part, L->d_hn2, L->d_wnorm, L->d_fb_list, L->d_fb, L->d_info, L->d_back, L->d_row_ptr, L->d_p2p_base, L->d_peer_x16, L->d_peer_info, L->d_peer_back,
                  L->d_router_phys, L->d_slot_map, L->d_weights, L->d_resident, L->d_stage, L->d_wg, L->d_wg_few, L->d_wg_many, L->d_route_cnt, L->d_logits, L->d_rbias, L->d_hidden,
                  L->d_router, L->d_out, L->d_x16, L->d_a16, L->d_y, L->d_counts, L->d_offsets,
                  L->d_cursor, L->d_row_of_pair, L->d_pair_of_row, L->d_out_row_map, L->d_seg, L->d_tiles, L->d_meta};
@@ -1613,9 +1615,8 @@ int csk_moe_ep_p2p_sync_dev(csk_moe_layer* L, int32_t which, const int32_t* d_co
     return fail(L, CSK_ERR_INVALID, "p2p sync: which must be 0..2, counts and all_counts go together");
   CSK_CUDA(L, cudaSetDevice(L->cfg.device));
   cudaStream_t s = pick(L, stream);
-  const int epoch = ++L->p2p_epoch[which];
-  k_ep_p2p_sync<<<1, 1024, 0, s>>>(L->d_peer_back, L->back_tail, L->p2p_rank, L->p2p_world, which, epoch, d_counts, L->E,
-                                   d_all_counts, L->d_meta);
+  k_ep_p2p_sync<<<1, 1024, 0, s>>>(L->d_peer_back, L->back_tail, L->p2p_rank, L->p2p_world, which, L->d_p2p_epoch,
+                                   d_counts, L->E, d_all_counts, L->d_meta);
   CSK_CUDA(L, cudaGetLastError());
   L->last_stream = s;
   return CSK_OK;

@@ -376,6 +376,7 @@ class EpBench:
         self.exchange = ("rows stored into peer memory by the dispatch and down-projection kernels (NVLink); counts and "
                          + ("barriers by flags in peer memory" if getattr(self.ep, "flags", False) else "barriers by NCCL")
                          if self.p2p else "all-to-all collectives (NCCL)")
+
         self.place = place
         self.load = load
         self.h_host = torch.from_numpy(h).pin_memory()
@@ -384,10 +385,41 @@ class EpBench:
         self.d_out = torch.empty_like(self.d_hidden)
         self.torch_stream = torch.cuda.Stream(device=self.dev)
         self.T = sh.tokens
+        self._graph, self._graph_ok = None, os.environ.get("CSK_EP_GRAPH", "1") != "0"
 
     def step_dev(self):
-        with self.torch.cuda.stream(self.torch_stream):
-            self.ep.forward(self.d_hidden, self.T, self.d_out)
+        """One step on the bench's stream.  The peer-memory step with flag barriers is a fixed sequence of
+        kernel launches (no host reads, barrier generations kept on the device), so it is captured into a
+        CUDA graph on first use and replayed: sixteen short kernels leave the host's launch path."""
+        torch = self.torch
+        if self._graph is None and self._graph_ok and self.p2p and getattr(self.ep, "flags", False):
+            try:
+                with torch.cuda.stream(self.torch_stream):
+                    self.ep.forward(self.d_hidden, self.T, self.d_out)   # warm: nothing is created lazily in capture
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=self.torch_stream, capture_error_mode="thread_local"):
+                    self.ep.forward(self.d_hidden, self.T, self.d_out)
+                self._graph = g
+                self.exchange += "; the step replayed as one CUDA graph"
+            except Exception as exc:  # capture refused: keep launching the stages one by one
+                import sys
+                print(f"[rank {self.rank}] step not captured ({exc}); launching eagerly", file=sys.stderr)
+                self._graph_ok = False
+                torch.cuda.synchronize()
+            # every rank must run the same way (a rank replaying against ranks launching eagerly is still
+            # the same kernel sequence, but keep the runs uniform)
+            import torch.distributed as dist
+            agree = torch.tensor([1 if self._graph is not None else 0], device=self.dev)
+            dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+            if not bool(agree.item()):
+                self._graph, self._graph_ok = None, False
+                self.exchange = self.exchange.replace("; the step replayed as one CUDA graph", "")
+        with torch.cuda.stream(self.torch_stream):
+            if self._graph is not None:
+                self._graph.replay()
+            else:
+                self.ep.forward(self.d_hidden, self.T, self.d_out)
 
     def sync(self):
         self.torch.cuda.synchronize()
