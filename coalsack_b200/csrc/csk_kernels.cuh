@@ -981,12 +981,18 @@ k_scan(int* __restrict__ counts, int E, int e_begin, int e_count, int tile_rows,
     }
     // step back over empty experts that share the offset: the owner is the last
     // expert with that offset that actually has tiles, i.e. the largest index.
-    const int r = (i - s_tile_off[lo]) * tile_rows;
     const int cnt = (lo < 1023 ? s_row_off[lo + 1] : s_row_off[1024]) - s_row_off[lo];
+    // An expert with two to four tensor-core tiles gets them equally tall (rounded up to the MMA's 16-row
+    // step) instead of full tiles and a short rest: a tile's cost is nearly flat below ~175 rows, so
+    // 128 + 128 rows are cheaper than 192 + 64.  (More tiles: only the last one would change.)
+    const int ntl = (cnt + tile_rows - 1) / tile_rows;
+    int per = tile_rows;
+    if (tile_rows >= 64 && ntl >= 2 && ntl <= 4) per = min(tile_rows, (((cnt + ntl - 1) / ntl) + 15) & ~15);
+    const int r = (i - s_tile_off[lo]) * per;
     RowTile t;
     t.expert = lo - e_begin;
     t.row0 = s_row_off[lo] + r;
-    t.rows = min(tile_rows, cnt - r);
+    t.rows = min(per, cnt - r);
     t.pad = 0;
     tiles[i] = t;
   }
