@@ -16,12 +16,15 @@
 //     (cvt.e2m1x2 -> half2, times 2^(e - e_max + 13)) and write it straight into
 //     tensor memory with tcgen05.st: thread = one weight row x the 64 columns of
 //     the k-step, one half of the tile after the other.  The groups alternate
-//     k-steps and each owns one slot of the two-slot weight ring; a half is
-//     published as soon as it is stored, so the MMAs of the first half run while
-//     the second is converted.  The dequantised weights never touch shared memory;
-//   * one lane issues eight tcgen05.mma (kind::f16, A from tensor memory, B = the
-//     token tile via a shared-memory descriptor) per k-step, four per half, into
-//     two fp32 accumulators in tensor memory;
+//     k-steps and each owns one slot of the two-slot weight ring; the first half
+//     is converted before the slot is awaited.  The dequantised weights never
+//     touch shared memory.  (fp16 weights -- the dense FFN, fp16 expert slices --
+//     take the same route with a copy in place of the conversion.);
+//   * the MMA warp runs its loop warp-wide with one elected lane issuing: per
+//     k-step ONE barrier test (the slot is full), then eight tcgen05.mma (kind::f16,
+//     A from tensor memory, B = the token tile via a shared-memory descriptor),
+//     four per half, into two fp32 accumulators in tensor memory, then one commit
+//     that releases both the shared-memory stage and the slot;
 //   * sixteen epilogue warps read the accumulators (lane = weight row, column =
 //     token), scale by the matrix's power of two, add the bias and either apply
 //     the gated activation (the gate and the up accumulator of a feature sit in the
