@@ -25,12 +25,12 @@
 //     A from tensor memory, B = the token tile via a shared-memory descriptor),
 //     four per half, into two fp32 accumulators in tensor memory, then one commit
 //     that releases both the shared-memory stage and the slot;
-//   * sixteen epilogue warps read the accumulators (lane = weight row, column =
-//     token), scale by the matrix's power of two, add the bias and either apply
-//     the gated activation (the gate and the up accumulator of a feature sit in the
-//     same lane, 192 columns apart; a warp finishes four lane quarters' worth of
-//     48 token columns) and store fp16 rows, or (plain matrix: per half, four lane
-//     quarters x two column ranges) store fp32 output rows.
+//   * twelve epilogue warps (three per lane quarter) read the accumulators (lane =
+//     weight row, column = token), scale by the matrix's power of two, add the bias
+//     and either apply the gated activation (the gate and the up accumulator of a
+//     feature sit in the same lane, 192 columns apart; a warp finishes 64 token
+//     columns) and store fp16 rows, or (plain matrix: a warp finishes 128 of the
+//     two halves' 2 x 192 columns) store fp32 output rows.
 //
 // Tensor memory (512 columns): [0,384) the accumulators of the two halves, 192
 // columns each; [384,512) a ring of two dequantised weight tiles, 2 x 32 columns
@@ -59,7 +59,7 @@ namespace csk {
 constexpr int kTileM = 192;          // token rows of a row tile (TMA box height, MMA N <= 192)
 constexpr int kTileW = 128;          // weight rows of half a weight tile (tensor-memory lanes, MMA M)
 constexpr int kDequantWarps = 8;
-constexpr int kEpilogueWarps = 16;
+constexpr int kEpilogueWarps = 12;    // four lane quarters x three column ranges (sixteen measured no faster)
 constexpr int kTileThreads = (2 + kDequantWarps + kEpilogueWarps) * 32;  // producer, MMA, dequantisers, epilogue
 constexpr int kTileABytes = kTileM * 128;                   // token tile in shared memory
 constexpr int kHalfPacked = 4352;                           // packed half tile: 4096 codes + 256 scales
@@ -560,7 +560,9 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
         if (halves > 1) {
           // h is reused: the stores above read their registers asynchronously, so they have to be waited for
           // before the registers change (with fp16 weights the second conversion is only eight loads, and
-          // without this wait rows of the first half were occasionally stored with the second half's values)
+          // without this wait rows of the first half were occasionally stored with the second half's values).
+          // Converting both halves ahead of the slot wait (64 registers), or giving each thread half a row
+          // of both halves (sixteen dequantiser warps), both measured slower than this.
           tmem_st_wait();
           convert(packed + HALF_B, emax, h);
           tmem_st16(t_slot + 32, h[0]);
@@ -576,18 +578,20 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
     // ------------------------------ epilogue ------------------------------
     const int quarter = warp & 3;  // tensor-memory lanes 32*quarter .. +31 belong to this warp
     const int ew = warp - 2 - kDequantWarps;
-    // plain matrix: a warp finishes one half x one of two column ranges; gate/up: both halves
-    // (gate and up of its lane's feature) x one of four 48-column ranges
-    const int half = GATED ? 0 : (ew >> 2) & 1;
-    const int c_begin = GATED ? (ew >> 2) * (kTileM / 4) : (ew >> 3) * (kTileM / 2);
-    const int c_end = c_begin + (GATED ? kTileM / 4 : kTileM / 2);
+    // three warps per lane quarter.  gate/up: both halves (gate and up of its lane's feature) x one of three
+    // 64-column ranges.  Plain matrix: the two halves' columns laid end to end (2 x 192) x one of three
+    // 128-column ranges, walked in steps of 32 that never straddle the halves.
+    constexpr int kRange = GATED ? kTileM / 3 : 2 * kTileM / 3;
+    static_assert(kTileM % 96 == 0, "three equal column ranges of whole 32-column steps");
+    const int c_begin = (ew >> 2) * kRange;
+    const int c_end = c_begin + kRange;
     const int trow = quarter * 32 + lane;
     long it = 0;
     bool ok = true;
     for (long item = blockIdx.x; ok && item < n_items; item += gridDim.x, ++it) {
       const RowTile rt = A.tiles[item / L.n_tiles];
       const int nt = (int)(item % L.n_tiles);
-      const bool active = half < L.halves(nt);
+      const int halves = L.halves(nt);
       const uint8_t* ebase = A.weights + (size_t)rt.expert * A.expert_stride;
       const float* bias = reinterpret_cast<const float*>(ebase + A.bias_offset);
       const int emax = reinterpret_cast<const int*>(ebase + A.meta_offset)[A.meta_slot];
@@ -597,10 +601,8 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
         break;
       }
       tc_fence_after();
-      const uint32_t t_acc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)half * kTileM;
-      if (!active) {
-        // this half of the last weight tile is padding: nothing to finish
-      } else if (GATED) {
+      const uint32_t t_acc = tmem_base + ((uint32_t)(quarter * 32) << 16);
+      if (GATED) {
         // lane = feature; its gate accumulator is in half 0, its up accumulator in half 1
         const int feat = nt * kTileW + trow;
         const bool feat_ok = feat < L.N;
@@ -626,12 +628,14 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
           }
         }
       } else {
-        const int n = nt * 2 * kTileW + half * kTileW + trow;
-        const bool n_ok = n < L.N;
-        const float my_bias = (A.has_bias && n_ok) ? bias[2 * A.F + n] : 0.f;
-        for (int c0 = c_begin; c0 < min(rt.rows, c_end); c0 += 32) {
+        for (int v0 = c_begin; v0 < c_end; v0 += 32) {
+          const int half = v0 >= kTileM ? 1 : 0, c0 = v0 - half * kTileM;
+          if (half >= halves || c0 >= rt.rows) continue;
+          const int n = nt * 2 * kTileW + half * kTileW + trow;
+          const bool n_ok = n < L.N;
+          const float my_bias = (A.has_bias && n_ok) ? bias[2 * A.F + n] : 0.f;
           uint32_t r[32];
-          tmem_ld32(t_acc + c0, r);
+          tmem_ld32(t_acc + (uint32_t)v0, r);
           tmem_ld_wait();
           // lane j fetches the address of token c0 + j's output row once; every lane then reads it by shuffle
           float* my_row = nullptr;
