@@ -517,7 +517,10 @@ int forward_dev(csk_moe_layer* L, const float* d_hidden, int64_t T, const float*
   const int tile_rows = tile_rows_for(L, path, only_expert >= 0 ? rows * std::max(1, L->Eloc) : rows);
   if (reinterpret_cast<uintptr_t>(d_hidden) % 16) return fail(L, CSK_ERR_INVALID, "hidden states must be 16-byte aligned");
   // small batches on the streaming kernel: no fp16 row buffer in between, the kernel gathers its rows
-  const bool gather = path == CSK_PATH_STREAM && T * L->k <= kOneBlockPairs;
+  // (up to 64 pairs: measured, the launch it saves is worth 2-3 us of a 50-190 us step there; with more rows per
+  // tile every work unit's copy of the gather costs more than the launch -- 7 % of the step at 32 tokens on 32 experts)
+  constexpr int64_t kGatherMaxPairs = 64;
+  const bool gather = path == CSK_PATH_STREAM && T * L->k <= kGatherMaxPairs;
   int rc = launch_permute(L, d_hidden, router, T, only_expert, tile_rows, L->e0, L->Eloc, L->d_x16,
                           L->ldx, L->max_rows, s, gather);
   if (rc) return rc;
