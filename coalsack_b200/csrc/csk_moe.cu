@@ -10,6 +10,7 @@
 
 #include "csk_common.cuh"
 #include "csk_kernels.cuh"
+#include "csk_kquant.cuh"
 #include "csk_stream.cuh"
 #include "csk_tile.cuh"
 #include "csk_tile2.cuh"
@@ -790,14 +791,17 @@ int csk_moe_set_router(csk_moe_layer* L, const float* gate_w, const float* gate_
 
 namespace {
 // One expert: raw blocks to a staging area, the four repacks, biases.  Enqueue only; `stage` is one
-// of the handle's two staging areas (3 * stage_bytes each).
+// of the handle's two staging areas (3 * stage_bytes each).  With null weight pointers the staging
+// area already holds the three matrices (decoded there by the caller).
 int load_expert_enqueue(csk_moe_layer* L, int le, const uint8_t* w_up, const uint8_t* w_gate, const uint8_t* w_down,
                         const float* b_up, const float* b_gate, const float* b_down, uint8_t* stage, cudaStream_t s) {
   uint8_t* base = L->d_weights + (size_t)le * L->expert_stride;
   uint8_t *s_up = stage, *s_gate = stage + L->stage_bytes, *s_down = stage + 2 * L->stage_bytes;
-  CSK_CUDA(L, cudaMemcpyAsync(s_up, w_up, L->stage_bytes, cudaMemcpyHostToDevice, s));
-  CSK_CUDA(L, cudaMemcpyAsync(s_gate, w_gate, L->stage_bytes, cudaMemcpyHostToDevice, s));
-  CSK_CUDA(L, cudaMemcpyAsync(s_down, w_down, L->stage_bytes, cudaMemcpyHostToDevice, s));
+  if (w_up) {
+    CSK_CUDA(L, cudaMemcpyAsync(s_up, w_up, L->stage_bytes, cudaMemcpyHostToDevice, s));
+    CSK_CUDA(L, cudaMemcpyAsync(s_gate, w_gate, L->stage_bytes, cudaMemcpyHostToDevice, s));
+    CSK_CUDA(L, cudaMemcpyAsync(s_down, w_down, L->stage_bytes, cudaMemcpyHostToDevice, s));
+  }
   int* emeta = reinterpret_cast<int*>(base + L->off_meta);
   CSK_CUDA(L, cudaMemsetAsync(emeta, 0, 16, s));
   if (L->w16) {
@@ -860,6 +864,113 @@ int csk_moe_load_expert_f16(csk_moe_layer* L, int32_t expert_id, const uint16_t*
   if (rc) return rc;
   CSK_CUDA(L, cudaStreamSynchronize(L->stream));
   L->resident[le] = 1;
+  return CSK_OK;
+}
+
+namespace {
+size_t ggml_bytes(int32_t type, int64_t n) {
+  switch (type) {
+    case CSK_GGML_F16: return (size_t)n * 2;
+    case CSK_GGML_Q4_K: return (size_t)(n / kQkK) * kQ4kBytes;
+    case CSK_GGML_Q6_K: return (size_t)(n / kQkK) * kQ6kBytes;
+  }
+  return 0;
+}
+// Raw blocks of one matrix (device) to fp16 (device).  Enqueue only.
+void ggml_decode_enqueue(int32_t type, const uint8_t* d_raw, unsigned short* d_f16, int64_t n, bool nearest,
+                         cudaStream_t s) {
+  const int64_t nb = n / kQkK;
+  if (type == CSK_GGML_Q4_K) {
+    const int grid = grid_for((size_t)nb * 4 * 32, 256, 8192);
+    if (nearest) k_dequant_q4k<true><<<grid, 256, 0, s>>>(d_raw, d_f16, nb);
+    else k_dequant_q4k<false><<<grid, 256, 0, s>>>(d_raw, d_f16, nb);
+  } else {
+    const int grid = grid_for((size_t)nb * 2 * 32, 256, 8192);
+    if (nearest) k_dequant_q6k<true><<<grid, 256, 0, s>>>(d_raw, d_f16, nb);
+    else k_dequant_q6k<false><<<grid, 256, 0, s>>>(d_raw, d_f16, nb);
+  }
+}
+}  // namespace
+
+int csk_moe_load_expert_ggml(csk_moe_layer* L, int32_t expert_id, int32_t type_up, const void* w_up,
+                             int32_t type_gate, const void* w_gate, int32_t type_down, const void* w_down,
+                             const float* b_up, const float* b_gate, const float* b_down, int32_t f16_rounding) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  if (!L->w16)
+    return fail(L, CSK_ERR_INVALID, "this layer holds MXFP4 weights: Q4_K / Q6_K / F16 slices need a layer created "
+                                    "with CSK_WEIGHTS_F16");
+  if (expert_id < L->e0 || expert_id >= L->e0 + L->Eloc)
+    return fail(L, CSK_ERR_INVALID, "expert %d is not resident on this device (range [%d,%d))",
+                expert_id, L->e0, L->e0 + L->Eloc);
+  if (!w_up || !w_gate || !w_down) return fail(L, CSK_ERR_INVALID, "null weight pointer");
+  if (L->cfg.has_bias && (!b_up || !b_gate || !b_down))
+    return fail(L, CSK_ERR_INVALID, "layer has biases but a bias pointer is null");
+  if (f16_rounding != CSK_F16_TRUNCATE && f16_rounding != CSK_F16_NEAREST)
+    return fail(L, CSK_ERR_INVALID, "f16_rounding must be CSK_F16_TRUNCATE or CSK_F16_NEAREST, got %d", f16_rounding);
+  const int32_t types[3] = {type_up, type_gate, type_down};
+  const void* src[3] = {w_up, w_gate, w_down};
+  const int64_t n = (int64_t)L->H * L->F;  // a multiple of 1024: whole super-blocks
+  for (int i = 0; i < 3; ++i)
+    if (types[i] != CSK_GGML_F16 && types[i] != CSK_GGML_Q4_K && types[i] != CSK_GGML_Q6_K)
+      return fail(L, CSK_ERR_INVALID, "ggml type %d is not handled (F16 = %d, Q4_K = %d, Q6_K = %d)", types[i],
+                  CSK_GGML_F16, CSK_GGML_Q4_K, CSK_GGML_Q6_K);
+  CSK_CUDA(L, cudaSetDevice(L->cfg.device));
+  if (!L->d_stage2) {
+    cudaError_t e = cudaMalloc(&L->d_stage2, 3 * L->stage_bytes);
+    if (e != cudaSuccess) return fail(L, CSK_ERR_NOMEM, "cudaMalloc failed: %s", cudaGetErrorString(e));
+  }
+  cudaStream_t s = L->stream;
+  for (int i = 0; i < 3; ++i) {
+    uint8_t* f16 = L->d_stage + (size_t)i * L->stage_bytes;
+    if (types[i] == CSK_GGML_F16) {
+      CSK_CUDA(L, cudaMemcpyAsync(f16, src[i], L->stage_bytes, cudaMemcpyHostToDevice, s));
+    } else {
+      // the blocks are smaller than the fp16 matrix: they fit the second staging area's slot
+      uint8_t* raw = L->d_stage2 + (size_t)i * L->stage_bytes;
+      CSK_CUDA(L, cudaMemcpyAsync(raw, src[i], ggml_bytes(types[i], n), cudaMemcpyHostToDevice, s));
+      ggml_decode_enqueue(types[i], raw, reinterpret_cast<unsigned short*>(f16), n, f16_rounding == CSK_F16_NEAREST, s);
+    }
+  }
+  CSK_CUDA(L, cudaGetLastError());
+  const int le = expert_id - L->e0;
+  int rc = load_expert_enqueue(L, le, nullptr, nullptr, nullptr, b_up, b_gate, b_down, L->d_stage, s);
+  if (rc) return rc;
+  CSK_CUDA(L, cudaStreamSynchronize(s));
+  L->resident[le] = 1;
+  return CSK_OK;
+}
+
+int csk_moe_dequant_ggml_f16(int32_t device, int32_t ggml_type, const void* blocks, int64_t n_elements, uint16_t* out_f16,
+                         int32_t f16_rounding) {
+  if (!blocks || !out_f16) return fail(nullptr, CSK_ERR_INVALID, "dequant_ggml: null argument");
+  if (ggml_type != CSK_GGML_Q4_K && ggml_type != CSK_GGML_Q6_K)
+    return fail(nullptr, CSK_ERR_INVALID, "dequant_ggml: ggml type %d is not handled (Q4_K = %d, Q6_K = %d)", ggml_type,
+                CSK_GGML_Q4_K, CSK_GGML_Q6_K);
+  if (n_elements <= 0 || n_elements % kQkK)
+    return fail(nullptr, CSK_ERR_INVALID, "dequant_ggml: the element count must be a positive multiple of %d, got %lld",
+                kQkK, (long long)n_elements);
+  if (f16_rounding != CSK_F16_TRUNCATE && f16_rounding != CSK_F16_NEAREST)
+    return fail(nullptr, CSK_ERR_INVALID, "dequant_ggml: f16_rounding must be CSK_F16_TRUNCATE or CSK_F16_NEAREST");
+  if (!csk_moe_device_ok(device)) return fail(nullptr, CSK_ERR_CUDA, "dequant_ggml: device %d is not an sm_100 GPU; no CPU fallback exists", device);
+  CSK_CUDA(nullptr, cudaSetDevice(device));
+  const size_t qb = ggml_bytes(ggml_type, n_elements);
+  uint8_t* d_raw = nullptr;
+  unsigned short* d_out = nullptr;
+  cudaError_t e = cudaMalloc(&d_raw, qb);
+  if (e == cudaSuccess) e = cudaMalloc(&d_out, (size_t)n_elements * 2);
+  if (e != cudaSuccess) {
+    cudaFree(d_raw);
+    return fail(nullptr, CSK_ERR_NOMEM, "dequant_ggml: cudaMalloc failed: %s", cudaGetErrorString(e));
+  }
+  e = cudaMemcpy(d_raw, blocks, qb, cudaMemcpyHostToDevice);
+  if (e == cudaSuccess) {
+    ggml_decode_enqueue(ggml_type, d_raw, d_out, n_elements, f16_rounding == CSK_F16_NEAREST, 0);
+    e = cudaGetLastError();
+  }
+  if (e == cudaSuccess) e = cudaMemcpy(out_f16, d_out, (size_t)n_elements * 2, cudaMemcpyDeviceToHost);
+  cudaFree(d_raw);
+  cudaFree(d_out);
+  if (e != cudaSuccess) return fail(nullptr, CSK_ERR_CUDA, "dequant_ggml: %s", cudaGetErrorString(e));
   return CSK_OK;
 }
 

@@ -1,12 +1,13 @@
-// GPU binding of coalsack's expert MLP operator for MXFP4 weights; takes the
-// place of include/coalsack/nn/nn_ops/expert_mlp_node.h.  One node = one expert:
-// from a result_message carrying hidden_states [B,S,H], w_up/w_gate [F,H] and
-// w_down [H,F] as dynamic_mx_tensor messages, optional fp32 biases and the
-// router output [B,S,k,2] it emits the dense [B,S,H] output of this expert
-// (zero rows for tokens that did not select it), or a {0}-shaped tensor when no
-// token selected it.  Weights are repacked and uploaded once per weight buffer
-// (csk_moe_load_expert_mxfp4); the forward is csk_moe_expert_forward.
-// fp16 expert weights are not handled by this binding.
+// GPU binding of coalsack's expert MLP operator; takes the place of
+// include/coalsack/nn/nn_ops/expert_mlp_node.h.  One node = one expert: from a
+// result_message carrying hidden_states [B,S,H], w_up/w_gate [F,H] and w_down
+// [H,F] -- MXFP4 blocks as dynamic_mx_tensor messages, or FLOAT16 matrices as
+// dynamic_tensor messages (what the weight provider makes of Q4_K / Q6_K / F16
+// expert slices) -- optional fp32 biases and the router output [B,S,k,2] it
+// emits the dense [B,S,H] output of this expert (zero rows for tokens that did
+// not select it), or a {0}-shaped tensor when no token selected it.  Weights are
+// repacked and uploaded once per weight buffer (csk_moe_load_expert_mxfp4 /
+// csk_moe_load_expert_f16); the forward is csk_moe_expert_forward.
 // In fused mode (csk_moe_handle.h) the node only passes the hidden states along and
 // answers with the {0}-shaped placeholder; the merge node runs the whole layer.
 #pragma once
@@ -41,6 +42,10 @@ class expert_mlp_node : public graph_node {
   void set_weight_before_ffn(bool v) { weight_before_ffn_ = v; }
   std::vector<std::string> get_input_names() const { return input_names_; }
   std::string get_output_name() const { return output_name_; }
+
+  // The FLOAT16-weight operator on plain tensors (the reference's test wrapper of the same name):
+  // hidden, w_up, w_gate, w_down[, b_up, b_gate, b_down], router_output.
+  dynamic_tensor compute_test(const std::vector<dynamic_tensor>& inputs) { return run_f16(inputs); }
 
   // One token through this expert with raw 17-byte-block weights.
   void compute_test_mxfp4(const float* hidden_vec, const uint8_t* w_up, const uint8_t* w_gate, const uint8_t* w_down,
@@ -77,19 +82,22 @@ class expert_mlp_node : public graph_node {
           output_->send(out);
           return;
         }
-        if (!std::dynamic_pointer_cast<dynamic_mx_tensor_message>(fields[1])) {
-          // plain tensors: what the fetch node sends to an expert no token selected ({0}-shaped); the
-          // reference then answers with the {0}-shaped tensor before it looks at any weight
-          // (expert_mlp_node.h:296-302).  Real fp16/fp32 expert weights are not handled here.
-          if (selected_by(as<dynamic_tensor_message>(fields.back(), "router")->get_tensor()))
-            throw std::runtime_error("expert_mlp: this GPU binding handles MXFP4 expert weights only");
-          out = result_message::ok({{output_name_, std::make_shared<dynamic_tensor_message>(dynamic_tensor(dtype::float32, {0}))}});
-          out->set_frame_number(frame);
-          out->set_timestamp(stamp);
-          output_->send(out);
-          return;
+        dynamic_tensor result;
+        if (std::dynamic_pointer_cast<dynamic_mx_tensor_message>(fields[1])) {
+          result = run_mxfp4(fields);
+        } else {
+          // plain tensors: FLOAT16 weights, or what the fetch node sends to an expert no token selected
+          // ({0}-shaped); the reference answers the latter with the {0}-shaped tensor before it looks at
+          // any weight (expert_mlp_node.h:296-302), and so does run_f16
+          std::vector<dynamic_tensor> inputs;
+          for (const auto& m : fields) {
+            auto t = std::dynamic_pointer_cast<dynamic_tensor_message>(m);
+            if (!t) throw std::runtime_error("expert_mlp: expected dynamic_tensor_message");
+            inputs.push_back(t->get_tensor());
+          }
+          result = run_f16(inputs);
         }
-        auto tensor = std::make_shared<dynamic_tensor_message>(run_mxfp4(fields));
+        auto tensor = std::make_shared<dynamic_tensor_message>(result);
         out = result_message::ok({{output_name_, tensor}});
       } catch (const std::exception& e) {
         spdlog::error("{} [{}]: {}", "expert_mlp", node_name_, e.what());
@@ -109,14 +117,84 @@ class expert_mlp_node : public graph_node {
     return p;
   }
 
-  bool selected_by(const dynamic_tensor& router) const {
+  // FLOAT16 weights: the checks, their order and texts are compute_fp16's (expert_mlp_node.h:269-389).
+  dynamic_tensor run_f16(const std::vector<dynamic_tensor>& in) {
+    if (in.size() != 5 && in.size() != 8)
+      throw std::runtime_error(
+          "expert_mlp: expected 5 or 8 inputs (hidden, w_up, w_gate, w_down[, b_up, b_gate, "
+          "b_down], router_output), got " +
+          std::to_string(in.size()));
+    const bool biased = in.size() == 8;
+    const dynamic_tensor &hidden = in[0], &up = in[1], &gate = in[2], &down = in[3], &router = in[biased ? 7 : 4];
     if (router.ndim() != 4 || router.dim(3) != 2)
-      throw std::runtime_error("expert_mlp: router_output must be 4D [batch, seq_len, top_k, 2]");
+      throw std::runtime_error("expert_mlp: router_output must be 4D [batch, seq_len, top_k, 2], got " +
+                               std::to_string(router.ndim()) + "D");
+    if (router.get_dtype() != dtype::float32) throw std::runtime_error("expert_mlp: router_output must be float32");
     const float* r = router.data_ptr<float>();
-    const int64_t n = router.dim(0) * router.dim(1) * router.dim(2);
-    for (int64_t i = 0; i < n; ++i)
-      if (static_cast<int>(r[2 * i]) == expert_id_) return true;
-    return false;
+    const int64_t pairs = router.dim(0) * router.dim(1) * router.dim(2), k = router.dim(2);
+    bool any = false;
+    int max_id = expert_id_;
+    for (int64_t i = 0; i < pairs; ++i) {
+      const int id = static_cast<int>(r[2 * i]);
+      any = any || id == expert_id_;
+      if (id > max_id) max_id = id;
+    }
+    if (!any) return dynamic_tensor(dtype::float32, {0});
+    if (hidden.ndim() != 3)
+      throw std::runtime_error("expert_mlp: hidden_states must be 3D [batch, seq_len, hidden_dim], got " +
+                               std::to_string(hidden.ndim()) + "D");
+    const int64_t B = hidden.dim(0), S = hidden.dim(1), H = hidden.dim(2);
+    if (up.ndim() != 2 || gate.ndim() != 2 || down.ndim() != 2)
+      throw std::runtime_error(
+          "expert_mlp: all weights must be 2D [expert_ffn_dim, hidden_dim] or [hidden_dim, "
+          "expert_ffn_dim]");
+    const int64_t F = up.dim(0);
+    auto dims = [](const dynamic_tensor& t) { return "[" + std::to_string(t.dim(0)) + ", " + std::to_string(t.dim(1)) + "]"; };
+    const std::string fh = "[" + std::to_string(F) + ", " + std::to_string(H) + "]";
+    if (up.dim(1) != H) throw std::runtime_error("expert_mlp: w_up must be " + fh + ", got " + dims(up));
+    if (gate.dim(0) != F || gate.dim(1) != H)
+      throw std::runtime_error("expert_mlp: w_gate must be " + fh + ", got " + dims(gate));
+    if (down.dim(0) != H || down.dim(1) != F)
+      throw std::runtime_error("expert_mlp: w_down must be [" + std::to_string(H) + ", " + std::to_string(F) +
+                               "], got " + dims(down));
+    if (biased) {
+      const dynamic_tensor &bu = in[4], &bg = in[5], &bd = in[6];
+      if (bu.ndim() != 1 || bu.dim(0) != F)
+        throw std::runtime_error("expert_mlp: b_up must be [expert_ffn_dim=" + std::to_string(F) + "], got [" +
+                                 std::to_string(bu.dim(0)) + "]");
+      if (bg.ndim() != 1 || bg.dim(0) != F)
+        throw std::runtime_error("expert_mlp: b_gate must be [expert_ffn_dim=" + std::to_string(F) + "], got [" +
+                                 std::to_string(bg.dim(0)) + "]");
+      if (bd.ndim() != 1 || bd.dim(0) != H)
+        throw std::runtime_error("expert_mlp: b_down must be [hidden_dim=" + std::to_string(H) + "], got [" +
+                                 std::to_string(bd.dim(0)) + "]");
+    }
+    if (up.get_dtype() != dtype::float16 || gate.get_dtype() != dtype::float16 || down.get_dtype() != dtype::float16)
+      throw std::runtime_error("expert_mlp: all weights must be FLOAT16");
+    if (hidden.get_dtype() != dtype::float32) throw std::runtime_error("expert_mlp: hidden_states must be FLOAT32");
+    // the tensor-core kernel's tiles: a limit of this binding, not of the reference
+    if (H % 32 || F % 32)
+      throw std::runtime_error("expert_mlp: this GPU binding needs hidden_dim and expert_ffn_dim to be multiples of 32, got " +
+                               std::to_string(H) + " and " + std::to_string(F));
+
+    csk_moe_layer* h = layer_for(H, F, biased, k, max_id + 1, B * S, CSK_WEIGHTS_F16);
+    const void *pu = up.data_ptr<uint16_t>(), *pg = gate.data_ptr<uint16_t>(), *pd = down.data_ptr<uint16_t>();
+    if (pu != last_up_ || pg != last_gate_ || pd != last_down_) {
+      csk_host::check(csk_moe_load_expert_f16(h, expert_id_, up.data_ptr<uint16_t>(), gate.data_ptr<uint16_t>(),
+                                              down.data_ptr<uint16_t>(), biased ? in[4].data_ptr<float>() : nullptr,
+                                              biased ? in[5].data_ptr<float>() : nullptr,
+                                              biased ? in[6].data_ptr<float>() : nullptr),
+                      h);
+      last_up_ = pu;
+      last_gate_ = pg;
+      last_down_ = pd;
+    }
+    dynamic_tensor out(dtype::float32, hidden.shape());
+    int32_t selected = 0;
+    csk_host::check(csk_moe_expert_forward(h, expert_id_, hidden.data_ptr<float>(), B * S, r, out.data_ptr<float>(),
+                                           &selected),
+                    h);
+    return out;
   }
 
   // Fused mode: true when this layer's context took over the frame (the fetch node made the selected
@@ -190,7 +268,8 @@ class expert_mlp_node : public graph_node {
   }
 
   // A layer handle on which this node's expert is the only resident one.
-  csk_moe_layer* layer_for(int64_t H, int64_t F, bool biased, int64_t k, int64_t id_space, int64_t tokens) {
+  csk_moe_layer* layer_for(int64_t H, int64_t F, bool biased, int64_t k, int64_t id_space, int64_t tokens,
+                          int32_t weight_format = CSK_WEIGHTS_MXFP4) {
     csk_moe_config c{};
     c.num_experts = static_cast<int32_t>(id_space > k ? id_space : k);
     c.top_k = static_cast<int32_t>(k);
@@ -202,6 +281,7 @@ class expert_mlp_node : public graph_node {
     c.expert_begin = expert_id_;
     c.expert_count = 1;
     c.max_tokens = tokens;
+    c.weight_format = weight_format;
     csk_moe_layer* h = handle_.get(c);
     if (handle_.just_created()) last_up_ = nullptr;
     return h;
@@ -230,7 +310,7 @@ class expert_mlp_node : public graph_node {
   activation_type activation_type_ = activation_type::MODIFIED_SWIGLU;
   bool weight_before_ffn_ = false;
   csk_host::layer_handle handle_;
-  const uint8_t *last_up_ = nullptr, *last_gate_ = nullptr, *last_down_ = nullptr;
+  const void *last_up_ = nullptr, *last_gate_ = nullptr, *last_down_ = nullptr;
 };
 
 }  // namespace coalsack

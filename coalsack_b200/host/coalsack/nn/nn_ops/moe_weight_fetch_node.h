@@ -3,12 +3,13 @@
 // add_expert_output and field names).
 //
 // Strict mode (default): what the reference does -- for every expert a frame selected, the
-// three MXFP4 matrices (and biases) from the moe_weight_provider travel to that expert's
+// three weight matrices (MXFP4 blocks, or the FLOAT16 tensors the provider makes of Q4_K / Q6_K /
+// F16 slices) and biases from the moe_weight_provider travel to that expert's
 // node; unselected experts get {0}-shaped tensors (moe_weight_fetch_node.h:162-218).
 //
 // Fused mode (csk_host::set_fused_moe): the layer's weights live on the GPU.  Only the
 // selected experts that are NOT resident yet are pulled from the provider and uploaded
-// (csk_moe_load_expert_mxfp4, one repack each); every expert node gets {0}-shaped
+// (csk_moe_load_expert_mxfp4 or csk_moe_load_expert_f16, one repack each); every expert node gets {0}-shaped
 // placeholders plus the router output, i.e. a few bytes instead of 13 MB of host tensors.
 #pragma once
 
@@ -103,7 +104,7 @@ class moe_weight_fetch_node : public graph_node {
         spdlog::error("moe_weight_fetch_node [{}]: {}", layer_prefix_, err);
         return fail_all(err);
       }
-      // not MXFP4 weights: this layer goes the strict way below
+      // weights the fused path does not take (fp32, odd sizes): this layer goes the strict way below
     }
 
     auto to_message = [](const auto& v) -> graph_message_ptr {
@@ -145,7 +146,7 @@ class moe_weight_fetch_node : public graph_node {
 
  private:
   // Fused mode: the layer's device handle exists and holds every selected expert.  Returns false with an
-  // empty `err` when the provider's tensors are not MXFP4 (the caller then goes the strict way).
+  // empty `err` when the provider's tensors are neither MXFP4 nor FLOAT16 (the caller then goes the strict way).
   bool make_resident(const dynamic_tensor& router, const std::set<int>& selected, std::string& err) {
     auto ctx = csk_host::layer_registry::get(layer_prefix_);
     std::lock_guard<std::mutex> lk(ctx->mu);
@@ -161,14 +162,28 @@ class moe_weight_fetch_node : public graph_node {
       if (selected.empty()) throw std::runtime_error("router output selects no expert");
       // shapes come from the first selected expert's up projection [F, H]
       auto up0 = weight_provider_->get(layer_prefix_ + ".ffn_up_exps.weight", *selected.begin());
-      if (!std::holds_alternative<dynamic_mx_tensor>(up0)) return false;
-      const dynamic_mx_tensor& u = std::get<dynamic_mx_tensor>(up0);
-      if (u.ndim() != 2) throw std::runtime_error("expert weights must be 2D");
+      // MXFP4 blocks, or the FLOAT16 matrices the provider makes of Q4_K / Q6_K / F16 slices
+      const bool is_mx = std::holds_alternative<dynamic_mx_tensor>(up0);
+      int64_t dim_f = 0, dim_h = 0;
+      if (is_mx) {
+        const dynamic_mx_tensor& u = std::get<dynamic_mx_tensor>(up0);
+        if (u.ndim() != 2) throw std::runtime_error("expert weights must be 2D");
+        dim_f = u.dim(0);
+        dim_h = u.dim(1);
+      } else {
+        const dynamic_tensor& u = std::get<dynamic_tensor>(up0);
+        // anything else (fp32 weights, sizes the tensor-core tiles do not take) goes the strict way,
+        // where the expert node answers with the reference's own message
+        if (u.get_dtype() != dtype::float16 || u.ndim() != 2 || u.dim(0) % 32 || u.dim(1) % 32) return false;
+        dim_f = u.dim(0);
+        dim_h = u.dim(1);
+      }
       csk_moe_config c{};
       c.num_experts = E;
       c.top_k = static_cast<int32_t>(router.dim(2));
-      c.hidden = static_cast<int32_t>(u.dim(1));
-      c.ffn = static_cast<int32_t>(u.dim(0));
+      c.hidden = static_cast<int32_t>(dim_h);
+      c.ffn = static_cast<int32_t>(dim_f);
+      c.weight_format = is_mx ? CSK_WEIGHTS_MXFP4 : CSK_WEIGHTS_F16;
       c.activation = CSK_ACT_MODIFIED_SWIGLU;  // the merge node sets what the expert nodes were configured with
       c.has_bias = has_bias_;
       c.weight_before_ffn = 0;
@@ -183,26 +198,37 @@ class moe_weight_fetch_node : public graph_node {
           if (!std::holds_alternative<dynamic_mx_tensor>(v)) throw std::runtime_error(std::string(name) + " is not MXFP4");
           return std::get<dynamic_mx_tensor>(v);
         };
-        auto f32 = [&](const char* name) -> dynamic_tensor {
+        auto plain = [&](const char* name) -> dynamic_tensor {
           auto v = weight_provider_->get(layer_prefix_ + name, id);
           if (!std::holds_alternative<dynamic_tensor>(v)) throw std::runtime_error(std::string(name) + " is not a plain tensor");
           return std::get<dynamic_tensor>(v);
         };
-        const dynamic_mx_tensor up = mx(".ffn_up_exps.weight"), gate = mx(".ffn_gate_exps.weight"), down = mx(".ffn_down_exps.weight");
-        if (up.dim(0) != c.ffn || up.dim(1) != c.hidden || gate.dim(0) != c.ffn || gate.dim(1) != c.hidden ||
-            down.dim(0) != c.hidden || down.dim(1) != c.ffn)
-          throw std::runtime_error("expert_mlp: weight dimension mismatch");
         dynamic_tensor bu, bg, bd;
         if (has_bias_) {
-          bu = f32(".ffn_up_exps.bias");
-          bg = f32(".ffn_gate_exps.bias");
-          bd = f32(".ffn_down_exps.bias");
+          bu = plain(".ffn_up_exps.bias");
+          bg = plain(".ffn_gate_exps.bias");
+          bd = plain(".ffn_down_exps.bias");
         }
-        csk_host::check(csk_moe_load_expert_mxfp4(h, id, up.data_ptr(), gate.data_ptr(), down.data_ptr(),
-                                                  has_bias_ ? bu.data_ptr<float>() : nullptr,
-                                                  has_bias_ ? bg.data_ptr<float>() : nullptr,
-                                                  has_bias_ ? bd.data_ptr<float>() : nullptr),
-                        h);
+        const float* pbu = has_bias_ ? bu.data_ptr<float>() : nullptr;
+        const float* pbg = has_bias_ ? bg.data_ptr<float>() : nullptr;
+        const float* pbd = has_bias_ ? bd.data_ptr<float>() : nullptr;
+        auto dims_ok = [&](const auto& up, const auto& gate, const auto& down) {
+          return up.ndim() == 2 && gate.ndim() == 2 && down.ndim() == 2 && up.dim(0) == c.ffn && up.dim(1) == c.hidden &&
+                 gate.dim(0) == c.ffn && gate.dim(1) == c.hidden && down.dim(0) == c.hidden && down.dim(1) == c.ffn;
+        };
+        if (is_mx) {
+          const dynamic_mx_tensor up = mx(".ffn_up_exps.weight"), gate = mx(".ffn_gate_exps.weight"), down = mx(".ffn_down_exps.weight");
+          if (!dims_ok(up, gate, down)) throw std::runtime_error("expert_mlp: weight dimension mismatch");
+          csk_host::check(csk_moe_load_expert_mxfp4(h, id, up.data_ptr(), gate.data_ptr(), down.data_ptr(), pbu, pbg, pbd), h);
+        } else {
+          const dynamic_tensor up = plain(".ffn_up_exps.weight"), gate = plain(".ffn_gate_exps.weight"), down = plain(".ffn_down_exps.weight");
+          if (!dims_ok(up, gate, down)) throw std::runtime_error("expert_mlp: weight dimension mismatch");
+          if (up.get_dtype() != dtype::float16 || gate.get_dtype() != dtype::float16 || down.get_dtype() != dtype::float16)
+            throw std::runtime_error("expert_mlp: all weights must be FLOAT16");
+          csk_host::check(csk_moe_load_expert_f16(h, id, up.data_ptr<uint16_t>(), gate.data_ptr<uint16_t>(),
+                                                  down.data_ptr<uint16_t>(), pbu, pbg, pbd),
+                          h);
+        }
         ctx->resident_gen[id] = ctx->generation;
       }
       ctx->usable = true;

@@ -22,6 +22,7 @@ from . import _lib
 from ._lib import Config, Timings
 
 PATH_AUTO, PATH_STREAM, PATH_TILE, PATH_TILE_PAIR = 0, 1, 2, 3
+GGML_F16, GGML_Q4_K, GGML_Q6_K = 1, 12, 14     # ggml_type values (gguf_types.h:24-39)
 
 
 class CskError(RuntimeError):
@@ -34,6 +35,21 @@ class CskError(RuntimeError):
 
 def _np_f32(a):
     return None if a is None else np.ascontiguousarray(a, dtype=np.float32)
+
+
+def dequant_ggml_f16(ggml_type, blocks, n_elements, nearest=False, device=0):
+    """Q4_K / Q6_K super-blocks (uint8) to ``n_elements`` float16 values on the device: what
+    moe_weight_provider.cpp:17-33 does on the host (``nearest``: the reference's F16C build of fp32_to_fp16)."""
+    lib = _lib.load()
+    blocks = np.ascontiguousarray(blocks, dtype=np.uint8).reshape(-1)
+    per = {GGML_Q4_K: 144, GGML_Q6_K: 210}.get(ggml_type)
+    if per is not None and n_elements % 256 == 0 and blocks.size != n_elements // 256 * per:
+        raise RuntimeError(f"ggml type {ggml_type}: expected {n_elements // 256 * per} bytes, got {blocks.size}")
+    out = np.empty(max(int(n_elements), 0), np.uint16)
+    rc = lib.csk_moe_dequant_ggml_f16(device, int(ggml_type), _p(blocks), int(n_elements), _p(out), int(bool(nearest)))
+    if rc != 0:
+        raise CskError(rc, lib.csk_moe_last_error(None).decode())
+    return out.view(np.float16)
 
 
 def _np_u8(a):
@@ -120,6 +136,30 @@ class MoeLayer:
             arrs.append(a.reshape(-1))
         b = [_np_f32(b_up), _np_f32(b_gate), _np_f32(b_down)]
         self._check(self._lib.csk_moe_load_expert_f16(self._h, expert_id, *map(_p, arrs), *map(_p, b)))
+
+    def load_expert_ggml(self, expert_id, w_up, w_gate, w_down, b_up=None, b_gate=None, b_down=None, nearest=False):
+        """Expert slices as the GGUF file holds them: each of w_up, w_gate, w_down is ``(ggml_type, array)`` with
+        ggml_type GGML_F16 (float16 / uint16 values), GGML_Q4_K or GGML_Q6_K (uint8 super-blocks); decoded on
+        the device to the fp16 values the reference's weight provider would make (``nearest``: its F16C build)."""
+        types, arrs = [], []
+        for t, a in (w_up, w_gate, w_down):
+            a = np.asarray(a)
+            if t == GGML_F16:
+                a = a.view(np.uint16) if a.dtype == np.float16 else a.astype(np.uint16, copy=False)
+                want = self.H * self.F
+            elif t in (GGML_Q4_K, GGML_Q6_K):
+                a = a.astype(np.uint8, copy=False)
+                want = self.H * self.F // 256 * (144 if t == GGML_Q4_K else 210)
+            else:
+                raise RuntimeError(f"ggml type {t} is not handled")
+            a = np.ascontiguousarray(a).reshape(-1)
+            if a.size != want:
+                raise RuntimeError(f"ggml type {t}: expected {want} elements, got {a.size}")
+            types.append(int(t))
+            arrs.append(a)
+        b = [_np_f32(b_up), _np_f32(b_gate), _np_f32(b_down)]
+        self._check(self._lib.csk_moe_load_expert_ggml(self._h, expert_id, types[0], _p(arrs[0]), types[1], _p(arrs[1]),
+                                                       types[2], _p(arrs[2]), *map(_p, b), int(bool(nearest))))
 
     def dense_forward(self, hidden):
         """The dense FFN (a layer with one expert and top-1): every row through the weight set."""

@@ -122,6 +122,26 @@ int csk_moe_load_experts_mxfp4(csk_moe_layer* layer, int32_t first_expert, int32
 int csk_moe_load_expert_f16(csk_moe_layer* layer, int32_t expert_id, const uint16_t* w_up, const uint16_t* w_gate,
                             const uint16_t* w_down, const float* b_up, const float* b_gate, const float* b_down);
 
+/* Expert slices in the GGUF block formats the reference's weight provider turns into fp16 on the host at
+ * fetch time (src/llm/moe_weight_provider.cpp:120-159: Q4_K and Q6_K through dequantize_block_q4_K /
+ * dequantize_block_q6_K, include/coalsack/gguf/gguf_dequant.h:147-261, then fp32_to_fp16, :458-489; F16 as
+ * it is).  Here the raw blocks are copied to the device and decoded there, bit for bit the fp16 values the
+ * provider would hand to expert_mlp_node.  For layers created with CSK_WEIGHTS_F16; each matrix has its own
+ * type (ggml_type values, include/coalsack/gguf/gguf_types.h:24-39); a slice is hidden * ffn values, i.e.
+ * hidden*ffn/256 super-blocks of 144 (Q4_K) or 210 (Q6_K) bytes.
+ * f16_rounding: the reference's fp32_to_fp16 has two builds.  CSK_F16_TRUNCATE is the portable one its
+ * CMake flags produce (mantissa truncated, NaN -> infinity, |x| < 2^-25 -> 0); CSK_F16_NEAREST is the F16C
+ * one (round to nearest even; NaN payloads are not reproduced). */
+enum { CSK_GGML_F16 = 1, CSK_GGML_Q4_K = 12, CSK_GGML_Q6_K = 14 };
+enum { CSK_F16_TRUNCATE = 0, CSK_F16_NEAREST = 1 };
+int csk_moe_load_expert_ggml(csk_moe_layer* layer, int32_t expert_id, int32_t type_up, const void* w_up,
+                             int32_t type_gate, const void* w_gate, int32_t type_down, const void* w_down,
+                             const float* b_up, const float* b_gate, const float* b_down, int32_t f16_rounding);
+/* The decoders alone, host to host through the device: n_elements (a multiple of 256) values of Q4_K or
+ * Q6_K blocks to fp16 bit patterns.  Errors go to csk_moe_last_error(NULL). */
+int csk_moe_dequant_ggml_f16(int32_t device, int32_t ggml_type, const void* blocks, int64_t n_elements,
+                         uint16_t* out_f16, int32_t f16_rounding);
+
 /* The dense gated FFN of dense_ffn_node (dense_ffn_node.h:28-219: every token through the one weight
  * set, standard SwiGLU, biases optional) on a layer created with num_experts = top_k = 1,
  * CSK_WEIGHTS_F16 and CSK_ACT_STANDARD_SWIGLU: no router is involved.  hidden and out [T,H] fp32. */

@@ -106,6 +106,15 @@ class _Lib:
         self._dense.restype = C.c_int
         self._dense.argtypes = [_f32p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p,
                                 C.c_void_p, C.c_void_p, C.c_void_p, _f32p]
+        if self.is_ref:
+            self._kq = L.ref_dequant_kquant_f16
+            self._kq.restype = C.c_int
+            self._kq.argtypes = [C.c_int, _u8p, C.c_int64, C.c_void_p]
+        else:
+            self._kq4, self._kq6 = L.orc_dequant_q4k_f16, L.orc_dequant_q6k_f16
+            for fn in (self._kq4, self._kq6):
+                fn.restype = C.c_int
+                fn.argtypes = [_u8p, C.c_int64, C.c_void_p, C.c_int]
         self._layer = getattr(L, prefix + "moe_layer")
         self._layer.restype = C.c_int
         if self.is_ref:
@@ -187,6 +196,25 @@ class _Lib:
         return out
 
     # --- expert ----------------------------------------------------------
+    def dequant_kquant(self, ggml_type: int, blocks: np.ndarray, n: int, nearest: bool = False) -> np.ndarray:
+        """Q4_K (12) or Q6_K (14) super-blocks to the fp16 values the weight provider makes of them
+        (moe_weight_provider.cpp:17-33); n values, a multiple of 256.  ``nearest`` (restatement only): the
+        reference's F16C build of fp32_to_fp16 instead of the portable one its build flags select."""
+        if ggml_type not in (12, 14):
+            raise ValueError("ggml_type must be 12 (Q4_K) or 14 (Q6_K)")
+        blocks = _u8(blocks).reshape(-1)
+        assert n % 256 == 0 and blocks.size == n // 256 * (144 if ggml_type == 12 else 210)
+        out = np.empty(n, np.uint16)
+        if self.is_ref:
+            if nearest:
+                raise ValueError("the compiled reference is the portable build")
+            rc = self._kq(ggml_type, _bp(blocks), n, out.ctypes.data)
+        else:
+            rc = (self._kq4 if ggml_type == 12 else self._kq6)(_bp(blocks), n, out.ctypes.data, int(nearest))
+        if rc:
+            self._err(rc, "dequant_kquant")
+        return out.view(np.float16)
+
     def expert_token(self, x, w_up, w_gate, w_down, b_up, b_gate, b_down, H, F, act):
         x = _f32(x)
         out = np.empty(H, np.float32)

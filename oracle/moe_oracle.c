@@ -365,3 +365,109 @@ int orc_dense_ffn_f16(const float* hidden, int64_t T, int64_t H, int64_t F, cons
   free(act);
   return 0;
 }
+
+/* ---- Q4_K / Q6_K expert slices to fp16 --------------------------------------------------------
+ * src/llm/moe_weight_provider.cpp:17-33: the slice is decoded to fp32 by dequantize_block_q4_K /
+ * dequantize_block_q6_K and each value then passes fp32_to_fp16. */
+
+/* include/coalsack/gguf/gguf_dequant.h:458-489.  nearest = 0: the branch the reference's own build
+ * flags select (no F16C): the mantissa is cut, not rounded; values below 2^-25 become zero, fp16
+ * subnormals are cut as well, everything from 2^16 up (NaN included) becomes infinity.
+ * nearest = 1: the F16C branch, round to nearest even (NaN payloads are not modelled: quiet NaN). */
+static uint16_t float_to_half_ref(float f, int nearest) {
+  uint32_t bits;
+  memcpy(&bits, &f, 4);
+  const uint32_t sign = (bits >> 16) & 0x8000u;
+  const int32_t exponent = (int32_t)((bits >> 23) & 0xFFu) - 127 + 15;
+  uint32_t mantissa = (bits >> 13) & 0x3FFu;
+  if (!nearest) {
+    if (exponent <= 0) {
+      if (exponent < -10) return (uint16_t)sign;
+      mantissa |= 0x400u;
+      mantissa >>= (1 - exponent);
+      return (uint16_t)(sign | mantissa);
+    }
+    if (exponent >= 31) return (uint16_t)(sign | 0x7C00u);
+    return (uint16_t)(sign | ((uint32_t)exponent << 10) | mantissa);
+  }
+  if (((bits >> 23) & 0xFFu) == 0xFFu) return (uint16_t)(sign | ((bits & 0x7FFFFFu) ? 0x7E00u : 0x7C00u));
+  if (exponent >= 31) return (uint16_t)(sign | 0x7C00u);
+  if (exponent <= 0) {
+    if (exponent < -10) return (uint16_t)sign;  /* below half of the smallest subnormal */
+    /* subnormal result: shift the 24-bit significand right by (14 - exponent), round to nearest even */
+    const uint32_t sig = (bits & 0x7FFFFFu) | 0x800000u;
+    const int sh = 14 - exponent;            /* 14 .. 24 */
+    uint32_t q = sig >> sh;
+    const uint32_t rem = sig & ((1u << sh) - 1u), halfway = 1u << (sh - 1);
+    if (rem > halfway || (rem == halfway && (q & 1u))) ++q;
+    return (uint16_t)(sign | q);
+  }
+  {
+    uint32_t h = ((uint32_t)exponent << 10) | mantissa;   /* a carry out of the mantissa raises the exponent */
+    const uint32_t rem = bits & 0x1FFFu;
+    if (rem > 0x1000u || (rem == 0x1000u && (h & 1u))) ++h;
+    return (uint16_t)(sign | h);
+  }
+}
+
+/* include/coalsack/gguf/gguf_dequant.h:147-207 -- 144-byte super-blocks: fp16 d, fp16 dmin, 12 bytes
+ * holding eight 6-bit scales and eight 6-bit minima, 128 bytes of nibbles; 32 bytes give 64 values:
+ * value l of sub-block 2p from the low nibbles, of sub-block 2p+1 from the high ones;
+ * y = (d * scale) * q - (dmin * min), each product and the difference rounded to fp32. */
+int orc_dequant_q4k_f16(const uint8_t* src, int64_t n, uint16_t* dst, int nearest) {
+  if (n % 256) return -3;
+  for (int64_t b = 0; b < n / 256; ++b, src += 144) {
+    uint16_t dh, mh;
+    memcpy(&dh, src, 2);
+    memcpy(&mh, src + 2, 2);
+    const float d = half_to_float(dh), dmin = half_to_float(mh);
+    const uint8_t* sc = src + 4;
+    const uint8_t* q = src + 16;
+    for (int j = 0; j < 8; ++j) {
+      uint8_t s, m;
+      if (j < 4) {
+        s = sc[j] & 0x3F;
+        m = sc[j + 4] & 0x3F;
+      } else {
+        s = (uint8_t)((sc[j + 4] & 0x0F) | ((sc[j - 4] >> 6) << 4));
+        m = (uint8_t)((sc[j + 4] >> 4) | ((sc[j] >> 6) << 4));
+      }
+      const float ds = d * (float)s, ms = dmin * (float)m;
+      for (int l = 0; l < 32; ++l) {
+        const uint8_t byte = q[(j / 2) * 32 + l];
+        const int v = (j & 1) ? (byte >> 4) : (byte & 0x0F);
+        const float prod = ds * (float)v;
+        dst[b * 256 + j * 32 + l] = float_to_half_ref(prod - ms, nearest);
+      }
+    }
+  }
+  return 0;
+}
+
+/* include/coalsack/gguf/gguf_dequant.h:220-261 -- 210-byte super-blocks: 128 bytes of low nibbles,
+ * 64 bytes of high bit pairs, 16 int8 scales (one per 16 values), fp16 d; per half of 128 values, value
+ * l + 32 i (i = 0..3) takes its low nibble from ql[l + 32 (i & 1)] (low half for i < 2, high half
+ * otherwise), its two high bits from qh[l] >> 2 i, its scale from sc[l / 16 + 2 i];
+ * y = (d * scale) * (q - 32), the products taken in that order. */
+int orc_dequant_q6k_f16(const uint8_t* src, int64_t n, uint16_t* dst, int nearest) {
+  if (n % 256) return -3;
+  for (int64_t b = 0; b < n / 256; ++b, src += 210) {
+    uint16_t dh;
+    memcpy(&dh, src + 208, 2);
+    const float d = half_to_float(dh);
+    for (int half = 0; half < 2; ++half) {
+      const uint8_t* ql = src + half * 64;
+      const uint8_t* qh = src + 128 + half * 32;
+      const int8_t* sc = (const int8_t*)(src + 192) + half * 8;
+      for (int l = 0; l < 32; ++l)
+        for (int i = 0; i < 4; ++i) {
+          const uint8_t lo = ql[l + 32 * (i & 1)];
+          const int nib = (i < 2) ? (lo & 0x0F) : (lo >> 4);
+          const int q = (nib | (((qh[l] >> (2 * i)) & 3) << 4)) - 32;
+          const float ds = d * (float)sc[l / 16 + 2 * i];
+          dst[b * 256 + half * 128 + l + 32 * i] = float_to_half_ref(ds * (float)q, nearest);
+        }
+    }
+  }
+  return 0;
+}

@@ -317,4 +317,26 @@ int ref_dense_ffn_f16(const float* hidden, int64_t T, int64_t H, int64_t F, cons
   }
 }
 
+// src/llm/moe_weight_provider.cpp:17-33 keeps these two helpers in an unnamed namespace of a file that
+// needs the GGUF loader; they are two calls into the reference's header, made here in the same order:
+// the block decoder to fp32, then fp32_to_fp16 on every value.
+int ref_dequant_kquant_f16(int ggml_type_id, const uint8_t* src, int64_t n, uint16_t* dst) {
+  try {
+    std::vector<float> temp(n);
+    if (ggml_type_id == static_cast<int>(ggml_type::Q4_K)) {
+      dequantize_block_q4_K(src, temp.data(), n);
+    } else if (ggml_type_id == static_cast<int>(ggml_type::Q6_K)) {
+      dequantize_block_q6_K(src, temp.data(), n);
+    } else {
+      g_last_error = "ref_dequant_kquant_f16: type not handled";
+      return -1;
+    }
+    for (int64_t i = 0; i < n; ++i) dst[i] = fp32_to_fp16(temp[i]);
+    return 0;
+  } catch (const std::exception& e) {
+    g_last_error = e.what();
+    return -1;
+  }
+}
+
 }  // extern "C"

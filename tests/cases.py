@@ -124,3 +124,61 @@ def dense_ffn_case(H=256, F=192, T=9, bias=True, seed=77):
     gate_w[0, :4] = np.array([6e-8, -3e-6, 1.5, -2.0], dtype=np.float16)   # subnormals and large values
     b = [(g.standard_normal(n) * 0.01).astype(np.float32) for n in (F, F, H)] if bias else [None, None, None]
     return hidden, gate_w, up_w, down_w, b[0], b[1], b[2]
+
+
+Q4_K, Q6_K = 12, 14                      # ggml_type values
+KQUANT_BLOCK_BYTES = {Q4_K: 144, Q6_K: 210}
+
+
+def kquant_blocks(ggml_type, nblocks, seed, wild=False, scale=0.01):
+    """Seeded Q4_K (fp16 d, fp16 dmin, 12 scale bytes, 128 nibble bytes) or Q6_K (128 low-nibble bytes, 64
+    high-bit bytes, 16 int8 scales, fp16 d) super-blocks, every code and scale byte uniform; the fp16 headers
+    N(0, scale), or with ``wild`` any 16-bit pattern (subnormals, infinities, NaNs)."""
+    g = np.random.default_rng(seed)
+    per = KQUANT_BLOCK_BYTES[ggml_type]
+    b = g.integers(0, 256, size=(nblocks, per), dtype=np.uint8)
+    nh = 2 if ggml_type == Q4_K else 1
+    if wild:
+        hdr = g.integers(0, 65536, size=(nblocks, nh)).astype(np.uint16)
+    else:
+        hdr = (g.standard_normal((nblocks, nh)) * scale).astype(np.float16).view(np.uint16)
+    off = 0 if ggml_type == Q4_K else 208
+    b[:, off:off + 2 * nh] = hdr.view(np.uint8).reshape(nblocks, 2 * nh)
+    return b
+
+
+def kquant_values_f32(ggml_type, blocks):
+    """The fp32 values of Q4_K / Q6_K super-blocks, written with numpy array arithmetic (float32 products and
+    differences, each rounded once): an independent statement of the layout, gguf_dequant.h:147-261."""
+    b = np.asarray(blocks, np.uint8).reshape(-1, KQUANT_BLOCK_BYTES[ggml_type])
+    nb = b.shape[0]
+    out = np.empty((nb, 256), np.float32)
+    with np.errstate(all="ignore"):
+        if ggml_type == Q4_K:
+            d = b[:, 0:2].copy().view(np.float16).astype(np.float32)           # [nb,1]
+            dmin = b[:, 2:4].copy().view(np.float16).astype(np.float32)
+            sc = b[:, 4:16].astype(np.int32)
+            q = b[:, 16:144].reshape(nb, 4, 32)
+            for j in range(8):
+                if j < 4:
+                    s, m = sc[:, j] & 0x3F, sc[:, j + 4] & 0x3F
+                else:
+                    s = (sc[:, j + 4] & 0x0F) | ((sc[:, j - 4] >> 6) << 4)
+                    m = (sc[:, j + 4] >> 4) | ((sc[:, j] >> 6) << 4)
+                ds = d * s[:, None].astype(np.float32)
+                ms = dmin * m[:, None].astype(np.float32)
+                v = (q[:, j // 2] >> 4) if (j & 1) else (q[:, j // 2] & 0x0F)
+                out[:, j * 32:(j + 1) * 32] = ds * v.astype(np.float32) - ms
+        else:
+            d = b[:, 208:210].copy().view(np.float16).astype(np.float32)
+            sc = b[:, 192:208].copy().view(np.int8).astype(np.float32)
+            for half in range(2):
+                ql = b[:, half * 64:half * 64 + 64].astype(np.int32)
+                qh = b[:, 128 + half * 32:128 + half * 32 + 32].astype(np.int32)
+                for i in range(4):
+                    lo = ql[:, 32 * (i & 1):32 * (i & 1) + 32]
+                    nib = (lo & 0x0F) if i < 2 else (lo >> 4)
+                    qv = (nib | (((qh >> (2 * i)) & 3) << 4)) - 32
+                    scale = np.repeat(sc[:, half * 8 + 2 * i:half * 8 + 2 * i + 2], 16, axis=1)   # l/16 + 2i
+                    out[:, half * 128 + 32 * i:half * 128 + 32 * i + 32] = (d * scale) * qv.astype(np.float32)
+    return out.reshape(-1)

@@ -13,6 +13,7 @@ OUT = os.path.join(HERE, "_build", "shim_check")
 
 GRAPH_OUT = os.path.join(HERE, "_build", "graph_check")
 DENSE_OUT = os.path.join(HERE, "_build", "dense_check")
+EXPERT_F16_OUT = os.path.join(HERE, "_build", "expert_f16_check")
 
 
 def _compile(src, out, ref, extra_inc=(), verbose=False):
@@ -44,6 +45,7 @@ def build(ref: str | None = None, verbose: bool = False) -> str | None:
     _compile(os.path.join(HERE, "shim_check.cpp"), OUT, ref, verbose=verbose)
     _compile(os.path.join(HERE, "graph_check.cpp"), GRAPH_OUT, ref, extra_inc=[os.path.join(HERE, "stub")], verbose=verbose)
     _compile(os.path.join(HERE, "dense_check.cpp"), DENSE_OUT, ref, verbose=verbose)
+    _compile(os.path.join(HERE, "expert_f16_check.cpp"), EXPERT_F16_OUT, ref, verbose=verbose)
     return OUT
 
 

@@ -47,6 +47,7 @@ int main(int argc, char** argv) {
   if (argc < 4) return 2;
   const bool fused = std::string(argv[3]) == "fused";
   const int frames = argc > 4 ? std::atoi(argv[4]) : 2;
+  const bool f16 = argc > 5 && std::string(argv[5]) == "f16";  // expert weights in the file are FLOAT16 matrices
   csk_host::set_fused_moe(fused);
   // file: int32 E,k,H,F,T,act,has_bias ; hidden[T,H] ; Wg[E,H] ; rb[E] ; per expert: up,gate,down bytes, b_up,b_gate,b_down
   std::vector<char> buf = slurp(argv[1]);
@@ -62,7 +63,12 @@ int main(int argc, char** argv) {
   auto provider = std::make_shared<moe_weight_provider>();
   for (int e = 0; e < E; ++e) {
     for (const char* w : {"up", "gate", "down"}) {
-      dynamic_mx_tensor t(std::string(w) == "down" ? std::vector<int64_t>{H, F} : std::vector<int64_t>{F, H});
+      const std::vector<int64_t> shape = std::string(w) == "down" ? std::vector<int64_t>{H, F} : std::vector<int64_t>{F, H};
+      if (f16) {
+        provider->put(L + ".ffn_" + w + "_exps.weight", e, dynamic_tensor(dtype::float16, shape, take(2u * H * F)));
+        continue;
+      }
+      dynamic_mx_tensor t(shape);
       std::memcpy(t.data_ptr(), take(wbytes), wbytes);
       provider->put(L + ".ffn_" + w + "_exps.weight", e, t);
     }

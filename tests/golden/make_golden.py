@@ -86,6 +86,14 @@ def main():
         g[tag + "_out"] = r.dense_ffn(hidden, gw, uw, dw, bg, bu, bd)
         g[tag + "_crc"] = cases.crc(hidden, gw.view(np.uint16), uw.view(np.uint16), dw.view(np.uint16))
 
+    # Q4_K / Q6_K expert slices to fp16 as the weight provider makes them (src/llm/moe_weight_provider.cpp:17-33):
+    # ordinary headers, and headers of any bit pattern (subnormal, infinite, NaN)
+    for name, t in (("q4k", cases.Q4_K), ("q6k", cases.Q6_K)):
+        for kind, wild in (("", False), ("_wild", True)):
+            blocks = cases.kquant_blocks(t, 48, 61 + t, wild)
+            g[f"{name}{kind}_f16"] = r.dequant_kquant(t, blocks, 48 * 256).view(np.uint16)
+            g[f"{name}{kind}_crc"] = cases.crc(blocks)
+
     np.savez_compressed(OUT, **g)
     print(f"wrote {OUT}: {os.path.getsize(OUT) / 1024:.1f} KiB, {len(g)} arrays")
 

@@ -37,6 +37,10 @@ def test_bindings_compile_against_reference_headers():
     syms = subprocess.run(["nm", "-D", build_check.DENSE_OUT], capture_output=True, text=True).stdout
     for s in ("csk_moe_load_expert_f16", "csk_moe_dense_forward"):
         assert s in syms, f"{s}: dense_check does not reach the GPU binding"
+    assert os.path.exists(build_check.EXPERT_F16_OUT)
+    syms = subprocess.run(["nm", "-D", build_check.EXPERT_F16_OUT], capture_output=True, text=True).stdout
+    for s in ("csk_moe_load_expert_f16", "csk_moe_expert_forward", "csk_moe_merge"):
+        assert s in syms, f"{s}: expert_f16_check does not reach the GPU binding"
 
 
 @pytest.mark.gpu
@@ -176,3 +180,86 @@ def test_dense_ffn_node_binding(gpu_lib, port, bias, tmp_path):
         want = port.dense_ffn(hidden, gate, uw, dw, bg, bu, bd)
         mx, mr = cases.err_stats(got, want)
         assert mx <= cases.MAX_ABS_OVER_RMS and mr <= cases.MEAN_REL, (mx, mr)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("bias", [True, False])
+def test_expert_node_binding_with_fp16_weights(gpu_lib, port, bias, tmp_path):
+    """coalsack's expert node fed FLOAT16 weight tensors (expert_mlp_node.h:269-389: what the provider makes
+    of Q4_K / Q6_K / F16 expert slices) with the GPU binding behind it: E expert nodes through process(), the
+    merge node, against the restatement; an expert nobody selected answers with the {0}-shaped tensor."""
+    exe = build_check.EXPERT_F16_OUT
+    if not os.path.exists(exe):
+        pytest.skip("tests/cpp/_build/expert_f16_check was not built (needs the reference checkout at build time)")
+    E, k, H, F, T = 7, 2, 256, 192, 45
+    rng = np.random.default_rng(97)
+    hidden = rng.standard_normal((T, H)).astype(np.float32)
+    ro = np.zeros((T, k, 2), np.float32)
+    for t in range(T):
+        ro[t, :, 0] = rng.choice(E - 1, size=k, replace=False)   # expert E-1 is never selected
+        w = np.exp(rng.standard_normal(k)).astype(np.float32)
+        ro[t, :, 1] = w / w.sum()
+    experts = [cases.dense_ffn_case(H=H, F=F, T=1, bias=True, seed=300 + e)[1:] for e in range(E)]
+    inp, outp = tmp_path / "in.bin", tmp_path / "out.bin"
+    with open(inp, "wb") as f:
+        f.write(np.array([E, k, H, F, T, 1, int(bias)], np.int32).tobytes())
+        f.write(hidden.tobytes())
+        f.write(ro.tobytes())
+        for gw, uw, dw, bg, bu, bd in experts:
+            for a in (uw, gw, dw) + ((bu, bg, bd) if bias else ()):
+                f.write(np.ascontiguousarray(a).tobytes())
+    r = subprocess.run([exe, str(inp), str(outp)], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "placeholders=1" in r.stdout, r.stdout
+    got = np.fromfile(outp, np.float32).reshape(T, H)
+    dense = [port.dense_ffn(hidden, gw, uw, dw, *((bg, bu, bd) if bias else (None, None, None)))
+             for gw, uw, dw, bg, bu, bd in experts]
+    want = np.zeros((T, H), np.float32)
+    for t in range(T):
+        for j in range(k):
+            want[t] = want[t] + np.float32(ro[t, j, 1]) * dense[int(ro[t, j, 0])][t]
+    mx, mr = cases.err_stats(got, want)
+    assert mx <= cases.MAX_ABS_OVER_RMS and mr <= cases.MEAN_REL, (mx, mr)
+
+
+@pytest.mark.gpu
+def test_graph_builder_subgraph_with_fp16_experts(gpu_lib, port, tmp_path):
+    """The MoE sub-graph wired by coalsack's graph_builder with a provider that serves FLOAT16 expert tensors (what
+    it makes of Q4_K / Q6_K / F16 models): strict and fused mode against the restatement; fused mode keeps the
+    experts resident (no provider traffic in the second frame beyond the shape probe)."""
+    if not os.path.exists(build_check.GRAPH_OUT):
+        pytest.skip("tests/cpp/_build/graph_check was not built (needs the reference checkout at build time)")
+    E, k, H, F, T = 6, 2, 256, 192, 33
+    rng = np.random.default_rng(141)
+    hidden = rng.standard_normal((T, H)).astype(np.float32)
+    Wg = (rng.standard_normal((E, H)) * 0.3).astype(np.float32)
+    rb = (rng.standard_normal(E) * 0.1).astype(np.float32)
+    experts = [cases.dense_ffn_case(H=H, F=F, T=1, bias=True, seed=700 + e)[1:] for e in range(E)]
+    inp = tmp_path / "in.bin"
+    with open(inp, "wb") as f:
+        f.write(np.array([E, k, H, F, T, 1, 1], np.int32).tobytes())
+        f.write(hidden.tobytes())
+        f.write(Wg.tobytes())
+        f.write(rb.tobytes())
+        for gw, uw, dw, bg, bu, bd in experts:
+            for a in (uw, gw, dw, bu, bg, bd):
+                f.write(np.ascontiguousarray(a).tobytes())
+    want_ro = port.router(hidden, Wg, rb, k)
+    dense = [port.dense_ffn(hidden, *experts[e]) for e in range(E)]
+    want = np.zeros((T, H), np.float32)
+    for t in range(T):
+        for j in range(k):
+            want[t] = want[t] + np.float32(want_ro[t, j, 1]) * dense[int(want_ro[t, j, 0])][t]
+    for mode in ("strict", "fused"):
+        outp = tmp_path / f"out_{mode}.bin"
+        r = subprocess.run([build_check.GRAPH_OUT, str(inp), str(outp), mode, "2", "f16"], capture_output=True, text=True,
+                           timeout=180)
+        assert r.returncode == 0, r.stdout + r.stderr
+        raw = np.fromfile(outp, np.float32)
+        ro, out = raw[:T * k * 2].reshape(T, k, 2), raw[T * k * 2:].reshape(T, H)
+        assert np.array_equal(ro[..., 0], want_ro[..., 0]), mode
+        mx, mr = cases.err_stats(out, want)
+        assert mx <= cases.MAX_ABS_OVER_RMS and mr <= cases.MEAN_REL, (mode, mx, mr)
+        if mode == "fused":
+            info = dict(kv.split("=") for kv in r.stdout.split("graph_check ok:")[1].split())
+            assert int(info["provider_gets_last_frame"]) <= 1, info

@@ -138,3 +138,69 @@ def test_dense_ffn_golden_and_reference(port, golden, tag, bias):
     if oracle.have_ref():
         args = cases.dense_ffn_case(H=2880, F=96, T=3, bias=bias, seed=78)
         assert np.array_equal(port.dense_ffn(*args), oracle.ref().dense_ffn(*args))
+
+
+@pytest.mark.parametrize("name,t", [("q4k", cases.Q4_K), ("q6k", cases.Q6_K)])
+def test_kquant_to_fp16_golden_and_reference(port, golden, name, t):
+    """Q4_K / Q6_K expert slices to fp16 (moe_weight_provider.cpp:17-33): the restatement equals the fixture the
+    reference produced bit for bit, ordinary and arbitrary headers; the compiled reference on fresh blocks;
+    and, in the F16C rounding, an independent numpy statement of the layout rounded by numpy."""
+    for kind, wild in (("", False), ("_wild", True)):
+        blocks = cases.kquant_blocks(t, 48, 61 + t, wild)
+        assert cases.crc(blocks) == golden[f"{name}{kind}_crc"]
+        got = port.dequant_kquant(t, blocks, 48 * 256)
+        assert np.array_equal(got.view(np.uint16), golden[f"{name}{kind}_f16"])
+    import oracle
+    if oracle.have_ref():
+        for wild in (False, True):
+            blocks = cases.kquant_blocks(t, 2048, 7, wild)
+            assert np.array_equal(port.dequant_kquant(t, blocks, 2048 * 256).view(np.uint16),
+                                  oracle.ref().dequant_kquant(t, blocks, 2048 * 256).view(np.uint16))
+    blocks = cases.kquant_blocks(t, 1024, 9, True)
+    with np.errstate(all="ignore"):
+        want = cases.kquant_values_f32(t, blocks).astype(np.float16)
+    got = port.dequant_kquant(t, blocks, 1024 * 256, nearest=True)
+    nan = np.isnan(want)
+    assert np.array_equal(np.isnan(got), nan)
+    assert np.array_equal(got.view(np.uint16)[~nan], want.view(np.uint16)[~nan])
+
+
+def test_kquant_known_answers(port):
+    """The known answers of the reference's own decoder tests (test/test_gguf_dequant.cpp:683-760: with d = 1,
+    dmin = 0 and sub-block scales 1, 2, 4, 8 value 2 is 1 * (low nibble of byte 2) = 2 and value 32 is
+    2 * (high nibble of byte 0) = 2; :396-445, 521-552: every value finite), and the truncating conversion:
+    0.1 * 63 * 15 - 0.05 * 21 with fp16 headers."""
+    b = np.zeros(144, np.uint8)
+    b[0:2] = np.array([1.0], np.float16).view(np.uint8)
+    b[4:8] = [1, 2, 4, 8]
+    i = np.arange(128)
+    b[16:] = (((i + 1) % 16) << 4) | (i % 16)
+    v = port.dequant_kquant(cases.Q4_K, b, 256).astype(np.float32)
+    assert v[2] == 2.0 and v[32] == 2.0 and v[0] == 0.0 and v[1] == 1.0
+    assert np.array_equal(v[:32], (i[:32] % 16).astype(np.float32))
+    assert np.array_equal(v[32:64], 2.0 * ((i[:32] + 1) % 16))
+    b = np.zeros(144, np.uint8)
+    b[0:2] = np.array([0.1], np.float16).view(np.uint8)
+    b[2:4] = np.array([0.05], np.float16).view(np.uint8)
+    b[4:16] = [0x3F, 0x80, 0xC5, 0x2A, 0x15, 0xF0, 0x88, 0x1F, 0xAA, 0x55, 0xCC, 0x33]
+    val = ((i // 32) * 3 + (i % 32)) % 16
+    b[16:] = val | ((15 - val) << 4)
+    v = port.dequant_kquant(cases.Q4_K, b, 256)
+    assert np.all(np.isfinite(v))
+    d, dmin = np.float32(np.float16(0.1)), np.float32(np.float16(0.05))
+    want = np.float32(np.float32(d * np.float32(63)) * np.float32(15)) - np.float32(dmin * np.float32(21))
+    bits = np.array([want], np.float32).view(np.uint32)[0]
+    trunc = np.uint16(((bits >> 16) & 0x8000) | ((((bits >> 23) & 0xFF) - 112) << 10) | ((bits >> 13) & 0x3FF))
+    assert v.view(np.uint16)[15] == trunc        # value 15: low nibble 15 of byte 15, sub-block 0 (scale 63, min 21)
+    b = np.zeros(210, np.uint8)
+    b[0:128] = (np.arange(128) * 13) % 256
+    b[128:192] = (np.arange(64) * 31) % 256
+    b[192:208] = (((np.arange(16) * 11) % 128) - 64).astype(np.int8).view(np.uint8)
+    b[208:210] = np.array([0.07], np.float16).view(np.uint8)
+    v = port.dequant_kquant(cases.Q6_K, b, 256)
+    assert np.all(np.isfinite(v))
+    with np.errstate(all="ignore"):
+        near = cases.kquant_values_f32(cases.Q6_K, b).astype(np.float16).astype(np.float32)
+    assert np.all(np.abs(v.astype(np.float32) - near) <= np.abs(near) * 2.0 ** -10 + 1e-7)
+    with pytest.raises(AssertionError):
+        port.dequant_kquant(cases.Q4_K, np.zeros(144, np.uint8), 255)
