@@ -36,6 +36,7 @@ SYMBOLS = {
     "csk_moe_set_router": (C.c_int, [_vp, _vp, _vp]),
     "csk_moe_load_expert_mxfp4": (C.c_int, [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp]),
     "csk_moe_load_expert_f16": (C.c_int, [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "csk_moe_load_expert_f32": (C.c_int, [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp]),
     "csk_moe_load_expert_ggml": (C.c_int, [_vp, _i32, _i32, _vp, _i32, _vp, _i32, _vp, _vp, _vp, _vp, _i32]),
     "csk_moe_dequant_ggml_f16": (C.c_int, [_i32, _i32, _vp, _i64, _vp, _i32]),
     "csk_moe_dense_forward": (C.c_int, [_vp, _vp, _i64, _vp]),

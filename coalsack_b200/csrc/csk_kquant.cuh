@@ -131,4 +131,19 @@ __global__ void __launch_bounds__(256) k_dequant_q6k(const uint8_t* __restrict__
   }
 }
 
+// fp32 weight matrices (the reference's dense FFN also takes FLOAT32 weights, dense_ffn_node.h:58-62, 121-149) to the
+// fp16 operands of the tensor-core kernel, round to nearest even.  A finite weight beyond the fp16 range would
+// become an infinity: counted in *overflow, and the load is refused.
+__global__ void __launch_bounds__(256) k_f32_to_f16(const float* __restrict__ src, unsigned short* __restrict__ dst,
+                                                    int64_t n, int* __restrict__ overflow) {
+  int bad = 0;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const float f = src[i];
+    const unsigned short h = __half_as_ushort(__float2half_rn(f));
+    if ((h & 0x7FFFu) == 0x7C00u && fabsf(f) <= 3.0e38f) bad = 1;   // finite in, infinite out
+    dst[i] = h;
+  }
+  if (bad) atomicAdd(overflow, 1);
+}
+
 }  // namespace csk

@@ -940,6 +940,50 @@ int csk_moe_load_expert_ggml(csk_moe_layer* L, int32_t expert_id, int32_t type_u
   return CSK_OK;
 }
 
+int csk_moe_load_expert_f32(csk_moe_layer* L, int32_t expert_id, const float* w_up, const float* w_gate,
+                            const float* w_down, const float* b_up, const float* b_gate, const float* b_down) {
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  if (!L->w16)
+    return fail(L, CSK_ERR_INVALID, "this layer holds MXFP4 weights: fp32 matrices need a layer created with CSK_WEIGHTS_F16");
+  if (expert_id < L->e0 || expert_id >= L->e0 + L->Eloc)
+    return fail(L, CSK_ERR_INVALID, "expert %d is not resident on this device (range [%d,%d))",
+                expert_id, L->e0, L->e0 + L->Eloc);
+  if (!w_up || !w_gate || !w_down) return fail(L, CSK_ERR_INVALID, "null weight pointer");
+  if (L->cfg.has_bias && (!b_up || !b_gate || !b_down))
+    return fail(L, CSK_ERR_INVALID, "layer has biases but a bias pointer is null");
+  CSK_CUDA(L, cudaSetDevice(L->cfg.device));
+  const int64_t n = (int64_t)L->H * L->F;
+  // one fp32 matrix at a time through a temporary of its size (load time only), plus the overflow counter
+  uint8_t* tmp = nullptr;
+  cudaError_t e = cudaMalloc(&tmp, (size_t)n * 4 + 16);
+  if (e != cudaSuccess) return fail(L, CSK_ERR_NOMEM, "cudaMalloc failed: %s", cudaGetErrorString(e));
+  int* d_over = reinterpret_cast<int*>(tmp + (size_t)n * 4);
+  cudaStream_t s = L->stream;
+  const float* src[3] = {w_up, w_gate, w_down};
+  int over = 0;
+  e = cudaMemsetAsync(d_over, 0, 4, s);
+  for (int i = 0; i < 3 && e == cudaSuccess; ++i) {
+    e = cudaMemcpyAsync(tmp, src[i], (size_t)n * 4, cudaMemcpyHostToDevice, s);
+    if (e != cudaSuccess) break;
+    k_f32_to_f16<<<grid_for((size_t)n, 256, 4096), 256, 0, s>>>(
+        reinterpret_cast<const float*>(tmp), reinterpret_cast<unsigned short*>(L->d_stage + (size_t)i * L->stage_bytes), n, d_over);
+    e = cudaGetLastError();
+  }
+  if (e == cudaSuccess) e = cudaMemcpyAsync(&over, d_over, 4, cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  cudaFree(tmp);
+  if (e != cudaSuccess) return fail(L, CSK_ERR_CUDA, "load_expert_f32: %s", cudaGetErrorString(e));
+  if (over)
+    return fail(L, CSK_ERR_INVALID, "load_expert_f32: a weight lies beyond the fp16 range (|w| > 65504); the tensor-core "
+                                    "kernel's operands are fp16");
+  const int le = expert_id - L->e0;
+  int rc = load_expert_enqueue(L, le, nullptr, nullptr, nullptr, b_up, b_gate, b_down, L->d_stage, s);
+  if (rc) return rc;
+  CSK_CUDA(L, cudaStreamSynchronize(s));
+  L->resident[le] = 1;
+  return CSK_OK;
+}
+
 int csk_moe_dequant_ggml_f16(int32_t device, int32_t ggml_type, const void* blocks, int64_t n_elements, uint16_t* out_f16,
                          int32_t f16_rounding) {
   if (!blocks || !out_f16) return fail(nullptr, CSK_ERR_INVALID, "dequant_ggml: null argument");

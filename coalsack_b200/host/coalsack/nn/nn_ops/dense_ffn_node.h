@@ -1,9 +1,10 @@
 // GPU binding of coalsack's dense FFN operator (the shared expert of MoE transformer blocks); takes the
 // place of include/coalsack/nn/nn_ops/dense_ffn_node.h.  Inputs: hidden [B,S,D] fp32, gate_w [F,D],
-// up_w [F,D], down_w [D,F] FLOAT16 [, gate_b [F], up_b [F], down_b [D] fp32]; output [B,S,D] fp32 =
-// down(silu(gate(x)) * up(x)), every token through the one weight set.  On the device this is a layer
-// with one expert and top-1 in the fp16 weight format (csk_moe_load_expert_f16, csk_moe_dense_forward).
-// FLOAT32 weights (the reference's scalar path) are not taken: the tensor-core kernel's operands are fp16.
+// up_w [F,D], down_w [D,F] all FLOAT16 or all FLOAT32 [, gate_b [F], up_b [F], down_b [D] fp32]; output
+// [B,S,D] fp32 = down(silu(gate(x)) * up(x)), every token through the one weight set.  On the device this is
+// a layer with one expert and top-1 in the fp16 weight format (csk_moe_load_expert_f16, csk_moe_dense_forward).
+// FLOAT32 weights (the reference's scalar path) are rounded to fp16 on the device, the tensor-core kernel's
+// operand type (csk_moe_load_expert_f32; refused when a weight exceeds the fp16 range).
 #pragma once
 
 #include <cstdint>
@@ -46,8 +47,6 @@ class dense_ffn_node : public variadic_op_node {
     if ((weight_dtype != dtype::float16 && weight_dtype != dtype::float32) || up_w.get_dtype() != weight_dtype ||
         down_w.get_dtype() != weight_dtype)
       throw std::runtime_error("dense_ffn: weight tensors must all be FLOAT16 or all FLOAT32");
-    if (weight_dtype != dtype::float16)
-      throw std::runtime_error("dense_ffn: the GPU operator takes FLOAT16 weights only");
     if (hidden.get_dtype() != dtype::float32) throw std::runtime_error("dense_ffn: hidden_states must be FLOAT32");
     const int64_t batch = hidden.dim(0), seq_len = hidden.dim(1), hidden_dim = hidden.dim(2);
     const int64_t ffn_dim = gate_w.dim(0);
@@ -70,18 +69,26 @@ class dense_ffn_node : public variadic_op_node {
     c.weight_format = CSK_WEIGHTS_F16;
     c.max_tokens = batch * seq_len;
     csk_moe_layer* h = handle_.get(c);
-    const size_t wbytes = sizeof(uint16_t) * (size_t)hidden_dim * ffn_dim;
-    const uint64_t key = csk_host::content_hash(gate_w.data_ptr<uint16_t>(), wbytes) ^
-                         (csk_host::content_hash(up_w.data_ptr<uint16_t>(), wbytes) * 3) ^
-                         (csk_host::content_hash(down_w.data_ptr<uint16_t>(), wbytes) * 5) ^
-                         (uint64_t)reinterpret_cast<uintptr_t>(gate_w.data_ptr<uint16_t>());
+    const bool f16 = weight_dtype == dtype::float16;
+    const size_t wbytes = (f16 ? sizeof(uint16_t) : sizeof(float)) * (size_t)hidden_dim * ffn_dim;
+    const void* pg = f16 ? static_cast<const void*>(gate_w.data_ptr<uint16_t>()) : gate_w.data_ptr<float>();
+    const void* pu = f16 ? static_cast<const void*>(up_w.data_ptr<uint16_t>()) : up_w.data_ptr<float>();
+    const void* pd = f16 ? static_cast<const void*>(down_w.data_ptr<uint16_t>()) : down_w.data_ptr<float>();
+    const uint64_t key = csk_host::content_hash(pg, wbytes) ^ (csk_host::content_hash(pu, wbytes) * 3) ^
+                         (csk_host::content_hash(pd, wbytes) * 5) ^ (uint64_t)reinterpret_cast<uintptr_t>(pg) ^
+                         (f16 ? 0 : 0x9E3779B97F4A7C15ull);
     if (handle_.just_created() || key != key_ || key_ == 0) {
-      csk_host::check(csk_moe_load_expert_f16(h, 0, up_w.data_ptr<uint16_t>(), gate_w.data_ptr<uint16_t>(),
-                                              down_w.data_ptr<uint16_t>(),
-                                              has_bias ? inputs[5].data_ptr<float>() : nullptr,
-                                              has_bias ? inputs[4].data_ptr<float>() : nullptr,
-                                              has_bias ? inputs[6].data_ptr<float>() : nullptr),
-                      h);
+      const float* bu = has_bias ? inputs[5].data_ptr<float>() : nullptr;
+      const float* bg = has_bias ? inputs[4].data_ptr<float>() : nullptr;
+      const float* bd = has_bias ? inputs[6].data_ptr<float>() : nullptr;
+      if (f16)
+        csk_host::check(csk_moe_load_expert_f16(h, 0, static_cast<const uint16_t*>(pu), static_cast<const uint16_t*>(pg),
+                                                static_cast<const uint16_t*>(pd), bu, bg, bd),
+                        h);
+      else
+        csk_host::check(csk_moe_load_expert_f32(h, 0, static_cast<const float*>(pu), static_cast<const float*>(pg),
+                                                static_cast<const float*>(pd), bu, bg, bd),
+                        h);
       key_ = key ? key : 1;
     }
     dynamic_tensor output(dtype::float32, {batch, seq_len, hidden_dim});

@@ -137,6 +137,17 @@ class MoeLayer:
         b = [_np_f32(b_up), _np_f32(b_gate), _np_f32(b_down)]
         self._check(self._lib.csk_moe_load_expert_f16(self._h, expert_id, *map(_p, arrs), *map(_p, b)))
 
+    def load_expert_f32(self, expert_id, w_up, w_gate, w_down, b_up=None, b_gate=None, b_down=None):
+        """fp32 weight matrices, rounded to fp16 on the device (refused when a weight exceeds the fp16 range)."""
+        arrs = []
+        for a, shape in ((w_up, (self.F, self.H)), (w_gate, (self.F, self.H)), (w_down, (self.H, self.F))):
+            a = _np_f32(a)
+            if a.size != shape[0] * shape[1]:
+                raise RuntimeError("dense_ffn: weight dimension mismatch")
+            arrs.append(a.reshape(-1))
+        b = [_np_f32(b_up), _np_f32(b_gate), _np_f32(b_down)]
+        self._check(self._lib.csk_moe_load_expert_f32(self._h, expert_id, *map(_p, arrs), *map(_p, b)))
+
     def load_expert_ggml(self, expert_id, w_up, w_gate, w_down, b_up=None, b_gate=None, b_down=None, nearest=False):
         """Expert slices as the GGUF file holds them: each of w_up, w_gate, w_down is ``(ggml_type, array)`` with
         ggml_type GGML_F16 (float16 / uint16 values), GGML_Q4_K or GGML_Q6_K (uint8 super-blocks); decoded on
@@ -513,8 +524,9 @@ class expert_mlp_node:
 
 class dense_ffn_node:
     """dense_ffn_node (dense_ffn_node.h:28-219): the shared expert's dense gated FFN with standard
-    SwiGLU; fp16 weights, fp32 hidden states and biases.  ``compute(inputs)`` takes the reference's
-    4 or 7 inputs: hidden [B,S,H], gate_w [F,H], up_w [F,H], down_w [H,F] (float16)
+    SwiGLU; fp16 or fp32 weights (the latter rounded to fp16 on the device: the tensor-core kernel's
+    operands), fp32 hidden states and biases.  ``compute(inputs)`` takes the reference's 4 or 7 inputs:
+    hidden [B,S,H], gate_w [F,H], up_w [F,H], down_w [H,F] (all float16 or all float32)
     [, gate_b [F], up_b [F], down_b [H]]."""
 
     def __init__(self, device=0):
@@ -532,8 +544,9 @@ class dense_ffn_node:
             raise RuntimeError(f"dense_ffn: hidden_states must be 3D [B, S, D], got {hidden.ndim}D")
         if any(np.asarray(w).ndim != 2 for w in (gate_w, up_w, down_w)):
             raise RuntimeError("dense_ffn: weight tensors must be 2D")
-        if any(np.asarray(w).dtype != np.float16 for w in (gate_w, up_w, down_w)):
-            raise RuntimeError("dense_ffn: this build takes FLOAT16 weights (FLOAT32 weights are not supported)")
+        wdt = np.asarray(gate_w).dtype
+        if wdt not in (np.float16, np.float32) or any(np.asarray(w).dtype != wdt for w in (up_w, down_w)):
+            raise RuntimeError("dense_ffn: weight tensors must all be FLOAT16 or all FLOAT32")
         if hidden.dtype != np.float32:
             raise RuntimeError("dense_ffn: hidden_states must be FLOAT32")
         B, S, H = hidden.shape
@@ -553,8 +566,9 @@ class dense_ffn_node:
                                    max_tokens=max(T, 64), weights_f16=True)
             b = inputs[4:7] if has_bias else (None, None, None)
             # the reference's input order is gate, up, down; biases gate, up, down
-            self._layer.load_expert_f16(0, up_w, gate_w, down_w, b[1] if has_bias else None,
-                                        b[0] if has_bias else None, b[2] if has_bias else None)
+            load = self._layer.load_expert_f16 if wdt == np.float16 else self._layer.load_expert_f32
+            load(0, up_w, gate_w, down_w, b[1] if has_bias else None, b[0] if has_bias else None,
+                 b[2] if has_bias else None)
             self._key = key
         return self._layer.dense_forward(hidden.reshape(T, H)).reshape(B, S, H)
 

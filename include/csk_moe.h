@@ -122,6 +122,13 @@ int csk_moe_load_experts_mxfp4(csk_moe_layer* layer, int32_t first_expert, int32
 int csk_moe_load_expert_f16(csk_moe_layer* layer, int32_t expert_id, const uint16_t* w_up, const uint16_t* w_gate,
                             const uint16_t* w_down, const float* b_up, const float* b_gate, const float* b_down);
 
+/* The same from fp32 matrices (dense_ffn_node also takes FLOAT32 weights, dense_ffn_node.h:58-62, 121-149):
+ * rounded to fp16 (nearest even) on the device, since the tensor-core kernel's operands are fp16; the result
+ * then differs from the reference's fp32 arithmetic by that rounding (2^-11 relative per weight, inside the
+ * stated tolerance).  CSK_ERR_INVALID when a finite weight lies beyond the fp16 range. */
+int csk_moe_load_expert_f32(csk_moe_layer* layer, int32_t expert_id, const float* w_up, const float* w_gate,
+                            const float* w_down, const float* b_up, const float* b_gate, const float* b_down);
+
 /* Expert slices in the GGUF block formats the reference's weight provider turns into fp16 on the host at
  * fetch time (src/llm/moe_weight_provider.cpp:120-159: Q4_K and Q6_K through dequantize_block_q4_K /
  * dequantize_block_q6_K, include/coalsack/gguf/gguf_dequant.h:147-261, then fp32_to_fp16, :458-489; F16 as

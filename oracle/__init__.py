@@ -106,6 +106,10 @@ class _Lib:
         self._dense.restype = C.c_int
         self._dense.argtypes = [_f32p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p,
                                 C.c_void_p, C.c_void_p, C.c_void_p, _f32p]
+        self._dense32 = getattr(L, prefix + "dense_ffn_f32")
+        self._dense32.restype = C.c_int
+        self._dense32.argtypes = [_f32p, C.c_int64, C.c_int64, C.c_int64, _f32p, _f32p, _f32p,
+                                  C.c_void_p, C.c_void_p, C.c_void_p, _f32p]
         if self.is_ref:
             self._kq = L.ref_dequant_kquant_f16
             self._kq.restype = C.c_int
@@ -181,9 +185,20 @@ class _Lib:
         return out
 
     def dense_ffn(self, hidden, gate_w, up_w, down_w, gate_b=None, up_b=None, down_b=None):
-        """dense_ffn_node: hidden [T,H] fp32; gate_w, up_w [F,H], down_w [H,F] float16; biases fp32 or None."""
+        """dense_ffn_node: hidden [T,H] fp32; gate_w, up_w [F,H], down_w [H,F] all float16 or all float32;
+        biases fp32 or None."""
         hidden = _f32(hidden)
         T, H = hidden.shape
+        if np.asarray(gate_w).dtype == np.float32:
+            w = [_f32(a) for a in (gate_w, up_w, down_w)]
+            F = w[0].shape[0]
+            b = [None if a is None else _f32(a) for a in (gate_b, up_b, down_b)]
+            out = np.empty((T, H), dtype=np.float32)
+            rc = self._dense32(_fp(hidden), T, H, F, *[_fp(a) for a in w],
+                               *[None if a is None else a.ctypes.data for a in b], _fp(out))
+            if rc:
+                self._err(rc, "dense_ffn")
+            return out
         w = [np.ascontiguousarray(np.asarray(a).view(np.uint16) if np.asarray(a).dtype == np.float16 else a,
                                   dtype=np.uint16) for a in (gate_w, up_w, down_w)]
         F = w[0].shape[0]

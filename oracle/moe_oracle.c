@@ -366,6 +366,38 @@ int orc_dense_ffn_f16(const float* hidden, int64_t T, int64_t H, int64_t F, cons
   return 0;
 }
 
+/* include/coalsack/nn/nn_ops/dense_ffn_node.h:121-149 -- the same FFN with FLOAT32 weights: plain scalar loops,
+ * one running sum per output taken in index order, product and sum rounded separately (the reference's build has
+ * no fused multiply-add and a sequential float sum is not reassociated). */
+int orc_dense_ffn_f32(const float* hidden, int64_t T, int64_t H, int64_t F, const float* gate_w,
+                      const float* up_w, const float* down_w, const float* gate_b, const float* up_b,
+                      const float* down_b, float* out) {
+  float* act = (float*)malloc(sizeof(float) * (size_t)F);
+  if (!act) return -2;
+  for (int64_t t = 0; t < T; ++t) {
+    const float* x = hidden + t * H;
+    for (int64_t o = 0; o < F; ++o) {
+      float g = 0.0f, u = 0.0f;
+      for (int64_t i = 0; i < H; ++i) {
+        g += x[i] * gate_w[o * H + i];
+        u += x[i] * up_w[o * H + i];
+      }
+      if (gate_b) g += gate_b[o];
+      if (up_b) u += up_b[o];
+      const float silu = g / (1.0f + expf(-g));
+      act[o] = silu * u;
+    }
+    for (int64_t o = 0; o < H; ++o) {
+      float s = 0.0f;
+      for (int64_t i = 0; i < F; ++i) s += act[i] * down_w[o * F + i];
+      if (down_b) s += down_b[o];
+      out[t * H + o] = s;
+    }
+  }
+  free(act);
+  return 0;
+}
+
 /* ---- Q4_K / Q6_K expert slices to fp16 --------------------------------------------------------
  * src/llm/moe_weight_provider.cpp:17-33: the slice is decoded to fp32 by dequantize_block_q4_K /
  * dequantize_block_q6_K and each value then passes fp32_to_fp16. */

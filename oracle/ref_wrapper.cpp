@@ -317,6 +317,29 @@ int ref_dense_ffn_f16(const float* hidden, int64_t T, int64_t H, int64_t F, cons
   }
 }
 
+int ref_dense_ffn_f32(const float* hidden, int64_t T, int64_t H, int64_t F, const float* gate_w, const float* up_w,
+                      const float* down_w, const float* gate_b, const float* up_b, const float* down_b, float* out) {
+  try {
+    dense_ffn_probe node;
+    std::vector<dynamic_tensor> in;
+    in.push_back(make_f32({1, T, H}, hidden));
+    in.push_back(make_f32({F, H}, gate_w));
+    in.push_back(make_f32({F, H}, up_w));
+    in.push_back(make_f32({H, F}, down_w));
+    if (gate_b) {
+      in.push_back(make_f32({F}, gate_b));
+      in.push_back(make_f32({F}, up_b));
+      in.push_back(make_f32({H}, down_b));
+    }
+    dynamic_tensor r = node.compute(in);
+    std::memcpy(out, r.data_ptr<float>(), sizeof(float) * T * H);
+    return 0;
+  } catch (const std::exception& e) {
+    g_last_error = e.what();
+    return -1;
+  }
+}
+
 // src/llm/moe_weight_provider.cpp:17-33 keeps these two helpers in an unnamed namespace of a file that
 // needs the GGUF loader; they are two calls into the reference's header, made here in the same order:
 // the block decoder to fp32, then fp32_to_fp16 on every value.

@@ -126,6 +126,15 @@ def dense_ffn_case(H=256, F=192, T=9, bias=True, seed=77):
     return hidden, gate_w, up_w, down_w, b[0], b[1], b[2]
 
 
+def dense_ffn_case_f32(H=256, F=192, T=9, bias=True, seed=177):
+    """The same with FLOAT32 weights (dense_ffn_node's scalar path): N(0, 0.05) values that are NOT fp16 numbers."""
+    g = np.random.default_rng(seed)
+    hidden = g.standard_normal((T, H)).astype(np.float32)
+    w = [(g.standard_normal(s) * 0.05).astype(np.float32) for s in ((F, H), (F, H), (H, F))]
+    b = [(g.standard_normal(n) * 0.01).astype(np.float32) for n in (F, F, H)] if bias else [None, None, None]
+    return hidden, w[0], w[1], w[2], b[0], b[1], b[2]
+
+
 Q4_K, Q6_K = 12, 14                      # ggml_type values
 KQUANT_BLOCK_BYTES = {Q4_K: 144, Q6_K: 210}
 

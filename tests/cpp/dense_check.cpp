@@ -15,17 +15,20 @@ using namespace coalsack;
 
 int main(int argc, char** argv) {
   if (argc < 3) return 2;
-  // file: int32 H, F, T, has_bias ; hidden[T,H] f32 ; gate[F,H] f16 ; up[F,H] f16 ; down[H,F] f16 ; (bg[F], bu[F], bd[H] f32)
+  // file: int32 H, F, T, flags (1: biases, 2: FLOAT32 weights) ; hidden[T,H] f32 ; gate[F,H] ; up[F,H] ; down[H,F]
+  //       (f16, or f32 with flag 2) ; (bg[F], bu[F], bd[H] f32)
   std::ifstream f(argv[1], std::ios::binary);
   std::vector<char> buf((std::istreambuf_iterator<char>(f)), std::istreambuf_iterator<char>());
   const char* p = buf.data();
   auto take = [&](size_t n) { const char* q = p; p += n; return q; };
   const int32_t* hd = reinterpret_cast<const int32_t*>(take(4 * 4));
-  const int H = hd[0], F = hd[1], T = hd[2], has_bias = hd[3];
+  const int H = hd[0], F = hd[1], T = hd[2], has_bias = hd[3] & 1, f32 = (hd[3] >> 1) & 1;
+  const dtype wt = f32 ? dtype::float32 : dtype::float16;
+  const size_t wb = (f32 ? 4u : 2u) * (size_t)F * H;
   dynamic_tensor hidden(dtype::float32, {1, T, H}, take(sizeof(float) * T * H));
-  dynamic_tensor gate(dtype::float16, {F, H}, take(2u * F * H));
-  dynamic_tensor up(dtype::float16, {F, H}, take(2u * F * H));
-  dynamic_tensor down(dtype::float16, {H, F}, take(2u * F * H));
+  dynamic_tensor gate(wt, {F, H}, take(wb));
+  dynamic_tensor up(wt, {F, H}, take(wb));
+  dynamic_tensor down(wt, {H, F}, take(wb));
   std::vector<dynamic_tensor> in = {hidden, gate, up, down};
   if (has_bias) {
     in.push_back(dynamic_tensor(dtype::float32, {F}, take(sizeof(float) * F)));
@@ -40,8 +43,13 @@ int main(int argc, char** argv) {
     return 1;
   }
   // the gate matrix refilled in place (negated): the upload is keyed on content, so the output must change
-  uint16_t* g = in[1].data_ptr<uint16_t>();
-  for (size_t i = 0; i < (size_t)F * H; ++i) g[i] ^= 0x8000u;
+  if (f32) {
+    float* g = in[1].data_ptr<float>();
+    for (size_t i = 0; i < (size_t)F * H; ++i) g[i] = -g[i];
+  } else {
+    uint16_t* g = in[1].data_ptr<uint16_t>();
+    for (size_t i = 0; i < (size_t)F * H; ++i) g[i] ^= 0x8000u;
+  }
   dynamic_tensor c = node.compute_test(in);
   std::ofstream o(argv[2], std::ios::binary);
   o.write(reinterpret_cast<const char*>(a.data_ptr<float>()), sizeof(float) * T * H);
@@ -54,6 +62,6 @@ int main(int argc, char** argv) {
   } catch (const std::exception& e) {
     if (std::string(e.what()).find("expected 4 or 7 inputs") == std::string::npos) return 1;
   }
-  std::printf("dense_check ok: H=%d F=%d T=%d bias=%d\n", H, F, T, has_bias);
+  std::printf("dense_check ok: H=%d F=%d T=%d bias=%d f32=%d\n", H, F, T, has_bias, f32);
   return 0;
 }

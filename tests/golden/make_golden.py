@@ -86,6 +86,11 @@ def main():
         g[tag + "_out"] = r.dense_ffn(hidden, gw, uw, dw, bg, bu, bd)
         g[tag + "_crc"] = cases.crc(hidden, gw.view(np.uint16), uw.view(np.uint16), dw.view(np.uint16))
 
+    # the same node with FLOAT32 weights (its scalar path)
+    args = cases.dense_ffn_case_f32()
+    g["dense32_out"] = r.dense_ffn(*args)
+    g["dense32_crc"] = cases.crc(*args[:4])
+
     # Q4_K / Q6_K expert slices to fp16 as the weight provider makes them (src/llm/moe_weight_provider.cpp:17-33):
     # ordinary headers, and headers of any bit pattern (subnormal, infinite, NaN)
     for name, t in (("q4k", cases.Q4_K), ("q6k", cases.Q6_K)):

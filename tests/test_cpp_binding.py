@@ -35,7 +35,7 @@ def test_bindings_compile_against_reference_headers():
         assert s in syms, f"{s}: graph_check does not reach the GPU bindings"
     assert os.path.exists(build_check.DENSE_OUT)
     syms = subprocess.run(["nm", "-D", build_check.DENSE_OUT], capture_output=True, text=True).stdout
-    for s in ("csk_moe_load_expert_f16", "csk_moe_dense_forward"):
+    for s in ("csk_moe_load_expert_f16", "csk_moe_load_expert_f32", "csk_moe_dense_forward"):
         assert s in syms, f"{s}: dense_check does not reach the GPU binding"
     assert os.path.exists(build_check.EXPERT_F16_OUT)
     syms = subprocess.run(["nm", "-D", build_check.EXPERT_F16_OUT], capture_output=True, text=True).stdout
@@ -160,17 +160,19 @@ def test_graph_fused_mode_at_the_20b_shape(gpu_lib, port, tmp_path):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("bias", [True, False])
-def test_dense_ffn_node_binding(gpu_lib, port, bias, tmp_path):
-    """coalsack's dense_ffn_node type with the GPU binding behind it: output against the restatement, the
-    weights uploaded once and again after an in-place refill, the reference's error text."""
+@pytest.mark.parametrize("bias,f32", [(True, False), (False, False), (True, True)])
+def test_dense_ffn_node_binding(gpu_lib, port, bias, f32, tmp_path):
+    """coalsack's dense_ffn_node type with the GPU binding behind it (FLOAT16 weights, and FLOAT32 ones, which the
+    device rounds to fp16): output against the restatement, the weights uploaded once and again after an in-place
+    refill, the reference's error text."""
     exe = build_check.DENSE_OUT
     if not os.path.exists(exe):
         pytest.skip("tests/cpp/_build/dense_check was not built (needs the reference checkout at build time)")
-    hidden, gw, uw, dw, bg, bu, bd = cases.dense_ffn_case(H=256, F=192, T=37, bias=bias, seed=83)
+    make = cases.dense_ffn_case_f32 if f32 else cases.dense_ffn_case
+    hidden, gw, uw, dw, bg, bu, bd = make(H=256, F=192, T=37, bias=bias, seed=83)
     inp, outp = tmp_path / "in.bin", tmp_path / "out.bin"
     with open(inp, "wb") as f:
-        f.write(np.array([256, 192, 37, int(bias)], np.int32).tobytes())
+        f.write(np.array([256, 192, 37, int(bias) | (2 if f32 else 0)], np.int32).tobytes())
         for a in (hidden, gw, uw, dw) + ((bg, bu, bd) if bias else ()):
             f.write(np.ascontiguousarray(a).tobytes())
     r = subprocess.run([exe, str(inp), str(outp)], capture_output=True, text=True, timeout=120)

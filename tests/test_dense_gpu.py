@@ -60,6 +60,30 @@ def test_dense_ffn_ragged_sizes(gpu_lib, port):
         node.close()
 
 
+def test_dense_ffn_fp32_weights(gpu_lib, golden, port):
+    """FLOAT32 weights (the reference's scalar path): rounded to fp16 on the device, inside the stated tolerance of
+    the reference's fp32 arithmetic; a weight beyond the fp16 range is refused."""
+    args = cases.dense_ffn_case_f32()
+    hidden = args[0]
+    node = dense_ffn_node()
+    out = node.compute([hidden[None]] + list(args[1:]))
+    assert_close(out[0], golden["dense32_out"], "dense fp32 weights")
+    node.close()
+    hidden, gw, uw, dw, _, _, _ = cases.dense_ffn_case_f32(H=352, F=288, T=200, bias=False, seed=179)
+    node = dense_ffn_node()
+    out = node.compute([hidden[None], gw, uw, dw])
+    assert_close(out[0], port.dense_ffn(hidden, gw, uw, dw), "dense fp32 weights, no bias")
+    node.close()
+    big = gw.copy()
+    big[3, 5] = 1.0e5
+    node = dense_ffn_node()
+    with pytest.raises(CskError, match="beyond the fp16 range"):
+        node.compute([hidden[None], big, uw, dw])
+    node.close()
+    with pytest.raises(RuntimeError, match="all be FLOAT16 or all FLOAT32"):
+        dense_ffn_node().compute([hidden[None], gw, uw.astype(np.float16), dw])
+
+
 def test_dense_ffn_errors(gpu_lib):
     hidden, gw, uw, dw, bg, bu, bd = cases.dense_ffn_case()
     node = dense_ffn_node()
@@ -74,7 +98,7 @@ def test_dense_ffn_errors(gpu_lib):
     with pytest.raises(RuntimeError, match="gate_w/up_w shape mismatch"):
         node.compute([hidden[None], gw, uw[:-32], dw])
     with pytest.raises(RuntimeError, match="FLOAT16"):
-        node.compute([hidden[None], gw.astype(np.float32), uw.astype(np.float32), dw.astype(np.float32)])
+        node.compute([hidden[None], gw.astype(np.float64), uw.astype(np.float64), dw.astype(np.float64)])
     # the two weight formats do not mix, and fp16 layers have the one-CTA tensor-core kernel only
     lay = MoeLayer(1, 1, 256, 192, activation=1, has_bias=False, max_tokens=16, weights_f16=True)
     with pytest.raises(CskError, match="fp16 weights"):

@@ -140,6 +140,18 @@ def test_dense_ffn_golden_and_reference(port, golden, tag, bias):
         assert np.array_equal(port.dense_ffn(*args), oracle.ref().dense_ffn(*args))
 
 
+def test_dense_ffn_fp32_weights_golden_and_reference(port, golden):
+    """dense_ffn_node's FLOAT32-weight path (dense_ffn_node.h:121-149): restatement against the fixture and,
+    where present, the compiled reference, bit for bit."""
+    args = cases.dense_ffn_case_f32()
+    assert cases.crc(*args[:4]) == golden["dense32_crc"]
+    assert np.array_equal(port.dense_ffn(*args), golden["dense32_out"])
+    import oracle
+    if oracle.have_ref():
+        args = cases.dense_ffn_case_f32(H=2880, F=96, T=3, bias=False, seed=178)
+        assert np.array_equal(port.dense_ffn(*args), oracle.ref().dense_ffn(*args))
+
+
 @pytest.mark.parametrize("name,t", [("q4k", cases.Q4_K), ("q6k", cases.Q6_K)])
 def test_kquant_to_fp16_golden_and_reference(port, golden, name, t):
     """Q4_K / Q6_K expert slices to fp16 (moe_weight_provider.cpp:17-33): the restatement equals the fixture the
