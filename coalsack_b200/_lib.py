@@ -56,6 +56,8 @@ SYMBOLS = {
     "csk_moe_set_ffn_norm": (C.c_int, [_vp, _vp, C.c_float]),
     "csk_moe_block_forward": (C.c_int, [_vp, _vp, _i64, _vp, _vp]),
     "csk_moe_block_forward_dev": (C.c_int, [_vp, _vp, _i64, _vp, _vp, _vp]),
+    "csk_moe_block_forward_shared": (C.c_int, [_vp, _vp, _vp, _i64, _vp, _vp]),
+    "csk_moe_block_forward_shared_dev": (C.c_int, [_vp, _vp, _vp, _i64, _vp, _vp, _vp]),
     "csk_moe_route_static": (C.c_int, [_vp, _i64, _i32, _vp, _vp, _i32, _i32, _i32, _vp, _vp]),
     "csk_moe_route_static_status": (C.c_int, []),
     "csk_moe_debug_set": (C.c_int, [_vp, _i32, _i64]),

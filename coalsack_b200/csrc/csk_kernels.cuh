@@ -1052,7 +1052,8 @@ __global__ void k_combine(const float* __restrict__ router_out, const int* __res
                           const float* __restrict__ y, int ldy, float* __restrict__ out, int T,
                           int k, int H, int unweighted, int dense_single,
                           const int* __restrict__ meta = nullptr, const int* __restrict__ counts = nullptr,
-                          int* __restrict__ carry = nullptr, int E = 0, const float* __restrict__ residual = nullptr) {
+                          int* __restrict__ carry = nullptr, int E = 0, const float* __restrict__ residual = nullptr,
+                          const float* __restrict__ shared_out = nullptr) {
   const int t = blockIdx.x;
   griddep_wait();
   griddep_launch();
@@ -1083,6 +1084,14 @@ __global__ void k_combine(const float* __restrict__ router_out, const int* __res
         acc.z = __fadd_rn(acc.z, __fmul_rn(w, v.z));
         acc.w = __fadd_rn(acc.w, __fmul_rn(w, v.w));
       }
+    }
+    if (shared_out) {
+      // the shared expert's dense FFN on the same rows: add(merge output, shared output), llm_engine.cpp:766-769
+      const float4 sh = *reinterpret_cast<const float4*>(shared_out + (size_t)t * H + d);
+      acc.x = __fadd_rn(acc.x, sh.x);
+      acc.y = __fadd_rn(acc.y, sh.y);
+      acc.z = __fadd_rn(acc.z, sh.z);
+      acc.w = __fadd_rn(acc.w, sh.w);
     }
     if (residual) {
       // the residual connection around the layer: add(residual, merge output), llm_engine.cpp:773-777

@@ -69,6 +69,8 @@ struct csk_moe_layer {
 
   float* d_norm_w = nullptr;   // [H] weight of the RMSNorm in front of the router (csk_moe_set_ffn_norm)
   float* d_normed = nullptr;   // [max_T,H] its output
+  float* d_shared_out = nullptr;  // [max_T,H] the shared expert's rows of a block forward
+  cudaEvent_t ev_shared_fork = nullptr, ev_shared_join = nullptr;
   float norm_eps = 1e-5f;
   int64_t max_T = 0, max_rows = 0;
   int max_tiles = 0;
@@ -484,7 +486,7 @@ void finish_timings(csk_moe_layer* L, int n_marks, bool routed) {
 // of that single expert node.
 int forward_dev(csk_moe_layer* L, const float* d_hidden, int64_t T, const float* d_router_in,
                 float* d_router_out, float* d_out, int only_expert, cudaStream_t s, bool sync_check,
-                const float* d_residual = nullptr) {
+                const float* d_residual = nullptr, const float* d_shared = nullptr, cudaEvent_t shared_ready = nullptr) {
   if (T <= 0 || T > L->max_T) return fail(L, CSK_ERR_NOMEM, "T=%lld outside (0, max_tokens=%lld]",
                                           (long long)T, (long long)L->max_T);
   if (L->has_slot_map)
@@ -531,9 +533,12 @@ int forward_dev(csk_moe_layer* L, const float* d_hidden, int64_t T, const float*
   rc = launch_experts(L, path, tile_rows, rows, T, L->d_x16, L->d_y, L->H, nullptr, s, tm);
   L->gather_hidden = nullptr;
   if (rc) return rc;
-  launch_k(k_combine, dim3((unsigned)T), dim3(256), 0, s, L->pdl, router, L->d_row_of_pair, (const float*)L->d_y, L->H,
-           d_out, (int)T, L->k, L->H, (int)L->cfg.weight_before_ffn, (int)(only_expert >= 0), (const int*)L->d_meta,
-           (const int*)L->d_counts, L->carry_active ? L->d_carry : (int*)nullptr, L->E, d_residual);
+  // the shared expert's rows come from another stream: the combine is the first kernel that reads them
+  if (shared_ready) CSK_CUDA(L, cudaStreamWaitEvent(s, shared_ready, 0));
+  launch_k(k_combine, dim3((unsigned)T), dim3(256), 0, s, L->pdl && !shared_ready, router, L->d_row_of_pair,
+           (const float*)L->d_y, L->H, d_out, (int)T, L->k, L->H, (int)L->cfg.weight_before_ffn, (int)(only_expert >= 0),
+           (const int*)L->d_meta, (const int*)L->d_counts, L->carry_active ? L->d_carry : (int*)nullptr, L->E, d_residual,
+           d_shared);
   CSK_CUDA(L, cudaGetLastError());
   L->last.launches++;
   tm.mark();
@@ -744,7 +749,7 @@ int csk_moe_destroy(csk_moe_layer* L) {
     if (g.exec) cudaGraphExecDestroy(g.exec);
   tile_destroy(L->tile);
   for (void* p : L->ipc_opened) cudaIpcCloseMemHandle(p);
-  void* dev[] = {L->d_p2p_epoch, L->d_unit_router, L->d_stage2, L->d_norm_w, L->d_normed, L->d_part, L->d_hn2, L->d_wnorm, L->d_fb_list, L->d_fb, L->d_info, L->d_back, L->d_row_ptr, L->d_p2p_base, L->d_peer_x16, L->d_peer_info, L->d_peer_back,
+  void* dev[] = {L->d_shared_out, L->d_p2p_epoch, L->d_unit_router, L->d_stage2, L->d_norm_w, L->d_normed, L->d_part, L->d_hn2, L->d_wnorm, L->d_fb_list, L->d_fb, L->d_info, L->d_back, L->d_row_ptr, L->d_p2p_base, L->d_peer_x16, L->d_peer_info, L->d_peer_back,
                  L->d_router_phys, L->d_slot_map, L->d_weights, L->d_resident, L->d_stage, L->d_wg, L->d_wg_few, L->d_wg_many, L->d_route_cnt, L->d_logits, L->d_rbias, L->d_hidden,
                  L->d_router, L->d_out, L->d_x16, L->d_a16, L->d_y, L->d_counts, L->d_offsets,
                  L->d_cursor, L->d_row_of_pair, L->d_pair_of_row, L->d_out_row_map, L->d_seg, L->d_tiles, L->d_meta};
@@ -759,6 +764,8 @@ int csk_moe_destroy(csk_moe_layer* L) {
   for (auto& e : L->ev_done)
     if (e) cudaEventDestroy(e);
   if (L->ev_free) cudaEventDestroy(L->ev_free);
+  if (L->ev_shared_fork) cudaEventDestroy(L->ev_shared_fork);
+  if (L->ev_shared_join) cudaEventDestroy(L->ev_shared_join);
   if (L->d_carry) cudaFree(L->d_carry);
   if (L->stream_in) cudaStreamDestroy(L->stream_in);
   if (L->stream_out) cudaStreamDestroy(L->stream_out);
@@ -1324,6 +1331,63 @@ int csk_moe_block_forward_dev(csk_moe_layer* L, const float* d_x, int64_t T, flo
   k_rmsnorm<<<blocks, 128, 4 * sizeof(float) * L->H, s>>>(d_x, L->d_norm_w, L->norm_eps, L->d_normed, (int)T, L->H);
   CSK_CUDA(L, cudaGetLastError());
   return forward_dev(L, L->d_normed, T, nullptr, d_router_out, d_out, -1, s, false, d_x);
+}
+
+int csk_moe_block_forward_shared_dev(csk_moe_layer* L, csk_moe_layer* S, const float* d_x, int64_t T,
+                                     float* d_router_out, float* d_out, void* stream) {
+  if (!S) return csk_moe_block_forward_dev(L, d_x, T, d_router_out, d_out, stream);
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  if (!d_x || !d_out) return fail(L, CSK_ERR_INVALID, "null argument");
+  if (!L->d_norm_w) return fail(L, CSK_ERR_INVALID, "the norm weight was never set (csk_moe_set_ffn_norm)");
+  if (T <= 0 || T > L->max_T) return fail(L, CSK_ERR_NOMEM, "T=%lld outside (0, max_tokens]", (long long)T);
+  if (S == L || !S->d_unit_router || S->H != L->H || S->cfg.device != L->cfg.device)
+    return fail(L, CSK_ERR_INVALID, "the shared expert must be another layer on the same device with num_experts = top_k = 1 "
+                                    "and the same hidden size");
+  if (T > S->max_T) return fail(L, CSK_ERR_NOMEM, "T=%lld exceeds the shared expert's max_tokens", (long long)T);
+  if (!S->resident[0]) return fail(L, CSK_ERR_MISSING, "the shared expert's weights are not loaded");
+  if (reinterpret_cast<uintptr_t>(d_x) % 16 || reinterpret_cast<uintptr_t>(d_out) % 16)
+    return fail(L, CSK_ERR_INVALID, "activations must be 16-byte aligned");
+  if ((size_t)L->H * sizeof(float) * 4 > 200 * 1024) return fail(L, CSK_ERR_NOMEM, "hidden dimension too large for the norm kernel's row buffer");
+  CSK_CUDA(L, cudaSetDevice(L->cfg.device));
+  if (!L->d_shared_out) {
+    cudaError_t e = cudaMalloc(&L->d_shared_out, sizeof(float) * L->max_T * L->H);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&L->ev_shared_fork, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&L->ev_shared_join, cudaEventDisableTiming);
+    if (e != cudaSuccess) return fail(L, CSK_ERR_NOMEM, "shared-expert buffers: %s", cudaGetErrorString(e));
+  }
+  cudaStream_t s = pick(L, stream);
+  const int blocks = (int)std::min<int64_t>((T + 3) / 4, 4 * (int64_t)L->sm_count);
+  k_rmsnorm<<<blocks, 128, 4 * sizeof(float) * L->H, s>>>(d_x, L->d_norm_w, L->norm_eps, L->d_normed, (int)T, L->H);
+  CSK_CUDA(L, cudaGetLastError());
+  // the shared expert reads the normed rows on its own stream, next to the routed experts; the combine joins them
+  CSK_CUDA(L, cudaEventRecord(L->ev_shared_fork, s));
+  CSK_CUDA(L, cudaStreamWaitEvent(S->stream, L->ev_shared_fork, 0));
+  int rc = csk_moe_dense_forward_dev(S, L->d_normed, T, L->d_shared_out, S->stream);
+  if (rc) return fail(L, rc, "shared expert: %s", S->err.c_str());
+  CSK_CUDA(L, cudaEventRecord(L->ev_shared_join, S->stream));
+  return forward_dev(L, L->d_normed, T, nullptr, d_router_out, d_out, -1, s, false, d_x, L->d_shared_out, L->ev_shared_join);
+}
+
+int csk_moe_block_forward_shared(csk_moe_layer* L, csk_moe_layer* S, const float* x, int64_t T, float* router_out,
+                                 float* out) {
+  if (!S) return csk_moe_block_forward(L, x, T, router_out, out);
+  if (check_layer(L)) return CSK_ERR_INVALID;
+  if (!x || !out) return fail(L, CSK_ERR_INVALID, "null argument");
+  if (T <= 0 || T > L->max_T) return fail(L, CSK_ERR_NOMEM, "T=%lld outside (0, max_tokens]", (long long)T);
+  CSK_CUDA(L, cudaSetDevice(L->cfg.device));
+  cudaStream_t s = L->stream;
+  CSK_CUDA(L, cudaMemcpyAsync(L->d_hidden, x, sizeof(float) * T * L->H, cudaMemcpyHostToDevice, s));
+  int rc = csk_moe_block_forward_shared_dev(L, S, L->d_hidden, T, L->d_router, L->d_out, s);
+  if (rc) return rc;
+  rc = check_device_status(L, s);
+  if (rc) return rc;
+  rc = check_device_status(S, S->stream);
+  if (rc) return fail(L, rc, "shared expert: %s", S->err.c_str());
+  CSK_CUDA(L, cudaMemcpyAsync(out, L->d_out, sizeof(float) * T * L->H, cudaMemcpyDeviceToHost, s));
+  if (router_out)
+    CSK_CUDA(L, cudaMemcpyAsync(router_out, L->d_router, sizeof(float) * T * L->k * 2, cudaMemcpyDeviceToHost, s));
+  CSK_CUDA(L, cudaStreamSynchronize(s));
+  return CSK_OK;
 }
 
 int csk_moe_block_forward(csk_moe_layer* L, const float* x, int64_t T, float* router_out, float* out) {

@@ -242,14 +242,22 @@ class MoeLayer:
             raise RuntimeError("rmsnorm: weight shape must be [hidden_dim]")
         self._check(self._lib.csk_moe_set_ffn_norm(self._h, _p(w), float(eps)))
 
-    def block_forward(self, x):
-        """(x + moe(rmsnorm(x) * weight), router_out): the layer with its norm and residual."""
+    def block_forward(self, x, shared=None):
+        """(x + moe(n) [+ shared(n)], router_out) with n = rmsnorm(x) * weight: the layer with its norm and residual,
+        and optionally the shared expert's dense FFN (``shared``: a dense MoeLayer, one expert, top-1, fp16 format)."""
         x = _np_f32(x).reshape(-1, self.H)
         T = x.shape[0]
         out = np.empty((T, self.H), np.float32)
         ro = np.empty((T, self.k, 2), np.float32)
-        self._check(self._lib.csk_moe_block_forward(self._h, _p(x), T, _p(ro), _p(out)))
+        if shared is None:
+            self._check(self._lib.csk_moe_block_forward(self._h, _p(x), T, _p(ro), _p(out)))
+        else:
+            self._check(self._lib.csk_moe_block_forward_shared(self._h, shared._h, _p(x), T, _p(ro), _p(out)))
         return out, ro
+
+    def block_forward_dev(self, d_x, T, d_router_out, d_out, stream=None, shared=None):
+        self._check(self._lib.csk_moe_block_forward_shared_dev(self._h, shared._h if shared is not None else None,
+                                                               _p(d_x), T, _p(d_router_out), _p(d_out), stream))
 
     def expert_forward(self, expert_id, hidden, router_out):
         """Dense [T,H] output of one expert node, or None for the {0}-shaped empty tensor."""

@@ -225,6 +225,15 @@ int csk_moe_set_ffn_norm(csk_moe_layer* layer, const float* norm_weight, float e
 int csk_moe_block_forward(csk_moe_layer* layer, const float* x, int64_t T, float* router_out_or_null, float* out);
 int csk_moe_block_forward_dev(csk_moe_layer* layer, const float* d_x, int64_t T, float* d_router_out_or_null,
                               float* d_out, void* stream);
+/* The same block with a shared expert (Llama-4 style, src/llm/llm_engine.cpp:755-777): out = x + (moe(n) + dense(n)),
+ * n = rmsnorm(x) * weight, `shared` a layer as csk_moe_dense_forward takes (num_experts = top_k = 1, fp16 weight
+ * format, same device and hidden size, weights loaded).  The dense FFN runs on the shared layer's own stream beside
+ * the routed experts; the combine kernel adds its rows to the merge output, then the residual, in the reference's
+ * order.  shared = NULL is csk_moe_block_forward. */
+int csk_moe_block_forward_shared(csk_moe_layer* layer, csk_moe_layer* shared, const float* x, int64_t T,
+                                 float* router_out_or_null, float* out);
+int csk_moe_block_forward_shared_dev(csk_moe_layer* layer, csk_moe_layer* shared, const float* d_x, int64_t T,
+                                     float* d_router_out_or_null, float* d_out, void* stream);
 
 /* Routing for callers that must not allocate.  No counterpart in the reference
  * (its router keeps its logits in a std::vector on the host).

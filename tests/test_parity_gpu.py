@@ -477,6 +477,46 @@ def test_block_with_norm_and_residual(gpu_lib, port, shape):
     lay.close()
 
 
+def test_block_with_shared_expert(gpu_lib, port):
+    """The Llama-4 style block (llm_engine.cpp:714-777): x -> rmsnorm -> [routed experts -> merge] + [shared dense FFN]
+    -> + x in one call.  Routing bit-exact after the fused norm; the result equals x + (layer + dense FFN) of the
+    checker on the normed rows; with the bit-exact pieces it equals the sum of the separate entry points bit for bit."""
+    sh = synth.tiny(seed=57, E=8, k=2, H=256, F=192, T=150, has_bias=True)
+    h, Wg, rb, ex = cases.layer_inputs(sh, router_scale=30.0)
+    g = np.random.default_rng(570)
+    x_all = (h * g.uniform(0.2, 5.0, size=(h.shape[0], 1))).astype(np.float32)
+    nw = (1.0 + 0.1 * g.standard_normal(sh.hidden)).astype(np.float32)
+    _, gw, uw, dw, bg, bu, bd = cases.dense_ffn_case(H=256, F=320, T=1, bias=True, seed=571)
+    lay = make_layer(sh, Wg, rb, ex, max_tokens=x_all.shape[0])
+    lay.set_ffn_norm(nw, 1e-5)
+    shared = MoeLayer(1, 1, 256, 320, activation=synth.STANDARD_SWIGLU, has_bias=True, max_tokens=x_all.shape[0],
+                      weights_f16=True)
+    shared.load_expert_f16(0, uw, gw, dw, bu, bg, bd)
+    for T in (150, 5):      # the tensor-core kernel; the streaming kernel with its captured launch sequence
+        x = x_all[:T]
+        for rep in range(2):
+            out, ro = lay.block_forward(x, shared=shared)
+        n = port.rmsnorm(x, nw, 1e-5)
+        want_ro = port.router(n, Wg, rb, sh.top_k)
+        assert np.array_equal(ro[..., 0], want_ro[..., 0]), "routing after the fused norm differs"
+        moe, _ = port.moe_layer(n, Wg, rb, ex, sh.top_k, sh.act, nthreads=16, router_out=ro)
+        dense = port.dense_ffn(n, gw, uw, dw, bg, bu, bd)
+        assert_close(out.astype(np.float64) - x, moe.astype(np.float64) + dense, f"block with shared expert, T={T}")
+        # the same from the separate entry points, added in the reference's order: x + (merge + shared)
+        out_moe, ro2 = lay.forward(n)
+        out_sh = shared.dense_forward(n)
+        assert np.array_equal(ro2[..., 0], ro[..., 0])
+        assert np.array_equal((x + (out_moe + out_sh)).astype(np.float32), out)
+    with pytest.raises(CskError, match="shared expert must be another layer"):
+        lay.block_forward(x_all[:4], shared=lay)
+    empty = MoeLayer(1, 1, 256, 320, activation=synth.STANDARD_SWIGLU, has_bias=False, max_tokens=8, weights_f16=True)
+    with pytest.raises(CskError, match="not loaded"):
+        lay.block_forward(x_all[:4], shared=empty)
+    empty.close()
+    shared.close()
+    lay.close()
+
+
 def test_bulk_load_and_weight_image(gpu_lib, port, tmp_path):
     """The model's [E, rows, cols] expert tensors loaded as slabs give the same layer as expert-by-expert
     loading, bit for bit; the repacked image written to a file and read into a fresh handle does too."""
