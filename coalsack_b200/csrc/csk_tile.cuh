@@ -62,6 +62,12 @@ constexpr int kDequantWarps = 8;
 constexpr int kEpilogueWarps = 12;    // four lane quarters x three column ranges (sixteen measured no faster)
 constexpr int kTileThreads = (2 + kDequantWarps + kEpilogueWarps) * 32;  // producer, MMA, dequantisers, epilogue
 constexpr int kTileABytes = kTileM * 128;                   // token tile in shared memory
+constexpr int kTileBoxes = kTileM / 32;                     // TMA boxes of 32, 64, ... kTileM rows: a row tile is fetched
+                                                            // with the smallest that holds it (a 128-row tile costs 16 KB
+                                                            // of L2 -> SM traffic per k-step instead of 24 KB)
+struct TileMaps {
+  CUtensorMap m[kTileBoxes];
+};
 constexpr int kHalfPacked = 4352;                           // packed half tile: 4096 codes + 256 scales
 constexpr int kTilePacked = 2 * kHalfPacked;                // packed weight tile (two halves)
 constexpr int kTileRawBytes = kTileABytes + 9216;           // one shared-memory stage (1024-byte multiple)
@@ -215,8 +221,8 @@ __global__ void k_unpack_tile(const uint8_t* __restrict__ packed, uint8_t* __res
 struct TileState {
   bool available = false;
   std::string err;
-  CUtensorMap tmap_x{};   // grouped input rows  [rows, ldx] fp16, boxes of kTileM rows
-  CUtensorMap tmap_a{};   // activated rows      [rows, lda] fp16, boxes of kTileM rows
+  TileMaps maps_x{};      // grouped input rows  [rows, ldx] fp16, one map per box height
+  TileMaps maps_a{};      // activated rows      [rows, lda] fp16
   CUtensorMap tmap_xh{};  // the same with boxes of half a row tile (the CTA-pair kernel's half tiles)
   CUtensorMap tmap_ah{};
   bool maps_ready = false;
@@ -330,7 +336,7 @@ inline size_t tile_smem_bytes(bool w16 = false) {
 
 template <bool GATED, bool W16>
 __global__ void __launch_bounds__(kTileThreads, 1)
-k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
+k_tile(const __grid_constant__ TileMaps maps, const TileArgs A) {
   extern __shared__ __align__(1024) uint8_t tile_smem[];
   const TileLayout& L = A.L;
   const int KT = L.k_tiles;
@@ -395,14 +401,17 @@ k_tile(const __grid_constant__ CUtensorMap tmap, const TileArgs A) {
         const uint8_t* wsrc =
             A.weights + (size_t)rt.expert * A.expert_stride + A.mat_offset + (size_t)nt * KT * TILE_B;
         const uint32_t w_bytes = (uint32_t)L.halves(nt) * HALF_B;
+        const int box = min(kTileBoxes - 1, max(0, (rt.rows + 31) / 32 - 1));
+        const CUtensorMap* tmap = &maps.m[box];
+        const uint32_t box_bytes = (uint32_t)(box + 1) * 32u * 128u;
         for (int kt = 0; kt < KT; ++kt) {
           if (!mbar_wait(bar_retired(s), ph ^ 1, abort_flag)) {
             ok = false;
             break;
           }
           const uint32_t st = smem_base + (uint32_t)s * RAW;
-          mbar_expect_tx(bar_full_raw(s), kTileABytes + w_bytes);
-          tma_load_2d(st, &tmap, kt * kTileK, rt.row0, bar_full_raw(s));
+          mbar_expect_tx(bar_full_raw(s), box_bytes + w_bytes);
+          tma_load_2d(st, tmap, kt * kTileK, rt.row0, bar_full_raw(s));
           bulk_load(st + kTileABytes, wsrc + (size_t)kt * TILE_B, w_bytes, bar_full_raw(s));
           ++issued;
           if (++s == NR) {
@@ -718,9 +727,11 @@ inline int tile_make_map(TileState& st, CUtensorMap* map, const __half* base, si
 
 inline int tile_set_buffers(TileState& st, const __half* x16, int ldx, const __half* a16, int lda, size_t rows_alloc) {
   if (!st.available) return CSK_OK;
-  int rc = tile_make_map(st, &st.tmap_x, x16, rows_alloc, ldx);
-  if (rc) return rc;
-  rc = tile_make_map(st, &st.tmap_a, a16, rows_alloc, lda);
+  int rc = CSK_OK;
+  for (int b = 0; b < kTileBoxes && !rc; ++b) {
+    rc = tile_make_map(st, &st.maps_x.m[b], x16, rows_alloc, ldx, 32 * (b + 1));
+    if (!rc) rc = tile_make_map(st, &st.maps_a.m[b], a16, rows_alloc, lda, 32 * (b + 1));
+  }
   if (!rc) rc = tile_make_map(st, &st.tmap_xh, x16, rows_alloc, ldx, kPairBoxRows);
   if (!rc) rc = tile_make_map(st, &st.tmap_ah, a16, rows_alloc, lda, kPairBoxRows);
   if (rc) return rc;
@@ -758,8 +769,8 @@ inline int tile_launch(TileState& st, const uint8_t* weights, size_t expert_stri
   a.a_out = a16;
   a.lda = lda;
   a.meta_slot = 0;
-  if (w16) k_tile<true, true><<<sm_count, kTileThreads, smem, s>>>(st.tmap_x, a);
-  else k_tile<true, false><<<sm_count, kTileThreads, smem, s>>>(st.tmap_x, a);
+  if (w16) k_tile<true, true><<<sm_count, kTileThreads, smem, s>>>(st.maps_x, a);
+  else k_tile<true, false><<<sm_count, kTileThreads, smem, s>>>(st.maps_x, a);
   mark();
   // down
   a.mat_offset = off_d;
@@ -769,8 +780,8 @@ inline int tile_launch(TileState& st, const uint8_t* weights, size_t expert_stri
   a.out_row_map = out_row_map;
   a.out_row_ptr = out_row_ptr;
   a.meta_slot = 1;
-  if (w16) k_tile<false, true><<<sm_count, kTileThreads, smem, s>>>(st.tmap_a, a);
-  else k_tile<false, false><<<sm_count, kTileThreads, smem, s>>>(st.tmap_a, a);
+  if (w16) k_tile<false, true><<<sm_count, kTileThreads, smem, s>>>(st.maps_a, a);
+  else k_tile<false, false><<<sm_count, kTileThreads, smem, s>>>(st.maps_a, a);
   mark();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
